@@ -1,0 +1,190 @@
+/*
+ * iflb200 — C ABI of the B200 (sm_100a) FP8 linear path.
+ *
+ * Every entry point takes plain device pointers, sizes and a CUDA stream handle
+ * (cudaStream_t passed as void*), enqueues work on that stream and returns at once
+ * with an int status: 0 = ok, > 0 = a cudaError_t from the launch, < 0 = one of the
+ * IFLB200_ERR_* codes below (argument rejected before any launch).  Nothing is
+ * allocated, nothing synchronises, no host code reads device memory: every call can
+ * be captured in a CUDA graph.  The caller owns every buffer.
+ *
+ * The comment on each declaration names the operator of the InstinctFlash reference
+ * (path inside that project, line range) that the entry point replaces.
+ *
+ * Conventions
+ *   - matrices are row-major with the last dimension contiguous; `ld_*` is the row
+ *     stride in ELEMENTS;
+ *   - e4m3 means the OCP "fn" variant (no infinities, 0x7F/0xFF = NaN, max 448);
+ *   - aux vectors (row/col scales, bias, gate, norm weights) are float32;
+ *   - optional pointers may be NULL.
+ */
+#ifndef IFLB200_H_
+#define IFLB200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define IFLB200_ABI_VERSION 1
+
+#if defined(__GNUC__)
+#define IFLB200_API __attribute__((visibility("default")))
+#else
+#define IFLB200_API
+#endif
+
+/* element types of activation-like buffers */
+#define IFLB200_F32 0
+#define IFLB200_BF16 1
+#define IFLB200_F16 2
+
+/* gated activations (instinctflash/kernels/activation.py:15-16) */
+#define IFLB200_ACT_GELU_TANH 0
+#define IFLB200_ACT_SILU 1
+
+/* accumulator rounding of the fused GEMM epilogues */
+#define IFLB200_ROUND_ENGINE 0 /* fp32 accumulator -> bf16 (RNE) -> fp32, then scales: the
+                                  reference's gemm() + consumer memory round trip */
+#define IFLB200_ROUND_EXACT 1  /* scales applied to the fp32 accumulator, one rounding */
+
+/* status codes (< 0) */
+#define IFLB200_OK 0
+#define IFLB200_ERR_ARG (-1)       /* NULL where a pointer is required, negative size */
+#define IFLB200_ERR_SHAPE (-2)     /* K or N not a multiple of 16, width above a kernel's maximum */
+#define IFLB200_ERR_ALIGN (-3)     /* base pointer or row stride breaks the 16-byte rule */
+#define IFLB200_ERR_DTYPE (-4)     /* element type code not supported by this entry point */
+#define IFLB200_ERR_DRIVER (-5)    /* cuTensorMapEncodeTiled unavailable or refused the layout */
+#define IFLB200_ERR_DEVICE (-6)    /* current device is not compute capability 10.x */
+#define IFLB200_ERR_WORKSPACE (-7) /* workspace missing or too small */
+
+IFLB200_API int iflb200_abi_version(void);
+IFLB200_API const char* iflb200_status_string(int status);
+
+/*
+ * Per-token (per-row) dynamic e4m3 quantiser with the optional consumer prologue.
+ *   v[m,k]  = x[m,k] (*row[m]) (*col[k]) (+bias[k])  [-> gelu_tanh]
+ *   amax    = max(max_k |v|, 1e-8);  qs[m] = amax / 448;  q[m,k] = e4m3(v * (448 / amax))
+ * Both divisions are PTX div.full.f32, the cast is cvt.rn.satfinite, as the reference's
+ * Triton kernel compiles to on sm_100.
+ * Replaces: instinctflash/kernels/norm.py:128-158 (_row_quant_kernel, row_quant).
+ */
+IFLB200_API int iflb200_row_quant(const void* x, int x_dtype, int64_t ld_x, int M, int K,
+                      const float* row, const float* col, const float* bias, int gelu,
+                      void* q, int64_t ld_q, float* qs, void* stream);
+
+/*
+ * Consumer of a raw accumulator: y[m,n] = out_dtype(x[m,n] (*row[m]) (*col[n]) (+bias[n])),
+ * the last multiply fused with the bias add (fma.rn) exactly as the reference compiles.
+ * Replaces: instinctflash/kernels/norm.py:162-185 (_dequant_rows_kernel, dequant_rows).
+ */
+IFLB200_API int iflb200_dequant_rows(const void* x, int x_dtype, int64_t ld_x, int M, int D,
+                         const float* row, const float* col, const float* bias,
+                         void* y, int y_dtype, int64_t ld_y, void* stream);
+
+/*
+ * Gated MLP activation on a raw accumulator [g | u] (each half F wide) followed by the
+ * per-token quantiser:  h = act(g*row*col[:F]) * (u*row*col[F:]),  q/qs as in row_quant.
+ * F <= 16384.
+ * Replaces: instinctflash/kernels/activation.py:20-56 (_gated_act_quant_kernel, gated_act_quant).
+ */
+IFLB200_API int iflb200_gated_act_quant(const void* gu, int gu_dtype, int64_t ld_gu, int M, int F,
+                            const float* row, const float* col, int act,
+                            void* q, int64_t ld_q, float* qs, void* stream);
+
+/*
+ * Residual update + RMS/LayerNorm + affine + adaptive modulation + per-token quantiser,
+ * one row per thread group (the MoE router tail of the reference kernel is not part of
+ * this path).
+ *   if delta: res[m] += (delta[m]*delta_row[m]*delta_col + bias) * gate[idx]   (stored in res's type)
+ *   y = norm(res[m]) (*weight) (+beta);  y = y*(1+mod_scale[idx]) + mod_shift[idx]
+ *   y_out[m] = y (optional);  q/qs[m] = quantiser(y) (optional)
+ * gate / mod_scale / mod_shift are [D], or tables [n, D] indexed by mod_index[m] when given.
+ * D <= 16384.  res_dtype is IFLB200_F32 or IFLB200_BF16; delta is bf16.
+ * Replaces: instinctflash/kernels/norm.py:26-124 (_residual_norm_quant_kernel,
+ * residual_norm_quant) without its `router` argument.
+ */
+IFLB200_API int iflb200_residual_norm_quant(void* res, int res_dtype, int64_t ld_res, int M, int D,
+                                const void* delta, int64_t ld_delta,
+                                const float* delta_row, const float* delta_col,
+                                const float* bias, const float* gate, int write_res,
+                                int layernorm, const float* weight, const float* beta,
+                                const float* mod_scale, const float* mod_shift,
+                                const int32_t* mod_index, float eps,
+                                void* q, int64_t ld_q, float* qs,
+                                void* y, int y_dtype, int64_t ld_y, void* stream);
+
+/*
+ * Raw-accumulator FP8 GEMM: out[M,N] (bf16) = bf16_rn(sum_k a[m,k] * w[n,k]), fp32
+ * accumulation on the tcgen05 tensor cores, unit scales.  K, N multiples of 16.
+ * Replaces: instinctflash/kernels/fp8.py:50-53 (gemm -> torch._scaled_mm).
+ */
+IFLB200_API int iflb200_gemm_fp8_raw(const void* a, int64_t ld_a, const void* w, int64_t ld_w,
+                         int M, int N, int K, void* out, int64_t ld_out, void* stream);
+
+/*
+ * Fused linear: GEMM + the dequant_rows consumer in the epilogue.
+ *   y[m,n] = out_dtype(fma(r*row_scale[m], col_scale[n], bias[n])),
+ *   r = fp32(bf16_rn(acc)) in IFLB200_ROUND_ENGINE, r = acc in IFLB200_ROUND_EXACT.
+ * row_scale_stride / col_scale_stride are 1 for per-token / per-channel vectors and 0
+ * for a single per-tensor scale (the per-tensor recipe of torch_fp8_linear.py).
+ * Replaces: instinctflash/kernels/fp8.py:50-53 followed by
+ * instinctflash/kernels/norm.py:162-185; with stride-0 scales and EXACT rounding also the
+ * torch._scaled_mm call of instinctflash/runtime/torch_fp8_linear.py:74-78.
+ */
+IFLB200_API int iflb200_fp8_linear(const void* a, int64_t ld_a, const void* w, int64_t ld_w,
+                       int M, int N, int K,
+                       const float* row_scale, int row_scale_stride,
+                       const float* col_scale, int col_scale_stride,
+                       const void* bias, int bias_dtype, int rounding,
+                       void* out, int out_dtype, int64_t ld_out, void* stream);
+
+/*
+ * Fused linear + residual update in the epilogue (in place on res):
+ *   res[m,n] = res_dtype(res[m,n] + (r*row_scale[m]*col_scale[n] (+bias[n])) (*gate[idx[m],n]))
+ * with the reference's contraction order (see residual_norm_quant).
+ * Replaces: instinctflash/kernels/fp8.py:50-53 followed by the residual part of
+ * instinctflash/kernels/norm.py:44-58.
+ */
+IFLB200_API int iflb200_fp8_linear_residual(const void* a, int64_t ld_a, const void* w, int64_t ld_w,
+                                int M, int N, int K,
+                                const float* row_scale, const float* col_scale,
+                                const float* bias, const float* gate, const int32_t* gate_index,
+                                void* res, int res_dtype, int64_t ld_res, void* stream);
+
+/*
+ * Per-tensor dynamic e4m3 pack (the torch-FP8-linear recipe):
+ *   amax = max |x| (NaN propagates);  scale = max(amax, 1e-12) * fp32(1/448);
+ *   q = e4m3_rn(clamp(x / scale, -448, 448))   (IEEE division, NaN propagates)
+ * x is contiguous bf16 with n elements; workspace holds iflb200_pack_workspace_bytes(n)
+ * bytes and needs no initialisation.
+ * Replaces: instinctflash/runtime/fp8_pack.py:27-92 (dynamic_pack_bf16_e4m3 and its three
+ * Triton kernels).
+ */
+IFLB200_API size_t iflb200_pack_workspace_bytes(int64_t n);
+IFLB200_API int iflb200_dynamic_pack_bf16_e4m3(const void* x, int64_t n, void* q, float* scale,
+                                   void* workspace, size_t workspace_bytes, void* stream);
+
+/*
+ * Fixed-scale pack: q = e4m3_rn(clamp(x / scale[0], -448, 448)).
+ * Replaces: instinctflash/runtime/fp8_pack.py:27-60 (_pack_kernel, pack_bf16_e4m3).
+ */
+IFLB200_API int iflb200_pack_bf16_e4m3(const void* x, int64_t n, const float* scale, void* q, void* stream);
+
+/*
+ * Diagnostics of the tcgen05 GEMM: every wait inside the kernel is bounded; a wait that
+ * runs out records (role, barrier, tile) in a device word and the kernel drains and
+ * returns.  This reads the word (synchronises the given stream) and clears it.
+ * Returns 0 if no kernel has timed out since the last call.  No reference counterpart.
+ */
+IFLB200_API int iflb200_gemm_take_timeout_record(uint32_t* record, void* stream);
+
+/* Tuning overrides for experiments and tests (0 = heuristic). No reference counterpart. */
+IFLB200_API int iflb200_gemm_set_config(int tile_n, int stages, int group_m);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* IFLB200_H_ */

@@ -1,0 +1,582 @@
+// FP8 (e4m3 x e4m3 -> fp32) GEMM for sm_100a with fused consumer epilogues.
+//
+//   out[M,N] = epilogue( sum_k A[m,k] * W[n,k] )        A [M,K], W [N,K], both K-major
+//
+// Persistent, warp-specialised, one CTA per SM:
+//   warp 0      TMA producer: cp.async.bulk.tensor loads of a 128 x 128-byte A tile and a
+//               BN x 128-byte W tile per stage, 128-byte swizzle, completion on an mbarrier;
+//   warp 1      MMA issuer: one thread issues tcgen05.mma (128 x BN x 32 per instruction,
+//               four per stage) into one of two TMEM accumulators and commits the stage's
+//               "empty" barrier / the accumulator's "full" barrier;
+//   warps 2..5  epilogue: tcgen05.ld the finished accumulator (one row per thread), apply the
+//               consumer arithmetic of the reference in its exact order and store.
+// The two TMEM accumulators let the epilogue of tile i overlap the main loop of tile i+1.
+// The K loop order is a function of K alone (128-byte steps, no split), so an output element
+// never depends on N, on the tile shape or on the grid: column-sharded weights give
+// bit-identical columns.
+//
+// Every wait is bounded: a wait that runs out records where in g_timeout_record, raises a
+// CTA-wide abort flag, every role leaves its loop, in-flight TMA loads are drained with a
+// bounded wait, TMEM is freed and the kernel returns.
+#include <cuda.h>
+#include <cuda_runtime.h>
+
+#include "../../include/iflb200.h"
+#include "rowmath.cuh"
+
+namespace iflb200 {
+
+constexpr int BM = 128;
+constexpr int BK = 128;  // bytes == e4m3 elements per stage along K
+constexpr int kGemmThreads = 192;
+constexpr uint64_t kWaitBudgetNs = 2000000000ull;  // 2 s per wait, then abort
+
+enum : int { EPI_RAW = 0, EPI_DEQUANT = 1, EPI_RESIDUAL = 2 };
+
+struct GemmParams {
+  int M, N, K;
+  int num_m, num_n, num_k, num_tiles, group_m;
+  int epilogue;
+  int exact;  // 1: scales applied to the fp32 accumulator without the bf16 rounding
+  const float* row;
+  int row_stride;
+  const float* col;
+  int col_stride;
+  const void* bias;
+  int bias_dtype;
+  const float* gate;
+  const int32_t* gate_index;
+  void* out;
+  int out_dtype;
+  int64_t ld_out;
+};
+
+// role << 24 | barrier kind << 16 | low 16 bits of the tile counter; 0 = no timeout.
+__device__ uint32_t g_timeout_record[4];
+
+template <int BN, int STAGES>
+struct SmemLayout {
+  static constexpr int kABytes = BM * BK;
+  static constexpr int kBBytes = BN * BK;
+  static constexpr int kStageBytes = kABytes + kBBytes;
+  static constexpr int kBarOffset = STAGES * kStageBytes;
+  // full[STAGES], empty[STAGES], tmem_full[2], tmem_empty[2], then the TMEM base word and the
+  // abort flag.
+  static constexpr int kNumBars = 2 * STAGES + 4;
+  static constexpr int kTotal = kBarOffset + kNumBars * 8 + 16;
+  static constexpr int kDynamic = kTotal + 1024;  // room to align the base to 1024 bytes
+};
+
+__device__ __forceinline__ void tile_coords(const GemmParams& p, int tile, int& m_blk, int& n_blk) {
+  // Bands of group_m row blocks, column blocks outermost inside a band: CTAs that run at the
+  // same time share W tiles through L2 and touch at most group_m A row blocks.
+  const int band = p.group_m * p.num_n;
+  const int g = tile / band;
+  const int first_m = g * p.group_m;
+  const int size = min(p.num_m - first_m, p.group_m);
+  const int r = tile - g * band;
+  m_blk = first_m + r % size;
+  n_blk = r / size;
+}
+
+// Bounded wait on an mbarrier phase.  Returns false when the CTA is aborting.
+__device__ __forceinline__ bool wait_bounded(uint32_t bar, uint32_t parity, volatile uint32_t* abort,
+                                             uint32_t code) {
+  if (mbar_try_wait(bar, parity)) return true;
+  uint64_t t0 = 0;
+  uint32_t spins = 0;
+  while (true) {
+    if (mbar_try_wait(bar, parity)) return true;
+    if (*abort) return false;
+    if (++spins > 2048) {
+      if (t0 == 0) t0 = globaltimer_ns();
+      __nanosleep(128);
+      if (globaltimer_ns() - t0 > kWaitBudgetNs) {
+        *abort = 1;
+        atomicCAS(&g_timeout_record[0], 0u, code);
+        return false;
+      }
+    }
+  }
+}
+
+template <int BN>
+__device__ __forceinline__ void epilogue_chunk(const GemmParams& p, const uint32_t (&acc)[32], int m,
+                                               int n0, bool row_ok, float rs, int64_t gofs) {
+  // 32 consecutive columns of one row.
+  float v[32];
+#pragma unroll
+  for (int i = 0; i < 32; ++i) {
+    const float a = __uint_as_float(acc[i]);
+    v[i] = p.exact ? a : __bfloat162float(__float2bfloat16_rn(a));
+  }
+  if (!row_ok) return;
+  const int valid = min(32, p.N - n0);  // multiple of 16 (N is), > 0
+  if (p.epilogue == EPI_RAW) {
+    __nv_bfloat16* o = reinterpret_cast<__nv_bfloat16*>(p.out) + (int64_t)m * p.ld_out + n0;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      if (j * 8 < valid) {
+        uint4 u;
+        u.x = f32_to_bf16_bits(v[8 * j + 0]) | (f32_to_bf16_bits(v[8 * j + 1]) << 16);
+        u.y = f32_to_bf16_bits(v[8 * j + 2]) | (f32_to_bf16_bits(v[8 * j + 3]) << 16);
+        u.z = f32_to_bf16_bits(v[8 * j + 4]) | (f32_to_bf16_bits(v[8 * j + 5]) << 16);
+        u.w = f32_to_bf16_bits(v[8 * j + 6]) | (f32_to_bf16_bits(v[8 * j + 7]) << 16);
+        *reinterpret_cast<uint4*>(o + 8 * j) = u;
+      }
+    }
+    return;
+  }
+  // Consumer arithmetic.  Column vectors are read with warp-uniform addresses (every thread
+  // of the warp has the same columns), which the L1 serves as broadcasts.
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    if (j * 8 >= valid) break;
+    const int64_t off = (int64_t)m * p.ld_out + n0 + 8 * j;
+    float res[8];
+    if (p.epilogue == EPI_RESIDUAL) {
+      if (p.out_dtype == IFLB200_F32) {
+        const float* o = reinterpret_cast<const float*>(p.out) + off;
+        const float4 a = *reinterpret_cast<const float4*>(o);
+        const float4 b = *reinterpret_cast<const float4*>(o + 4);
+        res[0] = a.x; res[1] = a.y; res[2] = a.z; res[3] = a.w;
+        res[4] = b.x; res[5] = b.y; res[6] = b.z; res[7] = b.w;
+      } else {
+        const uint4 u = *reinterpret_cast<const uint4*>(reinterpret_cast<const __nv_bfloat16*>(p.out) + off);
+        const uint32_t w[4] = {u.x, u.y, u.z, u.w};
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          res[2 * i] = __uint_as_float(w[i] << 16);
+          res[2 * i + 1] = __uint_as_float(w[i] & 0xFFFF0000u);
+        }
+      }
+    }
+    float y[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const int n = n0 + 8 * j + i;
+      Chain ch(v[8 * j + i]);
+      if (p.row) ch.mul(rs);
+      if (p.col) ch.mul(__ldg(p.col + (int64_t)n * p.col_stride));
+      if (p.bias) {
+        const float b = (p.bias_dtype == IFLB200_F32)
+                            ? __ldg(reinterpret_cast<const float*>(p.bias) + n)
+                            : __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(p.bias)[n]);
+        ch.add(b);
+      }
+      if (p.epilogue == EPI_RESIDUAL) {
+        if (p.gate) ch.mul(__ldg(p.gate + gofs + n));
+        ch.add(res[i]);  // res + d, contracted with d's last multiply when there is one
+      }
+      y[i] = ch.done();
+    }
+    if (p.out_dtype == IFLB200_F32) {
+      float* o = reinterpret_cast<float*>(p.out) + off;
+      *reinterpret_cast<float4*>(o) = make_float4(y[0], y[1], y[2], y[3]);
+      *reinterpret_cast<float4*>(o + 4) = make_float4(y[4], y[5], y[6], y[7]);
+    } else if (p.out_dtype == IFLB200_BF16) {
+      uint4 u;
+      u.x = f32_to_bf16_bits(y[0]) | (f32_to_bf16_bits(y[1]) << 16);
+      u.y = f32_to_bf16_bits(y[2]) | (f32_to_bf16_bits(y[3]) << 16);
+      u.z = f32_to_bf16_bits(y[4]) | (f32_to_bf16_bits(y[5]) << 16);
+      u.w = f32_to_bf16_bits(y[6]) | (f32_to_bf16_bits(y[7]) << 16);
+      *reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(p.out) + off) = u;
+    } else {
+      uint4 u;
+      u.x = f32_to_f16_bits(y[0]) | (f32_to_f16_bits(y[1]) << 16);
+      u.y = f32_to_f16_bits(y[2]) | (f32_to_f16_bits(y[3]) << 16);
+      u.z = f32_to_f16_bits(y[4]) | (f32_to_f16_bits(y[5]) << 16);
+      u.w = f32_to_f16_bits(y[6]) | (f32_to_f16_bits(y[7]) << 16);
+      *reinterpret_cast<uint4*>(reinterpret_cast<__half*>(p.out) + off) = u;
+    }
+  }
+}
+
+template <int BN, int STAGES>
+__global__ void __launch_bounds__(kGemmThreads, 1)
+gemm_fp8_tc5_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_w,
+                    const GemmParams p) {
+  using L = SmemLayout<BN, STAGES>;
+  constexpr uint32_t kTmemCols = (2 * BN < 32) ? 32 : 2 * BN;  // BN in {32,64,128,256}
+  constexpr uint32_t kIdesc = make_idesc_e4m3_f32(BM, BN);
+
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t raw_addr = smem_u32(smem_raw);
+  const uint32_t base = (raw_addr + 1023u) & ~1023u;
+  uint8_t* smem = smem_raw + (base - raw_addr);
+
+  const uint32_t bar0 = base + L::kBarOffset;
+  auto full_bar = [&](int s) { return bar0 + 8u * s; };
+  auto empty_bar = [&](int s) { return bar0 + 8u * (STAGES + s); };
+  auto tfull_bar = [&](int a) { return bar0 + 8u * (2 * STAGES + a); };
+  auto tempty_bar = [&](int a) { return bar0 + 8u * (2 * STAGES + 2 + a); };
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + L::kBarOffset + L::kNumBars * 8);
+  volatile uint32_t* abort_flag = tmem_slot + 1;
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(full_bar(s), 1);
+      mbar_init(empty_bar(s), 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(tfull_bar(a), 1);
+      mbar_init(tempty_bar(a), 4);  // one arrival per epilogue warp
+    }
+    tmem_slot[1] = 0;
+    fence_barrier_init();
+    fence_proxy_async_smem();
+  }
+  if (warp == 1) {
+    tmem_alloc(smem_u32(tmem_slot), kTmemCols);
+    tmem_relinquish();
+  }
+  if (warp == 0 && lane == 0) {
+    prefetch_tensormap(&tm_a);
+    prefetch_tensormap(&tm_w);
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------------ TMA producer
+    int stage = 0;
+    uint32_t phase = 0;
+    uint32_t armed = 0;        // stages armed at least once
+    uint32_t last_parity = 0;  // parity of the last arming per stage
+    bool ok = true;
+    uint32_t it = 0;
+    for (int tile = blockIdx.x; ok && tile < p.num_tiles; tile += gridDim.x, ++it) {
+      int m_blk, n_blk;
+      tile_coords(p, tile, m_blk, n_blk);
+      for (int kb = 0; kb < p.num_k; ++kb) {
+        ok = __all_sync(0xFFFFFFFFu, wait_bounded(empty_bar(stage), phase ^ 1, abort_flag,
+                                                  (1u << 24) | (1u << 16) | (it & 0xFFFF)));
+        if (!ok) break;
+        if (lane == 0) {
+          mbar_arrive_expect_tx(full_bar(stage), L::kStageBytes);
+          const uint32_t sa = base + stage * L::kStageBytes;
+          tma_load_2d(sa, &tm_a, full_bar(stage), kb * BK, m_blk * BM);
+          tma_load_2d(sa + L::kABytes, &tm_w, full_bar(stage), kb * BK, n_blk * BN);
+        }
+        armed |= 1u << stage;
+        last_parity = (last_parity & ~(1u << stage)) | (phase << stage);
+        __syncwarp();
+        if (++stage == STAGES) {
+          stage = 0;
+          phase ^= 1;
+        }
+      }
+    }
+    // Drain: every load this warp issued must have landed before the CTA's shared memory can
+    // go away.  Normal exit: the consumer has already waited on all of them, these return at
+    // once.  Abort: bounded.
+    for (int s = 0; s < STAGES; ++s) {
+      if (armed & (1u << s)) {
+        const uint32_t par = (last_parity >> s) & 1u;
+        uint32_t spins = 0;
+        while (!mbar_try_wait(full_bar(s), par) && ++spins < (1u << 20)) __nanosleep(64);
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------------ MMA issuer
+    int stage = 0;
+    uint32_t phase = 0;
+    bool ok = true;
+    uint32_t it = 0;
+    for (int tile = blockIdx.x; ok && tile < p.num_tiles; tile += gridDim.x, ++it) {
+      const uint32_t acc = it & 1u;
+      const uint32_t acc_phase = (it >> 1) & 1u;
+      ok = __all_sync(0xFFFFFFFFu, wait_bounded(tempty_bar(acc), acc_phase ^ 1, abort_flag,
+                                                (2u << 24) | (2u << 16) | (it & 0xFFFF)));
+      if (!ok) break;
+      tc_fence_after();
+      const uint32_t d_tmem = tmem_base + acc * BN;
+      for (int kb = 0; kb < p.num_k; ++kb) {
+        ok = __all_sync(0xFFFFFFFFu, wait_bounded(full_bar(stage), phase, abort_flag,
+                                                  (2u << 24) | (3u << 16) | (it & 0xFFFF)));
+        if (!ok) break;
+        tc_fence_after();
+        if (lane == 0) {
+          const uint32_t sa = base + stage * L::kStageBytes;
+          const uint64_t da = make_kmajor_sw128_desc(sa);
+          const uint64_t db = make_kmajor_sw128_desc(sa + L::kABytes);
+#pragma unroll
+          for (int j = 0; j < BK / 32; ++j) {
+            // 32 bytes further along K inside the swizzled 128-byte row: +2 in 16-byte units.
+            mma_f8f6f4(d_tmem, da + 2 * j, db + 2 * j, kIdesc, (kb | j) != 0 ? 1u : 0u);
+          }
+          mma_commit(empty_bar(stage));  // stage reusable once these MMAs have read it
+        }
+        __syncwarp();
+        if (++stage == STAGES) {
+          stage = 0;
+          phase ^= 1;
+        }
+      }
+      if (!ok) break;
+      if (lane == 0) mma_commit(tfull_bar(acc));  // accumulator complete
+      __syncwarp();
+    }
+  } else {
+    // ------------------------------------------------------------------ epilogue warps
+    const int quad = warp & 3;  // TMEM lanes [32*quad, 32*quad+32) are this warp's
+    bool ok = true;
+    uint32_t it = 0;
+    for (int tile = blockIdx.x; ok && tile < p.num_tiles; tile += gridDim.x, ++it) {
+      int m_blk, n_blk;
+      tile_coords(p, tile, m_blk, n_blk);
+      const uint32_t acc = it & 1u;
+      const uint32_t acc_phase = (it >> 1) & 1u;
+      ok = __all_sync(0xFFFFFFFFu, wait_bounded(tfull_bar(acc), acc_phase, abort_flag,
+                                                (3u << 24) | (4u << 16) | (it & 0xFFFF)));
+      if (!ok) break;
+      tc_fence_after();
+      const int m = m_blk * BM + quad * 32 + lane;
+      const bool row_ok = m < p.M;
+      const float rs = (row_ok && p.row) ? __ldg(p.row + (int64_t)m * p.row_stride) : 1.0f;
+      const int64_t gofs = (row_ok && p.gate_index) ? (int64_t)p.gate_index[m] * p.N : 0;
+      const uint32_t t_row = tmem_base + ((uint32_t)(quad * 32) << 16) + acc * BN;
+#pragma unroll 1
+      for (int c = 0; c < BN / 32; ++c) {
+        const int n0 = n_blk * BN + c * 32;
+        if (n0 >= p.N) break;  // uniform
+        uint32_t r[32];
+        tmem_ld_32x32b_x32(t_row + c * 32, r);
+        tmem_ld_wait();
+        epilogue_chunk<BN>(p, r, m, n0, row_ok, rs, gofs);
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(tempty_bar(acc));
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, kTmemCols);
+  }
+}
+
+// --------------------------------------------------------------------------------------------
+// Host side
+// --------------------------------------------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*,
+                                  CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion,
+                                  CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn get_encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  static bool tried = false;
+  if (!tried) {
+    tried = true;
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(p);
+  }
+  return fn;
+}
+
+// [rows, K] e4m3 matrix, K contiguous, row stride ld bytes; box = 128 bytes x box_rows with the
+// 128-byte swizzle; out-of-range elements read as zero.
+static int make_tensor_map(CUtensorMap* tm, const void* ptr, int rows, int K, int64_t ld, int box_rows) {
+  EncodeTiledFn enc = get_encode_fn();
+  if (!enc) return IFLB200_ERR_DRIVER;
+  const cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)rows};
+  const cuuint64_t strides[1] = {(cuuint64_t)ld};
+  const cuuint32_t box[2] = {(cuuint32_t)BK, (cuuint32_t)box_rows};
+  const cuuint32_t estr[2] = {1, 1};
+  const CUresult r = enc(tm, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(ptr), dims, strides, box,
+                         estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                         CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? IFLB200_OK : IFLB200_ERR_DRIVER;
+}
+
+struct DeviceInfo {
+  int sm_count = 0;
+  int cc_major = 0;
+  bool ready = false;
+};
+static DeviceInfo g_dev[64];
+
+static int device_info(DeviceInfo** out) {
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return (int)e;
+  if (dev < 0 || dev >= 64) return IFLB200_ERR_DEVICE;
+  DeviceInfo& d = g_dev[dev];
+  if (!d.ready) {
+    e = cudaDeviceGetAttribute(&d.sm_count, cudaDevAttrMultiProcessorCount, dev);
+    if (e != cudaSuccess) return (int)e;
+    e = cudaDeviceGetAttribute(&d.cc_major, cudaDevAttrComputeCapabilityMajor, dev);
+    if (e != cudaSuccess) return (int)e;
+    d.ready = true;
+  }
+  if (d.cc_major != 10) return IFLB200_ERR_DEVICE;
+  *out = &d;
+  return IFLB200_OK;
+}
+
+static int g_cfg_tile_n = 0, g_cfg_stages = 0, g_cfg_group_m = 0;
+
+template <int BN, int STAGES>
+static int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tw, const GemmParams& p, int grid,
+                       cudaStream_t s) {
+  using L = SmemLayout<BN, STAGES>;
+  static bool attr_set[64] = {};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (!attr_set[dev]) {
+    cudaError_t e = cudaFuncSetAttribute(gemm_fp8_tc5_kernel<BN, STAGES>,
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize, L::kDynamic);
+    if (e != cudaSuccess) return (int)e;
+    attr_set[dev] = true;
+  }
+  gemm_fp8_tc5_kernel<BN, STAGES><<<grid, kGemmThreads, L::kDynamic, s>>>(ta, tw, p);
+  return (int)cudaGetLastError();
+}
+
+static int run_gemm(const void* a, int64_t ld_a, const void* w, int64_t ld_w, GemmParams p, void* stream) {
+  if (p.M < 0 || p.N < 0 || p.K < 0) return IFLB200_ERR_ARG;
+  if (p.M == 0 || p.N == 0) return IFLB200_OK;
+  if (!a || !w || !p.out) return IFLB200_ERR_ARG;
+  if (p.K < 16 || p.K % 16 || p.N % 16) return IFLB200_ERR_SHAPE;
+  if (ld_a < p.K || ld_w < p.K || p.ld_out < p.N) return IFLB200_ERR_ARG;
+  const int oes = (p.out_dtype == IFLB200_F32) ? 4 : 2;
+  if ((reinterpret_cast<uintptr_t>(a) & 15) || (reinterpret_cast<uintptr_t>(w) & 15) || ld_a % 16 || ld_w % 16 ||
+      (reinterpret_cast<uintptr_t>(p.out) & 15) || (p.ld_out * oes) % 16)
+    return IFLB200_ERR_ALIGN;
+  DeviceInfo* dev = nullptr;
+  int st = device_info(&dev);
+  if (st != IFLB200_OK) return st;
+
+  // Tile width: the widest tile that still gives every SM work; narrower tiles for skinny
+  // problems so that more SMs stream weights.
+  p.num_m = (p.M + BM - 1) / BM;
+  int bn = g_cfg_tile_n;
+  if (bn == 0) {
+    bn = 256;
+    while (bn > 32 && (int64_t)p.num_m * ((p.N + bn - 1) / bn) < dev->sm_count) bn /= 2;
+    if (bn < 64) bn = 64;
+  }
+  p.num_n = (p.N + bn - 1) / bn;
+  p.num_k = (p.K + BK - 1) / BK;
+  p.num_tiles = p.num_m * p.num_n;
+  p.group_m = g_cfg_group_m > 0 ? g_cfg_group_m : 8;
+  const int grid = p.num_tiles < dev->sm_count ? p.num_tiles : dev->sm_count;
+
+  CUtensorMap ta, tw;
+  st = make_tensor_map(&ta, a, p.M, p.K, ld_a, BM);
+  if (st != IFLB200_OK) return st;
+  st = make_tensor_map(&tw, w, p.N, p.K, ld_w, bn);
+  if (st != IFLB200_OK) return st;
+  cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+  const int stages = g_cfg_stages;
+  switch (bn) {
+    case 256: return (stages == 3) ? launch_gemm<256, 3>(ta, tw, p, grid, s) : launch_gemm<256, 4>(ta, tw, p, grid, s);
+    case 128: return (stages == 4) ? launch_gemm<128, 4>(ta, tw, p, grid, s) : launch_gemm<128, 6>(ta, tw, p, grid, s);
+    case 64: return (stages == 4) ? launch_gemm<64, 4>(ta, tw, p, grid, s) : launch_gemm<64, 8>(ta, tw, p, grid, s);
+    default: return IFLB200_ERR_ARG;
+  }
+}
+
+}  // namespace iflb200
+
+using namespace iflb200;
+
+extern "C" int iflb200_gemm_set_config(int tile_n, int stages, int group_m) {
+  if (tile_n != 0 && tile_n != 64 && tile_n != 128 && tile_n != 256) return IFLB200_ERR_ARG;
+  if (stages < 0 || group_m < 0) return IFLB200_ERR_ARG;
+  g_cfg_tile_n = tile_n;
+  g_cfg_stages = stages;
+  g_cfg_group_m = group_m;
+  return IFLB200_OK;
+}
+
+extern "C" int iflb200_gemm_take_timeout_record(uint32_t* record, void* stream) {
+  if (!record) return IFLB200_ERR_ARG;
+  cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+  uint32_t host[4] = {0, 0, 0, 0};
+  cudaError_t e = cudaMemcpyFromSymbolAsync(host, g_timeout_record, sizeof(host), 0, cudaMemcpyDeviceToHost, s);
+  if (e != cudaSuccess) return (int)e;
+  e = cudaStreamSynchronize(s);
+  if (e != cudaSuccess) return (int)e;
+  *record = host[0];
+  if (host[0] != 0) {
+    const uint32_t zero[4] = {0, 0, 0, 0};
+    e = cudaMemcpyToSymbolAsync(g_timeout_record, zero, sizeof(zero), 0, cudaMemcpyHostToDevice, s);
+    if (e != cudaSuccess) return (int)e;
+    e = cudaStreamSynchronize(s);
+  }
+  return (int)e;
+}
+
+extern "C" int iflb200_gemm_fp8_raw(const void* a, int64_t ld_a, const void* w, int64_t ld_w, int M, int N,
+                                    int K, void* out, int64_t ld_out, void* stream) {
+  GemmParams p = {};
+  p.M = M; p.N = N; p.K = K;
+  p.epilogue = EPI_RAW;
+  p.out = out; p.out_dtype = IFLB200_BF16; p.ld_out = ld_out;
+  return run_gemm(a, ld_a, w, ld_w, p, stream);
+}
+
+extern "C" int iflb200_fp8_linear(const void* a, int64_t ld_a, const void* w, int64_t ld_w, int M, int N,
+                                  int K, const float* row_scale, int row_scale_stride,
+                                  const float* col_scale, int col_scale_stride, const void* bias,
+                                  int bias_dtype, int rounding, void* out, int out_dtype, int64_t ld_out,
+                                  void* stream) {
+  if (out_dtype != IFLB200_F32 && out_dtype != IFLB200_BF16 && out_dtype != IFLB200_F16) return IFLB200_ERR_DTYPE;
+  if (bias && bias_dtype != IFLB200_F32 && bias_dtype != IFLB200_BF16) return IFLB200_ERR_DTYPE;
+  if (rounding != IFLB200_ROUND_ENGINE && rounding != IFLB200_ROUND_EXACT) return IFLB200_ERR_ARG;
+  if ((row_scale_stride | 1) != 1 || (col_scale_stride | 1) != 1) return IFLB200_ERR_ARG;
+  GemmParams p = {};
+  p.M = M; p.N = N; p.K = K;
+  p.epilogue = EPI_DEQUANT;
+  p.exact = rounding == IFLB200_ROUND_EXACT;
+  p.row = row_scale; p.row_stride = row_scale_stride;
+  p.col = col_scale; p.col_stride = col_scale_stride;
+  p.bias = bias; p.bias_dtype = bias_dtype;
+  p.out = out; p.out_dtype = out_dtype; p.ld_out = ld_out;
+  return run_gemm(a, ld_a, w, ld_w, p, stream);
+}
+
+extern "C" int iflb200_fp8_linear_residual(const void* a, int64_t ld_a, const void* w, int64_t ld_w, int M,
+                                           int N, int K, const float* row_scale, const float* col_scale,
+                                           const float* bias, const float* gate, const int32_t* gate_index,
+                                           void* res, int res_dtype, int64_t ld_res, void* stream) {
+  if (res_dtype != IFLB200_F32 && res_dtype != IFLB200_BF16) return IFLB200_ERR_DTYPE;
+  GemmParams p = {};
+  p.M = M; p.N = N; p.K = K;
+  p.epilogue = EPI_RESIDUAL;
+  p.row = row_scale; p.row_stride = 1;
+  p.col = col_scale; p.col_stride = 1;
+  p.bias = bias; p.bias_dtype = IFLB200_F32;
+  p.gate = gate; p.gate_index = gate ? gate_index : nullptr;
+  p.out = res; p.out_dtype = res_dtype; p.ld_out = ld_res;
+  return run_gemm(a, ld_a, w, ld_w, p, stream);
+}
+
+extern "C" int iflb200_abi_version(void) { return IFLB200_ABI_VERSION; }
+
+extern "C" const char* iflb200_status_string(int status) {
+  switch (status) {
+    case IFLB200_OK: return "ok";
+    case IFLB200_ERR_ARG: return "invalid argument (null pointer, negative size or stride shorter than the row)";
+    case IFLB200_ERR_SHAPE: return "unsupported shape (K and N must be multiples of 16; width above the kernel's maximum)";
+    case IFLB200_ERR_ALIGN: return "pointer or row stride breaks the 16-byte alignment rule";
+    case IFLB200_ERR_DTYPE: return "unsupported element type";
+    case IFLB200_ERR_DRIVER: return "cuTensorMapEncodeTiled unavailable or rejected the layout";
+    case IFLB200_ERR_DEVICE: return "current device is not a compute capability 10.x GPU";
+    case IFLB200_ERR_WORKSPACE: return "workspace missing or too small";
+    default: return status > 0 ? cudaGetErrorString((cudaError_t)status) : "unknown status";
+  }
+}

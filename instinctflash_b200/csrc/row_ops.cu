@@ -1,0 +1,826 @@
+// Row kernels of the FP8 linear path for sm_100a: the per-token e4m3 quantiser and the
+// consumers of raw GEMM accumulators.  One group of TPR threads owns one row and keeps it in
+// registers, so each element is read once and written once; loads are 128-bit, codes are
+// stored 8 at a time.  All of them are HBM-bound: bytes per row are in the comments.
+#include <cuda_runtime.h>
+
+#include "../../include/iflb200.h"
+#include "rowmath.cuh"
+
+namespace iflb200 {
+
+constexpr int kItersMax = 4;  // 8-element chunks per thread
+constexpr int kMaxTpr = 512;  // threads per row at most (128 registers each stay available)
+constexpr int kMaxWidth = kMaxTpr * 8 * kItersMax;  // 16384 columns
+
+// --------------------------------------------------------------------------------------------
+// 8-element loads / stores
+// --------------------------------------------------------------------------------------------
+template <typename T>
+__device__ __forceinline__ void load8(const T* p, float (&o)[8]);
+template <>
+__device__ __forceinline__ void load8<__nv_bfloat16>(const __nv_bfloat16* p, float (&o)[8]) {
+  const uint4 u = *reinterpret_cast<const uint4*>(p);
+  const uint32_t w[4] = {u.x, u.y, u.z, u.w};
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    o[2 * i] = __uint_as_float(w[i] << 16);
+    o[2 * i + 1] = __uint_as_float(w[i] & 0xFFFF0000u);
+  }
+}
+template <>
+__device__ __forceinline__ void load8<__half>(const __half* p, float (&o)[8]) {
+  const uint4 u = *reinterpret_cast<const uint4*>(p);
+  const uint32_t w[4] = {u.x, u.y, u.z, u.w};
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&w[i]));
+    o[2 * i] = f.x;
+    o[2 * i + 1] = f.y;
+  }
+}
+template <>
+__device__ __forceinline__ void load8<float>(const float* p, float (&o)[8]) {
+  const float4 a = *reinterpret_cast<const float4*>(p);
+  const float4 b = *reinterpret_cast<const float4*>(p + 4);
+  o[0] = a.x; o[1] = a.y; o[2] = a.z; o[3] = a.w;
+  o[4] = b.x; o[5] = b.y; o[6] = b.z; o[7] = b.w;
+}
+
+// Chunk of a row: vector path when the whole chunk is inside the row and the buffers obey the
+// 16-byte rule, element-wise otherwise (zeros beyond the row end).
+template <typename T>
+__device__ __forceinline__ void load_chunk(const T* row_ptr, int c0, int width, bool vec,
+                                           float (&o)[8]) {
+  if (vec && c0 + 8 <= width) {
+    load8<T>(row_ptr + c0, o);
+  } else {
+#pragma unroll
+    for (int i = 0; i < 8; ++i) o[i] = (c0 + i < width) ? to_f32(row_ptr[c0 + i]) : 0.0f;
+  }
+}
+__device__ __forceinline__ void load_chunk_f32(const float* p, int c0, int width, bool vec,
+                                               float (&o)[8]) {
+  load_chunk<float>(p, c0, width, vec, o);
+}
+
+__device__ __forceinline__ void store_codes8(uint8_t* row_ptr, int c0, int width, bool vec,
+                                             const float (&v)[8], float inv) {
+  const uint32_t lo = cvt_e4m3x4(__fmul_rn(v[0], inv), __fmul_rn(v[1], inv), __fmul_rn(v[2], inv),
+                                 __fmul_rn(v[3], inv));
+  const uint32_t hi = cvt_e4m3x4(__fmul_rn(v[4], inv), __fmul_rn(v[5], inv), __fmul_rn(v[6], inv),
+                                 __fmul_rn(v[7], inv));
+  if (vec && c0 + 8 <= width) {
+    *reinterpret_cast<uint2*>(row_ptr + c0) = make_uint2(lo, hi);
+  } else {
+#pragma unroll
+    for (int i = 0; i < 8; ++i)
+      if (c0 + i < width) row_ptr[c0 + i] = (uint8_t)(((i < 4 ? lo : hi) >> (8 * (i & 3))) & 0xFF);
+  }
+}
+
+template <typename T>
+__device__ __forceinline__ void store_out8(T* row_ptr, int c0, int width, bool vec,
+                                           const float (&v)[8]);
+template <>
+__device__ __forceinline__ void store_out8<__nv_bfloat16>(__nv_bfloat16* row_ptr, int c0, int width,
+                                                          bool vec, const float (&v)[8]) {
+  if (vec && c0 + 8 <= width) {
+    uint4 u;
+    u.x = f32_to_bf16_bits(v[0]) | (f32_to_bf16_bits(v[1]) << 16);
+    u.y = f32_to_bf16_bits(v[2]) | (f32_to_bf16_bits(v[3]) << 16);
+    u.z = f32_to_bf16_bits(v[4]) | (f32_to_bf16_bits(v[5]) << 16);
+    u.w = f32_to_bf16_bits(v[6]) | (f32_to_bf16_bits(v[7]) << 16);
+    *reinterpret_cast<uint4*>(row_ptr + c0) = u;
+  } else {
+#pragma unroll
+    for (int i = 0; i < 8; ++i)
+      if (c0 + i < width) row_ptr[c0 + i] = __float2bfloat16_rn(v[i]);
+  }
+}
+template <>
+__device__ __forceinline__ void store_out8<__half>(__half* row_ptr, int c0, int width, bool vec,
+                                                   const float (&v)[8]) {
+  if (vec && c0 + 8 <= width) {
+    uint4 u;
+    u.x = f32_to_f16_bits(v[0]) | (f32_to_f16_bits(v[1]) << 16);
+    u.y = f32_to_f16_bits(v[2]) | (f32_to_f16_bits(v[3]) << 16);
+    u.z = f32_to_f16_bits(v[4]) | (f32_to_f16_bits(v[5]) << 16);
+    u.w = f32_to_f16_bits(v[6]) | (f32_to_f16_bits(v[7]) << 16);
+    *reinterpret_cast<uint4*>(row_ptr + c0) = u;
+  } else {
+#pragma unroll
+    for (int i = 0; i < 8; ++i)
+      if (c0 + i < width) row_ptr[c0 + i] = __float2half_rn(v[i]);
+  }
+}
+template <>
+__device__ __forceinline__ void store_out8<float>(float* row_ptr, int c0, int width, bool vec,
+                                                  const float (&v)[8]) {
+  if (vec && c0 + 8 <= width) {
+    *reinterpret_cast<float4*>(row_ptr + c0) = make_float4(v[0], v[1], v[2], v[3]);
+    *reinterpret_cast<float4*>(row_ptr + c0 + 4) = make_float4(v[4], v[5], v[6], v[7]);
+  } else {
+#pragma unroll
+    for (int i = 0; i < 8; ++i)
+      if (c0 + i < width) row_ptr[c0 + i] = v[i];
+  }
+}
+__device__ __forceinline__ void store_out8_dyn(void* base, int dtype, int64_t row_off, int c0,
+                                               int width, bool vec, const float (&v)[8]) {
+  if (dtype == IFLB200_BF16)
+    store_out8<__nv_bfloat16>(reinterpret_cast<__nv_bfloat16*>(base) + row_off, c0, width, vec, v);
+  else if (dtype == IFLB200_F16)
+    store_out8<__half>(reinterpret_cast<__half*>(base) + row_off, c0, width, vec, v);
+  else
+    store_out8<float>(reinterpret_cast<float*>(base) + row_off, c0, width, vec, v);
+}
+
+// --------------------------------------------------------------------------------------------
+// Reductions over the TPR threads of one row (TPR a multiple of 32; rows never share a warp).
+// `slot` is a per-reduction shared array of NT/32 floats.
+// --------------------------------------------------------------------------------------------
+template <int TPR, bool IS_MAX>
+__device__ __forceinline__ float row_reduce(float v, float* slot) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    const float other = __shfl_xor_sync(0xFFFFFFFFu, v, o);
+    v = IS_MAX ? max_f32(v, other) : __fadd_rn(v, other);
+  }
+  if (TPR > 32) {
+    const int warp = threadIdx.x >> 5;
+    if ((threadIdx.x & 31) == 0) slot[warp] = v;
+    __syncthreads();
+    constexpr int WPR = TPR / 32;
+    const int first = (warp / WPR) * WPR;
+    float r = slot[first];
+#pragma unroll
+    for (int i = 1; i < WPR; ++i) r = IS_MAX ? max_f32(r, slot[first + i]) : __fadd_rn(r, slot[first + i]);
+    v = r;
+  }
+  return v;
+}
+
+template <int TPR>
+__host__ __device__ constexpr int threads_per_cta() {
+  return TPR > 256 ? TPR : 256;
+}
+
+// --------------------------------------------------------------------------------------------
+// row_quant: 2K (bf16 in) + K (codes out) + 4 bytes per row.
+// --------------------------------------------------------------------------------------------
+struct RowQuantArgs {
+  const void* x;
+  int64_t ld_x;
+  int M, K, iters;
+  const float* row;
+  const float* col;
+  const float* bias;
+  int gelu;
+  uint8_t* q;
+  int64_t ld_q;
+  float* qs;
+  int vec;
+};
+
+template <typename XT, int TPR>
+__global__ void __launch_bounds__(threads_per_cta<TPR>())
+row_quant_kernel(const RowQuantArgs a) {
+  constexpr int NT = threads_per_cta<TPR>();
+  __shared__ float red[NT / 32];
+  const int t = threadIdx.x % TPR;
+  const int m = blockIdx.x * (NT / TPR) + threadIdx.x / TPR;
+  const bool live = m < a.M;
+  const XT* xr = reinterpret_cast<const XT*>(a.x) + (live ? (int64_t)m * a.ld_x : 0);
+  const bool vec = a.vec != 0;
+  const float rs = (live && a.row) ? a.row[m] : 1.0f;
+
+  float v[kItersMax][8];
+  float amax = 0.0f;
+#pragma unroll
+  for (int it = 0; it < kItersMax; ++it) {
+    const int c0 = (it * TPR + t) * 8;
+    if (it < a.iters && live && c0 < a.K) {
+      load_chunk<XT>(xr, c0, a.K, vec, v[it]);
+      if (a.row || a.col || a.bias || a.gelu) {
+        float cs[8], bs[8];
+        if (a.col) load_chunk_f32(a.col, c0, a.K, vec, cs);
+        if (a.bias) load_chunk_f32(a.bias, c0, a.K, vec, bs);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          Chain ch(v[it][i]);
+          if (a.row) ch.mul(rs);
+          if (a.col) ch.mul(cs[i]);
+          if (a.bias) ch.add(bs[i]);
+          float y = ch.done();
+          if (a.gelu) y = gelu_tanh_ref(y);
+          v[it][i] = (c0 + i < a.K) ? y : 0.0f;
+        }
+      }
+#pragma unroll
+      for (int i = 0; i < 8; ++i) amax = max_f32(amax, fabsf(v[it][i]));
+    }
+  }
+  amax = row_reduce<TPR, true>(amax, red);
+  float scale, inv;
+  quant_scales(amax, scale, inv);
+  if (!live) return;
+  if (t == 0) a.qs[m] = scale;
+  uint8_t* qr = a.q + (int64_t)m * a.ld_q;
+#pragma unroll
+  for (int it = 0; it < kItersMax; ++it) {
+    const int c0 = (it * TPR + t) * 8;
+    if (it < a.iters && c0 < a.K) store_codes8(qr, c0, a.K, vec, v[it], inv);
+  }
+}
+
+// --------------------------------------------------------------------------------------------
+// gated_act_quant: 4F (bf16 g,u in) + F (codes out) + 4 bytes per row.
+// --------------------------------------------------------------------------------------------
+struct GatedArgs {
+  const void* gu;
+  int64_t ld_gu;
+  int M, F, iters;
+  const float* row;
+  const float* col;
+  int act;
+  uint8_t* q;
+  int64_t ld_q;
+  float* qs;
+  int vec;
+};
+
+template <typename XT, int TPR>
+__global__ void __launch_bounds__(threads_per_cta<TPR>())
+gated_act_quant_kernel(const GatedArgs a) {
+  constexpr int NT = threads_per_cta<TPR>();
+  __shared__ float red[NT / 32];
+  const int t = threadIdx.x % TPR;
+  const int m = blockIdx.x * (NT / TPR) + threadIdx.x / TPR;
+  const bool live = m < a.M;
+  const XT* gr = reinterpret_cast<const XT*>(a.gu) + (live ? (int64_t)m * a.ld_gu : 0);
+  const XT* ur = gr + a.F;
+  const bool vec = a.vec != 0;
+  const float rs = (live && a.row) ? a.row[m] : 1.0f;
+
+  float h[kItersMax][8];
+  float amax = 0.0f;
+#pragma unroll
+  for (int it = 0; it < kItersMax; ++it) {
+    const int c0 = (it * TPR + t) * 8;
+    if (it < a.iters && live && c0 < a.F) {
+      float g[8], u[8], cg[8], cu[8];
+      load_chunk<XT>(gr, c0, a.F, vec, g);
+      load_chunk<XT>(ur, c0, a.F, vec, u);
+      if (a.col) {
+        load_chunk_f32(a.col, c0, a.F, vec, cg);
+        load_chunk_f32(a.col + a.F, c0, a.F, vec, cu);
+      }
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        float gg = g[i], uu = u[i];
+        if (a.row) {
+          gg = __fmul_rn(gg, rs);
+          uu = __fmul_rn(uu, rs);
+        }
+        if (a.col) {
+          gg = __fmul_rn(gg, cg[i]);
+          uu = __fmul_rn(uu, cu[i]);
+        }
+        const float act = (a.act == IFLB200_ACT_GELU_TANH) ? gelu_tanh_ref(gg) : silu_ref(gg);
+        // gelu: h = u * act; silu: h = act * u (same product either way).
+        const float y = __fmul_rn(uu, act);
+        h[it][i] = (c0 + i < a.F) ? y : 0.0f;
+        amax = max_f32(amax, fabsf(h[it][i]));
+      }
+    }
+  }
+  amax = row_reduce<TPR, true>(amax, red);
+  float scale, inv;
+  quant_scales(amax, scale, inv);
+  if (!live) return;
+  if (t == 0) a.qs[m] = scale;
+  uint8_t* qr = a.q + (int64_t)m * a.ld_q;
+#pragma unroll
+  for (int it = 0; it < kItersMax; ++it) {
+    const int c0 = (it * TPR + t) * 8;
+    if (it < a.iters && c0 < a.F) store_codes8(qr, c0, a.F, vec, h[it], inv);
+  }
+}
+
+// --------------------------------------------------------------------------------------------
+// dequant_rows: 2D in + out bytes per row; flat.
+// --------------------------------------------------------------------------------------------
+struct DequantArgs {
+  const void* x;
+  int64_t ld_x;
+  int M, D;
+  const float* row;
+  const float* col;
+  const float* bias;
+  void* y;
+  int y_dtype;
+  int64_t ld_y;
+  int vec;
+};
+
+template <typename XT>
+__global__ void __launch_bounds__(256) dequant_rows_kernel(const DequantArgs a) {
+  const int m = blockIdx.y;
+  const int c0 = (blockIdx.x * 256 + threadIdx.x) * 8;
+  if (c0 >= a.D) return;
+  const bool vec = a.vec != 0;
+  const XT* xr = reinterpret_cast<const XT*>(a.x) + (int64_t)m * a.ld_x;
+  float v[8], cs[8], bs[8];
+  load_chunk<XT>(xr, c0, a.D, vec, v);
+  if (a.col) load_chunk_f32(a.col, c0, a.D, vec, cs);
+  if (a.bias) load_chunk_f32(a.bias, c0, a.D, vec, bs);
+  const float rs = a.row ? a.row[m] : 1.0f;
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    Chain ch(v[i]);
+    if (a.row) ch.mul(rs);
+    if (a.col) ch.mul(cs[i]);
+    if (a.bias) ch.add(bs[i]);
+    v[i] = ch.done();
+  }
+  store_out8_dyn(a.y, a.y_dtype, (int64_t)m * a.ld_y, c0, a.D, vec, v);
+}
+
+// --------------------------------------------------------------------------------------------
+// residual_norm_quant
+// --------------------------------------------------------------------------------------------
+struct ResNormArgs {
+  void* res;
+  int64_t ld_res;
+  int M, D, iters;
+  const __nv_bfloat16* delta;
+  int64_t ld_delta;
+  const float* drow;
+  const float* dcol;
+  const float* bias;
+  const float* gate;
+  int write_res;
+  int layernorm;
+  const float* weight;
+  const float* beta;
+  const float* mod_scale;
+  const float* mod_shift;
+  const int32_t* mod_index;
+  float eps;
+  uint8_t* q;
+  int64_t ld_q;
+  float* qs;
+  void* y;
+  int y_dtype;
+  int64_t ld_y;
+  int vec;
+};
+
+template <typename RT>
+__device__ __forceinline__ float round_through(float x);
+template <>
+__device__ __forceinline__ float round_through<float>(float x) { return x; }
+template <>
+__device__ __forceinline__ float round_through<__nv_bfloat16>(float x) {
+  return __bfloat162float(__float2bfloat16_rn(x));
+}
+
+template <typename RT, int TPR>
+__global__ void __launch_bounds__(threads_per_cta<TPR>())
+residual_norm_quant_kernel(const ResNormArgs a) {
+  constexpr int NT = threads_per_cta<TPR>();
+  __shared__ float red[3][NT / 32];
+  const int t = threadIdx.x % TPR;
+  const int m = blockIdx.x * (NT / TPR) + threadIdx.x / TPR;
+  const bool live = m < a.M;
+  const bool vec = a.vec != 0;
+  RT* rr = reinterpret_cast<RT*>(a.res) + (live ? (int64_t)m * a.ld_res : 0);
+  const __nv_bfloat16* dr = a.delta ? a.delta + (live ? (int64_t)m * a.ld_delta : 0) : nullptr;
+  const int64_t mofs = (live && a.mod_index) ? (int64_t)a.mod_index[m] * a.D : 0;
+  const float drs = (live && a.drow) ? a.drow[m] : 1.0f;
+  const float fD = (float)a.D;
+
+  float x[kItersMax][8];
+  float sum = 0.0f, sumsq = 0.0f;
+#pragma unroll
+  for (int it = 0; it < kItersMax; ++it) {
+    const int c0 = (it * TPR + t) * 8;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) x[it][i] = 0.0f;
+    if (it < a.iters && live && c0 < a.D) {
+      load_chunk<RT>(rr, c0, a.D, vec, x[it]);
+      if (dr) {
+        float d[8], cs[8], bs[8], gs[8];
+        load_chunk<__nv_bfloat16>(dr, c0, a.D, vec, d);
+        if (a.dcol) load_chunk_f32(a.dcol, c0, a.D, vec, cs);
+        if (a.bias) load_chunk_f32(a.bias, c0, a.D, vec, bs);
+        if (a.gate) load_chunk_f32(a.gate + mofs, c0, a.D, vec, gs);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          Chain ch(d[i]);
+          if (a.drow) ch.mul(drs);
+          if (a.dcol) ch.mul(cs[i]);
+          if (a.bias) ch.add(bs[i]);
+          if (a.gate) ch.mul(gs[i]);
+          ch.add(x[it][i]);  // x + d, contracted with d's last multiply when there is one
+          const float nx = ch.done();
+          x[it][i] = (c0 + i < a.D) ? (a.write_res ? round_through<RT>(nx) : nx) : 0.0f;
+        }
+        if (a.write_res) store_out8<RT>(rr, c0, a.D, vec, x[it]);
+      }
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        sum = __fadd_rn(sum, x[it][i]);
+        sumsq = __fmaf_rn(x[it][i], x[it][i], sumsq);
+      }
+    }
+  }
+  if (a.q == nullptr && a.y == nullptr) return;  // residual update only (uniform across the CTA)
+
+  float rstd;
+  float mean = 0.0f;
+  if (a.layernorm) {
+    mean = div_full(row_reduce<TPR, false>(sum, red[0]), fD);
+    float sq = 0.0f;
+#pragma unroll
+    for (int it = 0; it < kItersMax; ++it) {
+      const int c0 = (it * TPR + t) * 8;
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        const bool ok = it < a.iters && live && (c0 + i < a.D);
+        x[it][i] = ok ? __fsub_rn(x[it][i], mean) : 0.0f;
+        sq = __fmaf_rn(x[it][i], x[it][i], sq);
+      }
+    }
+    const float var = div_full(row_reduce<TPR, false>(sq, red[1]), fD);
+    rstd = rsqrt_approx_ftz(__fadd_rn(var, a.eps));
+  } else {
+    const float var = div_full(row_reduce<TPR, false>(sumsq, red[1]), fD);
+    rstd = rsqrt_approx_ftz(__fadd_rn(var, a.eps));
+  }
+
+  float amax = 0.0f;
+#pragma unroll
+  for (int it = 0; it < kItersMax; ++it) {
+    const int c0 = (it * TPR + t) * 8;
+    if (it < a.iters && live && c0 < a.D) {
+      float ws[8], bs[8], ms[8], mh[8];
+      if (a.weight) load_chunk_f32(a.weight, c0, a.D, vec, ws);
+      if (a.beta) load_chunk_f32(a.beta, c0, a.D, vec, bs);
+      if (a.mod_scale) {
+        load_chunk_f32(a.mod_scale + mofs, c0, a.D, vec, ms);
+        load_chunk_f32(a.mod_shift + mofs, c0, a.D, vec, mh);
+      }
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        Chain ch(x[it][i]);
+        ch.mul(rstd);
+        if (a.weight) ch.mul(ws[i]);
+        if (a.beta) ch.add(bs[i]);
+        if (a.mod_scale) {
+          ch.mul(__fadd_rn(ms[i], 1.0f));
+          ch.add(mh[i]);
+        }
+        const float y = ch.done();
+        x[it][i] = (c0 + i < a.D) ? y : 0.0f;
+        amax = max_f32(amax, fabsf(x[it][i]));
+      }
+      if (a.y) store_out8_dyn(a.y, a.y_dtype, (int64_t)m * a.ld_y, c0, a.D, vec, x[it]);
+    }
+  }
+  if (a.q == nullptr) return;
+  amax = row_reduce<TPR, true>(amax, red[2]);
+  float scale, inv;
+  quant_scales(amax, scale, inv);
+  if (!live) return;
+  if (t == 0) a.qs[m] = scale;
+  uint8_t* qr = a.q + (int64_t)m * a.ld_q;
+#pragma unroll
+  for (int it = 0; it < kItersMax; ++it) {
+    const int c0 = (it * TPR + t) * 8;
+    if (it < a.iters && c0 < a.D) store_codes8(qr, c0, a.D, vec, x[it], inv);
+  }
+}
+
+// --------------------------------------------------------------------------------------------
+// Per-tensor pack (the torch-FP8-linear recipe)
+// --------------------------------------------------------------------------------------------
+constexpr int kPackThreads = 256;
+constexpr int kPackMaxCtas = 1024;
+
+// Maximum of |x| as an integer maximum of the bf16 magnitude bits: finite values order like
+// their bits, and every NaN pattern is larger than infinity, so NaN propagates.
+__global__ void __launch_bounds__(kPackThreads)
+amax_partial_kernel(const uint16_t* __restrict__ x, int64_t n, uint32_t* __restrict__ partial) {
+  __shared__ uint32_t red[kPackThreads / 32];
+  uint32_t best = 0;
+  const int64_t nvec = n / 8;
+  const bool vec = (reinterpret_cast<uintptr_t>(x) & 15) == 0;
+  const int64_t stride = (int64_t)gridDim.x * kPackThreads;
+  if (vec) {
+    const uint4* xv = reinterpret_cast<const uint4*>(x);
+    for (int64_t i = (int64_t)blockIdx.x * kPackThreads + threadIdx.x; i < nvec; i += stride) {
+      const uint4 u = xv[i];
+      const uint32_t w[4] = {u.x, u.y, u.z, u.w};
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        best = max(best, w[k] & 0x7FFFu);
+        best = max(best, (w[k] >> 16) & 0x7FFFu);
+      }
+    }
+    for (int64_t i = nvec * 8 + (int64_t)blockIdx.x * kPackThreads + threadIdx.x; i < n; i += stride)
+      best = max(best, (uint32_t)x[i] & 0x7FFFu);
+  } else {
+    for (int64_t i = (int64_t)blockIdx.x * kPackThreads + threadIdx.x; i < n; i += stride)
+      best = max(best, (uint32_t)x[i] & 0x7FFFu);
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) best = max(best, __shfl_xor_sync(0xFFFFFFFFu, best, o));
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = best;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    for (int i = 1; i < kPackThreads / 32; ++i) best = max(best, red[i]);
+    partial[blockIdx.x] = best;
+  }
+}
+
+__device__ __forceinline__ float pack_one(float x, float scale) {
+  const float d = __fdiv_rn(x, scale);
+  return (d != d) ? d : fminf(fmaxf(d, -448.0f), 448.0f);
+}
+
+// n_partial > 0: dynamic scale from the partial maxima (every CTA recomputes it; CTA 0 writes
+// it out).  n_partial == 0: fixed scale read from scale_in.
+__global__ void __launch_bounds__(kPackThreads)
+pack_kernel(const uint16_t* __restrict__ x, int64_t n, const uint32_t* __restrict__ partial,
+            int n_partial, const float* __restrict__ scale_in, float* __restrict__ scale_out,
+            uint8_t* __restrict__ q) {
+  __shared__ uint32_t red[kPackThreads / 32];
+  __shared__ float s_scale;
+  if (n_partial > 0) {
+    uint32_t best = 0;
+    for (int i = threadIdx.x; i < n_partial; i += kPackThreads) best = max(best, partial[i]);
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) best = max(best, __shfl_xor_sync(0xFFFFFFFFu, best, o));
+    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = best;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      for (int i = 1; i < kPackThreads / 32; ++i) best = max(best, red[i]);
+      float sc;
+      if (best > 0x7F80u) {
+        sc = __uint_as_float(0x7FC00000u);
+      } else {
+        const float amax = __uint_as_float(best << 16);
+        sc = __fmul_rn(fmaxf(amax, 1e-12f), (float)(1.0 / 448.0));
+      }
+      s_scale = sc;
+      if (blockIdx.x == 0) *scale_out = sc;
+    }
+    __syncthreads();
+  } else {
+    if (threadIdx.x == 0) s_scale = *scale_in;
+    __syncthreads();
+  }
+  const float scale = s_scale;
+  const bool vec = ((reinterpret_cast<uintptr_t>(x) & 15) == 0) && ((reinterpret_cast<uintptr_t>(q) & 7) == 0);
+  const int64_t stride = (int64_t)gridDim.x * kPackThreads;
+  const int64_t nvec = vec ? n / 8 : 0;
+  const uint4* xv = reinterpret_cast<const uint4*>(x);
+  for (int64_t i = (int64_t)blockIdx.x * kPackThreads + threadIdx.x; i < nvec; i += stride) {
+    const uint4 u = xv[i];
+    const uint32_t w[4] = {u.x, u.y, u.z, u.w};
+    float f[8];
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      f[2 * k] = pack_one(__uint_as_float(w[k] << 16), scale);
+      f[2 * k + 1] = pack_one(__uint_as_float(w[k] & 0xFFFF0000u), scale);
+    }
+    reinterpret_cast<uint2*>(q)[i] =
+        make_uint2(cvt_e4m3x4(f[0], f[1], f[2], f[3]), cvt_e4m3x4(f[4], f[5], f[6], f[7]));
+  }
+  for (int64_t i = nvec * 8 + (int64_t)blockIdx.x * kPackThreads + threadIdx.x; i < n; i += stride)
+    q[i] = (uint8_t)(cvt_e4m3x2(pack_one(__uint_as_float((uint32_t)x[i] << 16), scale), 0.0f) & 0xFF);
+}
+
+// --------------------------------------------------------------------------------------------
+// Host side: geometry selection and launches
+// --------------------------------------------------------------------------------------------
+static inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
+static inline bool aligned8(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 7) == 0; }
+static inline int esize(int dtype) { return dtype == IFLB200_F32 ? 4 : 2; }
+static inline bool dtype_ok(int d) { return d == IFLB200_F32 || d == IFLB200_BF16 || d == IFLB200_F16; }
+
+// Threads per row: the smallest group that covers the row in at most kItersMax chunks per
+// thread; with few rows a wider group (fewer chunks per thread) shortens the critical path.
+static int pick_tpr(int M, int width) {
+  int tpr = 32;
+  while (tpr < kMaxTpr && (int64_t)tpr * 8 * kItersMax < width) tpr *= 2;
+  if (M <= 1024)
+    while (tpr < kMaxTpr && (int64_t)tpr * 8 < width) tpr *= 2;
+  else
+    while (tpr < 256 && (int64_t)tpr * 8 * 2 < width) tpr *= 2;
+  return tpr;
+}
+static inline int iters_for(int tpr, int width) { return (width + tpr * 8 - 1) / (tpr * 8); }
+
+#define IFLB200_DISPATCH_TPR(TPR_VALUE, ...)                          \
+  switch (TPR_VALUE) {                                                \
+    case 32: { constexpr int TPR = 32; __VA_ARGS__; } break;          \
+    case 64: { constexpr int TPR = 64; __VA_ARGS__; } break;          \
+    case 128: { constexpr int TPR = 128; __VA_ARGS__; } break;        \
+    case 256: { constexpr int TPR = 256; __VA_ARGS__; } break;        \
+    default: { constexpr int TPR = 512; __VA_ARGS__; } break;         \
+  }
+
+template <typename XT>
+static void launch_row_quant(const RowQuantArgs& a, int tpr, cudaStream_t s) {
+  IFLB200_DISPATCH_TPR(tpr, {
+    constexpr int NT = threads_per_cta<TPR>();
+    const int rows_per_cta = NT / TPR;
+    row_quant_kernel<XT, TPR><<<(a.M + rows_per_cta - 1) / rows_per_cta, NT, 0, s>>>(a);
+  })
+}
+template <typename XT>
+static void launch_gated(const GatedArgs& a, int tpr, cudaStream_t s) {
+  IFLB200_DISPATCH_TPR(tpr, {
+    constexpr int NT = threads_per_cta<TPR>();
+    const int rows_per_cta = NT / TPR;
+    gated_act_quant_kernel<XT, TPR><<<(a.M + rows_per_cta - 1) / rows_per_cta, NT, 0, s>>>(a);
+  })
+}
+template <typename RT>
+static void launch_resnorm(const ResNormArgs& a, int tpr, cudaStream_t s) {
+  IFLB200_DISPATCH_TPR(tpr, {
+    constexpr int NT = threads_per_cta<TPR>();
+    const int rows_per_cta = NT / TPR;
+    residual_norm_quant_kernel<RT, TPR><<<(a.M + rows_per_cta - 1) / rows_per_cta, NT, 0, s>>>(a);
+  })
+}
+
+}  // namespace iflb200
+
+using namespace iflb200;
+
+extern "C" int iflb200_row_quant(const void* x, int x_dtype, int64_t ld_x, int M, int K,
+                                 const float* row, const float* col, const float* bias, int gelu,
+                                 void* q, int64_t ld_q, float* qs, void* stream) {
+  if (M < 0 || K < 0) return IFLB200_ERR_ARG;
+  if (M == 0 || K == 0) return IFLB200_OK;
+  if (!x || !q || !qs) return IFLB200_ERR_ARG;
+  if (!dtype_ok(x_dtype)) return IFLB200_ERR_DTYPE;
+  if (K > kMaxWidth) return IFLB200_ERR_SHAPE;
+  if (ld_x < K || ld_q < K) return IFLB200_ERR_ARG;
+  RowQuantArgs a;
+  a.x = x; a.ld_x = ld_x; a.M = M; a.K = K;
+  a.row = row; a.col = col; a.bias = bias; a.gelu = gelu;
+  a.q = reinterpret_cast<uint8_t*>(q); a.ld_q = ld_q; a.qs = qs;
+  a.vec = aligned16(x) && (ld_x * esize(x_dtype)) % 16 == 0 && aligned8(q) && ld_q % 8 == 0 &&
+          (!col || aligned16(col)) && (!bias || aligned16(bias));
+  const int tpr = pick_tpr(M, K);
+  a.iters = iters_for(tpr, K);
+  cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+  if (x_dtype == IFLB200_BF16) launch_row_quant<__nv_bfloat16>(a, tpr, s);
+  else if (x_dtype == IFLB200_F16) launch_row_quant<__half>(a, tpr, s);
+  else launch_row_quant<float>(a, tpr, s);
+  return (int)cudaGetLastError();
+}
+
+extern "C" int iflb200_gated_act_quant(const void* gu, int gu_dtype, int64_t ld_gu, int M, int F,
+                                       const float* row, const float* col, int act,
+                                       void* q, int64_t ld_q, float* qs, void* stream) {
+  if (M < 0 || F < 0) return IFLB200_ERR_ARG;
+  if (F > 16384) return IFLB200_ERR_SHAPE;
+  if (act != IFLB200_ACT_GELU_TANH && act != IFLB200_ACT_SILU) return IFLB200_ERR_ARG;
+  if (M == 0 || F == 0) return IFLB200_OK;
+  if (!gu || !q || !qs) return IFLB200_ERR_ARG;
+  if (!dtype_ok(gu_dtype)) return IFLB200_ERR_DTYPE;
+  if (ld_gu < 2 * (int64_t)F || ld_q < F) return IFLB200_ERR_ARG;
+  GatedArgs a;
+  a.gu = gu; a.ld_gu = ld_gu; a.M = M; a.F = F; a.row = row; a.col = col; a.act = act;
+  a.q = reinterpret_cast<uint8_t*>(q); a.ld_q = ld_q; a.qs = qs;
+  const int es = esize(gu_dtype);
+  a.vec = aligned16(gu) && (ld_gu * es) % 16 == 0 && ((int64_t)F * es) % 16 == 0 && aligned8(q) &&
+          ld_q % 8 == 0 && (!col || (aligned16(col) && F % 4 == 0));
+  const int tpr = pick_tpr(M, F);
+  a.iters = iters_for(tpr, F);
+  cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+  if (gu_dtype == IFLB200_BF16) launch_gated<__nv_bfloat16>(a, tpr, s);
+  else if (gu_dtype == IFLB200_F16) launch_gated<__half>(a, tpr, s);
+  else launch_gated<float>(a, tpr, s);
+  return (int)cudaGetLastError();
+}
+
+extern "C" int iflb200_dequant_rows(const void* x, int x_dtype, int64_t ld_x, int M, int D,
+                                    const float* row, const float* col, const float* bias,
+                                    void* y, int y_dtype, int64_t ld_y, void* stream) {
+  if (M < 0 || D < 0) return IFLB200_ERR_ARG;
+  if (M == 0 || D == 0) return IFLB200_OK;
+  if (!x || !y) return IFLB200_ERR_ARG;
+  if (!dtype_ok(x_dtype) || !dtype_ok(y_dtype)) return IFLB200_ERR_DTYPE;
+  if (ld_x < D || ld_y < D) return IFLB200_ERR_ARG;
+  if (M > 65535 * 1024) return IFLB200_ERR_SHAPE;
+  DequantArgs a;
+  a.x = x; a.ld_x = ld_x; a.M = M; a.D = D; a.row = row; a.col = col; a.bias = bias;
+  a.y = y; a.y_dtype = y_dtype; a.ld_y = ld_y;
+  a.vec = aligned16(x) && (ld_x * esize(x_dtype)) % 16 == 0 && aligned16(y) &&
+          (ld_y * esize(y_dtype)) % 16 == 0 && (!col || aligned16(col)) && (!bias || aligned16(bias));
+  cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+  const int chunks = (D + 2047) / 2048;
+  // blockIdx.y carries the row: split very tall inputs into slabs of 65535 rows.
+  for (int m0 = 0; m0 < M; m0 += 65535) {
+    DequantArgs b = a;
+    const int rows = (M - m0 < 65535) ? (M - m0) : 65535;
+    b.M = rows;
+    b.x = reinterpret_cast<const char*>(x) + (int64_t)m0 * ld_x * esize(x_dtype);
+    b.y = reinterpret_cast<char*>(y) + (int64_t)m0 * ld_y * esize(y_dtype);
+    b.row = row ? row + m0 : nullptr;
+    const dim3 grid(chunks, rows);
+    if (x_dtype == IFLB200_BF16) dequant_rows_kernel<__nv_bfloat16><<<grid, 256, 0, s>>>(b);
+    else if (x_dtype == IFLB200_F16) dequant_rows_kernel<__half><<<grid, 256, 0, s>>>(b);
+    else dequant_rows_kernel<float><<<grid, 256, 0, s>>>(b);
+  }
+  return (int)cudaGetLastError();
+}
+
+extern "C" int iflb200_residual_norm_quant(void* res, int res_dtype, int64_t ld_res, int M, int D,
+                                           const void* delta, int64_t ld_delta,
+                                           const float* delta_row, const float* delta_col,
+                                           const float* bias, const float* gate, int write_res,
+                                           int layernorm, const float* weight, const float* beta,
+                                           const float* mod_scale, const float* mod_shift,
+                                           const int32_t* mod_index, float eps,
+                                           void* q, int64_t ld_q, float* qs,
+                                           void* y, int y_dtype, int64_t ld_y, void* stream) {
+  if (M < 0 || D < 0) return IFLB200_ERR_ARG;
+  if (M == 0 || D == 0) return IFLB200_OK;
+  if (!res) return IFLB200_ERR_ARG;
+  if (res_dtype != IFLB200_F32 && res_dtype != IFLB200_BF16) return IFLB200_ERR_DTYPE;
+  if (y && !dtype_ok(y_dtype)) return IFLB200_ERR_DTYPE;
+  if (D > kMaxWidth) return IFLB200_ERR_SHAPE;
+  if (q && !qs) return IFLB200_ERR_ARG;
+  if ((mod_scale == nullptr) != (mod_shift == nullptr)) return IFLB200_ERR_ARG;
+  if (ld_res < D || (delta && ld_delta < D) || (q && ld_q < D) || (y && ld_y < D)) return IFLB200_ERR_ARG;
+  ResNormArgs a;
+  a.res = res; a.ld_res = ld_res; a.M = M; a.D = D;
+  a.delta = reinterpret_cast<const __nv_bfloat16*>(delta); a.ld_delta = ld_delta;
+  a.drow = delta ? delta_row : nullptr; a.dcol = delta ? delta_col : nullptr;
+  a.bias = delta ? bias : nullptr; a.gate = delta ? gate : nullptr;
+  a.write_res = (write_res && delta) ? 1 : 0;
+  a.layernorm = layernorm; a.weight = weight; a.beta = beta;
+  a.mod_scale = mod_scale; a.mod_shift = mod_shift; a.mod_index = mod_index; a.eps = eps;
+  a.q = reinterpret_cast<uint8_t*>(q); a.ld_q = ld_q; a.qs = qs;
+  a.y = y; a.y_dtype = y_dtype; a.ld_y = ld_y;
+  const bool tables_ok = (!a.dcol || aligned16(a.dcol)) && (!a.bias || aligned16(a.bias)) &&
+                         (!a.gate || aligned16(a.gate)) && (!weight || aligned16(weight)) &&
+                         (!beta || aligned16(beta)) && (!mod_scale || aligned16(mod_scale)) &&
+                         (!mod_shift || aligned16(mod_shift)) && (!mod_index || D % 4 == 0);
+  a.vec = aligned16(res) && (ld_res * esize(res_dtype)) % 16 == 0 &&
+          (!delta || (aligned16(delta) && (ld_delta * 2) % 16 == 0)) &&
+          (!q || (aligned8(q) && ld_q % 8 == 0)) &&
+          (!y || (aligned16(y) && (ld_y * esize(y_dtype)) % 16 == 0)) && tables_ok;
+  const int tpr = pick_tpr(M, D);
+  a.iters = iters_for(tpr, D);
+  cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+  if (res_dtype == IFLB200_F32) launch_resnorm<float>(a, tpr, s);
+  else launch_resnorm<__nv_bfloat16>(a, tpr, s);
+  return (int)cudaGetLastError();
+}
+
+static int pack_grid(int64_t n) {
+  int64_t ctas = (n + (int64_t)kPackThreads * 8 * 4 - 1) / ((int64_t)kPackThreads * 8 * 4);
+  if (ctas < 1) ctas = 1;
+  if (ctas > kPackMaxCtas) ctas = kPackMaxCtas;
+  return (int)ctas;
+}
+
+extern "C" size_t iflb200_pack_workspace_bytes(int64_t n) {
+  return (size_t)pack_grid(n < 0 ? 0 : n) * sizeof(uint32_t);
+}
+
+extern "C" int iflb200_dynamic_pack_bf16_e4m3(const void* x, int64_t n, void* q, float* scale,
+                                              void* workspace, size_t workspace_bytes,
+                                              void* stream) {
+  if (n <= 0 || !x || !q || !scale) return IFLB200_ERR_ARG;
+  if (!workspace || workspace_bytes < iflb200_pack_workspace_bytes(n)) return IFLB200_ERR_WORKSPACE;
+  if ((reinterpret_cast<uintptr_t>(x) & 1) || (reinterpret_cast<uintptr_t>(workspace) & 3))
+    return IFLB200_ERR_ALIGN;
+  const int grid = pack_grid(n);
+  cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+  uint32_t* partial = reinterpret_cast<uint32_t*>(workspace);
+  amax_partial_kernel<<<grid, kPackThreads, 0, s>>>(reinterpret_cast<const uint16_t*>(x), n, partial);
+  pack_kernel<<<grid, kPackThreads, 0, s>>>(reinterpret_cast<const uint16_t*>(x), n, partial, grid,
+                                            nullptr, scale, reinterpret_cast<uint8_t*>(q));
+  return (int)cudaGetLastError();
+}
+
+extern "C" int iflb200_pack_bf16_e4m3(const void* x, int64_t n, const float* scale, void* q,
+                                      void* stream) {
+  if (n < 0 || !scale) return IFLB200_ERR_ARG;
+  if (n == 0) return IFLB200_OK;
+  if (!x || !q) return IFLB200_ERR_ARG;
+  cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+  pack_kernel<<<pack_grid(n), kPackThreads, 0, s>>>(reinterpret_cast<const uint16_t*>(x), n, nullptr,
+                                                    0, scale, nullptr, reinterpret_cast<uint8_t*>(q));
+  return (int)cudaGetLastError();
+}

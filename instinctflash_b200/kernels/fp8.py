@@ -1,0 +1,138 @@
+"""Per-channel e4m3 weights, the raw-accumulator FP8 GEMM and the fused linear.
+
+Drop-in for ``instinctflash/kernels/fp8.py``: ``Fp8Weight`` has the same fields and layout
+(``w`` [N, K] e4m3 with K contiguous, ``scale`` [N] float32, ``bias`` [N] float32 or None —
+lines 19-27 there), ``quantize_weight`` packs with the same arithmetic (lines 30-37) and
+``gemm`` writes ``bf16(sum_k a[m,k] * w[n,k])`` with unit scales (lines 50-53).  The GEMM is the
+tcgen05 kernel of ``csrc/gemm_fp8_sm100.cu`` instead of ``torch._scaled_mm``.
+
+``fp8_linear`` and ``fp8_linear_residual`` are additions: the same GEMM with the consumer
+(``dequant_rows`` / the residual part of ``residual_norm_quant``) applied in its epilogue, so the
+[M, N] raw accumulator never travels through memory.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+
+import torch
+
+from .. import _lib
+from ._common import E4M3, ld, rows, stream, vec
+
+FP8_MAX = 448.0
+
+
+@dataclass
+class Fp8Weight:
+    w: torch.Tensor                   # [N, K] e4m3, K contiguous
+    scale: torch.Tensor               # [N] float32, per output channel: amax / 448
+    bias: torch.Tensor | None = None  # [N] float32
+
+    @property
+    def shape(self):
+        return tuple(self.w.shape)
+
+
+def quantize_weight(w: torch.Tensor, bias: torch.Tensor | None = None, device=None) -> Fp8Weight:
+    """Pack ``w`` [N, K] (any float dtype) with one scale per output channel on ``device``.
+
+    Load-time work, plain torch: scale = max(|row|, 1e-12) / 448, codes = e4m3_rn(clamp(w / scale)).
+    """
+    if w.ndim != 2:
+        raise ValueError(f"weight must be [N, K], got shape {tuple(w.shape)}")
+    target = device if device is not None else w.device
+    wf = w.to(device=target, dtype=torch.float32)
+    channel_max = wf.abs().amax(dim=1).clamp_min(1e-12)
+    scale = channel_max / FP8_MAX
+    codes = (wf / scale[:, None]).clamp_(-FP8_MAX, FP8_MAX).to(E4M3).contiguous()
+    packed_bias = None
+    if bias is not None:
+        packed_bias = bias.to(device=wf.device, dtype=torch.float32).contiguous()
+    return Fp8Weight(codes, scale.contiguous(), packed_bias)
+
+
+def _operands(a: torch.Tensor, w: Fp8Weight):
+    rows(a, "a", (E4M3,))
+    rows(w.w, "w.w", (E4M3,))
+    if w.w.device != a.device:
+        raise ValueError("activations and weights must be on the same device")
+    M, K = a.shape
+    N, Kw = w.w.shape
+    if K != Kw:
+        raise ValueError(f"a is [M, {K}] but the weight is [{N}, {Kw}]")
+    if K % 16 or N % 16:
+        raise ValueError("FP8 GEMM input/output dimensions must be multiples of 16")
+    return M, N, K
+
+
+def gemm(a: torch.Tensor, w: Fp8Weight, out: torch.Tensor) -> torch.Tensor:
+    """out[M, N] (bf16) = a[M, K] (e4m3) @ w.w[N, K]^T, unscaled raw accumulator."""
+    M, N, K = _operands(a, w)
+    rows(out, "out", (torch.bfloat16,))
+    if tuple(out.shape) != (M, N):
+        raise ValueError(f"out must be [{M}, {N}], got {tuple(out.shape)}")
+    st = _lib.lib().iflb200_gemm_fp8_raw(a.data_ptr(), ld(a), w.w.data_ptr(), ld(w.w), M, N, K,
+                                         out.data_ptr(), ld(out), stream(a))
+    _lib.check(st, "gemm")
+    return out
+
+
+def fp8_linear(a: torch.Tensor, a_scale: torch.Tensor | None, w: Fp8Weight, out: torch.Tensor, *,
+               bias: torch.Tensor | None = None, use_weight_bias: bool = True,
+               exact: bool = False) -> torch.Tensor:
+    """``gemm`` + ``dequant_rows`` in one kernel.
+
+    out[m, n] = out.dtype(fma(r * a_scale[m], w.scale[n], bias[n])) with r the accumulator
+    rounded to bf16 first (the reference's memory round trip) unless ``exact``.
+    ``a_scale`` is [M] (per token) or a single element (per tensor); ``w.scale`` likewise
+    [N] or one element.  ``bias`` overrides ``w.bias`` (float32 or bf16).
+    """
+    M, N, K = _operands(a, w)
+    rows(out, "out", (torch.float32, torch.bfloat16, torch.float16))
+    if tuple(out.shape) != (M, N):
+        raise ValueError(f"out must be [{M}, {N}], got {tuple(out.shape)}")
+    b = bias if bias is not None else (w.bias if use_weight_bias else None)
+    if b is not None:
+        if b.dtype not in (torch.float32, torch.bfloat16) or b.numel() != N or not b.is_contiguous():
+            raise ValueError("bias must be a contiguous float32 or bfloat16 vector of N elements")
+    rs = vec(a_scale, "a_scale", None, a.device)
+    cs = vec(w.scale, "w.scale", None, a.device)
+    if rs is not None and rs.numel() not in (1, M):
+        raise ValueError(f"a_scale must have 1 or {M} elements")
+    if cs is not None and cs.numel() not in (1, N):
+        raise ValueError(f"w.scale must have 1 or {N} elements")
+    st = _lib.lib().iflb200_fp8_linear(
+        a.data_ptr(), ld(a), w.w.data_ptr(), ld(w.w), M, N, K,
+        _lib.ptr(rs), 0 if (rs is not None and rs.numel() == 1 and M != 1) else 1,
+        _lib.ptr(cs), 0 if (cs is not None and cs.numel() == 1 and N != 1) else 1,
+        _lib.ptr(b), _lib.dtype_code(b.dtype) if b is not None else _lib.F32,
+        _lib.ROUND_EXACT if exact else _lib.ROUND_ENGINE,
+        out.data_ptr(), _lib.dtype_code(out.dtype), ld(out), stream(a))
+    _lib.check(st, "fp8_linear")
+    return out
+
+
+def fp8_linear_residual(a: torch.Tensor, a_scale: torch.Tensor, w: Fp8Weight, res: torch.Tensor, *,
+                        bias: torch.Tensor | None = None, gate: torch.Tensor | None = None,
+                        gate_index: torch.Tensor | None = None) -> torch.Tensor:
+    """``gemm`` + the residual part of ``residual_norm_quant`` in one kernel (in place on ``res``).
+
+    res[m, n] += (r * a_scale[m] * w.scale[n] (+ bias[n])) (* gate[idx[m], n]), r the bf16-rounded
+    accumulator; stored in ``res``'s dtype (float32, or bf16 for the Wan residual stream).
+    """
+    M, N, K = _operands(a, w)
+    rows(res, "res", (torch.float32, torch.bfloat16))
+    if tuple(res.shape) != (M, N):
+        raise ValueError(f"res must be [{M}, {N}], got {tuple(res.shape)}")
+    rs = vec(a_scale, "a_scale", M, a.device)
+    cs = vec(w.scale, "w.scale", N, a.device)
+    b = vec(bias, "bias", N, a.device)
+    g = vec(gate, "gate", N, a.device)
+    if gate_index is not None and (gate_index.dtype != torch.int32 or gate_index.numel() < M):
+        raise ValueError("gate_index must be int32 with one entry per row")
+    st = _lib.lib().iflb200_fp8_linear_residual(
+        a.data_ptr(), ld(a), w.w.data_ptr(), ld(w.w), M, N, K, _lib.ptr(rs), _lib.ptr(cs),
+        _lib.ptr(b), _lib.ptr(g), _lib.ptr(gate_index), res.data_ptr(), _lib.dtype_code(res.dtype),
+        ld(res), stream(a))
+    _lib.check(st, "fp8_linear_residual")
+    return res

@@ -1,0 +1,100 @@
+"""Row producers and consumers around the FP8 GEMM.
+
+Drop-in for the three operators of ``instinctflash/kernels/norm.py``:
+``row_quant`` (lines 128-158), ``dequant_rows`` (lines 162-185) and ``residual_norm_quant``
+(lines 26-124, without its MoE ``router`` tail).  Same argument names and meaning; the Triton
+tuning hints (``num_warps``, ``block``) are accepted and ignored.  The arithmetic follows the
+instruction order the reference compiles to on sm_100, so the e4m3 codes and scales of the
+quantiser are bit-identical to the reference's on the same inputs.
+"""
+from __future__ import annotations
+
+import torch
+
+from .. import _lib
+from ._common import E4M3, ld, rows, stream, vec
+
+FP8_MAX = 448.0
+_FLOATS = (torch.float32, torch.bfloat16, torch.float16)
+
+
+def row_quant(x, q, q_scale, *, row=None, col=None, bias=None, gelu=False, num_warps=None):
+    """q[m] = e4m3((x[m] * row[m] * col + bias) [-> gelu_tanh] / s[m]), s[m] = rowmax / 448."""
+    rows(x, "x", _FLOATS)
+    rows(q, "q", (E4M3,))
+    M, D = x.shape
+    if tuple(q.shape) != (M, D):
+        raise ValueError(f"q must be [{M}, {D}], got {tuple(q.shape)}")
+    vec(q_scale, "q_scale", M, x.device)
+    st = _lib.lib().iflb200_row_quant(
+        x.data_ptr(), _lib.dtype_code(x.dtype), ld(x), M, D,
+        _lib.ptr(vec(row, "row", M, x.device)), _lib.ptr(vec(col, "col", D, x.device)),
+        _lib.ptr(vec(bias, "bias", D, x.device)), int(bool(gelu)),
+        q.data_ptr(), ld(q), q_scale.data_ptr(), stream(x))
+    _lib.check(st, "row_quant")
+
+
+def dequant_rows(x, y, *, row=None, col=None, bias=None, block=None, num_warps=4):
+    """y[m] = x[m] * row[m] * col + bias (float dtypes in and out)."""
+    rows(x, "x", _FLOATS)
+    rows(y, "y", _FLOATS)
+    M, D = x.shape
+    if tuple(y.shape) != (M, D):
+        raise ValueError(f"y must be [{M}, {D}], got {tuple(y.shape)}")
+    st = _lib.lib().iflb200_dequant_rows(
+        x.data_ptr(), _lib.dtype_code(x.dtype), ld(x), M, D,
+        _lib.ptr(vec(row, "row", M, x.device)), _lib.ptr(vec(col, "col", D, x.device)),
+        _lib.ptr(vec(bias, "bias", D, x.device)),
+        y.data_ptr(), _lib.dtype_code(y.dtype), ld(y), stream(x))
+    _lib.check(st, "dequant_rows")
+
+
+def residual_norm_quant(res, *, delta=None, delta_row=None, delta_col=None, bias=None, gate=None,
+                        write_res=True, layernorm=False, weight=None, beta=None,
+                        mod_scale=None, mod_shift=None, q=None, q_scale=None, y=None, eps=1e-6,
+                        num_warps=None, router=None, mod_index=None):
+    """Residual update, RMS/LayerNorm, affine, adaptive modulation and per-token quantiser.
+
+        if delta:  res[m] += (delta[m] * delta_row[m] * delta_col + bias) * gate
+        y[m] = norm(res[m]) * weight + beta;  y[m] = y[m] * (1 + mod_scale) + mod_shift
+        q[m], s[m] = e4m3(y[m] / s[m]), rowmax(|y[m]|) / 448
+
+    ``res`` is float32 (bf16 for the Wan residual stream) and updated in place; ``gate``,
+    ``mod_scale`` and ``mod_shift`` are [D] or, with ``mod_index`` (int32 [M]), tables [n, D].
+    """
+    if router is not None:
+        raise NotImplementedError("the MoE router tail of residual_norm_quant is outside the FP8 linear path")
+    rows(res, "res", (torch.float32, torch.bfloat16))
+    M, D = res.shape
+    dev = res.device
+    if delta is not None:
+        rows(delta, "delta", (torch.bfloat16,))
+        if tuple(delta.shape) != (M, D):
+            raise ValueError(f"delta must be [{M}, {D}], got {tuple(delta.shape)}")
+    if q is not None:
+        rows(q, "q", (E4M3,))
+        if tuple(q.shape) != (M, D):
+            raise ValueError(f"q must be [{M}, {D}], got {tuple(q.shape)}")
+        if q_scale is None:
+            raise ValueError("q_scale is required with q")
+        vec(q_scale, "q_scale", M, dev)
+    if y is not None:
+        rows(y, "y", _FLOATS)
+        if tuple(y.shape) != (M, D):
+            raise ValueError(f"y must be [{M}, {D}], got {tuple(y.shape)}")
+    if (mod_scale is None) != (mod_shift is None):
+        raise ValueError("mod_scale and mod_shift come together")
+    if mod_index is not None and (mod_index.dtype != torch.int32 or mod_index.numel() < M):
+        raise ValueError("mod_index must be int32 with one entry per row")
+    st = _lib.lib().iflb200_residual_norm_quant(
+        res.data_ptr(), _lib.dtype_code(res.dtype), ld(res), M, D,
+        _lib.ptr(delta), ld(delta) if delta is not None else 0,
+        _lib.ptr(vec(delta_row, "delta_row", M, dev)), _lib.ptr(vec(delta_col, "delta_col", D, dev)),
+        _lib.ptr(vec(bias, "bias", D, dev)), _lib.ptr(vec(gate, "gate", D, dev)), int(bool(write_res)),
+        int(bool(layernorm)), _lib.ptr(vec(weight, "weight", D, dev)), _lib.ptr(vec(beta, "beta", D, dev)),
+        _lib.ptr(vec(mod_scale, "mod_scale", D, dev)), _lib.ptr(vec(mod_shift, "mod_shift", D, dev)),
+        _lib.ptr(mod_index), float(eps),
+        _lib.ptr(q), ld(q) if q is not None else 0, _lib.ptr(q_scale),
+        _lib.ptr(y), _lib.dtype_code(y.dtype) if y is not None else _lib.F32,
+        ld(y) if y is not None else 0, stream(res))
+    _lib.check(st, "residual_norm_quant")

@@ -1,0 +1,195 @@
+"""numpy/torch front end of the C restatement (``fp8_linear_oracle.c``).
+
+All inputs and outputs are CPU torch tensors.  Each function names the reference operator it
+restates; the arithmetic itself is in the C file (exact ``fmaf``, explicit rounding).
+TEST INFRASTRUCTURE ONLY — see the package docstring.
+"""
+from __future__ import annotations
+
+import ctypes
+
+import numpy as np
+import torch
+
+from . import build as _build
+
+E4M3 = torch.float8_e4m3fn
+F32, BF16, F16 = 0, 1, 2
+_DT = {torch.float32: F32, torch.bfloat16: BF16, torch.float16: F16}
+_LIB = None
+
+
+def _lib():
+    global _LIB
+    if _LIB is None:
+        _LIB = ctypes.CDLL(str(_build.build()))
+        _LIB.oracle_e4m3_encode.restype = ctypes.c_uint8
+        _LIB.oracle_e4m3_encode.argtypes = [ctypes.c_float]
+        _LIB.oracle_e4m3_decode.restype = ctypes.c_float
+        _LIB.oracle_e4m3_decode.argtypes = [ctypes.c_uint8]
+    return _LIB
+
+
+def _f32(t):
+    """Contiguous float32 numpy copy of a float tensor (widening is exact)."""
+    return None if t is None else np.ascontiguousarray(t.detach().to(torch.float32).cpu().numpy())
+
+
+def _p(a):
+    return None if a is None else a.ctypes.data_as(ctypes.c_void_p)
+
+
+def _codes(t):
+    return np.ascontiguousarray(t.detach().cpu().contiguous().view(torch.uint8).numpy())
+
+
+def _as_e4m3(codes: np.ndarray) -> torch.Tensor:
+    return torch.from_numpy(codes).view(E4M3)
+
+
+def e4m3_encode(x: torch.Tensor) -> torch.Tensor:
+    """fp32 -> e4m3 codes by the integer round-to-nearest-even cast
+    (instinctflash/runtime/fp8_pack.py:12-23; same result as cvt.rn.satfinite)."""
+    flat = x.detach().to(torch.float32).flatten().tolist()
+    lib = _lib()
+    out = np.fromiter((lib.oracle_e4m3_encode(v) for v in flat), dtype=np.uint8, count=len(flat))
+    return _as_e4m3(out.reshape(tuple(x.shape)))
+
+
+def quantize_weight(w: torch.Tensor, bias=None, *, reciprocal: bool = False):
+    """Per-output-channel pack (instinctflash/kernels/fp8.py:30-37).
+
+    ``reciprocal=False`` is torch's CPU arithmetic (true division by 448); ``True`` is its CUDA
+    arithmetic for tensor / python-scalar (multiply by fp32(1/448)), as the reference documents
+    at instinctflash/runtime/torch_fp8_linear.py:41-46.  Returns (codes e4m3 [N,K], scale, bias).
+    """
+    wf = w.detach().to(torch.float32).cpu()
+    amax = wf.abs().amax(dim=1).clamp_min(1e-12)
+    scale = amax * torch.tensor(1.0 / 448.0, dtype=torch.float32) if reciprocal else amax / 448.0
+    q = (wf / scale[:, None]).clamp_(-448.0, 448.0).to(E4M3)
+    b = None if bias is None else bias.detach().to(torch.float32).cpu().contiguous()
+    return q.contiguous(), scale.contiguous(), b
+
+
+def row_quant(x, *, row=None, col=None, bias=None, gelu=False):
+    """instinctflash/kernels/norm.py:128-147 -> (codes e4m3 [M,K], scales f32 [M])."""
+    xf = _f32(x)
+    M, K = xf.shape
+    q = np.empty((M, K), np.uint8)
+    qs = np.empty((M,), np.float32)
+    r, c, b = _f32(row), _f32(col), _f32(bias)
+    _lib().oracle_row_quant(_p(xf), ctypes.c_int64(K), M, K, _p(r), _p(c), _p(b), int(gelu), _p(q),
+                            ctypes.c_int64(K), _p(qs))
+    return _as_e4m3(q), torch.from_numpy(qs)
+
+
+def dequant_rows(x, *, row=None, col=None, bias=None, out_dtype=torch.bfloat16):
+    """instinctflash/kernels/norm.py:162-175 -> y [M,D] in out_dtype."""
+    xf = _f32(x)
+    M, D = xf.shape
+    y = np.empty((M, D), np.float32)
+    r, c, b = _f32(row), _f32(col), _f32(bias)
+    _lib().oracle_dequant_rows(_p(xf), ctypes.c_int64(D), M, D, _p(r), _p(c), _p(b), _p(y), ctypes.c_int64(D),
+                               _DT[out_dtype])
+    return torch.from_numpy(y).to(out_dtype)
+
+
+def gated_act_quant(gu, *, row=None, col=None, act=0):
+    """instinctflash/kernels/activation.py:20-43 -> (codes [M,F], scales [M])."""
+    gf = _f32(gu)
+    M, F2 = gf.shape
+    F = F2 // 2
+    q = np.empty((M, F), np.uint8)
+    qs = np.empty((M,), np.float32)
+    r, c = _f32(row), _f32(col)
+    _lib().oracle_gated_act_quant(_p(gf), ctypes.c_int64(F2), M, F, _p(r), _p(c), int(act), _p(q),
+                                  ctypes.c_int64(F), _p(qs))
+    return _as_e4m3(q), torch.from_numpy(qs)
+
+
+def residual_norm_quant(res, *, delta=None, delta_row=None, delta_col=None, bias=None, gate=None,
+                        write_res=True, layernorm=False, weight=None, beta=None, mod_scale=None,
+                        mod_shift=None, mod_index=None, eps=1e-6, quant=True, y_dtype=None):
+    """instinctflash/kernels/norm.py:26-94 (no router).
+
+    Returns dict(res=updated residual in res.dtype, q=codes|None, qs=scales|None, y=tensor|None).
+    """
+    rf = _f32(res)
+    M, D = rf.shape
+    d = _f32(delta)
+    q = np.empty((M, D), np.uint8) if quant else None
+    qs = np.empty((M,), np.float32) if quant else None
+    y = np.empty((M, D), np.float32) if y_dtype is not None else None
+    args = [_f32(t) for t in (delta_row, delta_col, bias, gate)]
+    w, b, ms, mh = _f32(weight), _f32(beta), _f32(mod_scale), _f32(mod_shift)
+    mi = None if mod_index is None else np.ascontiguousarray(mod_index.cpu().numpy().astype(np.int32))
+    _lib().oracle_residual_norm_quant(
+        _p(rf), ctypes.c_int64(D), _DT[res.dtype], M, D, _p(d), ctypes.c_int64(D), *[_p(a) for a in args],
+        int(bool(write_res)), int(bool(layernorm)), _p(w), _p(b), _p(ms), _p(mh), _p(mi), ctypes.c_float(eps),
+        _p(q), ctypes.c_int64(D), _p(qs), _p(y), ctypes.c_int64(D), _DT[y_dtype] if y_dtype is not None else 0)
+    return dict(res=torch.from_numpy(rf).to(res.dtype),
+                q=None if q is None else _as_e4m3(q),
+                qs=None if qs is None else torch.from_numpy(qs),
+                y=None if y is None else torch.from_numpy(y).to(y_dtype))
+
+
+def gemm_acc(a, w):
+    """fp32_rn of the exact sum_k a[m,k]*w[n,k] over e4m3 codes -> float32 [M,N]."""
+    ac, wc = _codes(a), _codes(w)
+    M, K = ac.shape
+    N = wc.shape[0]
+    out = np.empty((M, N), np.float32)
+    _lib().oracle_gemm_acc(_p(ac), ctypes.c_int64(K), _p(wc), ctypes.c_int64(K), M, N, K, _p(out), ctypes.c_int64(N))
+    return torch.from_numpy(out)
+
+
+def gemm(a, w):
+    """instinctflash/kernels/fp8.py:50-53: raw accumulator rounded to bf16."""
+    return gemm_acc(a, w).to(torch.bfloat16)
+
+
+def fp8_linear(a, a_scale, w, w_scale, bias=None, *, exact=False, out_dtype=torch.bfloat16):
+    """gemm (fp8.py:50-53) + dequant_rows (norm.py:162-175); ``exact`` skips the bf16 rounding of
+    the accumulator (the single-rounding form that the dequantise-and-matmul baseline and
+    torch._scaled_mm-with-scales approximate, torch_fp8_linear.py:74-78)."""
+    ac, wc = _codes(a), _codes(w)
+    M, K = ac.shape
+    N = wc.shape[0]
+    y = np.empty((M, N), np.float32)
+    r, c, b = _f32(a_scale), _f32(w_scale), _f32(bias)
+    rstride = 0 if (r is not None and r.size == 1 and M != 1) else 1
+    cstride = 0 if (c is not None and c.size == 1 and N != 1) else 1
+    _lib().oracle_fp8_linear(_p(ac), ctypes.c_int64(K), _p(wc), ctypes.c_int64(K), M, N, K, _p(r), rstride, _p(c),
+                             cstride, _p(b), int(bool(exact)), _p(y), ctypes.c_int64(N), _DT[out_dtype])
+    return torch.from_numpy(y).to(out_dtype)
+
+
+def dynamic_pack_bf16_e4m3(x: torch.Tensor):
+    """instinctflash/runtime/fp8_pack.py:62-92 -> (codes like x, scale f32 [1])."""
+    bits = np.ascontiguousarray(x.detach().cpu().contiguous().view(torch.int16).numpy().view(np.uint16))
+    q = np.empty(bits.shape, np.uint8)
+    scale = np.zeros((1,), np.float32)
+    _lib().oracle_pack_tensor(_p(bits), ctypes.c_int64(bits.size), 1, _p(scale), _p(q))
+    return _as_e4m3(q), torch.from_numpy(scale)
+
+
+def pack_bf16_e4m3(x: torch.Tensor, scale: torch.Tensor):
+    """instinctflash/runtime/fp8_pack.py:27-60 with a given scale."""
+    bits = np.ascontiguousarray(x.detach().cpu().contiguous().view(torch.int16).numpy().view(np.uint16))
+    q = np.empty(bits.shape, np.uint8)
+    s = np.ascontiguousarray(scale.detach().cpu().numpy().astype(np.float32).reshape(1))
+    _lib().oracle_pack_tensor(_p(bits), ctypes.c_int64(bits.size), 0, _p(s), _p(q))
+    return _as_e4m3(q)
+
+
+def decode(q: torch.Tensor) -> torch.Tensor:
+    return q.to(torch.float32)
+
+
+def dequantise_and_matmul(q, s_x, wq, s_w, bias=None, out_dtype=torch.bfloat16):
+    """The reference's CPU-runnable torch form of the linear
+    (benchmarks/native/fp8_probe.py:32-36): ((q*s_x) @ (Wq*s_w)^T + b) in fp32, then out_dtype."""
+    y = (q.to(torch.float32) * s_x[:, None]) @ (wq.to(torch.float32) * s_w[:, None]).t()
+    if bias is not None:
+        y = y + bias.to(torch.float32)
+    return y.to(out_dtype)
