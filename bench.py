@@ -1,0 +1,336 @@
+#!/usr/bin/env python
+"""Benchmark of the FP8 linear hot path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload c2|c3|c3ref|c4|c5] [--impl reference]
+
+A step is one pass of a layer stack (per-token e4m3 quantisers, FP8 GEMMs and their consumers
+in the reference engines' call order) over one batch of synthetic activations.  The default
+workload is the pi05 PaliGemma prefix stack (18 layers, M = 816).  With N > 1 every rank runs
+its own independent stack (independent robot episodes: data parallel, no collective) and the
+reported value is the aggregate.  Prints ONE JSON line on rank 0.
+
+``--impl reference`` times the reference's CPU form of the path (torch per-token quantiser +
+dequantise-and-matmul, restated in ``oracle/``) on the host cores over a bounded sample.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+from pathlib import Path
+
+import torch
+
+ROOT = Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT))
+
+METRIC = "fp8_linear_stack_tflops"
+UNIT = "TFLOP/s"
+NOMINAL_FP8_TFLOPS = 4500.0
+NOMINAL_HBM_GBS = 8000.0
+
+
+def measured_peaks():
+    p = ROOT / "MEASURED_PEAKS.json"
+    if p.exists():
+        d = json.loads(p.read_text())
+        return dict(hbm_gbs=float(d["hbm_gbs"]), bf16_tflops=float(d["bf16_tflops"]),
+                    bf16_tflops_sustained=float(d.get("bf16_tflops_sustained", d["bf16_tflops"])), source="measured")
+    return dict(hbm_gbs=6650.0, bf16_tflops=1590.0, bf16_tflops_sustained=1400.0, source="fallback")
+
+
+class ClockSampler:
+    """nvidia-smi clocks and throttle reasons sampled during the timed region."""
+
+    QUERY = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+             "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+             "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index, self.rows, self.proc = index, [], None
+
+    def __enter__(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits",
+                                          "-i", str(self.index), "-lms", "100"], stdout=subprocess.PIPE,
+                                         stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except OSError:
+            self.proc = None
+        return self
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([c.strip() for c in line.split(",")])
+
+    def __exit__(self, *exc):
+        if self.proc is not None:
+            self.proc.terminate()
+            try:
+                self.proc.wait(timeout=5)
+            except subprocess.TimeoutExpired:
+                self.proc.kill()
+
+    def summary(self):
+        sm, smax, reasons = [], [], set()
+        for r in self.rows:
+            try:
+                sm.append(float(r[1]))
+                smax.append(float(r[2]))
+            except (ValueError, IndexError):
+                continue
+            for name, cell in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), r[5:9]):
+                if cell.lower().startswith("active"):
+                    reasons.add(name)
+        if not sm:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
+        return {"sm_mhz": statistics.median(sm), "sm_max_mhz": max(smax), "reasons": sorted(reasons), "samples": len(sm)}
+
+
+def cpu_reference_step(spec, layers, sample_layers, threads):
+    """One bounded sample of the reference's CPU form of the path: per linear the torch per-token
+    quantiser and dequantise-and-matmul (instinctflash benchmarks/native/fp8_probe.py:32-36),
+    over `sample_layers` layers of the stack.  Returns (seconds, flops)."""
+    from oracle import oracle as O
+    torch.set_num_threads(threads)
+    E4M3 = torch.float8_e4m3fn
+    t0 = time.perf_counter()
+    flops = 0.0
+    for lw in layers[:sample_layers]:
+        for name, n, k in spec.linears():
+            x, wq, ws, b = lw[name]
+            amax = x.float().abs().amax(1).clamp_min(1e-8)
+            q = (x.float() * (448.0 / amax)[:, None]).to(E4M3)
+            O.dequantise_and_matmul(q, amax / 448.0, wq, ws, b)
+            flops += 2.0 * spec.M * n * k
+    return time.perf_counter() - t0, flops
+
+
+def build_cpu_sample(spec, sample_layers):
+    gen = torch.Generator().manual_seed(spec.seed)
+    E4M3 = torch.float8_e4m3fn
+    layers = []
+    for _ in range(sample_layers):
+        lw = {}
+        for name, n, k in spec.linears():
+            w = torch.randn(n, k, generator=gen) * spec.sigma
+            amax = w.abs().amax(1).clamp_min(1e-12)
+            ws = amax / 448.0
+            wq = (w / ws[:, None]).clamp_(-448, 448).to(E4M3)
+            x = torch.randn(spec.M, k, generator=gen).to(torch.bfloat16)
+            lw[name] = (x, wq, ws, torch.randn(n, generator=gen) * 0.01)
+        layers.append(lw)
+    return layers
+
+
+def run_reference(args, spec, rank, world):
+    if rank != 0:
+        return
+    threads = os.cpu_count() or 1
+    sample_layers = 1
+    layers = build_cpu_sample(spec, sample_layers)
+    for _ in range(max(1, min(args.warmup, 2))):
+        cpu_reference_step(spec, layers, sample_layers, threads)
+    secs, flops = 0.0, 0.0
+    for _ in range(args.steps):
+        s, f = cpu_reference_step(spec, layers, sample_layers, threads)
+        secs += s
+        flops += f
+    value = flops / secs / 1e12
+    sample = f"{sample_layers} of {spec.layers} layers of {spec.name} per step (all {len(spec.linears())} linears, M={spec.M})"
+    line = {
+        "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": secs / args.steps * 1e3, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "e4m3 x e4m3 -> f32 (computed in f32 on the CPU)", "data": "synthetic",
+        "config": {"workload": workload_name(spec), "note": "CPU dequantise-and-matmul port of the reference path"},
+        "cpu_baseline": {"value": value, "unit": UNIT, "cores": threads, "kind": "port", "sample": sample},
+        "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+def workload_name(spec):
+    names = {"c2": "pi05 PaliGemma prefix stack, 18 layers, M=816, hidden 2048 (qkv 2560, o 2048, gate_up 2x16384 GELU-tanh, down)",
+             "c3": "pi05 action-expert stack, 18 layers x 10 flow steps, M=50, hidden 1024",
+             "c3ref": "pi05 action-expert stack with the reference engine's true shapes, 18 layers x 10 steps, M=50",
+             "c4": "Wan2.2-5B-shape DiT linears, 30 blocks, M=4680, hidden 3072",
+             "c5": "Wan-14B-shape DiT linears, 40 blocks, M=16384, hidden 5120"}
+    return names.get(spec.name, spec.name)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--workload", default="c2")
+    ap.add_argument("--impl", default="native", choices=["native", "reference"])
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3) if args.impl == "native" else args.warmup
+
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+
+    from instinctflash_b200.stack import SPECS, LinearStack, make_inputs, make_weights
+    spec = SPECS[args.workload]
+
+    if args.impl == "reference":
+        run_reference(args, spec, rank, world)
+        return
+
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the FP8 linear path has no CPU fallback")
+    from instinctflash_b200 import _lib
+    _lib.lib()  # fail loudly when the CUDA library is missing
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    dist = None
+    if world > 1:
+        import torch.distributed as dist
+        dist.init_process_group("nccl", device_id=dev)
+
+    weights = make_weights(spec, dev)
+    stack = LinearStack(spec, weights, dev)
+    x_dev, attn = make_inputs(spec, dev)
+    x_host = x_dev.cpu().pin_memory()
+    out_host = torch.empty(spec.M, spec.hidden, dtype=stack.res.dtype).pin_memory()
+    stack.load(x_dev, attn)
+    graph = stack.capture()
+    launches_per_step = stack.launches_per_forward
+    flops = spec.flops()
+    stream = torch.cuda.current_stream(dev)
+
+    def barrier():
+        if dist is not None:
+            dist.barrier()
+        torch.cuda.synchronize(dev)
+
+    # ---- device-resident timing: inputs in HBM, one graph replay per step --------------------
+    for _ in range(args.warmup):
+        stack.load(x_dev, attn)
+        graph.replay()
+    barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    with ClockSampler(local_rank) as clocks:
+        e0.record(stream)
+        for _ in range(args.steps):
+            graph.replay()
+        e1.record(stream)
+        barrier()
+    ms = e0.elapsed_time(e1)
+    clock_summary = clocks.summary()
+
+    # ---- end to end: pinned host activations in, residual stream out, every step ---------------
+    x_stage = torch.empty_like(x_dev)
+    for _ in range(2):
+        x_stage.copy_(x_host, non_blocking=True)
+        stack.load(x_stage, attn)
+        graph.replay()
+        out_host.copy_(stack.res, non_blocking=True)
+    barrier()
+    f0, f1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    f0.record(stream)
+    for _ in range(args.steps):
+        x_stage.copy_(x_host, non_blocking=True)
+        stack.load(x_stage, attn)
+        graph.replay()
+        out_host.copy_(stack.res, non_blocking=True)
+    f1.record(stream)
+    barrier()
+    ms_e2e = f0.elapsed_time(f1)
+
+    # ---- dominant kernel: the widest FP8 GEMM of the stack, timed alone over rotating layers ----
+    from instinctflash_b200.kernels import fp8 as K
+    dom = max(spec.linears(), key=lambda t: t[1] * t[2])
+    name, n_dom, k_dom = dom
+    a_dom = stack._q8(k_dom)
+    out_dom = stack._raw(n_dom)
+    reps = max(args.steps, 10)
+    for lw in weights[:3]:
+        K.gemm(a_dom, lw.w[name], out_dom)
+    torch.cuda.synchronize(dev)
+    g0, g1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    g0.record(stream)
+    for i in range(reps):
+        K.gemm(a_dom, weights[i % len(weights)].w[name], out_dom)
+    g1.record(stream)
+    torch.cuda.synchronize(dev)
+    dom_ms = g0.elapsed_time(g1) / reps
+    dom_flops = 2.0 * spec.M * n_dom * k_dom
+    dom_bytes = n_dom * k_dom + spec.M * k_dom + 2.0 * spec.M * n_dom
+    peaks = measured_peaks()
+    tensor_bound = spec.M > 400
+    if tensor_bound:
+        peak = 2.0 * peaks["bf16_tflops"]   # dense FP8 runs at twice the bf16 rate on the same tensor pipe
+        achieved = dom_flops / (dom_ms * 1e-3) / 1e12
+        roofline = {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak,
+                    "traffic": None, "kernel": f"gemm_fp8_tc5_kernel {spec.M}x{n_dom}x{k_dom} ({name})",
+                    "peak_source": f"2 x bf16_tflops of MEASURED_PEAKS.json ({peaks['source']})",
+                    "frac_of_nominal_4500": achieved / NOMINAL_FP8_TFLOPS, "ms_per_launch": dom_ms}
+    else:
+        peak = peaks["hbm_gbs"]
+        achieved = dom_bytes / (dom_ms * 1e-3) / 1e9
+        roofline = {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
+                    "traffic": None, "kernel": f"gemm_fp8_tc5_kernel {spec.M}x{n_dom}x{k_dom} ({name})",
+                    "peak_source": f"hbm_gbs of MEASURED_PEAKS.json ({peaks['source']})",
+                    "frac_of_nominal_8000": achieved / NOMINAL_HBM_GBS, "ms_per_launch": dom_ms}
+    traffic_file = ROOT / "profiles" / "traffic.json"
+    if traffic_file.exists():
+        roofline["traffic"] = json.loads(traffic_file.read_text()).get(f"{spec.name}:{name}")
+
+    # ---- max over ranks -------------------------------------------------------------------------
+    if dist is not None:
+        t = torch.tensor([ms, ms_e2e], device=dev, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms, ms_e2e = float(t[0]), float(t[1])
+
+    # ---- CPU baseline (rank 0, N = 1): bounded sample of the same workload ----------------------
+    cpu = None
+    if rank == 0 and world == 1 and not args.no_cpu_baseline:
+        threads = os.cpu_count() or 1
+        sample_layers = 1
+        layers = build_cpu_sample(spec, sample_layers)
+        cpu_reference_step(spec, layers, sample_layers, threads)
+        best = None
+        spent = 0.0
+        while spent < 12.0:
+            secs, fl = cpu_reference_step(spec, layers, sample_layers, threads)
+            spent += secs
+            best = secs if best is None else min(best, secs)
+        cpu = {"value": fl / best / 1e12, "unit": UNIT, "cores": threads, "kind": "port",
+               "sample": f"{sample_layers} of {spec.layers} layers of {spec.name} (all {len(spec.linears())} linears, M={spec.M}), "
+                         f"best of repeats within 12 s"}
+
+    if rank == 0:
+        value = world * flops * args.steps / (ms * 1e-3) / 1e12
+        e2e_value = world * flops * args.steps / (ms_e2e * 1e-3) / 1e12
+        line = {
+            "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+            "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "dtype": "e4m3 x e4m3 -> f32", "data": "synthetic",
+            "config": {"workload": workload_name(spec), "parallelism": f"dp{world} (independent stacks, no collective)",
+                       "l2": f"weights streamed per step ({spec.weight_bytes() / 1e9:.2f} GB) exceed the 126 MB L2",
+                       "timing": "one CUDA-graph replay per step, CUDA events on the launching stream"},
+            "roofline": roofline, "cpu_baseline": cpu,
+            "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": x_host.numel() * x_host.element_size(),
+                    "d2h_bytes_per_step": out_host.numel() * out_host.element_size(), "ms_per_step": ms_e2e / args.steps},
+            "gpu_launches": launches_per_step * args.steps,
+            "clocks": clock_summary,
+            "stack_ms": ms / args.steps,
+        }
+        print(json.dumps(line), flush=True)
+    if dist is not None:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

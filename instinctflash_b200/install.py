@@ -1,0 +1,61 @@
+"""Rebind the reference's engine modules to the sm_100a operators.
+
+The reference's engines call module-level names imported into each engine module
+(``from ..kernels.fp8 import gemm`` ... at instinctflash/engines/pi05/engine.py:20-24 and the
+same lines of the vla4, vla2, groot_n17 and wan_va engines), resolved from module globals at call
+time.  ``install()`` replaces those names, in the kernel modules and in every engine module
+already imported, with the operators of this package.  It must run before an engine captures
+its CUDA graph (first ``infer``): a captured graph keeps the kernels it was captured with.
+"""
+from __future__ import annotations
+
+import importlib
+import sys
+
+from .kernels import activation, fp8, norm
+
+REPLACEMENTS = {
+    "gemm": fp8.gemm,
+    "quantize_weight": fp8.quantize_weight,
+    "Fp8Weight": fp8.Fp8Weight,
+    "row_quant": norm.row_quant,
+    "dequant_rows": norm.dequant_rows,
+    "residual_norm_quant": norm.residual_norm_quant,
+    "gated_act_quant": activation.gated_act_quant,
+}
+KERNEL_MODULES = {"instinctflash.kernels.fp8": ("gemm", "quantize_weight", "Fp8Weight"),
+                  "instinctflash.kernels.norm": ("row_quant", "dequant_rows", "residual_norm_quant"),
+                  "instinctflash.kernels.activation": ("gated_act_quant",)}
+ENGINE_MODULES = tuple(f"instinctflash.engines.{fam}.engine" for fam in ("pi05", "vla4", "vla2", "groot_n17", "wan_va"))
+
+
+def install(modules=None, *, import_missing: bool = False) -> dict:
+    """Rebind and return ``{module name: [names rebound]}``.
+
+    ``modules`` may be an iterable of module objects (tests pass fakes); by default the
+    reference's kernel and engine modules that are already imported (or all of them with
+    ``import_missing``) are patched.  ``Fp8Weight`` is only rebound in kernel modules: engine
+    weights built with the reference's dataclass have the same fields and are accepted as is.
+    """
+    report = {}
+    if modules is None:
+        modules = []
+        for name in (*KERNEL_MODULES, *ENGINE_MODULES):
+            mod = sys.modules.get(name)
+            if mod is None and import_missing:
+                try:
+                    mod = importlib.import_module(name)
+                except ImportError:
+                    mod = None
+            if mod is not None:
+                modules.append(mod)
+    for mod in modules:
+        done = []
+        for name, fn in REPLACEMENTS.items():
+            if name == "Fp8Weight" and getattr(mod, "__name__", "") not in KERNEL_MODULES:
+                continue
+            if hasattr(mod, name):
+                setattr(mod, name, fn)
+                done.append(name)
+        report[getattr(mod, "__name__", repr(mod))] = done
+    return report

@@ -1,0 +1,488 @@
+"""Parity of the sm_100a kernels (through the C ABI) with the reference's own FP8 path.
+
+Three kinds of evidence per operator:
+  1. bit-exact equality with vectors recorded from the unmodified reference on a B200
+     (``golden/golden_b200.json``: Triton kernels, ``torch._scaled_mm``);
+  2. the CPU oracle on the same seeded inputs (bit-exact where its arithmetic is exact, a
+     counted tolerance where the GPU uses approximate instructions);
+  3. size-independent properties at the full benchmark sizes.
+GEMM bar: relative Frobenius error <= 1e-3 and max|delta| <= 2^-7 x row absmax.
+"""
+import ctypes
+
+import pytest
+import torch
+
+import cases
+from util import (E4M3, assert_gemm_parity, assert_quant_close_to_oracle, golden, i32, rel_frobenius, sha, u8)
+
+pytestmark = pytest.mark.gpu
+
+DEV = "cuda"
+
+
+@pytest.fixture(scope="module")
+def ops():
+    from instinctflash_b200 import _lib
+    from instinctflash_b200.kernels import activation, fp8, norm
+    from instinctflash_b200.runtime import fp8_pack, torch_fp8_linear
+    lib = _lib.lib()   # raises if the CUDA library is missing: no fallback
+    return dict(lib=lib, _lib=_lib, fp8=fp8, norm=norm, act=activation, pack=fp8_pack, lin=torch_fp8_linear)
+
+
+@pytest.fixture(scope="module")
+def oracle():
+    from oracle import oracle as O
+    return O
+
+
+@pytest.fixture(scope="module")
+def B200():
+    return golden("golden_b200.json")
+
+
+def dev(t):
+    return None if t is None else t.to(DEV)
+
+
+def quantise(ops, x, **kw):
+    q = torch.empty(x.shape, device=DEV, dtype=E4M3)
+    s = torch.empty(x.shape[0], device=DEV, dtype=torch.float32)
+    ops["norm"].row_quant(x, q, s, **kw)
+    return q, s
+
+
+def no_timeout(ops):
+    rec = ctypes.c_uint32(0)
+    assert ops["lib"].iflb200_gemm_take_timeout_record(ctypes.byref(rec), None) == 0
+    assert rec.value == 0, f"a GEMM wait timed out: record {rec.value:#x}"
+
+
+# ------------------------------------------------------------------------------------- quantiser
+@pytest.mark.parametrize("name", [n for n, _ in cases.row_quant_cases()])
+def test_row_quant_bit_exact(ops, oracle, B200, name):
+    c = dict(cases.row_quant_cases())[name]
+    g = B200[f"row_quant/{name}"]
+    q, s = quantise(ops, dev(c["x"]))
+    assert i32(s).tolist() == g["qs_bits"], "scales differ from the reference's row_quant on a B200"
+    assert sha(q) == g["q_sha"], "codes differ from the reference's row_quant on a B200"
+    qo, so = oracle.row_quant(c["x"])
+    assert_quant_close_to_oracle(q, s, qo, so, name, max_scale_ulp=1)
+
+
+@pytest.mark.parametrize("name", [n for n, _ in cases.prologue_cases()])
+def test_row_quant_prologue_bit_exact(ops, oracle, B200, name):
+    c = dict(cases.prologue_cases())[name]
+    g = B200[f"row_quant_prologue/{name}"]
+    q, s = quantise(ops, dev(c["x"]), row=dev(c["row"]), col=dev(c["col"]), bias=dev(c["bias"]), gelu=c["gelu"])
+    assert i32(s).tolist() == g["qs_bits"] and sha(q) == g["q_sha"]
+    qo, so = oracle.row_quant(c["x"], row=c["row"], col=c["col"], bias=c["bias"], gelu=c["gelu"])
+    assert_quant_close_to_oracle(q, s, qo, so, name)
+
+
+def test_row_quant_strided_views_and_untouched_bytes(ops):
+    x = dev(cases.activations(40, 4096, 7))
+    xv = x[:, 1024:3072]
+    arena = torch.zeros(40, 4096, device=DEV, dtype=torch.uint8).view(E4M3)
+    qv = arena[:, 2048:]
+    s = torch.empty(40, device=DEV)
+    ops["norm"].row_quant(xv, qv, s)
+    q2, s2 = quantise(ops, xv.contiguous())
+    assert torch.equal(u8(qv), u8(q2)) and torch.equal(i32(s), i32(s2))
+    assert bool((u8(arena)[:, :2048] == 0).all())
+
+
+def test_row_quant_unaligned_falls_to_elementwise_path(ops):
+    x = dev(cases.activations(9, 1001, 8))          # odd row stride: no 16-byte vectors
+    q, s = quantise(ops, x)
+    xp = torch.zeros(9, 1008, device=DEV, dtype=torch.bfloat16)
+    xp[:, :1001] = x
+    q2, s2 = quantise(ops, xp)
+    assert torch.equal(u8(q), u8(q2[:, :1001].contiguous())) and torch.equal(i32(s), i32(s2))
+
+
+def test_row_quant_empty_and_errors(ops):
+    x = torch.empty(0, 64, device=DEV, dtype=torch.bfloat16)
+    quantise(ops, x)
+    with pytest.raises(RuntimeError, match="unsupported shape"):
+        quantise(ops, torch.zeros(2, 16384 + 16, device=DEV, dtype=torch.bfloat16))
+    with pytest.raises(ValueError):
+        ops["norm"].row_quant(torch.zeros(2, 16, device=DEV), torch.empty(2, 32, device=DEV, dtype=torch.uint8).view(E4M3),
+                              torch.empty(2, device=DEV))
+
+
+def test_row_quant_properties_at_full_size(ops):
+    """C5 activation shape: dequantised row maximum equals the row maximum to within one e4m3
+    step, the maximum element of each row encodes to +-448, scales are amax/448 to 2 ulp."""
+    x = dev(cases.activations(16384, 5120, 4, outlier_frac=0.005, outlier_scale=30.0))
+    q, s = quantise(ops, x)
+    amax = x.float().abs().amax(1)
+    assert (i32(s) - i32(amax / 448.0)).abs().max().item() <= 2
+    assert bool((q.float().abs().amax(1) == 448.0).all())
+    deq = q.float() * s[:, None]
+    assert ((deq - x.float()).abs().amax(1) <= amax * 2.0 ** -4 * 1.0001).all()
+    # idempotence: re-quantising the dequantised row gives the same codes
+    q2, _ = quantise(ops, deq)
+    assert (u8(q) != u8(q2)).float().mean().item() < 1e-3
+
+
+# ------------------------------------------------------------------------------------- consumers
+@pytest.mark.parametrize("name", [n for n, _ in cases.dequant_cases()])
+def test_dequant_rows_bit_exact(ops, oracle, B200, name):
+    c = dict(cases.dequant_cases())[name]
+    g = B200[f"dequant_rows/{name}"]
+    x = dev(c["x"])
+    for bias, key in ((c["bias"], "y_sha"), (None, "y_nobias_sha")):
+        y = torch.empty(x.shape, device=DEV, dtype=c["out_dtype"])
+        ops["norm"].dequant_rows(x, y, row=dev(c["row"]), col=dev(c["col"]), bias=dev(bias))
+        assert sha(y) == g[key]
+        assert torch.equal(y.cpu(), oracle.dequant_rows(c["x"], row=c["row"], col=c["col"], bias=bias, out_dtype=c["out_dtype"]))
+
+
+@pytest.mark.parametrize("name", [n for n, _ in cases.gated_cases()])
+def test_gated_act_quant_bit_exact(ops, oracle, B200, name):
+    c = dict(cases.gated_cases())[name]
+    g = B200[f"gated_act_quant/{name}"]
+    gu = dev(c["gu"])
+    M, F = gu.shape[0], gu.shape[1] // 2
+    q = torch.empty(M, F, device=DEV, dtype=E4M3)
+    s = torch.empty(M, device=DEV)
+    ops["act"].gated_act_quant(gu, q, s, row=dev(c["row"]), col=dev(c["col"]), act=c["act"])
+    assert i32(s).tolist() == g["qs_bits"] and sha(q) == g["q_sha"]
+    qo, so = oracle.gated_act_quant(c["gu"], row=c["row"], col=c["col"], act=c["act"])
+    assert_quant_close_to_oracle(q, s, qo, so, name, max_scale_ulp=4)
+
+
+def test_gated_act_quant_loose_reference_check(ops):
+    """The reference's own test (tests/test_gi_kernels.py:115-127): M=9, F=4096, < 0.07 of row amax."""
+    for act in (0, 1):
+        torch.manual_seed(4)
+        M, F = 9, 4096
+        gu = torch.randn(M, 2 * F, device=DEV).to(torch.bfloat16)
+        row, col = torch.rand(M, device=DEV), torch.rand(2 * F, device=DEV)
+        q = torch.empty(M, F, device=DEV, dtype=E4M3)
+        qs = torch.empty(M, device=DEV)
+        ops["act"].gated_act_quant(gu, q, qs, row=row, col=col, act=act)
+        x = gu.float() * row[:, None] * col
+        g, u = x[:, :F], x[:, F:]
+        a = torch.nn.functional.gelu(g, approximate="tanh") if act == 0 else torch.nn.functional.silu(g)
+        h = a * u
+        assert (((q.float() * qs[:, None]) - h).abs() / h.abs().amax(-1, keepdim=True)).max() < 0.07
+
+
+@pytest.mark.parametrize("name", [n for n, _ in cases.resnorm_cases()])
+def test_residual_norm_quant(ops, oracle, B200, name):
+    c = dict(cases.resnorm_cases())[name]
+    g = B200[f"residual_norm_quant/{name}"]
+    res = dev(c["res"]).clone()
+    M, D = res.shape
+    q = torch.empty(M, D, device=DEV, dtype=E4M3)
+    s = torch.empty(M, device=DEV)
+    kw = {k: dev(c[k]) for k in ("delta", "delta_row", "delta_col", "bias", "gate", "weight", "beta", "mod_scale",
+                                 "mod_shift", "mod_index")}
+    y = torch.empty(M, D, device=DEV, dtype=torch.float32)
+    ops["norm"].residual_norm_quant(res, layernorm=c["layernorm"], q=q, q_scale=s, y=y, **kw)
+    assert sha(res) == g["res_sha"], "residual update differs from the reference's on a B200"
+    # norm + quant tail: the row sums are reduced in a layout-specific order by the reference,
+    # so this part is tolerance-class: scales to 1e-5 relative, dequantised values to one e4m3 step
+    ref_s = torch.tensor(g["qs_bits"], dtype=torch.int32).view(torch.float32)
+    assert ((s.cpu() - ref_s).abs() / ref_s).max().item() < 1e-5
+    o = oracle.residual_norm_quant(c["res"], layernorm=c["layernorm"], y_dtype=torch.float32, **{k: c[k] for k in kw})
+    assert torch.equal(res.cpu(), o["res"])
+    assert (y.cpu() - o["y"]).abs().max().item() <= 2e-5 * o["y"].abs().max().item()
+    deq, deq_o = q.float().cpu() * s.cpu()[:, None], o["q"].float() * o["qs"][:, None]
+    assert ((deq - deq_o).abs().amax(1) <= deq_o.abs().amax(1) * 2.0 ** -3).all()
+    assert (u8(q) != u8(o["q"])).float().mean().item() < 2e-3
+
+
+def test_residual_norm_quant_reference_test_shape(ops):
+    """instinctflash tests/test_gi_kernels.py:94-112 (M=33, D=1152; residual to 1e-4, quant to 0.07)."""
+    for layernorm in (False, True):
+        torch.manual_seed(3)
+        M, D = 33, 1152
+        res = torch.randn(M, D, device=DEV)
+        delta = torch.randn(M, D, device=DEV).to(torch.bfloat16)
+        dr, dc, b, gate = torch.rand(M, device=DEV), torch.rand(D, device=DEV), torch.randn(D, device=DEV), torch.rand(D, device=DEV)
+        w, beta = torch.rand(D, device=DEV), torch.randn(D, device=DEV)
+        ms, mh = torch.randn(D, device=DEV) * 0.1, torch.randn(D, device=DEV) * 0.1
+        q = torch.empty(M, D, device=DEV, dtype=E4M3)
+        qs = torch.empty(M, device=DEV)
+        expect = res + (delta.float() * dr[:, None] * dc + b) * gate
+        ops["norm"].residual_norm_quant(res, delta=delta, delta_row=dr, delta_col=dc, bias=b, gate=gate, layernorm=layernorm,
+                                        weight=w, beta=beta, mod_scale=ms, mod_shift=mh, q=q, q_scale=qs)
+        assert (res - expect).abs().max() < 1e-4
+        x = expect - expect.mean(-1, keepdim=True) if layernorm else expect
+        y = x * torch.rsqrt(x.pow(2).mean(-1, keepdim=True) + 1e-6)
+        y = (y * w + beta) * (1 + ms) + mh
+        assert (((q.float() * qs[:, None]) - y).abs() / y.abs().amax(-1, keepdim=True)).max() < 0.07
+
+
+def test_residual_norm_quant_without_delta_and_write_res_false(ops, oracle):
+    c = dict(cases.resnorm_cases())["pi05_prefix"]
+    res = dev(c["res"]).clone()
+    before = res.clone()
+    M, D = res.shape
+    q = torch.empty(M, D, device=DEV, dtype=E4M3)
+    s = torch.empty(M, device=DEV)
+    ops["norm"].residual_norm_quant(res, q=q, q_scale=s)                      # norm + quant only
+    assert torch.equal(res, before)
+    o = oracle.residual_norm_quant(c["res"])
+    assert (u8(q) != u8(o["q"])).float().mean().item() < 2e-3
+    ops["norm"].residual_norm_quant(res, delta=dev(c["delta"]), delta_row=dev(c["delta_row"]), delta_col=dev(c["delta_col"]),
+                                    write_res=False, q=q, q_scale=s)
+    assert torch.equal(res, before)
+
+
+# ------------------------------------------------------------------------------------- GEMM
+@pytest.mark.parametrize("name", [n for n, _ in cases.gemm_cases()])
+def test_gemm_and_fused_linear(ops, oracle, B200, name):
+    c = dict(cases.gemm_cases())[name]
+    g = B200[f"gemm/{name}"]
+    fp8, norm = ops["fp8"], ops["norm"]
+    a, s = quantise(ops, dev(c["x"]))
+    assert sha(a) == g["a"]["q_sha"] and i32(s).tolist() == g["a"]["qs_bits"]
+    W = fp8.Fp8Weight(dev(c["wq"]), dev(c["wscale"]), dev(c["bias"]))
+    M, N = a.shape[0], W.w.shape[0]
+    raw = torch.full((M, N), float("nan"), device=DEV, dtype=torch.bfloat16)   # poisoned output
+    fp8.gemm(a, W, raw)
+    no_timeout(ops)
+    assert not torch.isnan(raw.float()).any()
+    exact = oracle.gemm_acc(a.cpu(), c["wq"])
+    # raw accumulator: the bf16 rounding of the exact sum, up to elements on a rounding boundary
+    assert (raw.cpu() != exact.to(torch.bfloat16)).float().mean().item() < 1e-3
+    assert rel_frobenius(raw.float(), exact.to(torch.bfloat16).float()) < 1e-4
+    # the reference's GPU path (torch._scaled_mm -> cuBLASLt on a B200), recorded: same K order
+    assert raw[0, :64].cpu().view(torch.int16).tolist() == g["raw_head"]
+    assert sha(raw) == g["raw_sha"], "raw accumulator differs from the reference's gemm on a B200"
+    # fused epilogue == gemm + dequant_rows, bit for bit, and == the reference's recorded output
+    y_unfused = torch.empty(M, N, device=DEV, dtype=torch.bfloat16)
+    norm.dequant_rows(raw, y_unfused, row=s, col=W.scale, bias=W.bias)
+    y = torch.full((M, N), float("nan"), device=DEV, dtype=torch.bfloat16)
+    fp8.fp8_linear(a, s, W, y)
+    assert torch.equal(y, y_unfused)
+    assert sha(y) == g["y_sha"], "fused linear differs from the reference's gemm + dequant_rows on a B200"
+    # the bar, against the engine-mode oracle
+    assert_gemm_parity(y.float(), oracle.fp8_linear(a.cpu(), s.cpu(), c["wq"], c["wscale"], c["bias"]).float(), name)
+    # exact rounding mode against the dequantise-and-matmul CPU baseline
+    y_exact = torch.empty(M, N, device=DEV, dtype=torch.bfloat16)
+    fp8.fp8_linear(a, s, W, y_exact, exact=True)
+    assert_gemm_parity(y_exact.float(), oracle.dequantise_and_matmul(a.cpu(), s.cpu(), c["wq"], c["wscale"], c["bias"]).float(),
+                       name + "/exact")
+    # fused residual epilogue == gemm + residual_norm_quant's residual part, bit for bit
+    for rdt in (torch.float32, torch.bfloat16):
+        res = dev(cases.activations(M, N, 77, dtype=torch.float32)).to(rdt)
+        r1, r2 = res.clone(), res.clone()
+        gate = dev(cases.vector(N, 78, sigma=0.5))
+        norm.residual_norm_quant(r1, delta=raw, delta_row=s, delta_col=W.scale, bias=W.bias, gate=gate)
+        fp8.fp8_linear_residual(a, s, W, r2, bias=W.bias, gate=gate)
+        assert torch.equal(r1, r2)
+    no_timeout(ops)
+
+
+@pytest.mark.parametrize("tile_n", [64, 128, 256])
+def test_gemm_tile_shapes_agree(ops, tile_n):
+    fp8 = ops["fp8"]
+    g = torch.Generator().manual_seed(tile_n)
+    a = dev((torch.randn(520, 3072, generator=g) * 60).clamp(-448, 448).to(E4M3))
+    w = dev((torch.randn(1040, 3072, generator=g) * 60).clamp(-448, 448).to(E4M3))
+    W = fp8.Fp8Weight(w, torch.ones(1040, device=DEV), None)
+    ref = torch.empty(520, 1040, device=DEV, dtype=torch.bfloat16)
+    fp8.gemm(a, W, ref)
+    try:
+        assert ops["lib"].iflb200_gemm_set_config(tile_n, 0, 3) == 0
+        out = torch.empty_like(ref)
+        fp8.gemm(a, W, out)
+    finally:
+        ops["lib"].iflb200_gemm_set_config(0, 0, 0)
+    assert torch.equal(out, ref)       # the K loop order does not depend on the tile shape
+    no_timeout(ops)
+
+
+def test_gemm_reference_test_shape(ops):
+    """instinctflash tests/test_gi_kernels.py:130-143: M=50, K=1024, N=2560 against x@w.T+b, < 0.05."""
+    fp8, norm = ops["fp8"], ops["norm"]
+    torch.manual_seed(5)
+    x = torch.randn(50, 1024, device=DEV)
+    w = torch.randn(2560, 1024, device=DEV) * 0.02
+    wq = fp8.quantize_weight(w, torch.randn(2560, device=DEV))
+    q, qs = quantise(ops, x)
+    raw = torch.empty(50, 2560, device=DEV, dtype=torch.bfloat16)
+    fp8.gemm(q, wq, raw)
+    y = torch.empty(50, 2560, device=DEV)
+    norm.dequant_rows(raw, y, row=qs, col=wq.scale, bias=wq.bias)
+    ref = x @ w.t() + wq.bias
+    assert ((y - ref).abs().max() / ref.abs().max()) < 0.05
+
+
+def test_gemm_strided_operands_and_output_views(ops):
+    fp8 = ops["fp8"]
+    g = torch.Generator().manual_seed(11)
+    arena_a = dev((torch.randn(70, 2048, generator=g) * 50).clamp(-448, 448).to(E4M3))
+    a = arena_a[:, 512:1536]                         # row stride 2048, K = 1024
+    w = dev((torch.randn(256, 1024, generator=g) * 50).clamp(-448, 448).to(E4M3))
+    W = fp8.Fp8Weight(w, torch.ones(256, device=DEV), None)
+    arena_o = torch.zeros(70, 1024, device=DEV, dtype=torch.bfloat16)
+    out = arena_o[:, 256:512]
+    fp8.gemm(a, W, out)
+    ref = torch.empty(70, 256, device=DEV, dtype=torch.bfloat16)
+    fp8.gemm(a.contiguous(), W, ref)
+    assert torch.equal(out, ref)
+    assert bool((arena_o[:, :256] == 0).all()) and bool((arena_o[:, 512:] == 0).all())
+    no_timeout(ops)
+
+
+def test_gemm_rejects_bad_shapes(ops):
+    fp8 = ops["fp8"]
+    a = torch.zeros(4, 24, device=DEV, dtype=torch.uint8).view(E4M3)
+    W = fp8.Fp8Weight(torch.zeros(16, 24, device=DEV, dtype=torch.uint8).view(E4M3), torch.ones(16, device=DEV), None)
+    with pytest.raises(ValueError, match="multiples of 16"):
+        fp8.gemm(a, W, torch.empty(4, 16, device=DEV, dtype=torch.bfloat16))
+    fp8.gemm(torch.zeros(0, 32, device=DEV, dtype=torch.uint8).view(E4M3),
+             fp8.Fp8Weight(torch.zeros(16, 32, device=DEV, dtype=torch.uint8).view(E4M3), torch.ones(16, device=DEV), None),
+             torch.empty(0, 16, device=DEV, dtype=torch.bfloat16))       # empty input is a no-op
+
+
+FULL_SIZE = [("c2_gate_up", 816, 32768, 2048, 1), ("c2_down", 816, 2048, 16384, 1), ("c4_qkv", 4680, 9216, 3072, 3),
+             ("c4_ff2", 4680, 3072, 14336, 3), ("c5_qkv", 16384, 15360, 5120, 4), ("c5_ff2", 16384, 5120, 13824, 4)]
+
+
+@pytest.mark.parametrize("name,M,N,K,seed", FULL_SIZE)
+def test_gemm_properties_at_full_size(ops, oracle, name, M, N, K, seed):
+    """At the benchmark sizes: (a) column shards of the weight give bit-identical columns
+    (N-partition invariance: the K loop order depends on K alone), (b) row shards of the
+    activations give bit-identical rows, (c) a sampled set of rows/columns matches the exact
+    oracle accumulator after bf16 rounding, (d) scaling an activation row by 2 scales its raw
+    output row by exactly 2 (linearity in the power-of-two sense)."""
+    fp8 = ops["fp8"]
+    g = torch.Generator().manual_seed(seed)
+    x = cases.activations(M, K, 2000 + seed, outlier_frac=0.005, outlier_scale=20.0)
+    a, s = quantise(ops, dev(x))
+    wq = (torch.randn(N, K, generator=g) * 120).clamp(-448, 448).to(E4M3)
+    W = fp8.Fp8Weight(dev(wq), torch.ones(N, device=DEV), None)
+    raw = torch.empty(M, N, device=DEV, dtype=torch.bfloat16)
+    fp8.gemm(a, W, raw)
+    no_timeout(ops)
+    # (a) column shards
+    for lo, hi in ((0, N // 2), (N // 2, N), (N // 4, N // 4 + 512)):
+        part = torch.empty(M, hi - lo, device=DEV, dtype=torch.bfloat16)
+        fp8.gemm(a, fp8.Fp8Weight(W.w[lo:hi], W.scale[lo:hi], None), part)
+        assert torch.equal(part, raw[:, lo:hi])
+    # (b) row shards
+    lo, hi = M // 3, M // 3 + 200
+    part = torch.empty(hi - lo, N, device=DEV, dtype=torch.bfloat16)
+    fp8.gemm(a[lo:hi], W, part)
+    assert torch.equal(part, raw[lo:hi])
+    # (c) sampled exact check
+    rows_idx = torch.randperm(M, generator=g)[:24]
+    cols_idx = torch.randperm(N, generator=g)[:384]
+    exact = oracle.gemm_acc(a.cpu()[rows_idx].contiguous(), wq[cols_idx].contiguous()).to(torch.bfloat16)
+    got = raw.cpu()[rows_idx][:, cols_idx]
+    assert (got != exact).float().mean().item() < 2e-3
+    assert rel_frobenius(got.float(), exact.float()) < 1e-4
+    # (d) e4m3 codes doubled in value (exponent + 1) double the accumulator exactly
+    sub = a[:64].clone()
+    bits = sub.view(torch.uint8)
+    ok = ((bits & 0x78) < 0x70) & ((bits & 0x78) > 0)          # normal numbers with headroom
+    doubled = torch.where(ok, bits + 8, torch.zeros_like(bits))
+    base = torch.where(ok, bits, torch.zeros_like(bits))
+    r1 = torch.empty(64, N, device=DEV, dtype=torch.bfloat16)
+    r2 = torch.empty(64, N, device=DEV, dtype=torch.bfloat16)
+    fp8.gemm(base.view(E4M3), W, r1)
+    fp8.gemm(doubled.view(E4M3), W, r2)
+    assert torch.equal(r2.float(), r1.float() * 2)
+    no_timeout(ops)
+
+
+def test_gemm_is_deterministic_and_graph_replayable(ops):
+    fp8, norm = ops["fp8"], ops["norm"]
+    x = dev(cases.activations(816, 2048, 31))
+    W = fp8.Fp8Weight(dev((torch.randn(2560, 2048) * 100).clamp(-448, 448).to(E4M3)), torch.rand(2560, device=DEV) * 1e-3,
+                      torch.randn(2560, device=DEV))
+    a = torch.empty(816, 2048, device=DEV, dtype=E4M3)
+    s = torch.empty(816, device=DEV)
+    y = torch.empty(816, 2560, device=DEV, dtype=torch.bfloat16)
+
+    def step():
+        norm.row_quant(x, a, s)
+        fp8.fp8_linear(a, s, W, y)
+
+    step()
+    eager = y.clone()
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        for _ in range(2):
+            step()
+    torch.cuda.current_stream().wait_stream(side)
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        step()
+    y.zero_()
+    graph.replay()
+    assert torch.equal(y, eager)
+    x.copy_(dev(cases.activations(816, 2048, 32)))       # changed input, same graph
+    graph.replay()
+    replayed = y.clone()
+    step()
+    assert torch.equal(y, replayed)
+    no_timeout(ops)
+
+
+# ------------------------------------------------------------------------------------- per-tensor recipe
+@pytest.mark.parametrize("name", [n for n, _ in cases.pack_cases()])
+def test_dynamic_pack_bit_exact(ops, oracle, B200, name):
+    x = dict(cases.pack_cases())[name]["x"]
+    g = B200[f"dynamic_pack/{name}"]
+    q, s = ops["pack"].dynamic_pack_bf16_e4m3(dev(x))
+    assert i32(s).tolist() == g["scale_bits"] and sha(q) == g["q_sha"]
+    qo, so = oracle.dynamic_pack_bf16_e4m3(x)
+    assert torch.equal(i32(s), i32(so)) and torch.equal(u8(q), u8(qo))
+    # the torch expression of the reference's own test (tests/test_dynamic_fp8_pack.py:14-17)
+    xd = dev(x)
+    expected_scale = xd.abs().amax().float().clamp_min(1e-12).reshape(1) / 448.
+    expected = (xd.float() / expected_scale).clamp(-448, 448).to(E4M3)
+    assert torch.equal(s, expected_scale) and torch.equal(u8(q), u8(expected))
+    q2 = ops["pack"].pack_bf16_e4m3(dev(x), s)
+    assert torch.equal(u8(q2), u8(q))
+
+
+def test_dynamic_pack_nan_and_graph_replay(ops):
+    pack = ops["pack"].dynamic_pack_bf16_e4m3
+    x = torch.randn((40, 2048), device=DEV, dtype=torch.bfloat16)
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        for _ in range(3):
+            pack(x)
+    torch.cuda.current_stream().wait_stream(side)
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph, stream=side):
+        packed, scale = pack(x)
+    for magnitude in (0, 1e-4, 20):
+        x.copy_(torch.randn_like(x) * magnitude)
+        graph.replay()
+        eager, eager_scale = pack(x)
+        assert torch.equal(scale, eager_scale) and torch.equal(u8(packed), u8(eager))
+    x.fill_(float("nan"))
+    _, scale = pack(x)
+    assert torch.isnan(scale).all()
+
+
+def test_sm100_fp8_linear_matches_reference_module_output(ops, B200):
+    c = cases.thor_linear_case()
+    g = B200["thor_fp8_linear/40x1024x2048"]
+    lin = torch.nn.Linear(2048, 1024, bias=True, dtype=torch.bfloat16)
+    with torch.no_grad():
+        lin.weight.copy_(c["weight"])
+        lin.bias.copy_(c["bias"])
+    mod = ops["lin"].SM100FP8Linear(lin.to(DEV))
+    assert sha(mod.weight_fp8) == g["weight_sha"] and i32(mod.weight_scale).tolist() == g["weight_scale_bits"]
+    y = mod(dev(c["x"]))
+    assert y.dtype == torch.bfloat16 and y.shape == (40, 1024)
+    ref_head = torch.tensor(g["y_head"], dtype=torch.int16).view(torch.bfloat16).float()
+    assert (y[0, :64].cpu().float() - ref_head).abs().max().item() <= ref_head.abs().max().item() * 2.0 ** -7
+    assert mod(dev(c["x"]).reshape(2, 20, 2048)).shape == (2, 20, 1024)
+    assert mod(torch.empty(0, 2048, device=DEV, dtype=torch.bfloat16)).shape == (0, 1024)
+    with pytest.raises(ValueError):
+        mod(dev(c["x"]).float())
+    no_timeout(ops)
