@@ -53,21 +53,32 @@ class ClockSampler:
 
     def __init__(self, index: int):
         self.index, self.rows, self.proc = index, [], None
+        self.t_begin = self.t_end = None
+
+    def begin(self):
+        """Mark the start of the timed region (samples outside the marks are dropped)."""
+        self.t_begin = time.monotonic()
+
+    def end(self):
+        self.t_end = time.monotonic()
 
     def __enter__(self):
         try:
             self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits",
-                                          "-i", str(self.index), "-lms", "100"], stdout=subprocess.PIPE,
+                                          "-i", str(self.index), "-lms", "20"], stdout=subprocess.PIPE,
                                          stderr=subprocess.DEVNULL, text=True)
             self.thread = threading.Thread(target=self._read, daemon=True)
             self.thread.start()
         except OSError:
             self.proc = None
+        deadline = time.monotonic() + 5.0   # nvidia-smi needs a moment before its first line
+        while self.proc is not None and not self.rows and time.monotonic() < deadline:
+            time.sleep(0.05)
         return self
 
     def _read(self):
         for line in self.proc.stdout:
-            self.rows.append([c.strip() for c in line.split(",")])
+            self.rows.append((time.monotonic(), [c.strip() for c in line.split(",")]))
 
     def __exit__(self, *exc):
         if self.proc is not None:
@@ -79,7 +90,8 @@ class ClockSampler:
 
     def summary(self):
         sm, smax, reasons = [], [], set()
-        for r in self.rows:
+        inside = [r for t, r in self.rows if self.t_begin is None or (self.t_begin <= t <= (self.t_end or t))]
+        for r in inside or [r for _, r in self.rows[-1:]]:
             try:
                 sm.append(float(r[1]))
                 smax.append(float(r[2]))
@@ -168,7 +180,7 @@ def workload_name(spec):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--steps", type=int, default=50)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--workload", default="c2")
     ap.add_argument("--impl", default="native", choices=["native", "reference"])
@@ -215,17 +227,19 @@ def main():
         torch.cuda.synchronize(dev)
 
     # ---- device-resident timing: inputs in HBM, one graph replay per step --------------------
-    for _ in range(args.warmup):
-        stack.load(x_dev, attn)
-        graph.replay()
-    barrier()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     with ClockSampler(local_rank) as clocks:
+        for _ in range(args.warmup):
+            stack.load(x_dev, attn)
+            graph.replay()
+        barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        clocks.begin()
         e0.record(stream)
         for _ in range(args.steps):
             graph.replay()
         e1.record(stream)
         barrier()
+        clocks.end()
     ms = e0.elapsed_time(e1)
     clock_summary = clocks.summary()
 

@@ -17,7 +17,11 @@ PKG = Path(__file__).resolve().parent
 CSRC = PKG / "csrc"
 INCLUDE = PKG.parent / "include"
 LIBRARY = PKG / "libiflb200.so"
-SOURCES = ("gemm_fp8_sm100.cu", "row_ops.cu")
+# (source, extra defines, object stem): row_ops.cu is compiled as three translation units in parallel
+SOURCES = (("gemm_fp8_sm100.cu", (), "gemm_fp8_sm100"),
+           ("row_ops.cu", ("-DIFLB200_ROW_PART=0",), "row_ops_quant"),
+           ("row_ops.cu", ("-DIFLB200_ROW_PART=1",), "row_ops_gated_pack"),
+           ("row_ops.cu", ("-DIFLB200_ROW_PART=2",), "row_ops_resnorm"))
 NVCC_FLAGS = (
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
     "-Xcompiler", "-fPIC", "-Xcompiler", "-fvisibility=hidden",
@@ -46,15 +50,15 @@ def build(force: bool = False, verbose: bool = False) -> Path:
     obj_dir.mkdir(exist_ok=True)
     nvcc = _nvcc()
     objects, jobs = [], []
-    for name in SOURCES:
+    for name, defines, stem in SOURCES:
         src = CSRC / name
         tag = _digest([src] + headers)
-        obj = obj_dir / f"{src.stem}.{tag}.o"
+        obj = obj_dir / f"{stem}.{tag}.o"
         objects.append(obj)
         if force or not obj.exists():
-            for old in obj_dir.glob(f"{src.stem}.*.o"):
+            for old in obj_dir.glob(f"{stem}.*.o"):
                 old.unlink()
-            cmd = [nvcc, *NVCC_FLAGS, "-I", str(INCLUDE), "-c", str(src), "-o", str(obj)]
+            cmd = [nvcc, *NVCC_FLAGS, *defines, "-I", str(INCLUDE), "-c", str(src), "-o", str(obj)]
             if verbose:
                 cmd.insert(1, "-Xptxas=-v")
             jobs.append(cmd)

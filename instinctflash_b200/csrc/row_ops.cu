@@ -7,11 +7,22 @@
 #include "../../include/iflb200.h"
 #include "rowmath.cuh"
 
+// The file compiles as one translation unit, or as three (IFLB200_ROW_PART = 0, 1, 2) so that
+// the build can run them in parallel: 0 = row_quant + dequant_rows, 1 = gated_act_quant + the
+// per-tensor pack, 2 = residual_norm_quant.
+#ifndef IFLB200_ROW_PART
+#define IFLB200_ROW_PART -1
+#endif
+
 namespace iflb200 {
 
-constexpr int kItersMax = 4;  // 8-element chunks per thread
-constexpr int kMaxTpr = 512;  // threads per row at most (128 registers each stay available)
-constexpr int kMaxWidth = kMaxTpr * 8 * kItersMax;  // 16384 columns
+// Each thread owns IT chunks of 8 elements of its row.  Two compiled depths: a short one (few
+// registers, for narrow rows or few rows, where latency matters) and a long one (64 values per
+// thread in flight, for wide rows of many-row inputs, where bytes in flight per SM matter).
+constexpr int kItersShort = 2;
+constexpr int kItersLong = 8;
+constexpr int kMaxTpr = 1024;  // threads per row at most (short depth only: 64 registers each)
+constexpr int kMaxWidth = 16384;
 
 // --------------------------------------------------------------------------------------------
 // 8-element loads / stores
@@ -62,6 +73,92 @@ __device__ __forceinline__ void load_chunk(const T* row_ptr, int c0, int width, 
 __device__ __forceinline__ void load_chunk_f32(const float* p, int c0, int width, bool vec,
                                                float (&o)[8]) {
   load_chunk<float>(p, c0, width, vec, o);
+}
+
+
+// Eight elements as they sit in memory, held in registers until they are needed: every load
+// of a row is issued before the first value is used, so a thread has all its chunks in flight
+// at once (bytes in flight per SM, not arithmetic, bound these kernels).
+template <typename T>
+struct Raw8 {
+  uint4 u;
+};
+template <>
+struct Raw8<float> {
+  float4 a, b;
+};
+template <typename T>
+__device__ __forceinline__ Raw8<T> raw_zero() {
+  Raw8<T> r;
+  r.u = make_uint4(0u, 0u, 0u, 0u);
+  return r;
+}
+template <>
+__device__ __forceinline__ Raw8<float> raw_zero<float>() {
+  Raw8<float> r;
+  r.a = make_float4(0.f, 0.f, 0.f, 0.f);
+  r.b = r.a;
+  return r;
+}
+template <typename T>
+__device__ __forceinline__ Raw8<T> raw_load(const T* p) {
+  Raw8<T> r;
+  r.u = *reinterpret_cast<const uint4*>(p);
+  return r;
+}
+template <>
+__device__ __forceinline__ Raw8<float> raw_load<float>(const float* p) {
+  Raw8<float> r;
+  r.a = *reinterpret_cast<const float4*>(p);
+  r.b = *reinterpret_cast<const float4*>(p + 4);
+  return r;
+}
+// Element-wise gather for rows that break the 16-byte rule or end inside the chunk.
+template <typename T>
+__device__ __forceinline__ Raw8<T> raw_gather(const T* row_ptr, int c0, int width) {
+  uint32_t w[4] = {0u, 0u, 0u, 0u};
+  const uint16_t* p = reinterpret_cast<const uint16_t*>(row_ptr);
+#pragma unroll
+  for (int i = 0; i < 8; ++i)
+    if (c0 + i < width) w[i >> 1] |= (uint32_t)p[c0 + i] << (16 * (i & 1));
+  Raw8<T> r;
+  r.u = make_uint4(w[0], w[1], w[2], w[3]);
+  return r;
+}
+template <>
+__device__ __forceinline__ Raw8<float> raw_gather<float>(const float* row_ptr, int c0, int width) {
+  float f[8];
+#pragma unroll
+  for (int i = 0; i < 8; ++i) f[i] = (c0 + i < width) ? row_ptr[c0 + i] : 0.0f;
+  Raw8<float> r;
+  r.a = make_float4(f[0], f[1], f[2], f[3]);
+  r.b = make_float4(f[4], f[5], f[6], f[7]);
+  return r;
+}
+template <typename T>
+__device__ __forceinline__ Raw8<T> raw_fetch(const T* row_ptr, int c0, int width, bool vec) {
+  return (vec && c0 + 8 <= width) ? raw_load<T>(row_ptr + c0) : raw_gather<T>(row_ptr, c0, width);
+}
+__device__ __forceinline__ void raw_unpack(const Raw8<__nv_bfloat16>& r, float (&o)[8]) {
+  const uint32_t w[4] = {r.u.x, r.u.y, r.u.z, r.u.w};
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    o[2 * i] = __uint_as_float(w[i] << 16);
+    o[2 * i + 1] = __uint_as_float(w[i] & 0xFFFF0000u);
+  }
+}
+__device__ __forceinline__ void raw_unpack(const Raw8<__half>& r, float (&o)[8]) {
+  const uint32_t w[4] = {r.u.x, r.u.y, r.u.z, r.u.w};
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&w[i]));
+    o[2 * i] = f.x;
+    o[2 * i + 1] = f.y;
+  }
+}
+__device__ __forceinline__ void raw_unpack(const Raw8<float>& r, float (&o)[8]) {
+  o[0] = r.a.x; o[1] = r.a.y; o[2] = r.a.z; o[3] = r.a.w;
+  o[4] = r.b.x; o[5] = r.b.y; o[6] = r.b.z; o[7] = r.b.w;
 }
 
 __device__ __forceinline__ void store_codes8(uint8_t* row_ptr, int c0, int width, bool vec,
@@ -183,8 +280,11 @@ struct RowQuantArgs {
   int vec;
 };
 
-template <typename XT, int TPR>
-__global__ void __launch_bounds__(threads_per_cta<TPR>())
+// PLAIN: no prologue.  The row then stays in registers as loaded (4 registers per 8 elements)
+// and is widened twice, once for the maximum and once for the cast, which keeps enough CTAs
+// resident to cover the HBM latency.
+template <typename XT, int TPR, int IT, bool PLAIN>
+__global__ void __launch_bounds__(threads_per_cta<TPR>(), PLAIN ? (768 / threads_per_cta<TPR>() > 0 ? 768 / threads_per_cta<TPR>() : 1) : 1)
 row_quant_kernel(const RowQuantArgs a) {
   constexpr int NT = threads_per_cta<TPR>();
   __shared__ float red[NT / 32];
@@ -195,31 +295,60 @@ row_quant_kernel(const RowQuantArgs a) {
   const bool vec = a.vec != 0;
   const float rs = (live && a.row) ? a.row[m] : 1.0f;
 
-  float v[kItersMax][8];
-  float amax = 0.0f;
+  Raw8<XT> raw[IT];
 #pragma unroll
-  for (int it = 0; it < kItersMax; ++it) {
+  for (int it = 0; it < IT; ++it) {
     const int c0 = (it * TPR + t) * 8;
-    if (it < a.iters && live && c0 < a.K) {
-      load_chunk<XT>(xr, c0, a.K, vec, v[it]);
-      if (a.row || a.col || a.bias || a.gelu) {
-        float cs[8], bs[8];
-        if (a.col) load_chunk_f32(a.col, c0, a.K, vec, cs);
-        if (a.bias) load_chunk_f32(a.bias, c0, a.K, vec, bs);
+    raw[it] = (it < a.iters && live && c0 < a.K) ? raw_fetch<XT>(xr, c0, a.K, vec) : raw_zero<XT>();
+  }
+  float amax = 0.0f;
+  if (PLAIN) {
 #pragma unroll
-        for (int i = 0; i < 8; ++i) {
-          Chain ch(v[it][i]);
-          if (a.row) ch.mul(rs);
-          if (a.col) ch.mul(cs[i]);
-          if (a.bias) ch.add(bs[i]);
-          float y = ch.done();
-          if (a.gelu) y = gelu_tanh_ref(y);
-          v[it][i] = (c0 + i < a.K) ? y : 0.0f;
-        }
-      }
+    for (int it = 0; it < IT; ++it) {
+      float w[8];
+      raw_unpack(raw[it], w);
 #pragma unroll
-      for (int i = 0; i < 8; ++i) amax = max_f32(amax, fabsf(v[it][i]));
+      for (int i = 0; i < 8; ++i) amax = max_f32(amax, fabsf(w[i]));
     }
+    amax = row_reduce<TPR, true>(amax, red);
+    float scale, inv;
+    quant_scales(amax, scale, inv);
+    if (!live) return;
+    if (t == 0) a.qs[m] = scale;
+    uint8_t* qr = a.q + (int64_t)m * a.ld_q;
+#pragma unroll
+    for (int it = 0; it < IT; ++it) {
+      const int c0 = (it * TPR + t) * 8;
+      if (it < a.iters && c0 < a.K) {
+        float w[8];
+        raw_unpack(raw[it], w);
+        store_codes8(qr, c0, a.K, vec, w, inv);
+      }
+    }
+    return;
+  }
+  float v[IT][8];
+#pragma unroll
+  for (int it = 0; it < IT; ++it) {
+    const int c0 = (it * TPR + t) * 8;
+    raw_unpack(raw[it], v[it]);
+    if (it < a.iters && live && c0 < a.K) {
+      float cs[8], bs[8];
+      if (a.col) load_chunk_f32(a.col, c0, a.K, vec, cs);
+      if (a.bias) load_chunk_f32(a.bias, c0, a.K, vec, bs);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        Chain ch(v[it][i]);
+        if (a.row) ch.mul(rs);
+        if (a.col) ch.mul(cs[i]);
+        if (a.bias) ch.add(bs[i]);
+        float y = ch.done();
+        if (a.gelu) y = gelu_tanh_ref(y);
+        v[it][i] = (c0 + i < a.K) ? y : 0.0f;
+      }
+    }
+#pragma unroll
+    for (int i = 0; i < 8; ++i) amax = max_f32(amax, fabsf(v[it][i]));
   }
   amax = row_reduce<TPR, true>(amax, red);
   float scale, inv;
@@ -228,7 +357,7 @@ row_quant_kernel(const RowQuantArgs a) {
   if (t == 0) a.qs[m] = scale;
   uint8_t* qr = a.q + (int64_t)m * a.ld_q;
 #pragma unroll
-  for (int it = 0; it < kItersMax; ++it) {
+  for (int it = 0; it < IT; ++it) {
     const int c0 = (it * TPR + t) * 8;
     if (it < a.iters && c0 < a.K) store_codes8(qr, c0, a.K, vec, v[it], inv);
   }
@@ -250,7 +379,7 @@ struct GatedArgs {
   int vec;
 };
 
-template <typename XT, int TPR>
+template <typename XT, int TPR, int IT>
 __global__ void __launch_bounds__(threads_per_cta<TPR>())
 gated_act_quant_kernel(const GatedArgs a) {
   constexpr int NT = threads_per_cta<TPR>();
@@ -263,36 +392,42 @@ gated_act_quant_kernel(const GatedArgs a) {
   const bool vec = a.vec != 0;
   const float rs = (live && a.row) ? a.row[m] : 1.0f;
 
-  float h[kItersMax][8];
+  Raw8<XT> rg[IT], ru[IT];
+#pragma unroll
+  for (int it = 0; it < IT; ++it) {
+    const int c0 = (it * TPR + t) * 8;
+    const bool on = it < a.iters && live && c0 < a.F;
+    rg[it] = on ? raw_fetch<XT>(gr, c0, a.F, vec) : raw_zero<XT>();
+    ru[it] = on ? raw_fetch<XT>(ur, c0, a.F, vec) : raw_zero<XT>();
+  }
+  float h[IT][8];
   float amax = 0.0f;
 #pragma unroll
-  for (int it = 0; it < kItersMax; ++it) {
+  for (int it = 0; it < IT; ++it) {
     const int c0 = (it * TPR + t) * 8;
-    if (it < a.iters && live && c0 < a.F) {
-      float g[8], u[8], cg[8], cu[8];
-      load_chunk<XT>(gr, c0, a.F, vec, g);
-      load_chunk<XT>(ur, c0, a.F, vec, u);
-      if (a.col) {
-        load_chunk_f32(a.col, c0, a.F, vec, cg);
-        load_chunk_f32(a.col + a.F, c0, a.F, vec, cu);
-      }
+    float g[8], u[8], cg[8], cu[8];
+    raw_unpack(rg[it], g);
+    raw_unpack(ru[it], u);
+    const bool on = it < a.iters && live && c0 < a.F;
+    if (on && a.col) {
+      load_chunk_f32(a.col, c0, a.F, vec, cg);
+      load_chunk_f32(a.col + a.F, c0, a.F, vec, cu);
+    }
 #pragma unroll
-      for (int i = 0; i < 8; ++i) {
-        float gg = g[i], uu = u[i];
-        if (a.row) {
-          gg = __fmul_rn(gg, rs);
-          uu = __fmul_rn(uu, rs);
-        }
-        if (a.col) {
-          gg = __fmul_rn(gg, cg[i]);
-          uu = __fmul_rn(uu, cu[i]);
-        }
-        const float act = (a.act == IFLB200_ACT_GELU_TANH) ? gelu_tanh_ref(gg) : silu_ref(gg);
-        // gelu: h = u * act; silu: h = act * u (same product either way).
-        const float y = __fmul_rn(uu, act);
-        h[it][i] = (c0 + i < a.F) ? y : 0.0f;
-        amax = max_f32(amax, fabsf(h[it][i]));
+    for (int i = 0; i < 8; ++i) {
+      float gg = g[i], uu = u[i];
+      if (a.row) {
+        gg = __fmul_rn(gg, rs);
+        uu = __fmul_rn(uu, rs);
       }
+      if (on && a.col) {
+        gg = __fmul_rn(gg, cg[i]);
+        uu = __fmul_rn(uu, cu[i]);
+      }
+      const float act = (a.act == IFLB200_ACT_GELU_TANH) ? gelu_tanh_ref(gg) : silu_ref(gg);
+      const float y = __fmul_rn(uu, act);  // act(g) * u
+      h[it][i] = (on && c0 + i < a.F) ? y : 0.0f;
+      amax = max_f32(amax, fabsf(h[it][i]));
     }
   }
   amax = row_reduce<TPR, true>(amax, red);
@@ -302,7 +437,7 @@ gated_act_quant_kernel(const GatedArgs a) {
   if (t == 0) a.qs[m] = scale;
   uint8_t* qr = a.q + (int64_t)m * a.ld_q;
 #pragma unroll
-  for (int it = 0; it < kItersMax; ++it) {
+  for (int it = 0; it < IT; ++it) {
     const int c0 = (it * TPR + t) * 8;
     if (it < a.iters && c0 < a.F) store_codes8(qr, c0, a.F, vec, h[it], inv);
   }
@@ -386,7 +521,7 @@ __device__ __forceinline__ float round_through<__nv_bfloat16>(float x) {
   return __bfloat162float(__float2bfloat16_rn(x));
 }
 
-template <typename RT, int TPR>
+template <typename RT, int TPR, int IT>
 __global__ void __launch_bounds__(threads_per_cta<TPR>())
 residual_norm_quant_kernel(const ResNormArgs a) {
   constexpr int NT = threads_per_cta<TPR>();
@@ -401,18 +536,25 @@ residual_norm_quant_kernel(const ResNormArgs a) {
   const float drs = (live && a.drow) ? a.drow[m] : 1.0f;
   const float fD = (float)a.D;
 
-  float x[kItersMax][8];
+  Raw8<RT> rres[IT];
+  Raw8<__nv_bfloat16> rdel[IT];
+#pragma unroll
+  for (int it = 0; it < IT; ++it) {
+    const int c0 = (it * TPR + t) * 8;
+    const bool on = it < a.iters && live && c0 < a.D;
+    rres[it] = on ? raw_fetch<RT>(rr, c0, a.D, vec) : raw_zero<RT>();
+    rdel[it] = (on && dr) ? raw_fetch<__nv_bfloat16>(dr, c0, a.D, vec) : raw_zero<__nv_bfloat16>();
+  }
+  float x[IT][8];
   float sum = 0.0f, sumsq = 0.0f;
 #pragma unroll
-  for (int it = 0; it < kItersMax; ++it) {
+  for (int it = 0; it < IT; ++it) {
     const int c0 = (it * TPR + t) * 8;
-#pragma unroll
-    for (int i = 0; i < 8; ++i) x[it][i] = 0.0f;
+    raw_unpack(rres[it], x[it]);
     if (it < a.iters && live && c0 < a.D) {
-      load_chunk<RT>(rr, c0, a.D, vec, x[it]);
       if (dr) {
         float d[8], cs[8], bs[8], gs[8];
-        load_chunk<__nv_bfloat16>(dr, c0, a.D, vec, d);
+        raw_unpack(rdel[it], d);
         if (a.dcol) load_chunk_f32(a.dcol, c0, a.D, vec, cs);
         if (a.bias) load_chunk_f32(a.bias, c0, a.D, vec, bs);
         if (a.gate) load_chunk_f32(a.gate + mofs, c0, a.D, vec, gs);
@@ -444,7 +586,7 @@ residual_norm_quant_kernel(const ResNormArgs a) {
     mean = div_full(row_reduce<TPR, false>(sum, red[0]), fD);
     float sq = 0.0f;
 #pragma unroll
-    for (int it = 0; it < kItersMax; ++it) {
+    for (int it = 0; it < IT; ++it) {
       const int c0 = (it * TPR + t) * 8;
 #pragma unroll
       for (int i = 0; i < 8; ++i) {
@@ -462,7 +604,7 @@ residual_norm_quant_kernel(const ResNormArgs a) {
 
   float amax = 0.0f;
 #pragma unroll
-  for (int it = 0; it < kItersMax; ++it) {
+  for (int it = 0; it < IT; ++it) {
     const int c0 = (it * TPR + t) * 8;
     if (it < a.iters && live && c0 < a.D) {
       float ws[8], bs[8], ms[8], mh[8];
@@ -497,12 +639,13 @@ residual_norm_quant_kernel(const ResNormArgs a) {
   if (t == 0) a.qs[m] = scale;
   uint8_t* qr = a.q + (int64_t)m * a.ld_q;
 #pragma unroll
-  for (int it = 0; it < kItersMax; ++it) {
+  for (int it = 0; it < IT; ++it) {
     const int c0 = (it * TPR + t) * 8;
     if (it < a.iters && c0 < a.D) store_codes8(qr, c0, a.D, vec, x[it], inv);
   }
 }
 
+#if IFLB200_ROW_PART == 1 || IFLB200_ROW_PART == -1
 // --------------------------------------------------------------------------------------------
 // Per-tensor pack (the torch-FP8-linear recipe)
 // --------------------------------------------------------------------------------------------
@@ -603,6 +746,8 @@ pack_kernel(const uint16_t* __restrict__ x, int64_t n, const uint32_t* __restric
     q[i] = (uint8_t)(cvt_e4m3x2(pack_one(__uint_as_float((uint32_t)x[i] << 16), scale), 0.0f) & 0xFF);
 }
 
+#endif  // pack kernels
+
 // --------------------------------------------------------------------------------------------
 // Host side: geometry selection and launches
 // --------------------------------------------------------------------------------------------
@@ -611,18 +756,30 @@ static inline bool aligned8(const void* p) { return (reinterpret_cast<uintptr_t>
 static inline int esize(int dtype) { return dtype == IFLB200_F32 ? 4 : 2; }
 static inline bool dtype_ok(int d) { return d == IFLB200_F32 || d == IFLB200_BF16 || d == IFLB200_F16; }
 
-// Threads per row: the smallest group that covers the row in at most kItersMax chunks per
-// thread; with few rows a wider group (fewer chunks per thread) shortens the critical path.
-static int pick_tpr(int M, int width) {
+// Geometry of a row kernel: threads per row and chunks per thread.  Many-row inputs get deep
+// threads (up to 8 chunks each: more bytes in flight per SM); few-row inputs get wide groups
+// (1-2 chunks each: shortest critical path).
+struct RowGeom {
+  int tpr;
+  int iters;
+};
+// `streaming`: the kernel only moves bytes (plain quantiser): many-row inputs get deep threads
+// (8 chunks each, 80 registers, 3 CTAs per SM: bytes in flight).  Otherwise the kernel is bound
+// by its arithmetic (GELU / SiLU / normalisation chains): shallow threads (<= 2 chunks, ~60
+// registers) keep four times as many warps resident.  Few-row inputs always get one chunk per
+// thread (shortest critical path).
+static RowGeom pick_geom(int M, int width, bool streaming) {
+  const int chunks = (width + 7) / 8;
+  const bool big = (int64_t)M * width >= (int64_t)4 << 20;
+  const int per_thread = !big ? 1 : (streaming ? kItersLong : kItersShort);
+  const int cap = (big && streaming) ? 512 : kMaxTpr;
   int tpr = 32;
-  while (tpr < kMaxTpr && (int64_t)tpr * 8 * kItersMax < width) tpr *= 2;
-  if (M <= 1024)
-    while (tpr < kMaxTpr && (int64_t)tpr * 8 < width) tpr *= 2;
-  else
-    while (tpr < 256 && (int64_t)tpr * 8 * 2 < width) tpr *= 2;
-  return tpr;
+  while (tpr < cap && tpr * per_thread < chunks) tpr *= 2;
+  RowGeom g;
+  g.tpr = tpr;
+  g.iters = (chunks + tpr - 1) / tpr;
+  return g;
 }
-static inline int iters_for(int tpr, int width) { return (width + tpr * 8 - 1) / (tpr * 8); }
 
 #define IFLB200_DISPATCH_TPR(TPR_VALUE, ...)                          \
   switch (TPR_VALUE) {                                                \
@@ -630,31 +787,41 @@ static inline int iters_for(int tpr, int width) { return (width + tpr * 8 - 1) /
     case 64: { constexpr int TPR = 64; __VA_ARGS__; } break;          \
     case 128: { constexpr int TPR = 128; __VA_ARGS__; } break;        \
     case 256: { constexpr int TPR = 256; __VA_ARGS__; } break;        \
-    default: { constexpr int TPR = 512; __VA_ARGS__; } break;         \
+    case 512: { constexpr int TPR = 512; __VA_ARGS__; } break;        \
+    default: { constexpr int TPR = 1024; __VA_ARGS__; } break;        \
   }
 
 template <typename XT>
 static void launch_row_quant(const RowQuantArgs& a, int tpr, cudaStream_t s) {
   IFLB200_DISPATCH_TPR(tpr, {
     constexpr int NT = threads_per_cta<TPR>();
-    const int rows_per_cta = NT / TPR;
-    row_quant_kernel<XT, TPR><<<(a.M + rows_per_cta - 1) / rows_per_cta, NT, 0, s>>>(a);
+    const int grid = (a.M + NT / TPR - 1) / (NT / TPR);
+    const bool plain = !(a.row || a.col || a.bias || a.gelu);
+    if (a.iters <= kItersShort) {
+      if (plain) row_quant_kernel<XT, TPR, kItersShort, true><<<grid, NT, 0, s>>>(a);
+      else row_quant_kernel<XT, TPR, kItersShort, false><<<grid, NT, 0, s>>>(a);
+    } else if constexpr (TPR <= 512) {
+      if (plain) row_quant_kernel<XT, TPR, kItersLong, true><<<grid, NT, 0, s>>>(a);
+      else row_quant_kernel<XT, TPR, kItersLong, false><<<grid, NT, 0, s>>>(a);
+    }
   })
 }
 template <typename XT>
 static void launch_gated(const GatedArgs& a, int tpr, cudaStream_t s) {
   IFLB200_DISPATCH_TPR(tpr, {
     constexpr int NT = threads_per_cta<TPR>();
-    const int rows_per_cta = NT / TPR;
-    gated_act_quant_kernel<XT, TPR><<<(a.M + rows_per_cta - 1) / rows_per_cta, NT, 0, s>>>(a);
+    const int grid = (a.M + NT / TPR - 1) / (NT / TPR);
+    if (a.iters <= kItersShort) gated_act_quant_kernel<XT, TPR, kItersShort><<<grid, NT, 0, s>>>(a);
+    else if constexpr (TPR <= 512) gated_act_quant_kernel<XT, TPR, kItersLong><<<grid, NT, 0, s>>>(a);
   })
 }
 template <typename RT>
 static void launch_resnorm(const ResNormArgs& a, int tpr, cudaStream_t s) {
   IFLB200_DISPATCH_TPR(tpr, {
     constexpr int NT = threads_per_cta<TPR>();
-    const int rows_per_cta = NT / TPR;
-    residual_norm_quant_kernel<RT, TPR><<<(a.M + rows_per_cta - 1) / rows_per_cta, NT, 0, s>>>(a);
+    const int grid = (a.M + NT / TPR - 1) / (NT / TPR);
+    if (a.iters <= kItersShort) residual_norm_quant_kernel<RT, TPR, kItersShort><<<grid, NT, 0, s>>>(a);
+    else if constexpr (TPR <= 512) residual_norm_quant_kernel<RT, TPR, kItersLong><<<grid, NT, 0, s>>>(a);
   })
 }
 
@@ -662,6 +829,7 @@ static void launch_resnorm(const ResNormArgs& a, int tpr, cudaStream_t s) {
 
 using namespace iflb200;
 
+#if IFLB200_ROW_PART == 0 || IFLB200_ROW_PART == -1
 extern "C" int iflb200_row_quant(const void* x, int x_dtype, int64_t ld_x, int M, int K,
                                  const float* row, const float* col, const float* bias, int gelu,
                                  void* q, int64_t ld_q, float* qs, void* stream) {
@@ -677,8 +845,9 @@ extern "C" int iflb200_row_quant(const void* x, int x_dtype, int64_t ld_x, int M
   a.q = reinterpret_cast<uint8_t*>(q); a.ld_q = ld_q; a.qs = qs;
   a.vec = aligned16(x) && (ld_x * esize(x_dtype)) % 16 == 0 && aligned8(q) && ld_q % 8 == 0 &&
           (!col || aligned16(col)) && (!bias || aligned16(bias));
-  const int tpr = pick_tpr(M, K);
-  a.iters = iters_for(tpr, K);
+  const RowGeom geom = pick_geom(M, K, !(row || col || bias || gelu));
+  const int tpr = geom.tpr;
+  a.iters = geom.iters;
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
   if (x_dtype == IFLB200_BF16) launch_row_quant<__nv_bfloat16>(a, tpr, s);
   else if (x_dtype == IFLB200_F16) launch_row_quant<__half>(a, tpr, s);
@@ -686,6 +855,9 @@ extern "C" int iflb200_row_quant(const void* x, int x_dtype, int64_t ld_x, int M
   return (int)cudaGetLastError();
 }
 
+#endif
+
+#if IFLB200_ROW_PART == 1 || IFLB200_ROW_PART == -1
 extern "C" int iflb200_gated_act_quant(const void* gu, int gu_dtype, int64_t ld_gu, int M, int F,
                                        const float* row, const float* col, int act,
                                        void* q, int64_t ld_q, float* qs, void* stream) {
@@ -702,8 +874,9 @@ extern "C" int iflb200_gated_act_quant(const void* gu, int gu_dtype, int64_t ld_
   const int es = esize(gu_dtype);
   a.vec = aligned16(gu) && (ld_gu * es) % 16 == 0 && ((int64_t)F * es) % 16 == 0 && aligned8(q) &&
           ld_q % 8 == 0 && (!col || (aligned16(col) && F % 4 == 0));
-  const int tpr = pick_tpr(M, F);
-  a.iters = iters_for(tpr, F);
+  const RowGeom geom = pick_geom(M, F, false);
+  const int tpr = geom.tpr;
+  a.iters = geom.iters;
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
   if (gu_dtype == IFLB200_BF16) launch_gated<__nv_bfloat16>(a, tpr, s);
   else if (gu_dtype == IFLB200_F16) launch_gated<__half>(a, tpr, s);
@@ -711,6 +884,9 @@ extern "C" int iflb200_gated_act_quant(const void* gu, int gu_dtype, int64_t ld_
   return (int)cudaGetLastError();
 }
 
+#endif
+
+#if IFLB200_ROW_PART == 0 || IFLB200_ROW_PART == -1
 extern "C" int iflb200_dequant_rows(const void* x, int x_dtype, int64_t ld_x, int M, int D,
                                     const float* row, const float* col, const float* bias,
                                     void* y, int y_dtype, int64_t ld_y, void* stream) {
@@ -743,6 +919,9 @@ extern "C" int iflb200_dequant_rows(const void* x, int x_dtype, int64_t ld_x, in
   return (int)cudaGetLastError();
 }
 
+#endif
+
+#if IFLB200_ROW_PART == 2 || IFLB200_ROW_PART == -1
 extern "C" int iflb200_residual_norm_quant(void* res, int res_dtype, int64_t ld_res, int M, int D,
                                            const void* delta, int64_t ld_delta,
                                            const float* delta_row, const float* delta_col,
@@ -779,14 +958,18 @@ extern "C" int iflb200_residual_norm_quant(void* res, int res_dtype, int64_t ld_
           (!delta || (aligned16(delta) && (ld_delta * 2) % 16 == 0)) &&
           (!q || (aligned8(q) && ld_q % 8 == 0)) &&
           (!y || (aligned16(y) && (ld_y * esize(y_dtype)) % 16 == 0)) && tables_ok;
-  const int tpr = pick_tpr(M, D);
-  a.iters = iters_for(tpr, D);
+  const RowGeom geom = pick_geom(M, D, false);
+  const int tpr = geom.tpr;
+  a.iters = geom.iters;
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
   if (res_dtype == IFLB200_F32) launch_resnorm<float>(a, tpr, s);
   else launch_resnorm<__nv_bfloat16>(a, tpr, s);
   return (int)cudaGetLastError();
 }
 
+#endif
+
+#if IFLB200_ROW_PART == 1 || IFLB200_ROW_PART == -1
 static int pack_grid(int64_t n) {
   int64_t ctas = (n + (int64_t)kPackThreads * 8 * 4 - 1) / ((int64_t)kPackThreads * 8 * 4);
   if (ctas < 1) ctas = 1;
@@ -824,3 +1007,5 @@ extern "C" int iflb200_pack_bf16_e4m3(const void* x, int64_t n, const float* sca
                                                     0, scale, nullptr, reinterpret_cast<uint8_t*>(q));
   return (int)cudaGetLastError();
 }
+#endif
+
