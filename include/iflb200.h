@@ -59,6 +59,7 @@ extern "C" {
 #define IFLB200_ERR_DRIVER (-5)    /* cuTensorMapEncodeTiled unavailable or refused the layout */
 #define IFLB200_ERR_DEVICE (-6)    /* current device is not compute capability 10.x */
 #define IFLB200_ERR_WORKSPACE (-7) /* workspace missing or too small */
+#define IFLB200_ERR_TOO_LARGE (-8) /* input larger than the fixed capacity of a no-allocation entry point */
 
 IFLB200_API int iflb200_abi_version(void);
 IFLB200_API const char* iflb200_status_string(int status);
@@ -166,6 +167,27 @@ IFLB200_API int iflb200_fp8_linear_residual(const void* a, int64_t ld_a, const v
 IFLB200_API size_t iflb200_pack_workspace_bytes(int64_t n);
 IFLB200_API int iflb200_dynamic_pack_bf16_e4m3(const void* x, int64_t n, void* q, float* scale,
                                    void* workspace, size_t workspace_bytes, void* stream);
+
+/*
+ * The dynamic pack for hosts that have no way to hand over scratch memory.  Same result as
+ * iflb200_dynamic_pack_bf16_e4m3 (same kernels), but the partial-maximum scratch is a 4 KB device
+ * array inside the library image, so the call needs no workspace and performs no allocation of
+ * any kind (no cudaMalloc / cudaFree, no allocating library routine).  Meant for callers that
+ * run from a memory plan fixed at start-up, have no allocator behind them, or sit in a
+ * latency-critical loop where cudaMalloc's device-wide synchronisation is not acceptable.
+ *   - n must not exceed IFLB200_PACK_NOALLOC_MAX_ELEMENTS; larger inputs are refused with
+ *     IFLB200_ERR_TOO_LARGE before anything is launched.
+ *   - The first call on each device looks up the array's device address (the device must be
+ *     current); make that first call before any stream capture begins.
+ *   - All calls on a device share the one array and it keeps whatever the previous call left in
+ *     it.  Nothing in it has to start at zero (every word that is read was written by the same
+ *     call), but two calls that overlap on the GPU -- different streams, or graph branches that
+ *     may run concurrently -- race on it.  Keep calls on one device ordered.
+ * This entry point has no counterpart in the reference.
+ */
+#define IFLB200_PACK_NOALLOC_MAX_ELEMENTS ((int64_t)1 << 28)
+IFLB200_API int iflb200_dynamic_pack_bf16_e4m3_noalloc(const void* x, int64_t n, void* q, float* scale,
+                                                       void* stream);
 
 /*
  * Fixed-scale pack: q = e4m3_rn(clamp(x / scale[0], -448, 448)).

@@ -39,6 +39,7 @@ SIGNATURES = {
     "iflb200_fp8_linear_residual": (_i, [_p, _l, _p, _l, _i, _i, _i, _p, _p, _p, _p, _p, _p, _i, _l, _p]),
     "iflb200_pack_workspace_bytes": (_z, [_l]),
     "iflb200_dynamic_pack_bf16_e4m3": (_i, [_p, _l, _p, _p, _p, _z, _p]),
+    "iflb200_dynamic_pack_bf16_e4m3_noalloc": (_i, [_p, _l, _p, _p, _p]),
     "iflb200_pack_bf16_e4m3": (_i, [_p, _l, _p, _p, _p]),
     "iflb200_gemm_take_timeout_record": (_i, [ctypes.POINTER(ctypes.c_uint32), _p]),
     "iflb200_gemm_set_config": (_i, [_i, _i, _i]),

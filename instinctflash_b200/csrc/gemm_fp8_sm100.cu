@@ -590,6 +590,7 @@ extern "C" const char* iflb200_status_string(int status) {
     case IFLB200_ERR_DRIVER: return "cuTensorMapEncodeTiled unavailable or rejected the layout";
     case IFLB200_ERR_DEVICE: return "current device is not a compute capability 10.x GPU";
     case IFLB200_ERR_WORKSPACE: return "workspace missing or too small";
+    case IFLB200_ERR_TOO_LARGE: return "input exceeds the fixed capacity of this no-allocation entry point";
     default: return status > 0 ? cudaGetErrorString((cudaError_t)status) : "unknown status";
   }
 }

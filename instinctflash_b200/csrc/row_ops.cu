@@ -1007,5 +1007,58 @@ extern "C" int iflb200_pack_bf16_e4m3(const void* x, int64_t n, const float* sca
                                                     0, scale, nullptr, reinterpret_cast<uint8_t*>(q));
   return (int)cudaGetLastError();
 }
+// --------------------------------------------------------------------------------------------
+// Dynamic pack for callers that cannot allocate.
+//
+// The dynamic pack needs a few hundred words of scratch (one partial maximum per CTA of the first
+// kernel).  Hosts that drive this library from a fixed memory plan -- an embedded control loop
+// whose device memory was carved up at start-up, a C or C++ runtime that has no caching
+// allocator behind it, a real-time loop that cannot afford the device-wide stall of a
+// cudaMalloc -- have nowhere to get that scratch from.  For them
+// the scratch lives in the library image itself: a file-scope device array, resident on every GPU
+// that loads the library until the process exits (4 KB).
+//
+// Host code must not pass the array's name to a kernel: on the host that name is only a
+// stand-in symbol, not a device address.  The address is looked up once per device with
+// cudaGetSymbolAddress while that device is current, and that pointer is what the kernels get.
+// --------------------------------------------------------------------------------------------
+static __device__ __align__(256) uint32_t g_pack_noalloc_scratch[kPackMaxCtas];
+
+static int pack_noalloc_scratch(uint32_t** out) {
+  static uint32_t* resolved[64] = {};
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return (int)e;
+  if (dev < 0 || dev >= 64) return IFLB200_ERR_DEVICE;
+  uint32_t* p = __atomic_load_n(&resolved[dev], __ATOMIC_ACQUIRE);
+  if (p == nullptr) {
+    // First call on this device (which is the current one): resolve the symbol.  Two host
+    // threads racing here resolve the same address; the store is idempotent.
+    void* addr = nullptr;
+    e = cudaGetSymbolAddress(&addr, g_pack_noalloc_scratch);
+    if (e != cudaSuccess) return (int)e;
+    if (addr == nullptr) return IFLB200_ERR_DEVICE;
+    p = reinterpret_cast<uint32_t*>(addr);
+    __atomic_store_n(&resolved[dev], p, __ATOMIC_RELEASE);
+  }
+  *out = p;
+  return IFLB200_OK;
+}
+
+extern "C" int iflb200_dynamic_pack_bf16_e4m3_noalloc(const void* x, int64_t n, void* q, float* scale,
+                                                      void* stream) {
+  if (n <= 0 || !x || !q || !scale) return IFLB200_ERR_ARG;
+  if (n > IFLB200_PACK_NOALLOC_MAX_ELEMENTS) return IFLB200_ERR_TOO_LARGE;
+  if (reinterpret_cast<uintptr_t>(x) & 1) return IFLB200_ERR_ALIGN;
+  uint32_t* partial = nullptr;
+  const int st = pack_noalloc_scratch(&partial);
+  if (st != IFLB200_OK) return st;
+  const int grid = pack_grid(n);  // <= kPackMaxCtas words of scratch, all written before they are read
+  cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+  amax_partial_kernel<<<grid, kPackThreads, 0, s>>>(reinterpret_cast<const uint16_t*>(x), n, partial);
+  pack_kernel<<<grid, kPackThreads, 0, s>>>(reinterpret_cast<const uint16_t*>(x), n, partial, grid, nullptr,
+                                            scale, reinterpret_cast<uint8_t*>(q));
+  return (int)cudaGetLastError();
+}
 #endif
 
