@@ -205,6 +205,17 @@ IFLB200_API int iflb200_gemm_take_timeout_record(uint32_t* record, void* stream)
 
 /* Tuning overrides for experiments and tests (0 = heuristic). No reference counterpart. */
 IFLB200_API int iflb200_gemm_set_config(int tile_n, int stages, int group_m);
+/* Row kernels: force the number of threads that share one row (power of two, 32..1024;
+ * 0 = heuristic).  For experiments and tests.  No reference counterpart. */
+IFLB200_API int iflb200_row_set_group(int threads_per_row);
+/* Kernel family: 0 = heuristic, 1 = single-CTA tiles only, 2 / 3 = 256x256 tiles on CTA pairs
+ * (cta_group::2) with one / two tensor-memory accumulators; add 16 to store the epilogue
+ * straight from registers instead of through shared memory and TMA.  For experiments and
+ * tests.  No reference counterpart. */
+IFLB200_API int iflb200_gemm_set_mode(int mode);
+/* Diagnostics: tensor-memory base addresses seen by the two CTAs of the first pair of the last
+ * CTA-pair launch.  Synchronises the stream.  No reference counterpart. */
+IFLB200_API int iflb200_gemm_debug_words(uint32_t* out4, void* stream);
 
 #ifdef __cplusplus
 }

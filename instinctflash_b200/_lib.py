@@ -43,6 +43,9 @@ SIGNATURES = {
     "iflb200_pack_bf16_e4m3": (_i, [_p, _l, _p, _p, _p]),
     "iflb200_gemm_take_timeout_record": (_i, [ctypes.POINTER(ctypes.c_uint32), _p]),
     "iflb200_gemm_set_config": (_i, [_i, _i, _i]),
+    "iflb200_gemm_set_mode": (_i, [_i]),
+    "iflb200_row_set_group": (_i, [_i]),
+    "iflb200_gemm_debug_words": (_i, [ctypes.POINTER(ctypes.c_uint32), _p]),
 }
 
 _LIB = None

@@ -20,6 +20,7 @@
 // bounded wait, TMEM is freed and the kernel returns.
 #include <cuda.h>
 #include <cuda_runtime.h>
+#include <string.h>
 
 #include "../../include/iflb200.h"
 #include "rowmath.cuh"
@@ -30,6 +31,8 @@ constexpr int BM = 128;
 constexpr int BK = 128;  // bytes == e4m3 elements per stage along K
 constexpr int kGemmThreads = 192;
 constexpr uint64_t kWaitBudgetNs = 2000000000ull;  // 2 s per wait, then abort
+
+constexpr int kStagingBytes = 4 * 2 * 32 * 128;  // 4 epilogue warps x 2 buffers x 32 rows x 128 B
 
 enum : int { EPI_RAW = 0, EPI_DEQUANT = 1, EPI_RESIDUAL = 2 };
 
@@ -49,6 +52,7 @@ struct GemmParams {
   void* out;
   int out_dtype;
   int64_t ld_out;
+  int tma_store;  // 1: the epilogue stages 128-byte row pieces in shared memory and TMA-stores them
 };
 
 // role << 24 | barrier kind << 16 | low 16 bits of the tile counter; 0 = no timeout.
@@ -59,7 +63,9 @@ struct SmemLayout {
   static constexpr int kABytes = BM * BK;
   static constexpr int kBBytes = BN * BK;
   static constexpr int kStageBytes = kABytes + kBBytes;
-  static constexpr int kBarOffset = STAGES * kStageBytes;
+  // epilogue staging: per epilogue warp two 32-row x 128-byte buffers (TMA-store sources)
+  static constexpr int kStagingOffset = STAGES * kStageBytes;
+  static constexpr int kBarOffset = kStagingOffset + kStagingBytes;
   // full[STAGES], empty[STAGES], tmem_full[2], tmem_empty[2], then the TMEM base word and the
   // abort flag.
   static constexpr int kNumBars = 2 * STAGES + 4;
@@ -192,10 +198,105 @@ __device__ __forceinline__ void epilogue_chunk(const GemmParams& p, const uint32
   }
 }
 
+// Consumer arithmetic on 32 consecutive columns of one accumulator row (y in fp32, before the
+// cast to the output type).  Scale / bias vectors are read with warp-uniform addresses.
+__device__ __forceinline__ void epilogue_values(const GemmParams& p, const uint32_t (&acc)[32], int n0, float rs,
+                                                float (&y)[32]) {
+#pragma unroll
+  for (int i = 0; i < 32; ++i) {
+    const float a = __uint_as_float(acc[i]);
+    y[i] = p.exact ? a : __bfloat162float(__float2bfloat16_rn(a));
+  }
+  if (p.epilogue == EPI_RAW) return;
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    float v[8], cs[8], bs[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const int n = n0 + 8 * j + i;
+      const bool in = n < p.N;
+      v[i] = y[8 * j + i];
+      cs[i] = (p.col && in) ? __ldg(p.col + (int64_t)n * p.col_stride) : 0.0f;
+      bs[i] = 0.0f;
+      if (p.bias && in)
+        bs[i] = (p.bias_dtype == IFLB200_F32) ? __ldg(reinterpret_cast<const float*>(p.bias) + n)
+                                               : __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(p.bias)[n]);
+    }
+    Chain8 ch(v);
+    if (p.row) ch.mul(rs);
+    if (p.col) ch.mul(cs);
+    if (p.bias) ch.add(bs);
+    ch.done(v);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) y[8 * j + i] = v[i];
+  }
+}
+
+// Epilogue of one accumulator (BN columns) for one warp's 32 rows through shared memory:
+// 128 bytes of each output row (64 two-byte or 32 four-byte columns) are staged with the
+// 128-byte swizzle and written by one TMA store, so global memory sees whole 128-byte lines
+// instead of 16-byte pieces of 32 different rows.  Two staging buffers per warp alternate.
+template <int BN>
+__device__ __forceinline__ void epilogue_tma_store(const GemmParams& p, const CUtensorMap* tm_out, uint32_t t_row,
+                                                   uint32_t staging, uint8_t* staging_ptr, int row0, int m, int n_base,
+                                                   float rs, int lane, uint32_t& buf) {
+  const int es = (p.out_dtype == IFLB200_F32) ? 4 : 2;
+  const int cols_per_store = 128 / es;  // 64 or 32
+#pragma unroll 1
+  for (int c = 0; c < BN; c += cols_per_store) {
+    const int n0 = n_base + c;
+    if (n0 >= p.N) break;  // uniform
+    if (lane == 0) bulk_wait_group_read<1>();  // the buffer written two stores ago has been read
+    __syncwarp();
+    uint8_t* mine = staging_ptr + buf * 4096 + lane * 128;
+#pragma unroll 1
+    for (int sub = 0; sub < cols_per_store; sub += 32) {
+      uint32_t r[32];
+      tmem_ld_32x32b_x32(t_row + c + sub, r);
+      tmem_ld_wait();
+      float y[32];
+      epilogue_values(p, r, n0 + sub, rs, y);
+      if (es == 2) {
+        // 32 values = 64 bytes = four 16-byte chunks; chunk index within the 128-byte row
+        const int first = sub / 8;  // 0 or 4
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          uint4 u;
+          if (p.out_dtype == IFLB200_BF16) {
+            u.x = f32_to_bf16_bits(y[8 * j + 0]) | (f32_to_bf16_bits(y[8 * j + 1]) << 16);
+            u.y = f32_to_bf16_bits(y[8 * j + 2]) | (f32_to_bf16_bits(y[8 * j + 3]) << 16);
+            u.z = f32_to_bf16_bits(y[8 * j + 4]) | (f32_to_bf16_bits(y[8 * j + 5]) << 16);
+            u.w = f32_to_bf16_bits(y[8 * j + 6]) | (f32_to_bf16_bits(y[8 * j + 7]) << 16);
+          } else {
+            u.x = f32_to_f16_bits(y[8 * j + 0]) | (f32_to_f16_bits(y[8 * j + 1]) << 16);
+            u.y = f32_to_f16_bits(y[8 * j + 2]) | (f32_to_f16_bits(y[8 * j + 3]) << 16);
+            u.z = f32_to_f16_bits(y[8 * j + 4]) | (f32_to_f16_bits(y[8 * j + 5]) << 16);
+            u.w = f32_to_f16_bits(y[8 * j + 6]) | (f32_to_f16_bits(y[8 * j + 7]) << 16);
+          }
+          *reinterpret_cast<uint4*>(mine + (((first + j) ^ (lane & 7)) * 16)) = u;
+        }
+      } else {
+#pragma unroll
+        for (int j = 0; j < 8; ++j)
+          *reinterpret_cast<float4*>(mine + ((j ^ (lane & 7)) * 16)) =
+              make_float4(y[4 * j + 0], y[4 * j + 1], y[4 * j + 2], y[4 * j + 3]);
+      }
+    }
+    fence_proxy_async_smem();  // generic-proxy writes visible to the TMA unit
+    __syncwarp();
+    if (lane == 0) {
+      tma_store_2d(tm_out, staging + buf * 4096, n0, row0);
+      bulk_commit_group();
+    }
+    buf ^= 1u;
+  }
+  (void)m;
+}
+
 template <int BN, int STAGES>
 __global__ void __launch_bounds__(kGemmThreads, 1)
 gemm_fp8_tc5_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_w,
-                    const GemmParams p) {
+                    const __grid_constant__ CUtensorMap tm_out, const GemmParams p) {
   using L = SmemLayout<BN, STAGES>;
   constexpr uint32_t kTmemCols = (2 * BN < 32) ? 32 : 2 * BN;  // BN in {32,64,128,256}
   constexpr uint32_t kIdesc = make_idesc_e4m3_f32(BM, BN);
@@ -325,6 +426,9 @@ gemm_fp8_tc5_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
   } else {
     // ------------------------------------------------------------------ epilogue warps
     const int quad = warp & 3;  // TMEM lanes [32*quad, 32*quad+32) are this warp's
+    const uint32_t staging = base + L::kStagingOffset + (uint32_t)(warp - 2) * 8192u;
+    uint8_t* staging_ptr = smem + L::kStagingOffset + (warp - 2) * 8192;
+    uint32_t store_buf = 0;
     bool ok = true;
     uint32_t it = 0;
     for (int tile = blockIdx.x; ok && tile < p.num_tiles; tile += gridDim.x, ++it) {
@@ -341,19 +445,26 @@ gemm_fp8_tc5_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
       const float rs = (row_ok && p.row) ? __ldg(p.row + (int64_t)m * p.row_stride) : 1.0f;
       const int64_t gofs = (row_ok && p.gate_index) ? (int64_t)p.gate_index[m] * p.N : 0;
       const uint32_t t_row = tmem_base + ((uint32_t)(quad * 32) << 16) + acc * BN;
+      if (p.tma_store) {
+        epilogue_tma_store<BN>(p, &tm_out, t_row, staging, staging_ptr, m_blk * BM + quad * 32, m, n_blk * BN, rs,
+                               lane, store_buf);
+      } else {
 #pragma unroll 1
-      for (int c = 0; c < BN / 32; ++c) {
-        const int n0 = n_blk * BN + c * 32;
-        if (n0 >= p.N) break;  // uniform
-        uint32_t r[32];
-        tmem_ld_32x32b_x32(t_row + c * 32, r);
-        tmem_ld_wait();
-        epilogue_chunk<BN>(p, r, m, n0, row_ok, rs, gofs);
+        for (int c = 0; c < BN / 32; ++c) {
+          const int n0 = n_blk * BN + c * 32;
+          if (n0 >= p.N) break;  // uniform
+          uint32_t r[32];
+          tmem_ld_32x32b_x32(t_row + c * 32, r);
+          tmem_ld_wait();
+          epilogue_chunk<BN>(p, r, m, n0, row_ok, rs, gofs);
+        }
       }
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(tempty_bar(acc));
     }
+    if (lane == 0) bulk_wait_group_read<0>();  // staging buffers no longer read by the TMA unit
+    __syncwarp();
   }
 
   tc_fence_before();
@@ -361,6 +472,215 @@ gemm_fp8_tc5_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
   if (warp == 1) {
     tc_fence_after();
     tmem_dealloc(tmem_base, kTmemCols);
+  }
+}
+
+// --------------------------------------------------------------------------------------------
+// CTA-pair variant: one 256 x BN tile per pair of CTAs (a cluster of two, cta_group::2).
+//
+// Each CTA loads its own 128 rows of A and HALF of the W tile (BN/2 rows): 32 KB per 128-byte
+// K step instead of 48 KB, for the same MMA work per SM.  The per-SM TMA request rate is what
+// bounds the single-CTA kernel, so this is worth ~1.5x on the main loop, and the smaller stage
+// leaves room for 6 stages.  The leader (even CTA) issues tcgen05.mma.cta_group::2, which reads
+// both CTAs' shared memory and writes both CTAs' tensor memory (rows 0..127 of the tile in the
+// leader, 128..255 in its peer).  Barriers: both CTAs' TMA loads complete on the leader's
+// "full" barrier; the leader's commits arrive on the "empty" / "accumulator full" barriers of
+// both CTAs; both CTAs' epilogue warps arrive on the leader's "accumulator empty" barrier.
+// --------------------------------------------------------------------------------------------
+template <int BN, int STAGES>
+struct PairSmemLayout {
+  static constexpr int kABytes = BM * BK;
+  static constexpr int kBBytes = (BN / 2) * BK;
+  static constexpr int kStageBytes = kABytes + kBBytes;  // per CTA
+  static constexpr int kStagingOffset = STAGES * kStageBytes;
+  static constexpr int kBarOffset = kStagingOffset + kStagingBytes;
+  static constexpr int kNumBars = 2 * STAGES + 4;
+  static constexpr int kTotal = kBarOffset + kNumBars * 8 + 16;
+  static constexpr int kDynamic = kTotal + 1024;
+};
+
+// tensor-memory base addresses seen by the two CTAs of cluster 0 (diagnostics)
+__device__ uint32_t g_pair_debug[4];
+
+template <int BN, int STAGES, int ACC>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
+gemm_fp8_tc5_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_w,
+                         const __grid_constant__ CUtensorMap tm_out, const GemmParams p) {
+  using L = PairSmemLayout<BN, STAGES>;
+  constexpr uint32_t kTmemCols = ACC * BN;  // 256 or 512
+  constexpr uint32_t kIdesc = make_idesc_e4m3_f32(2 * BM, BN);
+
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t raw_addr = smem_u32(smem_raw);
+  const uint32_t base = (raw_addr + 1023u) & ~1023u;
+  uint8_t* smem = smem_raw + (base - raw_addr);
+
+  const uint32_t bar0 = base + L::kBarOffset;
+  auto full_bar = [&](int s) { return bar0 + 8u * s; };
+  auto empty_bar = [&](int s) { return bar0 + 8u * (STAGES + s); };
+  auto tfull_bar = [&](int a) { return bar0 + 8u * (2 * STAGES + a); };
+  auto tempty_bar = [&](int a) { return bar0 + 8u * (2 * STAGES + 2 + a); };
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + L::kBarOffset + L::kNumBars * 8);
+  volatile uint32_t* abort_flag = tmem_slot + 1;
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const uint32_t rank = cluster_ctarank();
+  const bool leader = rank == 0;
+  const int pair_id = blockIdx.x >> 1;
+  const int pair_stride = gridDim.x >> 1;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(full_bar(s), 1);   // leader's producer arms it; bytes of both CTAs complete it
+      mbar_init(empty_bar(s), 1);  // one multicast commit from the leader
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(tfull_bar(a), 1);
+      mbar_init(tempty_bar(a), 8);  // four epilogue warps in each of the two CTAs
+    }
+    tmem_slot[1] = 0;
+    fence_barrier_init();
+    fence_proxy_async_smem();
+  }
+  if (warp == 1) {
+    tmem_alloc_pair(smem_u32(tmem_slot), kTmemCols);
+    tmem_relinquish_pair();
+  }
+  if (warp == 0 && lane == 0) {
+    prefetch_tensormap(&tm_a);
+    prefetch_tensormap(&tm_w);
+  }
+  tc_fence_before();
+  cluster_sync_all();  // barriers of both CTAs initialised before any remote signal
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+  if (pair_id == 0 && threadIdx.x == 0) g_pair_debug[rank] = tmem_base;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------------ TMA producer (both CTAs)
+    int stage = 0;
+    uint32_t phase = 0;
+    bool ok = true;
+    uint32_t it = 0;
+    for (int tile = pair_id; ok && tile < p.num_tiles; tile += pair_stride, ++it) {
+      int m_blk, n_blk;
+      tile_coords(p, tile, m_blk, n_blk);
+      const int m0 = m_blk * 2 * BM + (int)rank * BM;
+      const int n0 = n_blk * BN + (int)rank * (BN / 2);
+      for (int kb = 0; kb < p.num_k; ++kb) {
+        ok = __all_sync(0xFFFFFFFFu, wait_bounded(empty_bar(stage), phase ^ 1, abort_flag,
+                                                  (1u << 24) | (1u << 16) | (it & 0xFFFF)));
+        if (!ok) break;
+        if (lane == 0) {
+          if (leader) mbar_arrive_expect_tx(full_bar(stage), 2 * L::kStageBytes);
+          const uint32_t sa = base + stage * L::kStageBytes;
+          const uint32_t lead_full = full_bar(stage) & kPeerBitMask;
+          tma_load_2d_pair(sa, &tm_a, lead_full, kb * BK, m0);
+          tma_load_2d_pair(sa + L::kABytes, &tm_w, lead_full, kb * BK, n0);
+        }
+        __syncwarp();
+        if (++stage == STAGES) {
+          stage = 0;
+          phase ^= 1;
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------------ MMA issuer (leader only)
+    if (leader) {
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      uint32_t it = 0;
+      for (int tile = pair_id; ok && tile < p.num_tiles; tile += pair_stride, ++it) {
+        const uint32_t acc = (ACC == 2) ? (it & 1u) : 0u;
+        const uint32_t acc_phase = (ACC == 2) ? ((it >> 1) & 1u) : (it & 1u);
+        ok = __all_sync(0xFFFFFFFFu, wait_bounded(tempty_bar(acc), acc_phase ^ 1, abort_flag,
+                                                  (2u << 24) | (2u << 16) | (it & 0xFFFF)));
+        if (!ok) break;
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + acc * BN;
+        for (int kb = 0; kb < p.num_k; ++kb) {
+          ok = __all_sync(0xFFFFFFFFu, wait_bounded(full_bar(stage), phase, abort_flag,
+                                                    (2u << 24) | (3u << 16) | (it & 0xFFFF)));
+          if (!ok) break;
+          tc_fence_after();
+          if (lane == 0) {
+            const uint32_t sa = base + stage * L::kStageBytes;
+            const uint64_t da = make_kmajor_sw128_desc(sa);
+            const uint64_t db = make_kmajor_sw128_desc(sa + L::kABytes);
+#pragma unroll
+            for (int j = 0; j < BK / 32; ++j)
+              mma_f8f6f4_pair(d_tmem, da + 2 * j, db + 2 * j, kIdesc, (kb | j) != 0 ? 1u : 0u);
+            mma_commit_pair(empty_bar(stage), 3);  // stage free in both CTAs
+          }
+          __syncwarp();
+          if (++stage == STAGES) {
+            stage = 0;
+            phase ^= 1;
+          }
+        }
+        if (!ok) break;
+        if (lane == 0) mma_commit_pair(tfull_bar(acc), 3);  // accumulator complete in both CTAs
+        __syncwarp();
+      }
+    }
+  } else {
+    // ------------------------------------------------------------------ epilogue warps (both CTAs)
+    const int quad = warp & 3;
+    const uint32_t staging = base + L::kStagingOffset + (uint32_t)(warp - 2) * 8192u;
+    uint8_t* staging_ptr = smem + L::kStagingOffset + (warp - 2) * 8192;
+    uint32_t store_buf = 0;
+    bool ok = true;
+    uint32_t it = 0;
+    for (int tile = pair_id; ok && tile < p.num_tiles; tile += pair_stride, ++it) {
+      int m_blk, n_blk;
+      tile_coords(p, tile, m_blk, n_blk);
+      const uint32_t acc = (ACC == 2) ? (it & 1u) : 0u;
+      const uint32_t acc_phase = (ACC == 2) ? ((it >> 1) & 1u) : (it & 1u);
+      ok = __all_sync(0xFFFFFFFFu, wait_bounded(tfull_bar(acc), acc_phase, abort_flag,
+                                                (3u << 24) | (4u << 16) | (it & 0xFFFF)));
+      if (!ok) break;
+      tc_fence_after();
+      const int m = m_blk * 2 * BM + (int)rank * BM + quad * 32 + lane;
+      const bool row_ok = m < p.M;
+      const float rs = (row_ok && p.row) ? __ldg(p.row + (int64_t)m * p.row_stride) : 1.0f;
+      const int64_t gofs = (row_ok && p.gate_index) ? (int64_t)p.gate_index[m] * p.N : 0;
+      const uint32_t t_row = tmem_base + ((uint32_t)(quad * 32) << 16) + acc * BN;
+      if (p.tma_store) {
+        epilogue_tma_store<BN>(p, &tm_out, t_row, staging, staging_ptr,
+                               m_blk * 2 * BM + (int)rank * BM + quad * 32, m, n_blk * BN, rs, lane, store_buf);
+      } else {
+#pragma unroll 1
+        for (int c = 0; c < BN / 32; ++c) {
+          const int n0 = n_blk * BN + c * 32;
+          if (n0 >= p.N) break;
+          uint32_t r[32];
+          tmem_ld_32x32b_x32(t_row + c * 32, r);
+          tmem_ld_wait();
+          epilogue_chunk<BN>(p, r, m, n0, row_ok, rs, gofs);
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive_cluster(tempty_bar(acc), 0);  // on the leader's barrier
+    }
+    if (lane == 0) bulk_wait_group_read<0>();
+    __syncwarp();
+  }
+
+  // No CTA of the pair may leave (or free tensor memory) while its peer can still read its
+  // shared memory, write its tensor memory or signal its barriers.  After a timed-out wait,
+  // give loads that are still in flight time to land before shared memory goes away.
+  if (*abort_flag) {
+    for (int i = 0; i < 64; ++i) __nanosleep(1000);
+  }
+  tc_fence_before();
+  cluster_sync_all();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc_pair(tmem_base, kTmemCols);
   }
 }
 
@@ -401,6 +721,20 @@ static int make_tensor_map(CUtensorMap* tm, const void* ptr, int rows, int K, in
   return r == CUDA_SUCCESS ? IFLB200_OK : IFLB200_ERR_DRIVER;
 }
 
+// [M, N] output matrix of 2- or 4-byte elements; box = 128 bytes x 32 rows, 128-byte swizzle.
+static int make_out_map(CUtensorMap* tm, void* ptr, int M, int N, int64_t ld, int esize) {
+  EncodeTiledFn enc = get_encode_fn();
+  if (!enc) return IFLB200_ERR_DRIVER;
+  const cuuint64_t dims[2] = {(cuuint64_t)N, (cuuint64_t)M};
+  const cuuint64_t strides[1] = {(cuuint64_t)ld * esize};
+  const cuuint32_t box[2] = {(cuuint32_t)(128 / esize), 32u};
+  const cuuint32_t estr[2] = {1, 1};
+  const CUresult r = enc(tm, esize == 2 ? CU_TENSOR_MAP_DATA_TYPE_UINT16 : CU_TENSOR_MAP_DATA_TYPE_UINT32, 2, ptr,
+                         dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                         CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? IFLB200_OK : IFLB200_ERR_DRIVER;
+}
+
 struct DeviceInfo {
   int sm_count = 0;
   int cc_major = 0;
@@ -427,10 +761,12 @@ static int device_info(DeviceInfo** out) {
 }
 
 static int g_cfg_tile_n = 0, g_cfg_stages = 0, g_cfg_group_m = 0;
+static int g_cfg_direct_store = 0;  // 1: epilogue stores straight from registers (experiments)
+static int g_cfg_mode = 0;  // 0 auto, 1 single-CTA tiles only, 2 CTA pairs with one accumulator, 3 CTA pairs with two
 
 template <int BN, int STAGES>
-static int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tw, const GemmParams& p, int grid,
-                       cudaStream_t s) {
+static int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tw, const CUtensorMap& to, const GemmParams& p,
+                       int grid, cudaStream_t s) {
   using L = SmemLayout<BN, STAGES>;
   static bool attr_set[64] = {};
   int dev = 0;
@@ -441,7 +777,24 @@ static int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tw, const GemmP
     if (e != cudaSuccess) return (int)e;
     attr_set[dev] = true;
   }
-  gemm_fp8_tc5_kernel<BN, STAGES><<<grid, kGemmThreads, L::kDynamic, s>>>(ta, tw, p);
+  gemm_fp8_tc5_kernel<BN, STAGES><<<grid, kGemmThreads, L::kDynamic, s>>>(ta, tw, to, p);
+  return (int)cudaGetLastError();
+}
+
+template <int BN, int STAGES, int ACC>
+static int launch_gemm_pair(const CUtensorMap& ta, const CUtensorMap& tw, const CUtensorMap& to,
+                            const GemmParams& p, int grid, cudaStream_t s) {
+  using L = PairSmemLayout<BN, STAGES>;
+  static bool attr_set[64] = {};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (!attr_set[dev]) {
+    cudaError_t e = cudaFuncSetAttribute(gemm_fp8_tc5_pair_kernel<BN, STAGES, ACC>,
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize, L::kDynamic);
+    if (e != cudaSuccess) return (int)e;
+    attr_set[dev] = true;
+  }
+  gemm_fp8_tc5_pair_kernel<BN, STAGES, ACC><<<grid, kGemmThreads, L::kDynamic, s>>>(ta, tw, to, p);
   return (int)cudaGetLastError();
 }
 
@@ -458,6 +811,36 @@ static int run_gemm(const void* a, int64_t ld_a, const void* w, int64_t ld_w, Ge
   DeviceInfo* dev = nullptr;
   int st = device_info(&dev);
   if (st != IFLB200_OK) return st;
+
+  cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+  // Raw and dequant epilogues go through shared memory and TMA stores; the residual epilogue
+  // updates its operand in place with plain loads and stores.
+  CUtensorMap to;
+  p.tma_store = (p.epilogue != EPI_RESIDUAL && g_cfg_direct_store == 0) ? 1 : 0;
+  if (p.tma_store) {
+    st = make_out_map(&to, p.out, p.M, p.N, p.ld_out, oes);
+    if (st != IFLB200_OK) return st;
+  } else {
+    memset(&to, 0, sizeof(to));
+  }
+  if (g_cfg_mode >= 2 && p.N >= 256) {
+    // CTA pairs: 256 x 256 tiles, each CTA loads 128 rows of A and 128 rows of W per K step.
+    constexpr int PBN = 256;
+    p.num_m = (p.M + 2 * BM - 1) / (2 * BM);
+    p.num_n = (p.N + PBN - 1) / PBN;
+    p.num_k = (p.K + BK - 1) / BK;
+    p.num_tiles = p.num_m * p.num_n;
+    p.group_m = g_cfg_group_m > 0 ? g_cfg_group_m : 4;
+    const int pairs = dev->sm_count / 2;
+    const int grid = 2 * (p.num_tiles < pairs ? p.num_tiles : pairs);
+    CUtensorMap ta, tw;
+    st = make_tensor_map(&ta, a, p.M, p.K, ld_a, BM);
+    if (st != IFLB200_OK) return st;
+    st = make_tensor_map(&tw, w, p.N, p.K, ld_w, PBN / 2);
+    if (st != IFLB200_OK) return st;
+    return g_cfg_mode == 2 ? launch_gemm_pair<PBN, 6, 1>(ta, tw, to, p, grid, s)
+                           : launch_gemm_pair<PBN, 6, 2>(ta, tw, to, p, grid, s);
+  }
 
   // Tile width by a measured cost model: a CTA's main loop is bound by the rate at which its
   // TMA unit turns 128-byte rows into requests, so one 128-byte K step costs about 590 / 690 /
@@ -492,12 +875,11 @@ static int run_gemm(const void* a, int64_t ld_a, const void* w, int64_t ld_w, Ge
   if (st != IFLB200_OK) return st;
   st = make_tensor_map(&tw, w, p.N, p.K, ld_w, bn);
   if (st != IFLB200_OK) return st;
-  cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
   const int stages = g_cfg_stages;
   switch (bn) {
-    case 256: return (stages == 3) ? launch_gemm<256, 3>(ta, tw, p, grid, s) : launch_gemm<256, 4>(ta, tw, p, grid, s);
-    case 128: return (stages == 4) ? launch_gemm<128, 4>(ta, tw, p, grid, s) : launch_gemm<128, 6>(ta, tw, p, grid, s);
-    case 64: return (stages == 4) ? launch_gemm<64, 4>(ta, tw, p, grid, s) : launch_gemm<64, 8>(ta, tw, p, grid, s);
+    case 256: return (stages == 3) ? launch_gemm<256, 3>(ta, tw, to, p, grid, s) : launch_gemm<256, 4>(ta, tw, to, p, grid, s);
+    case 128: return (stages == 4) ? launch_gemm<128, 4>(ta, tw, to, p, grid, s) : launch_gemm<128, 6>(ta, tw, to, p, grid, s);
+    case 64: return (stages == 4) ? launch_gemm<64, 4>(ta, tw, to, p, grid, s) : launch_gemm<64, 8>(ta, tw, to, p, grid, s);
     default: return IFLB200_ERR_ARG;
   }
 }
@@ -513,6 +895,23 @@ extern "C" int iflb200_gemm_set_config(int tile_n, int stages, int group_m) {
   g_cfg_stages = stages;
   g_cfg_group_m = group_m;
   return IFLB200_OK;
+}
+
+extern "C" int iflb200_gemm_set_mode(int mode) {
+  // bit 4 (value 16) selects the direct-store epilogue; the low bits the kernel family
+  const int family = mode & 15;
+  if (mode < 0 || family > 3 || (mode & ~31)) return IFLB200_ERR_ARG;
+  g_cfg_mode = family;
+  g_cfg_direct_store = (mode & 16) ? 1 : 0;
+  return IFLB200_OK;
+}
+
+extern "C" int iflb200_gemm_debug_words(uint32_t* out4, void* stream) {
+  if (!out4) return IFLB200_ERR_ARG;
+  cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+  cudaError_t e = cudaMemcpyFromSymbolAsync(out4, g_pair_debug, 4 * sizeof(uint32_t), 0, cudaMemcpyDeviceToHost, s);
+  if (e != cudaSuccess) return (int)e;
+  return (int)cudaStreamSynchronize(s);
 }
 
 extern "C" int iflb200_gemm_take_timeout_record(uint32_t* record, void* stream) {

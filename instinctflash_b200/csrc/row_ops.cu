@@ -16,13 +16,13 @@
 
 namespace iflb200 {
 
-// Each thread owns IT chunks of 8 elements of its row.  Two compiled depths: a short one (few
-// registers, for narrow rows or few rows, where latency matters) and a long one (64 values per
-// thread in flight, for wide rows of many-row inputs, where bytes in flight per SM matter).
-constexpr int kItersShort = 2;
-constexpr int kItersLong = 8;
-constexpr int kMaxTpr = 1024;  // threads per row at most (short depth only: 64 registers each)
-constexpr int kMaxWidth = 16384;
+// CTAs have 256 threads.  A row is owned by a group of TPR threads, each holding IT chunks of 8
+// elements: narrow rows share a CTA (TPR = 32 / 64 / 128, one chunk per thread), wide rows take
+// the whole CTA with 1, 2, 4 or 8 chunks per thread (up to 16384 columns).  Measured on B200,
+// 256-thread groups beat wider ones at every size: the two or three block-wide synchronisations
+// per row are hidden by the other CTAs resident on the SM, not by more threads per row.
+constexpr int kRowThreads = 256;
+constexpr int kMaxWidth = kRowThreads * 8 * 8;  // 16384 columns
 
 // --------------------------------------------------------------------------------------------
 // 8-element loads / stores
@@ -258,9 +258,11 @@ __device__ __forceinline__ float row_reduce(float v, float* slot) {
   return v;
 }
 
-template <int TPR>
-__host__ __device__ constexpr int threads_per_cta() {
-  return TPR > 256 ? TPR : 256;
+// Resident CTAs per SM the compiler must leave room for (register cap): the block-wide
+// synchronisations of one row are hidden by the other CTAs on the SM.
+template <int IT>
+__host__ __device__ constexpr int row_min_blocks() {
+  return IT <= 2 ? 3 : 2;
 }
 
 // --------------------------------------------------------------------------------------------
@@ -284,9 +286,9 @@ struct RowQuantArgs {
 // and is widened twice, once for the maximum and once for the cast, which keeps enough CTAs
 // resident to cover the HBM latency.
 template <typename XT, int TPR, int IT, bool PLAIN>
-__global__ void __launch_bounds__(threads_per_cta<TPR>(), PLAIN ? (768 / threads_per_cta<TPR>() > 0 ? 768 / threads_per_cta<TPR>() : 1) : 1)
+__global__ void __launch_bounds__(kRowThreads, PLAIN ? (IT <= 2 ? 4 : 3) : row_min_blocks<IT>())
 row_quant_kernel(const RowQuantArgs a) {
-  constexpr int NT = threads_per_cta<TPR>();
+  constexpr int NT = kRowThreads;
   __shared__ float red[NT / 32];
   const int t = threadIdx.x % TPR;
   const int m = blockIdx.x * (NT / TPR) + threadIdx.x / TPR;
@@ -336,16 +338,17 @@ row_quant_kernel(const RowQuantArgs a) {
       float cs[8], bs[8];
       if (a.col) load_chunk_f32(a.col, c0, a.K, vec, cs);
       if (a.bias) load_chunk_f32(a.bias, c0, a.K, vec, bs);
+      Chain8 ch(v[it]);
+      if (a.row) ch.mul(rs);
+      if (a.col) ch.mul(cs);
+      if (a.bias) ch.add(bs);
+      ch.done(v[it]);
+      if (a.gelu) {
 #pragma unroll
-      for (int i = 0; i < 8; ++i) {
-        Chain ch(v[it][i]);
-        if (a.row) ch.mul(rs);
-        if (a.col) ch.mul(cs[i]);
-        if (a.bias) ch.add(bs[i]);
-        float y = ch.done();
-        if (a.gelu) y = gelu_tanh_ref(y);
-        v[it][i] = (c0 + i < a.K) ? y : 0.0f;
+        for (int i = 0; i < 8; ++i) v[it][i] = gelu_tanh_ref(v[it][i]);
       }
+#pragma unroll
+      for (int i = 0; i < 8; ++i) v[it][i] = (c0 + i < a.K) ? v[it][i] : 0.0f;
     }
 #pragma unroll
     for (int i = 0; i < 8; ++i) amax = max_f32(amax, fabsf(v[it][i]));
@@ -380,9 +383,9 @@ struct GatedArgs {
 };
 
 template <typename XT, int TPR, int IT>
-__global__ void __launch_bounds__(threads_per_cta<TPR>())
+__global__ void __launch_bounds__(kRowThreads, row_min_blocks<IT>())
 gated_act_quant_kernel(const GatedArgs a) {
-  constexpr int NT = threads_per_cta<TPR>();
+  constexpr int NT = kRowThreads;
   __shared__ float red[NT / 32];
   const int t = threadIdx.x % TPR;
   const int m = blockIdx.x * (NT / TPR) + threadIdx.x / TPR;
@@ -413,20 +416,30 @@ gated_act_quant_kernel(const GatedArgs a) {
       load_chunk_f32(a.col, c0, a.F, vec, cg);
       load_chunk_f32(a.col + a.F, c0, a.F, vec, cu);
     }
+    if (a.row) {
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        g[i] = __fmul_rn(g[i], rs);
+        u[i] = __fmul_rn(u[i], rs);
+      }
+    }
+    if (on && a.col) {
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        g[i] = __fmul_rn(g[i], cg[i]);
+        u[i] = __fmul_rn(u[i], cu[i]);
+      }
+    }
+    if (a.act == IFLB200_ACT_GELU_TANH) {
+#pragma unroll
+      for (int i = 0; i < 8; ++i) h[it][i] = __fmul_rn(u[i], gelu_tanh_ref(g[i]));
+    } else {
+#pragma unroll
+      for (int i = 0; i < 8; ++i) h[it][i] = __fmul_rn(u[i], silu_ref(g[i]));
+    }
 #pragma unroll
     for (int i = 0; i < 8; ++i) {
-      float gg = g[i], uu = u[i];
-      if (a.row) {
-        gg = __fmul_rn(gg, rs);
-        uu = __fmul_rn(uu, rs);
-      }
-      if (on && a.col) {
-        gg = __fmul_rn(gg, cg[i]);
-        uu = __fmul_rn(uu, cu[i]);
-      }
-      const float act = (a.act == IFLB200_ACT_GELU_TANH) ? gelu_tanh_ref(gg) : silu_ref(gg);
-      const float y = __fmul_rn(uu, act);  // act(g) * u
-      h[it][i] = (on && c0 + i < a.F) ? y : 0.0f;
+      h[it][i] = (on && c0 + i < a.F) ? h[it][i] : 0.0f;
       amax = max_f32(amax, fabsf(h[it][i]));
     }
   }
@@ -471,14 +484,11 @@ __global__ void __launch_bounds__(256) dequant_rows_kernel(const DequantArgs a) 
   if (a.col) load_chunk_f32(a.col, c0, a.D, vec, cs);
   if (a.bias) load_chunk_f32(a.bias, c0, a.D, vec, bs);
   const float rs = a.row ? a.row[m] : 1.0f;
-#pragma unroll
-  for (int i = 0; i < 8; ++i) {
-    Chain ch(v[i]);
-    if (a.row) ch.mul(rs);
-    if (a.col) ch.mul(cs[i]);
-    if (a.bias) ch.add(bs[i]);
-    v[i] = ch.done();
-  }
+  Chain8 ch(v);
+  if (a.row) ch.mul(rs);
+  if (a.col) ch.mul(cs);
+  if (a.bias) ch.add(bs);
+  ch.done(v);
   store_out8_dyn(a.y, a.y_dtype, (int64_t)m * a.ld_y, c0, a.D, vec, v);
 }
 
@@ -522,9 +532,9 @@ __device__ __forceinline__ float round_through<__nv_bfloat16>(float x) {
 }
 
 template <typename RT, int TPR, int IT>
-__global__ void __launch_bounds__(threads_per_cta<TPR>())
+__global__ void __launch_bounds__(kRowThreads, row_min_blocks<IT>())
 residual_norm_quant_kernel(const ResNormArgs a) {
-  constexpr int NT = threads_per_cta<TPR>();
+  constexpr int NT = kRowThreads;
   __shared__ float red[3][NT / 32];
   const int t = threadIdx.x % TPR;
   const int m = blockIdx.x * (NT / TPR) + threadIdx.x / TPR;
@@ -558,17 +568,19 @@ residual_norm_quant_kernel(const ResNormArgs a) {
         if (a.dcol) load_chunk_f32(a.dcol, c0, a.D, vec, cs);
         if (a.bias) load_chunk_f32(a.bias, c0, a.D, vec, bs);
         if (a.gate) load_chunk_f32(a.gate + mofs, c0, a.D, vec, gs);
+        Chain8 ch(d);
+        if (a.drow) ch.mul(drs);
+        if (a.dcol) ch.mul(cs);
+        if (a.bias) ch.add(bs);
+        if (a.gate) ch.mul(gs);
+        ch.add(x[it]);  // x + d, contracted with d's last multiply when there is one
+        ch.done(x[it]);
+        if (a.write_res) {
 #pragma unroll
-        for (int i = 0; i < 8; ++i) {
-          Chain ch(d[i]);
-          if (a.drow) ch.mul(drs);
-          if (a.dcol) ch.mul(cs[i]);
-          if (a.bias) ch.add(bs[i]);
-          if (a.gate) ch.mul(gs[i]);
-          ch.add(x[it][i]);  // x + d, contracted with d's last multiply when there is one
-          const float nx = ch.done();
-          x[it][i] = (c0 + i < a.D) ? (a.write_res ? round_through<RT>(nx) : nx) : 0.0f;
+          for (int i = 0; i < 8; ++i) x[it][i] = round_through<RT>(x[it][i]);
         }
+#pragma unroll
+        for (int i = 0; i < 8; ++i) x[it][i] = (c0 + i < a.D) ? x[it][i] : 0.0f;
         if (a.write_res) store_out8<RT>(rr, c0, a.D, vec, x[it]);
       }
 #pragma unroll
@@ -614,18 +626,20 @@ residual_norm_quant_kernel(const ResNormArgs a) {
         load_chunk_f32(a.mod_scale + mofs, c0, a.D, vec, ms);
         load_chunk_f32(a.mod_shift + mofs, c0, a.D, vec, mh);
       }
+      Chain8 ch(x[it]);
+      ch.mul(rstd);
+      if (a.weight) ch.mul(ws);
+      if (a.beta) ch.add(bs);
+      if (a.mod_scale) {
+#pragma unroll
+        for (int i = 0; i < 8; ++i) ms[i] = __fadd_rn(ms[i], 1.0f);
+        ch.mul(ms);
+        ch.add(mh);
+      }
+      ch.done(x[it]);
 #pragma unroll
       for (int i = 0; i < 8; ++i) {
-        Chain ch(x[it][i]);
-        ch.mul(rstd);
-        if (a.weight) ch.mul(ws[i]);
-        if (a.beta) ch.add(bs[i]);
-        if (a.mod_scale) {
-          ch.mul(__fadd_rn(ms[i], 1.0f));
-          ch.add(mh[i]);
-        }
-        const float y = ch.done();
-        x[it][i] = (c0 + i < a.D) ? y : 0.0f;
+        x[it][i] = (c0 + i < a.D) ? x[it][i] : 0.0f;
         amax = max_f32(amax, fabsf(x[it][i]));
       }
       if (a.y) store_out8_dyn(a.y, a.y_dtype, (int64_t)m * a.ld_y, c0, a.D, vec, x[it]);
@@ -756,73 +770,81 @@ static inline bool aligned8(const void* p) { return (reinterpret_cast<uintptr_t>
 static inline int esize(int dtype) { return dtype == IFLB200_F32 ? 4 : 2; }
 static inline bool dtype_ok(int d) { return d == IFLB200_F32 || d == IFLB200_BF16 || d == IFLB200_F16; }
 
-// Geometry of a row kernel: threads per row and chunks per thread.  Many-row inputs get deep
-// threads (up to 8 chunks each: more bytes in flight per SM); few-row inputs get wide groups
-// (1-2 chunks each: shortest critical path).
+// Geometry of a row kernel: threads per row and chunks per thread (see kRowThreads above).
 struct RowGeom {
   int tpr;
   int iters;
 };
-// `streaming`: the kernel only moves bytes (plain quantiser): many-row inputs get deep threads
-// (8 chunks each, 80 registers, 3 CTAs per SM: bytes in flight).  Otherwise the kernel is bound
-// by its arithmetic (GELU / SiLU / normalisation chains): shallow threads (<= 2 chunks, ~60
-// registers) keep four times as many warps resident.  Few-row inputs always get one chunk per
-// thread (shortest critical path).
-static RowGeom pick_geom(int M, int width, bool streaming) {
+// experiments: force the group size (0 = choose); one definition shared by the three units
+#if IFLB200_ROW_PART == 0 || IFLB200_ROW_PART == -1
+int g_row_tpr_override = 0;
+#else
+extern int g_row_tpr_override;
+#endif
+
+static RowGeom pick_geom(int width) {
   const int chunks = (width + 7) / 8;
-  const bool big = (int64_t)M * width >= (int64_t)4 << 20;
-  const int per_thread = !big ? 1 : (streaming ? kItersLong : kItersShort);
-  const int cap = (big && streaming) ? 512 : kMaxTpr;
   int tpr = 32;
-  while (tpr < cap && tpr * per_thread < chunks) tpr *= 2;
+  while (tpr < kRowThreads && tpr < chunks) tpr *= 2;
+  if (g_row_tpr_override && (chunks + g_row_tpr_override - 1) / g_row_tpr_override <= 8) tpr = g_row_tpr_override;
   RowGeom g;
   g.tpr = tpr;
   g.iters = (chunks + tpr - 1) / tpr;
   return g;
 }
 
-#define IFLB200_DISPATCH_TPR(TPR_VALUE, ...)                          \
-  switch (TPR_VALUE) {                                                \
-    case 32: { constexpr int TPR = 32; __VA_ARGS__; } break;          \
-    case 64: { constexpr int TPR = 64; __VA_ARGS__; } break;          \
-    case 128: { constexpr int TPR = 128; __VA_ARGS__; } break;        \
-    case 256: { constexpr int TPR = 256; __VA_ARGS__; } break;        \
-    case 512: { constexpr int TPR = 512; __VA_ARGS__; } break;        \
-    default: { constexpr int TPR = 1024; __VA_ARGS__; } break;        \
+// Calls `launch(tpr_tag, it_tag)` with compile-time tags for the geometry: groups narrower than
+// the CTA always hold one chunk per thread; full-CTA groups hold 1, 2, 4 or 8.
+template <int V>
+struct IntTag {
+  static constexpr int value = V;
+};
+template <typename F>
+static void dispatch_geom(const RowGeom& g, F&& launch) {
+  if (g.iters <= 1) {
+    switch (g.tpr) {
+      case 32: launch(IntTag<32>{}, IntTag<1>{}); return;
+      case 64: launch(IntTag<64>{}, IntTag<1>{}); return;
+      case 128: launch(IntTag<128>{}, IntTag<1>{}); return;
+      default: launch(IntTag<256>{}, IntTag<1>{}); return;
+    }
   }
+  switch (g.tpr) {  // forced narrow groups with several chunks (experiments): deepest variant
+    case 32: launch(IntTag<32>{}, IntTag<8>{}); return;
+    case 64: launch(IntTag<64>{}, IntTag<8>{}); return;
+    case 128: launch(IntTag<128>{}, IntTag<8>{}); return;
+    default: break;
+  }
+  if (g.iters <= 2) launch(IntTag<256>{}, IntTag<2>{});
+  else if (g.iters <= 4) launch(IntTag<256>{}, IntTag<4>{});
+  else launch(IntTag<256>{}, IntTag<8>{});
+}
 
 template <typename XT>
-static void launch_row_quant(const RowQuantArgs& a, int tpr, cudaStream_t s) {
-  IFLB200_DISPATCH_TPR(tpr, {
-    constexpr int NT = threads_per_cta<TPR>();
-    const int grid = (a.M + NT / TPR - 1) / (NT / TPR);
-    const bool plain = !(a.row || a.col || a.bias || a.gelu);
-    if (a.iters <= kItersShort) {
-      if (plain) row_quant_kernel<XT, TPR, kItersShort, true><<<grid, NT, 0, s>>>(a);
-      else row_quant_kernel<XT, TPR, kItersShort, false><<<grid, NT, 0, s>>>(a);
-    } else if constexpr (TPR <= 512) {
-      if (plain) row_quant_kernel<XT, TPR, kItersLong, true><<<grid, NT, 0, s>>>(a);
-      else row_quant_kernel<XT, TPR, kItersLong, false><<<grid, NT, 0, s>>>(a);
-    }
-  })
+static void launch_row_quant(const RowQuantArgs& a, const RowGeom& g, cudaStream_t s) {
+  const bool plain = !(a.row || a.col || a.bias || a.gelu);
+  dispatch_geom(g, [&](auto tpr, auto it) {
+    constexpr int TPR = decltype(tpr)::value, IT = decltype(it)::value;
+    const int grid = (a.M + kRowThreads / TPR - 1) / (kRowThreads / TPR);
+    if (plain) row_quant_kernel<XT, TPR, IT, true><<<grid, kRowThreads, 0, s>>>(a);
+    else row_quant_kernel<XT, TPR, IT, false><<<grid, kRowThreads, 0, s>>>(a);
+  });
 }
 template <typename XT>
-static void launch_gated(const GatedArgs& a, int tpr, cudaStream_t s) {
-  IFLB200_DISPATCH_TPR(tpr, {
-    constexpr int NT = threads_per_cta<TPR>();
-    const int grid = (a.M + NT / TPR - 1) / (NT / TPR);
-    if (a.iters <= kItersShort) gated_act_quant_kernel<XT, TPR, kItersShort><<<grid, NT, 0, s>>>(a);
-    else if constexpr (TPR <= 512) gated_act_quant_kernel<XT, TPR, kItersLong><<<grid, NT, 0, s>>>(a);
-  })
+static void launch_gated(const GatedArgs& a, const RowGeom& g, cudaStream_t s) {
+  dispatch_geom(g, [&](auto tpr, auto it) {
+    constexpr int TPR = decltype(tpr)::value, IT = decltype(it)::value;
+    const int grid = (a.M + kRowThreads / TPR - 1) / (kRowThreads / TPR);
+    gated_act_quant_kernel<XT, TPR, IT><<<grid, kRowThreads, 0, s>>>(a);
+  });
 }
 template <typename RT>
-static void launch_resnorm(const ResNormArgs& a, int tpr, cudaStream_t s) {
-  IFLB200_DISPATCH_TPR(tpr, {
-    constexpr int NT = threads_per_cta<TPR>();
-    const int grid = (a.M + NT / TPR - 1) / (NT / TPR);
-    if (a.iters <= kItersShort) residual_norm_quant_kernel<RT, TPR, kItersShort><<<grid, NT, 0, s>>>(a);
-    else if constexpr (TPR <= 512) residual_norm_quant_kernel<RT, TPR, kItersLong><<<grid, NT, 0, s>>>(a);
-  })
+static void launch_resnorm(const ResNormArgs& a, const RowGeom& g, cudaStream_t s) {
+  dispatch_geom(g, [&](auto tpr, auto it) {
+    constexpr int TPR = decltype(tpr)::value, IT = decltype(it)::value;
+    const int grid = (a.M + kRowThreads / TPR - 1) / (kRowThreads / TPR);
+    residual_norm_quant_kernel<RT, TPR, IT><<<grid, kRowThreads, 0, s>>>(a);
+  });
 }
 
 }  // namespace iflb200
@@ -830,6 +852,14 @@ static void launch_resnorm(const ResNormArgs& a, int tpr, cudaStream_t s) {
 using namespace iflb200;
 
 #if IFLB200_ROW_PART == 0 || IFLB200_ROW_PART == -1
+extern "C" int iflb200_row_set_group(int threads_per_row) {
+  if (threads_per_row != 0 && (threads_per_row < 32 || threads_per_row > kRowThreads ||
+                               (threads_per_row & (threads_per_row - 1))))
+    return IFLB200_ERR_ARG;
+  iflb200::g_row_tpr_override = threads_per_row;
+  return IFLB200_OK;
+}
+
 extern "C" int iflb200_row_quant(const void* x, int x_dtype, int64_t ld_x, int M, int K,
                                  const float* row, const float* col, const float* bias, int gelu,
                                  void* q, int64_t ld_q, float* qs, void* stream) {
@@ -845,13 +875,12 @@ extern "C" int iflb200_row_quant(const void* x, int x_dtype, int64_t ld_x, int M
   a.q = reinterpret_cast<uint8_t*>(q); a.ld_q = ld_q; a.qs = qs;
   a.vec = aligned16(x) && (ld_x * esize(x_dtype)) % 16 == 0 && aligned8(q) && ld_q % 8 == 0 &&
           (!col || aligned16(col)) && (!bias || aligned16(bias));
-  const RowGeom geom = pick_geom(M, K, !(row || col || bias || gelu));
-  const int tpr = geom.tpr;
+  const RowGeom geom = pick_geom(K);
   a.iters = geom.iters;
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
-  if (x_dtype == IFLB200_BF16) launch_row_quant<__nv_bfloat16>(a, tpr, s);
-  else if (x_dtype == IFLB200_F16) launch_row_quant<__half>(a, tpr, s);
-  else launch_row_quant<float>(a, tpr, s);
+  if (x_dtype == IFLB200_BF16) launch_row_quant<__nv_bfloat16>(a, geom, s);
+  else if (x_dtype == IFLB200_F16) launch_row_quant<__half>(a, geom, s);
+  else launch_row_quant<float>(a, geom, s);
   return (int)cudaGetLastError();
 }
 
@@ -874,13 +903,12 @@ extern "C" int iflb200_gated_act_quant(const void* gu, int gu_dtype, int64_t ld_
   const int es = esize(gu_dtype);
   a.vec = aligned16(gu) && (ld_gu * es) % 16 == 0 && ((int64_t)F * es) % 16 == 0 && aligned8(q) &&
           ld_q % 8 == 0 && (!col || (aligned16(col) && F % 4 == 0));
-  const RowGeom geom = pick_geom(M, F, false);
-  const int tpr = geom.tpr;
+  const RowGeom geom = pick_geom(F);
   a.iters = geom.iters;
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
-  if (gu_dtype == IFLB200_BF16) launch_gated<__nv_bfloat16>(a, tpr, s);
-  else if (gu_dtype == IFLB200_F16) launch_gated<__half>(a, tpr, s);
-  else launch_gated<float>(a, tpr, s);
+  if (gu_dtype == IFLB200_BF16) launch_gated<__nv_bfloat16>(a, geom, s);
+  else if (gu_dtype == IFLB200_F16) launch_gated<__half>(a, geom, s);
+  else launch_gated<float>(a, geom, s);
   return (int)cudaGetLastError();
 }
 
@@ -958,12 +986,11 @@ extern "C" int iflb200_residual_norm_quant(void* res, int res_dtype, int64_t ld_
           (!delta || (aligned16(delta) && (ld_delta * 2) % 16 == 0)) &&
           (!q || (aligned8(q) && ld_q % 8 == 0)) &&
           (!y || (aligned16(y) && (ld_y * esize(y_dtype)) % 16 == 0)) && tables_ok;
-  const RowGeom geom = pick_geom(M, D, false);
-  const int tpr = geom.tpr;
+  const RowGeom geom = pick_geom(D);
   a.iters = geom.iters;
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
-  if (res_dtype == IFLB200_F32) launch_resnorm<float>(a, tpr, s);
-  else launch_resnorm<__nv_bfloat16>(a, tpr, s);
+  if (res_dtype == IFLB200_F32) launch_resnorm<float>(a, geom, s);
+  else launch_resnorm<__nv_bfloat16>(a, geom, s);
   return (int)cudaGetLastError();
 }
 

@@ -37,6 +37,53 @@ struct Chain {
   }
 };
 
+// The same for the eight elements of a chunk at once.  Which operations exist is decided by
+// kernel arguments, the same for every element, so `pending` is uniform: the compiler emits
+// one uniform branch per stage and chunk instead of selects per element.
+struct Chain8 {
+  float v[8];
+  float p[8];
+  bool pending;
+  __device__ __forceinline__ explicit Chain8(const float (&x)[8]) : pending(false) {
+#pragma unroll
+    for (int i = 0; i < 8; ++i) v[i] = x[i];
+  }
+  __device__ __forceinline__ void flush() {
+    if (pending) {
+#pragma unroll
+      for (int i = 0; i < 8; ++i) v[i] = __fmul_rn(v[i], p[i]);
+    }
+  }
+  __device__ __forceinline__ void mul(const float (&f)[8]) {
+    flush();
+#pragma unroll
+    for (int i = 0; i < 8; ++i) p[i] = f[i];
+    pending = true;
+  }
+  __device__ __forceinline__ void mul(float f) {
+    flush();
+#pragma unroll
+    for (int i = 0; i < 8; ++i) p[i] = f;
+    pending = true;
+  }
+  __device__ __forceinline__ void add(const float (&c)[8]) {
+    if (pending) {
+#pragma unroll
+      for (int i = 0; i < 8; ++i) v[i] = __fmaf_rn(v[i], p[i], c[i]);
+      pending = false;
+    } else {
+#pragma unroll
+      for (int i = 0; i < 8; ++i) v[i] = __fadd_rn(v[i], c[i]);
+    }
+  }
+  __device__ __forceinline__ void done(float (&out)[8]) {
+    flush();
+    pending = false;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) out[i] = v[i];
+  }
+};
+
 // gelu_pytorch_tanh as written in the reference: 0.5*v*(1 + (2/(1+exp(-2*inner)) - 1)),
 // inner = 0.79788456*(v + 0.044715*v^3), with exp lowered to ex2.approx and the division to
 // div.full (instinctflash/kernels/norm.py:143-145, instinctflash/kernels/activation.py:35-37).
