@@ -25,62 +25,13 @@ constexpr int kRowThreads = 256;
 constexpr int kMaxWidth = kRowThreads * 8 * 8;  // 16384 columns
 
 // --------------------------------------------------------------------------------------------
-// 8-element loads / stores
+// Chunks of 8 elements.  FAST kernels are launched when every buffer obeys the 16-byte rule and
+// the row width is a multiple of 8: every access is one or two 128-bit instructions and a chunk
+// is either wholly inside the row or wholly outside, so there is no per-element masking.  The
+// other instantiation is fully element-wise (any alignment, any width).
 // --------------------------------------------------------------------------------------------
 template <typename T>
-__device__ __forceinline__ void load8(const T* p, float (&o)[8]);
-template <>
-__device__ __forceinline__ void load8<__nv_bfloat16>(const __nv_bfloat16* p, float (&o)[8]) {
-  const uint4 u = *reinterpret_cast<const uint4*>(p);
-  const uint32_t w[4] = {u.x, u.y, u.z, u.w};
-#pragma unroll
-  for (int i = 0; i < 4; ++i) {
-    o[2 * i] = __uint_as_float(w[i] << 16);
-    o[2 * i + 1] = __uint_as_float(w[i] & 0xFFFF0000u);
-  }
-}
-template <>
-__device__ __forceinline__ void load8<__half>(const __half* p, float (&o)[8]) {
-  const uint4 u = *reinterpret_cast<const uint4*>(p);
-  const uint32_t w[4] = {u.x, u.y, u.z, u.w};
-#pragma unroll
-  for (int i = 0; i < 4; ++i) {
-    const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&w[i]));
-    o[2 * i] = f.x;
-    o[2 * i + 1] = f.y;
-  }
-}
-template <>
-__device__ __forceinline__ void load8<float>(const float* p, float (&o)[8]) {
-  const float4 a = *reinterpret_cast<const float4*>(p);
-  const float4 b = *reinterpret_cast<const float4*>(p + 4);
-  o[0] = a.x; o[1] = a.y; o[2] = a.z; o[3] = a.w;
-  o[4] = b.x; o[5] = b.y; o[6] = b.z; o[7] = b.w;
-}
-
-// Chunk of a row: vector path when the whole chunk is inside the row and the buffers obey the
-// 16-byte rule, element-wise otherwise (zeros beyond the row end).
-template <typename T>
-__device__ __forceinline__ void load_chunk(const T* row_ptr, int c0, int width, bool vec,
-                                           float (&o)[8]) {
-  if (vec && c0 + 8 <= width) {
-    load8<T>(row_ptr + c0, o);
-  } else {
-#pragma unroll
-    for (int i = 0; i < 8; ++i) o[i] = (c0 + i < width) ? to_f32(row_ptr[c0 + i]) : 0.0f;
-  }
-}
-__device__ __forceinline__ void load_chunk_f32(const float* p, int c0, int width, bool vec,
-                                               float (&o)[8]) {
-  load_chunk<float>(p, c0, width, vec, o);
-}
-
-
-// Eight elements as they sit in memory, held in registers until they are needed: every load
-// of a row is issued before the first value is used, so a thread has all its chunks in flight
-// at once (bytes in flight per SM, not arithmetic, bound these kernels).
-template <typename T>
-struct Raw8 {
+struct Raw8 {  // eight elements as they sit in memory
   uint4 u;
 };
 template <>
@@ -113,7 +64,6 @@ __device__ __forceinline__ Raw8<float> raw_load<float>(const float* p) {
   r.b = *reinterpret_cast<const float4*>(p + 4);
   return r;
 }
-// Element-wise gather for rows that break the 16-byte rule or end inside the chunk.
 template <typename T>
 __device__ __forceinline__ Raw8<T> raw_gather(const T* row_ptr, int c0, int width) {
   uint32_t w[4] = {0u, 0u, 0u, 0u};
@@ -135,11 +85,15 @@ __device__ __forceinline__ Raw8<float> raw_gather<float>(const float* row_ptr, i
   r.b = make_float4(f[4], f[5], f[6], f[7]);
   return r;
 }
-template <typename T>
-__device__ __forceinline__ Raw8<T> raw_fetch(const T* row_ptr, int c0, int width, bool vec) {
-  return (vec && c0 + 8 <= width) ? raw_load<T>(row_ptr + c0) : raw_gather<T>(row_ptr, c0, width);
+// All loads of a row are issued through this before the first value is used, so a thread has
+// every chunk in flight at once.  `on`: the chunk belongs to a live row and starts inside it.
+template <bool FAST, typename T>
+__device__ __forceinline__ Raw8<T> fetch(const T* row_ptr, int c0, int width, bool on) {
+  if (!on) return raw_zero<T>();
+  if (FAST) return raw_load<T>(row_ptr + c0);
+  return raw_gather<T>(row_ptr, c0, width);
 }
-__device__ __forceinline__ void raw_unpack(const Raw8<__nv_bfloat16>& r, float (&o)[8]) {
+__device__ __forceinline__ void unpack(const Raw8<__nv_bfloat16>& r, float (&o)[8]) {
   const uint32_t w[4] = {r.u.x, r.u.y, r.u.z, r.u.w};
 #pragma unroll
   for (int i = 0; i < 4; ++i) {
@@ -147,7 +101,7 @@ __device__ __forceinline__ void raw_unpack(const Raw8<__nv_bfloat16>& r, float (
     o[2 * i + 1] = __uint_as_float(w[i] & 0xFFFF0000u);
   }
 }
-__device__ __forceinline__ void raw_unpack(const Raw8<__half>& r, float (&o)[8]) {
+__device__ __forceinline__ void unpack(const Raw8<__half>& r, float (&o)[8]) {
   const uint32_t w[4] = {r.u.x, r.u.y, r.u.z, r.u.w};
 #pragma unroll
   for (int i = 0; i < 4; ++i) {
@@ -156,18 +110,35 @@ __device__ __forceinline__ void raw_unpack(const Raw8<__half>& r, float (&o)[8])
     o[2 * i + 1] = f.y;
   }
 }
-__device__ __forceinline__ void raw_unpack(const Raw8<float>& r, float (&o)[8]) {
+__device__ __forceinline__ void unpack(const Raw8<float>& r, float (&o)[8]) {
   o[0] = r.a.x; o[1] = r.a.y; o[2] = r.a.z; o[3] = r.a.w;
   o[4] = r.b.x; o[5] = r.b.y; o[6] = r.b.z; o[7] = r.b.w;
 }
-
-__device__ __forceinline__ void store_codes8(uint8_t* row_ptr, int c0, int width, bool vec,
-                                             const float (&v)[8], float inv) {
+// float32 vector operand (scales, bias, gates, norm weights) for one chunk.
+template <bool FAST>
+__device__ __forceinline__ void load_f32(const float* p, int c0, int width, float (&o)[8]) {
+  if (FAST) {
+    unpack(raw_load<float>(p + c0), o);
+  } else {
+#pragma unroll
+    for (int i = 0; i < 8; ++i) o[i] = (c0 + i < width) ? p[c0 + i] : 0.0f;
+  }
+}
+// Zero the elements of a chunk that lie beyond the row end (element-wise kernels only).
+template <bool FAST>
+__device__ __forceinline__ void mask_tail(float (&v)[8], int c0, int width) {
+  if (!FAST) {
+#pragma unroll
+    for (int i = 0; i < 8; ++i) v[i] = (c0 + i < width) ? v[i] : 0.0f;
+  }
+}
+template <bool FAST>
+__device__ __forceinline__ void store_codes(uint8_t* row_ptr, int c0, int width, const float (&v)[8], float inv) {
   const uint32_t lo = cvt_e4m3x4(__fmul_rn(v[0], inv), __fmul_rn(v[1], inv), __fmul_rn(v[2], inv),
                                  __fmul_rn(v[3], inv));
   const uint32_t hi = cvt_e4m3x4(__fmul_rn(v[4], inv), __fmul_rn(v[5], inv), __fmul_rn(v[6], inv),
                                  __fmul_rn(v[7], inv));
-  if (vec && c0 + 8 <= width) {
+  if (FAST) {
     *reinterpret_cast<uint2*>(row_ptr + c0) = make_uint2(lo, hi);
   } else {
 #pragma unroll
@@ -175,67 +146,47 @@ __device__ __forceinline__ void store_codes8(uint8_t* row_ptr, int c0, int width
       if (c0 + i < width) row_ptr[c0 + i] = (uint8_t)(((i < 4 ? lo : hi) >> (8 * (i & 3))) & 0xFF);
   }
 }
-
+template <bool FAST>
+__device__ __forceinline__ void store_out(void* base, int dtype, int64_t row_off, int c0, int width,
+                                          const float (&v)[8]) {
+  if (dtype == IFLB200_F32) {
+    float* o = reinterpret_cast<float*>(base) + row_off + c0;
+    if (FAST) {
+      *reinterpret_cast<float4*>(o) = make_float4(v[0], v[1], v[2], v[3]);
+      *reinterpret_cast<float4*>(o + 4) = make_float4(v[4], v[5], v[6], v[7]);
+    } else {
+#pragma unroll
+      for (int i = 0; i < 8; ++i)
+        if (c0 + i < width) o[i] = v[i];
+    }
+    return;
+  }
+  uint32_t w[4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i)
+    w[i] = (dtype == IFLB200_BF16) ? (f32_to_bf16_bits(v[2 * i]) | (f32_to_bf16_bits(v[2 * i + 1]) << 16))
+                                   : (f32_to_f16_bits(v[2 * i]) | (f32_to_f16_bits(v[2 * i + 1]) << 16));
+  uint16_t* o = reinterpret_cast<uint16_t*>(base) + row_off + c0;
+  if (FAST) {
+    *reinterpret_cast<uint4*>(o) = make_uint4(w[0], w[1], w[2], w[3]);
+  } else {
+#pragma unroll
+    for (int i = 0; i < 8; ++i)
+      if (c0 + i < width) o[i] = (uint16_t)(w[i >> 1] >> (16 * (i & 1)));
+  }
+}
 template <typename T>
-__device__ __forceinline__ void store_out8(T* row_ptr, int c0, int width, bool vec,
-                                           const float (&v)[8]);
+__host__ __device__ constexpr int dtype_of();
 template <>
-__device__ __forceinline__ void store_out8<__nv_bfloat16>(__nv_bfloat16* row_ptr, int c0, int width,
-                                                          bool vec, const float (&v)[8]) {
-  if (vec && c0 + 8 <= width) {
-    uint4 u;
-    u.x = f32_to_bf16_bits(v[0]) | (f32_to_bf16_bits(v[1]) << 16);
-    u.y = f32_to_bf16_bits(v[2]) | (f32_to_bf16_bits(v[3]) << 16);
-    u.z = f32_to_bf16_bits(v[4]) | (f32_to_bf16_bits(v[5]) << 16);
-    u.w = f32_to_bf16_bits(v[6]) | (f32_to_bf16_bits(v[7]) << 16);
-    *reinterpret_cast<uint4*>(row_ptr + c0) = u;
-  } else {
-#pragma unroll
-    for (int i = 0; i < 8; ++i)
-      if (c0 + i < width) row_ptr[c0 + i] = __float2bfloat16_rn(v[i]);
-  }
-}
+__host__ __device__ constexpr int dtype_of<float>() { return IFLB200_F32; }
 template <>
-__device__ __forceinline__ void store_out8<__half>(__half* row_ptr, int c0, int width, bool vec,
-                                                   const float (&v)[8]) {
-  if (vec && c0 + 8 <= width) {
-    uint4 u;
-    u.x = f32_to_f16_bits(v[0]) | (f32_to_f16_bits(v[1]) << 16);
-    u.y = f32_to_f16_bits(v[2]) | (f32_to_f16_bits(v[3]) << 16);
-    u.z = f32_to_f16_bits(v[4]) | (f32_to_f16_bits(v[5]) << 16);
-    u.w = f32_to_f16_bits(v[6]) | (f32_to_f16_bits(v[7]) << 16);
-    *reinterpret_cast<uint4*>(row_ptr + c0) = u;
-  } else {
-#pragma unroll
-    for (int i = 0; i < 8; ++i)
-      if (c0 + i < width) row_ptr[c0 + i] = __float2half_rn(v[i]);
-  }
-}
+__host__ __device__ constexpr int dtype_of<__nv_bfloat16>() { return IFLB200_BF16; }
 template <>
-__device__ __forceinline__ void store_out8<float>(float* row_ptr, int c0, int width, bool vec,
-                                                  const float (&v)[8]) {
-  if (vec && c0 + 8 <= width) {
-    *reinterpret_cast<float4*>(row_ptr + c0) = make_float4(v[0], v[1], v[2], v[3]);
-    *reinterpret_cast<float4*>(row_ptr + c0 + 4) = make_float4(v[4], v[5], v[6], v[7]);
-  } else {
-#pragma unroll
-    for (int i = 0; i < 8; ++i)
-      if (c0 + i < width) row_ptr[c0 + i] = v[i];
-  }
-}
-__device__ __forceinline__ void store_out8_dyn(void* base, int dtype, int64_t row_off, int c0,
-                                               int width, bool vec, const float (&v)[8]) {
-  if (dtype == IFLB200_BF16)
-    store_out8<__nv_bfloat16>(reinterpret_cast<__nv_bfloat16*>(base) + row_off, c0, width, vec, v);
-  else if (dtype == IFLB200_F16)
-    store_out8<__half>(reinterpret_cast<__half*>(base) + row_off, c0, width, vec, v);
-  else
-    store_out8<float>(reinterpret_cast<float*>(base) + row_off, c0, width, vec, v);
-}
+__host__ __device__ constexpr int dtype_of<__half>() { return IFLB200_F16; }
 
 // --------------------------------------------------------------------------------------------
 // Reductions over the TPR threads of one row (TPR a multiple of 32; rows never share a warp).
-// `slot` is a per-reduction shared array of NT/32 floats.
+// `slot` is a per-reduction shared array of kRowThreads/32 floats.
 // --------------------------------------------------------------------------------------------
 template <int TPR, bool IS_MAX>
 __device__ __forceinline__ float row_reduce(float v, float* slot) {
@@ -279,36 +230,33 @@ struct RowQuantArgs {
   uint8_t* q;
   int64_t ld_q;
   float* qs;
-  int vec;
 };
 
 // PLAIN: no prologue.  The row then stays in registers as loaded (4 registers per 8 elements)
 // and is widened twice, once for the maximum and once for the cast, which keeps enough CTAs
 // resident to cover the HBM latency.
-template <typename XT, int TPR, int IT, bool PLAIN>
+template <typename XT, int TPR, int IT, bool PLAIN, bool FAST>
 __global__ void __launch_bounds__(kRowThreads, PLAIN ? (IT <= 2 ? 4 : 3) : row_min_blocks<IT>())
 row_quant_kernel(const RowQuantArgs a) {
-  constexpr int NT = kRowThreads;
-  __shared__ float red[NT / 32];
+  __shared__ float red[kRowThreads / 32];
   const int t = threadIdx.x % TPR;
-  const int m = blockIdx.x * (NT / TPR) + threadIdx.x / TPR;
+  const int m = blockIdx.x * (kRowThreads / TPR) + threadIdx.x / TPR;
   const bool live = m < a.M;
   const XT* xr = reinterpret_cast<const XT*>(a.x) + (live ? (int64_t)m * a.ld_x : 0);
-  const bool vec = a.vec != 0;
   const float rs = (live && a.row) ? a.row[m] : 1.0f;
 
   Raw8<XT> raw[IT];
 #pragma unroll
   for (int it = 0; it < IT; ++it) {
     const int c0 = (it * TPR + t) * 8;
-    raw[it] = (it < a.iters && live && c0 < a.K) ? raw_fetch<XT>(xr, c0, a.K, vec) : raw_zero<XT>();
+    raw[it] = fetch<FAST, XT>(xr, c0, a.K, it < a.iters && live && c0 < a.K);
   }
   float amax = 0.0f;
   if (PLAIN) {
 #pragma unroll
     for (int it = 0; it < IT; ++it) {
       float w[8];
-      raw_unpack(raw[it], w);
+      unpack(raw[it], w);
 #pragma unroll
       for (int i = 0; i < 8; ++i) amax = max_f32(amax, fabsf(w[i]));
     }
@@ -323,8 +271,8 @@ row_quant_kernel(const RowQuantArgs a) {
       const int c0 = (it * TPR + t) * 8;
       if (it < a.iters && c0 < a.K) {
         float w[8];
-        raw_unpack(raw[it], w);
-        store_codes8(qr, c0, a.K, vec, w, inv);
+        unpack(raw[it], w);
+        store_codes<FAST>(qr, c0, a.K, w, inv);
       }
     }
     return;
@@ -333,11 +281,11 @@ row_quant_kernel(const RowQuantArgs a) {
 #pragma unroll
   for (int it = 0; it < IT; ++it) {
     const int c0 = (it * TPR + t) * 8;
-    raw_unpack(raw[it], v[it]);
+    unpack(raw[it], v[it]);
     if (it < a.iters && live && c0 < a.K) {
       float cs[8], bs[8];
-      if (a.col) load_chunk_f32(a.col, c0, a.K, vec, cs);
-      if (a.bias) load_chunk_f32(a.bias, c0, a.K, vec, bs);
+      if (a.col) load_f32<FAST>(a.col, c0, a.K, cs);
+      if (a.bias) load_f32<FAST>(a.bias, c0, a.K, bs);
       Chain8 ch(v[it]);
       if (a.row) ch.mul(rs);
       if (a.col) ch.mul(cs);
@@ -347,11 +295,10 @@ row_quant_kernel(const RowQuantArgs a) {
 #pragma unroll
         for (int i = 0; i < 8; ++i) v[it][i] = gelu_tanh_ref(v[it][i]);
       }
+      mask_tail<FAST>(v[it], c0, a.K);
 #pragma unroll
-      for (int i = 0; i < 8; ++i) v[it][i] = (c0 + i < a.K) ? v[it][i] : 0.0f;
+      for (int i = 0; i < 8; ++i) amax = max_f32(amax, fabsf(v[it][i]));
     }
-#pragma unroll
-    for (int i = 0; i < 8; ++i) amax = max_f32(amax, fabsf(v[it][i]));
   }
   amax = row_reduce<TPR, true>(amax, red);
   float scale, inv;
@@ -362,12 +309,13 @@ row_quant_kernel(const RowQuantArgs a) {
 #pragma unroll
   for (int it = 0; it < IT; ++it) {
     const int c0 = (it * TPR + t) * 8;
-    if (it < a.iters && c0 < a.K) store_codes8(qr, c0, a.K, vec, v[it], inv);
+    if (it < a.iters && c0 < a.K) store_codes<FAST>(qr, c0, a.K, v[it], inv);
   }
 }
 
 // --------------------------------------------------------------------------------------------
-// gated_act_quant: 4F (bf16 g,u in) + F (codes out) + 4 bytes per row.
+// gated_act_quant: 4F (bf16 g,u in) + F (codes out) + 4 bytes per row.  Bound by instruction
+// issue, not by HBM: ~40 instructions per element (the reference's ex2.approx / div.full chains).
 // --------------------------------------------------------------------------------------------
 struct GatedArgs {
   const void* gu;
@@ -379,20 +327,17 @@ struct GatedArgs {
   uint8_t* q;
   int64_t ld_q;
   float* qs;
-  int vec;
 };
 
-template <typename XT, int TPR, int IT>
+template <typename XT, int TPR, int IT, bool FAST>
 __global__ void __launch_bounds__(kRowThreads, row_min_blocks<IT>())
 gated_act_quant_kernel(const GatedArgs a) {
-  constexpr int NT = kRowThreads;
-  __shared__ float red[NT / 32];
+  __shared__ float red[kRowThreads / 32];
   const int t = threadIdx.x % TPR;
-  const int m = blockIdx.x * (NT / TPR) + threadIdx.x / TPR;
+  const int m = blockIdx.x * (kRowThreads / TPR) + threadIdx.x / TPR;
   const bool live = m < a.M;
   const XT* gr = reinterpret_cast<const XT*>(a.gu) + (live ? (int64_t)m * a.ld_gu : 0);
   const XT* ur = gr + a.F;
-  const bool vec = a.vec != 0;
   const float rs = (live && a.row) ? a.row[m] : 1.0f;
 
   Raw8<XT> rg[IT], ru[IT];
@@ -400,47 +345,47 @@ gated_act_quant_kernel(const GatedArgs a) {
   for (int it = 0; it < IT; ++it) {
     const int c0 = (it * TPR + t) * 8;
     const bool on = it < a.iters && live && c0 < a.F;
-    rg[it] = on ? raw_fetch<XT>(gr, c0, a.F, vec) : raw_zero<XT>();
-    ru[it] = on ? raw_fetch<XT>(ur, c0, a.F, vec) : raw_zero<XT>();
+    rg[it] = fetch<FAST, XT>(gr, c0, a.F, on);
+    ru[it] = fetch<FAST, XT>(ur, c0, a.F, on);
   }
   float h[IT][8];
   float amax = 0.0f;
 #pragma unroll
   for (int it = 0; it < IT; ++it) {
     const int c0 = (it * TPR + t) * 8;
-    float g[8], u[8], cg[8], cu[8];
-    raw_unpack(rg[it], g);
-    raw_unpack(ru[it], u);
-    const bool on = it < a.iters && live && c0 < a.F;
-    if (on && a.col) {
-      load_chunk_f32(a.col, c0, a.F, vec, cg);
-      load_chunk_f32(a.col + a.F, c0, a.F, vec, cu);
-    }
-    if (a.row) {
 #pragma unroll
-      for (int i = 0; i < 8; ++i) {
-        g[i] = __fmul_rn(g[i], rs);
-        u[i] = __fmul_rn(u[i], rs);
+    for (int i = 0; i < 8; ++i) h[it][i] = 0.0f;
+    if (it < a.iters && live && c0 < a.F) {
+      float g[8], u[8];
+      unpack(rg[it], g);
+      unpack(ru[it], u);
+      if (a.row) {
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          g[i] = __fmul_rn(g[i], rs);
+          u[i] = __fmul_rn(u[i], rs);
+        }
       }
-    }
-    if (on && a.col) {
+      if (a.col) {
+        float cg[8], cu[8];
+        load_f32<FAST>(a.col, c0, a.F, cg);
+        load_f32<FAST>(a.col + a.F, c0, a.F, cu);
 #pragma unroll
-      for (int i = 0; i < 8; ++i) {
-        g[i] = __fmul_rn(g[i], cg[i]);
-        u[i] = __fmul_rn(u[i], cu[i]);
+        for (int i = 0; i < 8; ++i) {
+          g[i] = __fmul_rn(g[i], cg[i]);
+          u[i] = __fmul_rn(u[i], cu[i]);
+        }
       }
-    }
-    if (a.act == IFLB200_ACT_GELU_TANH) {
+      if (a.act == IFLB200_ACT_GELU_TANH) {
 #pragma unroll
-      for (int i = 0; i < 8; ++i) h[it][i] = __fmul_rn(u[i], gelu_tanh_ref(g[i]));
-    } else {
+        for (int i = 0; i < 8; ++i) h[it][i] = __fmul_rn(u[i], gelu_tanh_ref(g[i]));
+      } else {
 #pragma unroll
-      for (int i = 0; i < 8; ++i) h[it][i] = __fmul_rn(u[i], silu_ref(g[i]));
-    }
+        for (int i = 0; i < 8; ++i) h[it][i] = __fmul_rn(u[i], silu_ref(g[i]));
+      }
+      mask_tail<FAST>(h[it], c0, a.F);
 #pragma unroll
-    for (int i = 0; i < 8; ++i) {
-      h[it][i] = (on && c0 + i < a.F) ? h[it][i] : 0.0f;
-      amax = max_f32(amax, fabsf(h[it][i]));
+      for (int i = 0; i < 8; ++i) amax = max_f32(amax, fabsf(h[it][i]));
     }
   }
   amax = row_reduce<TPR, true>(amax, red);
@@ -452,12 +397,12 @@ gated_act_quant_kernel(const GatedArgs a) {
 #pragma unroll
   for (int it = 0; it < IT; ++it) {
     const int c0 = (it * TPR + t) * 8;
-    if (it < a.iters && c0 < a.F) store_codes8(qr, c0, a.F, vec, h[it], inv);
+    if (it < a.iters && c0 < a.F) store_codes<FAST>(qr, c0, a.F, h[it], inv);
   }
 }
 
 // --------------------------------------------------------------------------------------------
-// dequant_rows: 2D in + out bytes per row; flat.
+// dequant_rows: 2D in + out bytes per row; flat, one chunk per thread.
 // --------------------------------------------------------------------------------------------
 struct DequantArgs {
   const void* x;
@@ -469,31 +414,29 @@ struct DequantArgs {
   void* y;
   int y_dtype;
   int64_t ld_y;
-  int vec;
 };
 
-template <typename XT>
+template <typename XT, bool FAST>
 __global__ void __launch_bounds__(256) dequant_rows_kernel(const DequantArgs a) {
   const int m = blockIdx.y;
   const int c0 = (blockIdx.x * 256 + threadIdx.x) * 8;
   if (c0 >= a.D) return;
-  const bool vec = a.vec != 0;
   const XT* xr = reinterpret_cast<const XT*>(a.x) + (int64_t)m * a.ld_x;
   float v[8], cs[8], bs[8];
-  load_chunk<XT>(xr, c0, a.D, vec, v);
-  if (a.col) load_chunk_f32(a.col, c0, a.D, vec, cs);
-  if (a.bias) load_chunk_f32(a.bias, c0, a.D, vec, bs);
+  unpack(fetch<FAST, XT>(xr, c0, a.D, true), v);
+  if (a.col) load_f32<FAST>(a.col, c0, a.D, cs);
+  if (a.bias) load_f32<FAST>(a.bias, c0, a.D, bs);
   const float rs = a.row ? a.row[m] : 1.0f;
   Chain8 ch(v);
   if (a.row) ch.mul(rs);
   if (a.col) ch.mul(cs);
   if (a.bias) ch.add(bs);
   ch.done(v);
-  store_out8_dyn(a.y, a.y_dtype, (int64_t)m * a.ld_y, c0, a.D, vec, v);
+  store_out<FAST>(a.y, a.y_dtype, (int64_t)m * a.ld_y, c0, a.D, v);
 }
 
 // --------------------------------------------------------------------------------------------
-// residual_norm_quant
+// residual_norm_quant: (f32 residual) 2D delta + 4D res in, 4D res + D codes out, + 4 bytes.
 // --------------------------------------------------------------------------------------------
 struct ResNormArgs {
   void* res;
@@ -519,7 +462,6 @@ struct ResNormArgs {
   void* y;
   int y_dtype;
   int64_t ld_y;
-  int vec;
 };
 
 template <typename RT>
@@ -531,15 +473,13 @@ __device__ __forceinline__ float round_through<__nv_bfloat16>(float x) {
   return __bfloat162float(__float2bfloat16_rn(x));
 }
 
-template <typename RT, int TPR, int IT>
+template <typename RT, int TPR, int IT, bool FAST>
 __global__ void __launch_bounds__(kRowThreads, row_min_blocks<IT>())
 residual_norm_quant_kernel(const ResNormArgs a) {
-  constexpr int NT = kRowThreads;
-  __shared__ float red[3][NT / 32];
+  __shared__ float red[3][kRowThreads / 32];
   const int t = threadIdx.x % TPR;
-  const int m = blockIdx.x * (NT / TPR) + threadIdx.x / TPR;
+  const int m = blockIdx.x * (kRowThreads / TPR) + threadIdx.x / TPR;
   const bool live = m < a.M;
-  const bool vec = a.vec != 0;
   RT* rr = reinterpret_cast<RT*>(a.res) + (live ? (int64_t)m * a.ld_res : 0);
   const __nv_bfloat16* dr = a.delta ? a.delta + (live ? (int64_t)m * a.ld_delta : 0) : nullptr;
   const int64_t mofs = (live && a.mod_index) ? (int64_t)a.mod_index[m] * a.D : 0;
@@ -552,22 +492,22 @@ residual_norm_quant_kernel(const ResNormArgs a) {
   for (int it = 0; it < IT; ++it) {
     const int c0 = (it * TPR + t) * 8;
     const bool on = it < a.iters && live && c0 < a.D;
-    rres[it] = on ? raw_fetch<RT>(rr, c0, a.D, vec) : raw_zero<RT>();
-    rdel[it] = (on && dr) ? raw_fetch<__nv_bfloat16>(dr, c0, a.D, vec) : raw_zero<__nv_bfloat16>();
+    rres[it] = fetch<FAST, RT>(rr, c0, a.D, on);
+    rdel[it] = fetch<FAST, __nv_bfloat16>(dr, c0, a.D, on && dr != nullptr);
   }
   float x[IT][8];
   float sum = 0.0f, sumsq = 0.0f;
 #pragma unroll
   for (int it = 0; it < IT; ++it) {
     const int c0 = (it * TPR + t) * 8;
-    raw_unpack(rres[it], x[it]);
+    unpack(rres[it], x[it]);
     if (it < a.iters && live && c0 < a.D) {
       if (dr) {
         float d[8], cs[8], bs[8], gs[8];
-        raw_unpack(rdel[it], d);
-        if (a.dcol) load_chunk_f32(a.dcol, c0, a.D, vec, cs);
-        if (a.bias) load_chunk_f32(a.bias, c0, a.D, vec, bs);
-        if (a.gate) load_chunk_f32(a.gate + mofs, c0, a.D, vec, gs);
+        unpack(rdel[it], d);
+        if (a.dcol) load_f32<FAST>(a.dcol, c0, a.D, cs);
+        if (a.bias) load_f32<FAST>(a.bias, c0, a.D, bs);
+        if (a.gate) load_f32<FAST>(a.gate + mofs, c0, a.D, gs);
         Chain8 ch(d);
         if (a.drow) ch.mul(drs);
         if (a.dcol) ch.mul(cs);
@@ -579,9 +519,8 @@ residual_norm_quant_kernel(const ResNormArgs a) {
 #pragma unroll
           for (int i = 0; i < 8; ++i) x[it][i] = round_through<RT>(x[it][i]);
         }
-#pragma unroll
-        for (int i = 0; i < 8; ++i) x[it][i] = (c0 + i < a.D) ? x[it][i] : 0.0f;
-        if (a.write_res) store_out8<RT>(rr, c0, a.D, vec, x[it]);
+        mask_tail<FAST>(x[it], c0, a.D);
+        if (a.write_res) store_out<FAST>(a.res, dtype_of<RT>(), (int64_t)m * a.ld_res, c0, a.D, x[it]);
       }
 #pragma unroll
       for (int i = 0; i < 8; ++i) {
@@ -593,18 +532,18 @@ residual_norm_quant_kernel(const ResNormArgs a) {
   if (a.q == nullptr && a.y == nullptr) return;  // residual update only (uniform across the CTA)
 
   float rstd;
-  float mean = 0.0f;
   if (a.layernorm) {
-    mean = div_full(row_reduce<TPR, false>(sum, red[0]), fD);
+    const float mean = div_full(row_reduce<TPR, false>(sum, red[0]), fD);
     float sq = 0.0f;
 #pragma unroll
     for (int it = 0; it < IT; ++it) {
       const int c0 = (it * TPR + t) * 8;
+      if (it < a.iters && live && c0 < a.D) {
 #pragma unroll
-      for (int i = 0; i < 8; ++i) {
-        const bool ok = it < a.iters && live && (c0 + i < a.D);
-        x[it][i] = ok ? __fsub_rn(x[it][i], mean) : 0.0f;
-        sq = __fmaf_rn(x[it][i], x[it][i], sq);
+        for (int i = 0; i < 8; ++i) x[it][i] = __fsub_rn(x[it][i], mean);
+        mask_tail<FAST>(x[it], c0, a.D);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) sq = __fmaf_rn(x[it][i], x[it][i], sq);
       }
     }
     const float var = div_full(row_reduce<TPR, false>(sq, red[1]), fD);
@@ -620,11 +559,11 @@ residual_norm_quant_kernel(const ResNormArgs a) {
     const int c0 = (it * TPR + t) * 8;
     if (it < a.iters && live && c0 < a.D) {
       float ws[8], bs[8], ms[8], mh[8];
-      if (a.weight) load_chunk_f32(a.weight, c0, a.D, vec, ws);
-      if (a.beta) load_chunk_f32(a.beta, c0, a.D, vec, bs);
+      if (a.weight) load_f32<FAST>(a.weight, c0, a.D, ws);
+      if (a.beta) load_f32<FAST>(a.beta, c0, a.D, bs);
       if (a.mod_scale) {
-        load_chunk_f32(a.mod_scale + mofs, c0, a.D, vec, ms);
-        load_chunk_f32(a.mod_shift + mofs, c0, a.D, vec, mh);
+        load_f32<FAST>(a.mod_scale + mofs, c0, a.D, ms);
+        load_f32<FAST>(a.mod_shift + mofs, c0, a.D, mh);
       }
       Chain8 ch(x[it]);
       ch.mul(rstd);
@@ -637,12 +576,10 @@ residual_norm_quant_kernel(const ResNormArgs a) {
         ch.add(mh);
       }
       ch.done(x[it]);
+      mask_tail<FAST>(x[it], c0, a.D);
 #pragma unroll
-      for (int i = 0; i < 8; ++i) {
-        x[it][i] = (c0 + i < a.D) ? x[it][i] : 0.0f;
-        amax = max_f32(amax, fabsf(x[it][i]));
-      }
-      if (a.y) store_out8_dyn(a.y, a.y_dtype, (int64_t)m * a.ld_y, c0, a.D, vec, x[it]);
+      for (int i = 0; i < 8; ++i) amax = max_f32(amax, fabsf(x[it][i]));
+      if (a.y) store_out<FAST>(a.y, a.y_dtype, (int64_t)m * a.ld_y, c0, a.D, x[it]);
     }
   }
   if (a.q == nullptr) return;
@@ -655,7 +592,7 @@ residual_norm_quant_kernel(const ResNormArgs a) {
 #pragma unroll
   for (int it = 0; it < IT; ++it) {
     const int c0 = (it * TPR + t) * 8;
-    if (it < a.iters && c0 < a.D) store_codes8(qr, c0, a.D, vec, x[it], inv);
+    if (it < a.iters && c0 < a.D) store_codes<FAST>(qr, c0, a.D, x[it], inv);
   }
 }
 
@@ -820,30 +757,61 @@ static void dispatch_geom(const RowGeom& g, F&& launch) {
   else launch(IntTag<256>{}, IntTag<8>{});
 }
 
+// The element-wise (any alignment) kernels exist in one geometry only: a full-CTA group with up
+// to 8 chunks per thread.
+static RowGeom slow_geom(int width) {
+  RowGeom g;
+  g.tpr = kRowThreads;
+  g.iters = ((width + 7) / 8 + kRowThreads - 1) / kRowThreads;
+  return g;
+}
+
 template <typename XT>
-static void launch_row_quant(const RowQuantArgs& a, const RowGeom& g, cudaStream_t s) {
+static void launch_row_quant(RowQuantArgs a, bool fast, cudaStream_t s) {
   const bool plain = !(a.row || a.col || a.bias || a.gelu);
+  if (!fast) {
+    a.iters = slow_geom(a.K).iters;
+    if (plain) row_quant_kernel<XT, kRowThreads, 8, true, false><<<a.M, kRowThreads, 0, s>>>(a);
+    else row_quant_kernel<XT, kRowThreads, 8, false, false><<<a.M, kRowThreads, 0, s>>>(a);
+    return;
+  }
+  const RowGeom g = pick_geom(a.K);
+  a.iters = g.iters;
   dispatch_geom(g, [&](auto tpr, auto it) {
     constexpr int TPR = decltype(tpr)::value, IT = decltype(it)::value;
     const int grid = (a.M + kRowThreads / TPR - 1) / (kRowThreads / TPR);
-    if (plain) row_quant_kernel<XT, TPR, IT, true><<<grid, kRowThreads, 0, s>>>(a);
-    else row_quant_kernel<XT, TPR, IT, false><<<grid, kRowThreads, 0, s>>>(a);
+    if (plain) row_quant_kernel<XT, TPR, IT, true, true><<<grid, kRowThreads, 0, s>>>(a);
+    else row_quant_kernel<XT, TPR, IT, false, true><<<grid, kRowThreads, 0, s>>>(a);
   });
 }
 template <typename XT>
-static void launch_gated(const GatedArgs& a, const RowGeom& g, cudaStream_t s) {
+static void launch_gated(GatedArgs a, bool fast, cudaStream_t s) {
+  if (!fast) {
+    a.iters = slow_geom(a.F).iters;
+    gated_act_quant_kernel<XT, kRowThreads, 8, false><<<a.M, kRowThreads, 0, s>>>(a);
+    return;
+  }
+  const RowGeom g = pick_geom(a.F);
+  a.iters = g.iters;
   dispatch_geom(g, [&](auto tpr, auto it) {
     constexpr int TPR = decltype(tpr)::value, IT = decltype(it)::value;
     const int grid = (a.M + kRowThreads / TPR - 1) / (kRowThreads / TPR);
-    gated_act_quant_kernel<XT, TPR, IT><<<grid, kRowThreads, 0, s>>>(a);
+    gated_act_quant_kernel<XT, TPR, IT, true><<<grid, kRowThreads, 0, s>>>(a);
   });
 }
 template <typename RT>
-static void launch_resnorm(const ResNormArgs& a, const RowGeom& g, cudaStream_t s) {
+static void launch_resnorm(ResNormArgs a, bool fast, cudaStream_t s) {
+  if (!fast) {
+    a.iters = slow_geom(a.D).iters;
+    residual_norm_quant_kernel<RT, kRowThreads, 8, false><<<a.M, kRowThreads, 0, s>>>(a);
+    return;
+  }
+  const RowGeom g = pick_geom(a.D);
+  a.iters = g.iters;
   dispatch_geom(g, [&](auto tpr, auto it) {
     constexpr int TPR = decltype(tpr)::value, IT = decltype(it)::value;
     const int grid = (a.M + kRowThreads / TPR - 1) / (kRowThreads / TPR);
-    residual_norm_quant_kernel<RT, TPR, IT><<<grid, kRowThreads, 0, s>>>(a);
+    residual_norm_quant_kernel<RT, TPR, IT, true><<<grid, kRowThreads, 0, s>>>(a);
   });
 }
 
@@ -873,14 +841,12 @@ extern "C" int iflb200_row_quant(const void* x, int x_dtype, int64_t ld_x, int M
   a.x = x; a.ld_x = ld_x; a.M = M; a.K = K;
   a.row = row; a.col = col; a.bias = bias; a.gelu = gelu;
   a.q = reinterpret_cast<uint8_t*>(q); a.ld_q = ld_q; a.qs = qs;
-  a.vec = aligned16(x) && (ld_x * esize(x_dtype)) % 16 == 0 && aligned8(q) && ld_q % 8 == 0 &&
-          (!col || aligned16(col)) && (!bias || aligned16(bias));
-  const RowGeom geom = pick_geom(K);
-  a.iters = geom.iters;
+  const bool fast = K % 8 == 0 && aligned16(x) && (ld_x * esize(x_dtype)) % 16 == 0 && aligned8(q) &&
+                    ld_q % 8 == 0 && (!col || aligned16(col)) && (!bias || aligned16(bias));
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
-  if (x_dtype == IFLB200_BF16) launch_row_quant<__nv_bfloat16>(a, geom, s);
-  else if (x_dtype == IFLB200_F16) launch_row_quant<__half>(a, geom, s);
-  else launch_row_quant<float>(a, geom, s);
+  if (x_dtype == IFLB200_BF16) launch_row_quant<__nv_bfloat16>(a, fast, s);
+  else if (x_dtype == IFLB200_F16) launch_row_quant<__half>(a, fast, s);
+  else launch_row_quant<float>(a, fast, s);
   return (int)cudaGetLastError();
 }
 
@@ -901,14 +867,12 @@ extern "C" int iflb200_gated_act_quant(const void* gu, int gu_dtype, int64_t ld_
   a.gu = gu; a.ld_gu = ld_gu; a.M = M; a.F = F; a.row = row; a.col = col; a.act = act;
   a.q = reinterpret_cast<uint8_t*>(q); a.ld_q = ld_q; a.qs = qs;
   const int es = esize(gu_dtype);
-  a.vec = aligned16(gu) && (ld_gu * es) % 16 == 0 && ((int64_t)F * es) % 16 == 0 && aligned8(q) &&
-          ld_q % 8 == 0 && (!col || (aligned16(col) && F % 4 == 0));
-  const RowGeom geom = pick_geom(F);
-  a.iters = geom.iters;
+  const bool fast = F % 8 == 0 && aligned16(gu) && (ld_gu * es) % 16 == 0 && aligned8(q) && ld_q % 8 == 0 &&
+                    (!col || aligned16(col));
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
-  if (gu_dtype == IFLB200_BF16) launch_gated<__nv_bfloat16>(a, geom, s);
-  else if (gu_dtype == IFLB200_F16) launch_gated<__half>(a, geom, s);
-  else launch_gated<float>(a, geom, s);
+  if (gu_dtype == IFLB200_BF16) launch_gated<__nv_bfloat16>(a, fast, s);
+  else if (gu_dtype == IFLB200_F16) launch_gated<__half>(a, fast, s);
+  else launch_gated<float>(a, fast, s);
   return (int)cudaGetLastError();
 }
 
@@ -927,8 +891,8 @@ extern "C" int iflb200_dequant_rows(const void* x, int x_dtype, int64_t ld_x, in
   DequantArgs a;
   a.x = x; a.ld_x = ld_x; a.M = M; a.D = D; a.row = row; a.col = col; a.bias = bias;
   a.y = y; a.y_dtype = y_dtype; a.ld_y = ld_y;
-  a.vec = aligned16(x) && (ld_x * esize(x_dtype)) % 16 == 0 && aligned16(y) &&
-          (ld_y * esize(y_dtype)) % 16 == 0 && (!col || aligned16(col)) && (!bias || aligned16(bias));
+  const bool fast = D % 8 == 0 && aligned16(x) && (ld_x * esize(x_dtype)) % 16 == 0 && aligned16(y) &&
+                    (ld_y * esize(y_dtype)) % 16 == 0 && (!col || aligned16(col)) && (!bias || aligned16(bias));
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
   const int chunks = (D + 2047) / 2048;
   // blockIdx.y carries the row: split very tall inputs into slabs of 65535 rows.
@@ -940,9 +904,15 @@ extern "C" int iflb200_dequant_rows(const void* x, int x_dtype, int64_t ld_x, in
     b.y = reinterpret_cast<char*>(y) + (int64_t)m0 * ld_y * esize(y_dtype);
     b.row = row ? row + m0 : nullptr;
     const dim3 grid(chunks, rows);
-    if (x_dtype == IFLB200_BF16) dequant_rows_kernel<__nv_bfloat16><<<grid, 256, 0, s>>>(b);
-    else if (x_dtype == IFLB200_F16) dequant_rows_kernel<__half><<<grid, 256, 0, s>>>(b);
-    else dequant_rows_kernel<float><<<grid, 256, 0, s>>>(b);
+    if (fast) {
+      if (x_dtype == IFLB200_BF16) dequant_rows_kernel<__nv_bfloat16, true><<<grid, 256, 0, s>>>(b);
+      else if (x_dtype == IFLB200_F16) dequant_rows_kernel<__half, true><<<grid, 256, 0, s>>>(b);
+      else dequant_rows_kernel<float, true><<<grid, 256, 0, s>>>(b);
+    } else {
+      if (x_dtype == IFLB200_BF16) dequant_rows_kernel<__nv_bfloat16, false><<<grid, 256, 0, s>>>(b);
+      else if (x_dtype == IFLB200_F16) dequant_rows_kernel<__half, false><<<grid, 256, 0, s>>>(b);
+      else dequant_rows_kernel<float, false><<<grid, 256, 0, s>>>(b);
+    }
   }
   return (int)cudaGetLastError();
 }
@@ -981,16 +951,14 @@ extern "C" int iflb200_residual_norm_quant(void* res, int res_dtype, int64_t ld_
   const bool tables_ok = (!a.dcol || aligned16(a.dcol)) && (!a.bias || aligned16(a.bias)) &&
                          (!a.gate || aligned16(a.gate)) && (!weight || aligned16(weight)) &&
                          (!beta || aligned16(beta)) && (!mod_scale || aligned16(mod_scale)) &&
-                         (!mod_shift || aligned16(mod_shift)) && (!mod_index || D % 4 == 0);
-  a.vec = aligned16(res) && (ld_res * esize(res_dtype)) % 16 == 0 &&
-          (!delta || (aligned16(delta) && (ld_delta * 2) % 16 == 0)) &&
-          (!q || (aligned8(q) && ld_q % 8 == 0)) &&
-          (!y || (aligned16(y) && (ld_y * esize(y_dtype)) % 16 == 0)) && tables_ok;
-  const RowGeom geom = pick_geom(D);
-  a.iters = geom.iters;
+                         (!mod_shift || aligned16(mod_shift));
+  const bool fast = D % 8 == 0 && aligned16(res) && (ld_res * esize(res_dtype)) % 16 == 0 &&
+                    (!delta || (aligned16(delta) && (ld_delta * 2) % 16 == 0)) &&
+                    (!q || (aligned8(q) && ld_q % 8 == 0)) &&
+                    (!y || (aligned16(y) && (ld_y * esize(y_dtype)) % 16 == 0)) && tables_ok;
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
-  if (res_dtype == IFLB200_F32) launch_resnorm<float>(a, geom, s);
-  else launch_resnorm<__nv_bfloat16>(a, geom, s);
+  if (res_dtype == IFLB200_F32) launch_resnorm<float>(a, fast, s);
+  else launch_resnorm<__nv_bfloat16>(a, fast, s);
   return (int)cudaGetLastError();
 }
 
