@@ -177,6 +177,77 @@ def workload_name(spec):
     return names.get(spec.name, spec.name)
 
 
+def run_tensor_parallel(args, spec, dev, dist, rank, world):
+    """Strong scaling of one Wan-shape stack over `world` GPUs (total work fixed)."""
+    from instinctflash_b200.stack import make_inputs, make_weights
+    from instinctflash_b200.tp import Comm, WanTPStack
+    if dist is None:
+        import torch.distributed as dist
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        os.environ.setdefault("MASTER_PORT", "29555")
+        dist.init_process_group("nccl", rank=0, world_size=1, device_id=dev)
+    torch.manual_seed(1234)   # identical full weights on every rank, sharded afterwards
+    weights = make_weights(spec, dev)
+    stack = WanTPStack(spec, weights, dev, Comm())
+    del weights
+    torch.cuda.empty_cache()
+    x, attn = make_inputs(spec, dev)
+    stack.load(x, attn)
+    stream = torch.cuda.current_stream(dev)
+    graph = None
+    try:
+        side = torch.cuda.Stream(dev)
+        side.wait_stream(stream)
+        with torch.cuda.stream(side):
+            stack.forward()
+        stream.wait_stream(side)
+        torch.cuda.synchronize(dev)
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            stack.forward()
+    except Exception:
+        graph = None
+
+    def step():
+        if graph is not None:
+            graph.replay()
+        else:
+            stack.forward()
+
+    for _ in range(args.warmup):
+        step()
+    dist.barrier()
+    torch.cuda.synchronize(dev)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    with ClockSampler(dev.index) as clocks:
+        clocks.begin()
+        e0.record(stream)
+        for _ in range(args.steps):
+            step()
+        e1.record(stream)
+        dist.barrier()
+        torch.cuda.synchronize(dev)
+        clocks.end()
+    t = torch.tensor([e0.elapsed_time(e1)], device=dev, dtype=torch.float64)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms = float(t[0])
+    if rank == 0:
+        p = world
+        D, M = spec.hidden, spec.M
+        n_row = 3 if spec.cross else 2
+        comm_bytes = spec.layers * n_row * ((4 * M * D) + (M * D + 4 * M) + 4 * M) * (p - 1) / p
+        line = {"metric": METRIC, "value": spec.flops() * args.steps / (ms * 1e-3) / 1e12, "unit": UNIT, "n_gpus": world,
+                "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms / args.steps, "higher_is_better": True,
+                "scaling": "strong", "vs_baseline": None, "dtype": "e4m3 x e4m3 -> f32", "data": "synthetic",
+                "config": {"workload": workload_name(spec), "parallelism": f"tp{world} (column-split qkv/cross-q/ff1, "
+                           "row-split o/cross-o/ff2, NCCL all-reduce-max + fp32 reduce-scatter + all-gather)",
+                           "cuda_graph": graph is not None,
+                           "nvlink_bytes_per_rank_per_step": comm_bytes},
+                "clocks": clocks.summary(), "gpu_launches": None}
+        print(json.dumps(line), flush=True)
+    dist.destroy_process_group()
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -185,6 +256,9 @@ def main():
     ap.add_argument("--workload", default="c2")
     ap.add_argument("--impl", default="native", choices=["native", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--parallel", default="dp", choices=["dp", "tp"],
+                    help="dp: every rank runs its own stack (default); tp: the Wan-shape stacks (c4, c5) are "
+                         "column/row split over the ranks with NCCL all-gather / reduce-scatter")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "native" else args.warmup
 
@@ -209,6 +283,10 @@ def main():
     if world > 1:
         import torch.distributed as dist
         dist.init_process_group("nccl", device_id=dev)
+
+    if args.parallel == "tp":
+        run_tensor_parallel(args, spec, dev, dist, rank, world)
+        return
 
     weights = make_weights(spec, dev)
     stack = LinearStack(spec, weights, dev)

@@ -77,6 +77,20 @@ IFLB200_API int iflb200_row_quant(const void* x, int x_dtype, int64_t ld_x, int 
                       void* q, int64_t ld_q, float* qs, void* stream);
 
 /*
+ * The quantiser for rows whose columns are sharded over several GPUs (tensor-parallel
+ * column split).  Phase 1 writes each row's maximum of |v| over the LOCAL columns to amax[m]
+ * and stops.  After an all-reduce-max of amax over the shards, phase 2 quantises the local
+ * columns with the global maximum read from amax[m] and writes qs[m] and the codes: they are
+ * bit-identical to the codes of the unsharded row.  (col and bias are the local slices.)
+ * Extends instinctflash/kernels/norm.py:128-158, which is single-GPU; no reference counterpart
+ * for the split itself.
+ */
+IFLB200_API int iflb200_row_quant_sharded(const void* x, int x_dtype, int64_t ld_x, int M, int K,
+                              const float* row, const float* col, const float* bias, int gelu,
+                              int phase, float* amax, void* q, int64_t ld_q, float* qs,
+                              void* stream);
+
+/*
  * Consumer of a raw accumulator: y[m,n] = out_dtype(x[m,n] (*row[m]) (*col[n]) (+bias[n])),
  * the last multiply fused with the bias add (fma.rn) exactly as the reference compiles.
  * Replaces: instinctflash/kernels/norm.py:162-185 (_dequant_rows_kernel, dequant_rows).

@@ -230,6 +230,11 @@ struct RowQuantArgs {
   uint8_t* q;
   int64_t ld_q;
   float* qs;
+  // Column-sharded rows (tensor parallel): phase 1 writes the shard's row maximum to `amax` and
+  // stops; phase 2 takes the row maximum from `amax` (after an all-reduce-max over the shards)
+  // instead of its own, so the codes equal those of the unsharded row.  0: one pass.
+  int phase;
+  float* amax;
 };
 
 // PLAIN: no prologue.  The row then stays in registers as loaded (4 registers per 8 elements)
@@ -261,6 +266,11 @@ row_quant_kernel(const RowQuantArgs a) {
       for (int i = 0; i < 8; ++i) amax = max_f32(amax, fabsf(w[i]));
     }
     amax = row_reduce<TPR, true>(amax, red);
+    if (a.phase == 1) {
+      if (live && t == 0) a.amax[m] = amax;
+      return;
+    }
+    if (a.phase == 2 && live) amax = a.amax[m];
     float scale, inv;
     quant_scales(amax, scale, inv);
     if (!live) return;
@@ -301,6 +311,11 @@ row_quant_kernel(const RowQuantArgs a) {
     }
   }
   amax = row_reduce<TPR, true>(amax, red);
+  if (a.phase == 1) {
+    if (live && t == 0) a.amax[m] = amax;
+    return;
+  }
+  if (a.phase == 2 && live) amax = a.amax[m];
   float scale, inv;
   quant_scales(amax, scale, inv);
   if (!live) return;
@@ -828,26 +843,44 @@ extern "C" int iflb200_row_set_group(int threads_per_row) {
   return IFLB200_OK;
 }
 
-extern "C" int iflb200_row_quant(const void* x, int x_dtype, int64_t ld_x, int M, int K,
-                                 const float* row, const float* col, const float* bias, int gelu,
-                                 void* q, int64_t ld_q, float* qs, void* stream) {
+static int row_quant_impl(const void* x, int x_dtype, int64_t ld_x, int M, int K, const float* row,
+                          const float* col, const float* bias, int gelu, void* q, int64_t ld_q, float* qs,
+                          int phase, float* amax, void* stream) {
   if (M < 0 || K < 0) return IFLB200_ERR_ARG;
   if (M == 0 || K == 0) return IFLB200_OK;
-  if (!x || !q || !qs) return IFLB200_ERR_ARG;
+  if (!x) return IFLB200_ERR_ARG;
+  if (phase != 1 && (!q || !qs)) return IFLB200_ERR_ARG;
+  if (phase != 0 && !amax) return IFLB200_ERR_ARG;
   if (!dtype_ok(x_dtype)) return IFLB200_ERR_DTYPE;
   if (K > kMaxWidth) return IFLB200_ERR_SHAPE;
-  if (ld_x < K || ld_q < K) return IFLB200_ERR_ARG;
+  if (ld_x < K || (phase != 1 && ld_q < K)) return IFLB200_ERR_ARG;
   RowQuantArgs a;
   a.x = x; a.ld_x = ld_x; a.M = M; a.K = K;
   a.row = row; a.col = col; a.bias = bias; a.gelu = gelu;
   a.q = reinterpret_cast<uint8_t*>(q); a.ld_q = ld_q; a.qs = qs;
-  const bool fast = K % 8 == 0 && aligned16(x) && (ld_x * esize(x_dtype)) % 16 == 0 && aligned8(q) &&
-                    ld_q % 8 == 0 && (!col || aligned16(col)) && (!bias || aligned16(bias));
+  a.phase = phase; a.amax = amax;
+  const bool fast = K % 8 == 0 && aligned16(x) && (ld_x * esize(x_dtype)) % 16 == 0 &&
+                    (phase == 1 || (aligned8(q) && ld_q % 8 == 0)) && (!col || aligned16(col)) &&
+                    (!bias || aligned16(bias));
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
   if (x_dtype == IFLB200_BF16) launch_row_quant<__nv_bfloat16>(a, fast, s);
   else if (x_dtype == IFLB200_F16) launch_row_quant<__half>(a, fast, s);
   else launch_row_quant<float>(a, fast, s);
   return (int)cudaGetLastError();
+}
+
+extern "C" int iflb200_row_quant(const void* x, int x_dtype, int64_t ld_x, int M, int K,
+                                 const float* row, const float* col, const float* bias, int gelu,
+                                 void* q, int64_t ld_q, float* qs, void* stream) {
+  return row_quant_impl(x, x_dtype, ld_x, M, K, row, col, bias, gelu, q, ld_q, qs, 0, nullptr, stream);
+}
+
+extern "C" int iflb200_row_quant_sharded(const void* x, int x_dtype, int64_t ld_x, int M, int K,
+                                         const float* row, const float* col, const float* bias, int gelu,
+                                         int phase, float* amax, void* q, int64_t ld_q, float* qs,
+                                         void* stream) {
+  if (phase != 1 && phase != 2) return IFLB200_ERR_ARG;
+  return row_quant_impl(x, x_dtype, ld_x, M, K, row, col, bias, gelu, q, ld_q, qs, phase, amax, stream);
 }
 
 #endif

@@ -34,6 +34,30 @@ def row_quant(x, q, q_scale, *, row=None, col=None, bias=None, gelu=False, num_w
     _lib.check(st, "row_quant")
 
 
+def row_quant_sharded(x, q, q_scale, amax, phase, *, row=None, col=None, bias=None, gelu=False):
+    """The quantiser for rows whose columns are sharded over GPUs (no reference counterpart:
+    the reference is single-GPU).  ``phase=1`` writes the local row maxima to ``amax`` [M];
+    after an all-reduce-max of ``amax`` over the shards, ``phase=2`` writes ``q`` and ``q_scale``
+    from the global maxima: bit-identical to the codes of the unsharded row."""
+    rows(x, "x", _FLOATS)
+    M, D = x.shape
+    vec(amax, "amax", M, x.device)
+    if phase == 2:
+        rows(q, "q", (E4M3,))
+        if tuple(q.shape) != (M, D):
+            raise ValueError(f"q must be [{M}, {D}], got {tuple(q.shape)}")
+        vec(q_scale, "q_scale", M, x.device)
+    elif phase != 1:
+        raise ValueError("phase must be 1 (local maxima) or 2 (quantise with the reduced maxima)")
+    st = _lib.lib().iflb200_row_quant_sharded(
+        x.data_ptr(), _lib.dtype_code(x.dtype), ld(x), M, D,
+        _lib.ptr(vec(row, "row", M, x.device)), _lib.ptr(vec(col, "col", D, x.device)),
+        _lib.ptr(vec(bias, "bias", D, x.device)), int(bool(gelu)), int(phase), amax.data_ptr(),
+        _lib.ptr(q) if phase == 2 else None, ld(q) if phase == 2 else 0,
+        _lib.ptr(q_scale) if phase == 2 else None, stream(x))
+    _lib.check(st, "row_quant_sharded")
+
+
 def dequant_rows(x, y, *, row=None, col=None, bias=None, block=None, num_warps=4):
     """y[m] = x[m] * row[m] * col + bias (float dtypes in and out)."""
     rows(x, "x", _FLOATS)

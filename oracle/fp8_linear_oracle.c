@@ -152,6 +152,38 @@ ORACLE_API void oracle_row_quant(const float* x, int64_t ld_x, int M, int K, con
   }
 }
 
+/* The two phases of the quantiser for column-sharded rows (tensor parallel): phase 1 returns
+ * the local row maxima of |v|, phase 2 quantises with maxima supplied by the caller (the
+ * all-reduce-max over the shards).  v is the same prologue chain as oracle_row_quant. */
+ORACLE_API void oracle_row_quant_sharded(const float* x, int64_t ld_x, int M, int K, const float* row,
+                                         const float* col, const float* bias, int gelu, int phase,
+                                         float* amax_io, uint8_t* q, int64_t ld_q, float* qs) {
+#pragma omp parallel for schedule(static)
+  for (int m = 0; m < M; ++m) {
+    float* h = (float*)malloc(sizeof(float) * (size_t)K);
+    float amax = 0.0f;
+    for (int k = 0; k < K; ++k) {
+      chain_t c; ch_init(&c, x[m * ld_x + k]);
+      if (row) ch_mul(&c, row[m]);
+      if (col) ch_mul(&c, col[k]);
+      if (bias) ch_add(&c, bias[k]);
+      float v = ch_done(&c);
+      if (gelu) v = gelu_tanh_ref(v);
+      h[k] = v;
+      amax = max_nn(amax, fabsf(v));
+    }
+    if (phase == 1) {
+      amax_io[m] = amax;
+    } else {
+      float a = max_nn(amax_io[m], u2f(0x322BCC77u));
+      qs[m] = a / 448.0f;
+      const float inv = 448.0f / a;
+      for (int k = 0; k < K; ++k) q[m * ld_q + k] = oracle_e4m3_encode(h[k] * inv);
+    }
+    free(h);
+  }
+}
+
 ORACLE_API void oracle_dequant_rows(const float* x, int64_t ld_x, int M, int D, const float* row,
                                     const float* col, const float* bias, float* y, int64_t ld_y,
                                     int y_dtype) {

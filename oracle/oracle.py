@@ -83,6 +83,23 @@ def row_quant(x, *, row=None, col=None, bias=None, gelu=False):
     return _as_e4m3(q), torch.from_numpy(qs)
 
 
+def row_quant_sharded(x, amax, phase, *, row=None, col=None, bias=None, gelu=False):
+    """Two-phase quantiser for column-sharded rows (the tensor-parallel split of
+    instinctflash/kernels/norm.py:128-147).  phase 1 -> local row maxima [M];
+    phase 2 (amax = reduced maxima) -> (codes, scales)."""
+    xf = _f32(x)
+    M, K = xf.shape
+    r, c, b = _f32(row), _f32(col), _f32(bias)
+    am = np.ascontiguousarray(amax.detach().cpu().numpy().astype(np.float32)) if phase == 2 else np.empty((M,), np.float32)
+    q = np.empty((M, K), np.uint8)
+    qs = np.empty((M,), np.float32)
+    _lib().oracle_row_quant_sharded(_p(xf), ctypes.c_int64(K), M, K, _p(r), _p(c), _p(b), int(gelu), int(phase),
+                                    _p(am), _p(q), ctypes.c_int64(K), _p(qs))
+    if phase == 1:
+        return torch.from_numpy(am)
+    return _as_e4m3(q), torch.from_numpy(qs)
+
+
 def dequant_rows(x, *, row=None, col=None, bias=None, out_dtype=torch.bfloat16):
     """instinctflash/kernels/norm.py:162-175 -> y [M,D] in out_dtype."""
     xf = _f32(x)

@@ -1,0 +1,68 @@
+"""Host-side logic of the layer-stack and tensor-parallel drivers, on CPU: the drivers run on an
+operator set built from the CPU oracle; the N > 1 path runs as two gloo ranks."""
+import os
+import subprocess
+import sys
+from pathlib import Path
+
+import pytest
+import torch
+
+import oracle_ops
+from instinctflash_b200.stack import SPECS, LinearStack, StackSpec, make_inputs, make_weights, small_spec
+from instinctflash_b200 import tp
+
+ROOT = Path(__file__).resolve().parents[1]
+
+
+def test_spec_flops_and_weight_bytes_match_the_benchmark_tables():
+    assert abs(SPECS["c2"].flops() - 3.234e12) / 3.234e12 < 1e-3
+    assert abs(SPECS["c2"].weight_bytes() - 1.985e9) / 1.985e9 < 2e-3
+    assert abs(SPECS["c4"].flops() - 40.63e12) / 40.63e12 < 2e-3
+    assert abs(SPECS["c5"].flops() - 322.98e12) / 322.98e12 < 2e-3
+    assert abs(SPECS["c3"].weight_bytes() * 10 - 2.556e9) / 2.556e9 < 5e-3  # BASELINE counts scales too
+    assert [n for n, _, _ in SPECS["c2"].linears()] == ["qkv", "o", "gate_up", "down"]
+    assert [n for n, _, _ in SPECS["c4"].linears()] == ["qkv", "o", "cross_q", "cross_o", "ff1", "ff2"]
+
+
+@pytest.mark.parametrize("kind", ["gemma", "wan"])
+def test_stack_driver_runs_the_reference_call_order_on_cpu(kind):
+    spec = StackSpec("tiny", kind, layers=2, M=24, hidden=64, ffn=128, qkv=96, o_in=64, cross=kind == "wan", seed=5)
+    weights = make_weights(spec, "cpu", cpu_seeded=True)
+    x, attn = make_inputs(spec, "cpu")
+    stack = LinearStack(spec, weights, "cpu", ops=oracle_ops.ops())
+    stack.load(x, attn)
+    before = stack.res.clone()
+    out = stack.forward()
+    assert torch.isfinite(out.float()).all() and not torch.equal(out, before)
+    per_layer = 8 if kind == "gemma" else 12
+    assert stack.launches_per_forward == spec.layers * per_layer
+    # deterministic: a second stack on the same seeds gives the same bits
+    again = LinearStack(spec, make_weights(spec, "cpu", cpu_seeded=True), "cpu", ops=oracle_ops.ops())
+    again.load(x, attn)
+    assert torch.equal(again.forward(), out)
+
+
+def test_weight_sharding_keeps_full_matrix_scales():
+    from instinctflash_b200.kernels.fp8 import quantize_weight
+    w = quantize_weight(torch.randn(64, 96) * 0.02, torch.randn(64))
+    parts = [tp.shard_columns(w, r, 2) for r in range(2)]
+    assert torch.equal(torch.cat([p.w.view(torch.uint8) for p in parts], 0), w.w.view(torch.uint8))
+    assert torch.equal(torch.cat([p.scale for p in parts]), w.scale)
+    assert torch.equal(torch.cat([p.bias for p in parts]), w.bias)
+    rows = [tp.shard_rows(w, r, 2) for r in range(2)]
+    assert torch.equal(torch.cat([p.w.view(torch.uint8) for p in rows], 1), w.w.view(torch.uint8))
+    assert all(p.scale is w.scale and p.w.is_contiguous() for p in rows)
+    with pytest.raises(ValueError):
+        tp.shard_columns(w, 0, 3)
+
+
+def test_tensor_parallel_driver_two_gloo_ranks_match_single_process():
+    env = dict(os.environ, IFLB200_TP_BACKEND="gloo", MASTER_ADDR="127.0.0.1", MASTER_PORT="29533",
+               OMP_NUM_THREADS="2")
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", "2",
+           "--master-addr", "127.0.0.1", "--master-port", "29533", str(ROOT / "tests" / "tp_worker.py")]
+    r = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=600)
+    assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-2000:]
+    line = [l for l in r.stdout.splitlines() if l.startswith("TP_RESULT")][-1]
+    assert "'exact_ok': True" in line, line
