@@ -245,12 +245,13 @@ def run_tensor_parallel(args, spec, dev, dist, rank, world):
                            "nvlink_bytes_per_rank_per_step": comm_bytes},
                 "clocks": clocks.summary(), "gpu_launches": None}
         print(json.dumps(line), flush=True)
-    # a captured graph holds NCCL work: release it before the process group goes away
-    graph = None
+    # A captured graph holds NCCL work, and tearing the process group down under it has hung
+    # (watchdog stuck in event destruction): finish all work, then leave without the teardown.
     torch.cuda.synchronize(dev)
     dist.barrier()
     torch.cuda.synchronize(dev)
-    dist.destroy_process_group()
+    sys.stdout.flush()
+    os._exit(0)
 
 
 def main():
