@@ -262,6 +262,10 @@ def main():
     ap.add_argument("--workload", default="c2")
     ap.add_argument("--impl", default="native", choices=["native", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--episodes", type=int, default=1,
+                    help="c3 only: independent episodes stacked along M on each GPU (rows are independent: "
+                         "per-token scales and per-row norms, so this is arithmetically the same as separate runs)")
+    ap.add_argument("--per-op", action="store_true", help="c3: one launch per operator instead of the persistent kernel")
     ap.add_argument("--parallel", default="dp", choices=["dp", "tp"],
                     help="dp: every rank runs its own stack (default); tp: the Wan-shape stacks (c4, c5) are "
                          "column/row split over the ranks with NCCL all-gather / reduce-scatter")
@@ -274,6 +278,9 @@ def main():
 
     from instinctflash_b200.stack import SPECS, LinearStack, make_inputs, make_weights
     spec = SPECS[args.workload]
+    if args.episodes > 1:
+        from instinctflash_b200.stack import StackSpec
+        spec = StackSpec(**{**spec.__dict__, "M": spec.M * args.episodes})
 
     if args.impl == "reference":
         run_reference(args, spec, rank, world)
@@ -295,7 +302,32 @@ def main():
         return
 
     weights = make_weights(spec, dev)
-    stack = LinearStack(spec, weights, dev)
+    persistent = (spec.kind == "gemma" and not spec.o_in and spec.M <= 128 and not args.per_op)
+    if persistent:
+        # skinny expert loop: the whole stack is one cooperative launch
+        from instinctflash_b200.stack_persistent import PersistentExpertStack
+
+        class _Persistent(PersistentExpertStack):
+            def load(self, x, attn=None):
+                super().load(x)
+
+            def capture(self):
+                self.forward()
+                torch.cuda.synchronize(self.dev)
+                g = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(g):
+                    self.forward()
+                return g
+
+            def _q8(self, cols):
+                return (self.q8 if cols == self.spec.hidden else self.q8f)
+
+            def _raw(self, cols):
+                return torch.empty(self.spec.M, cols, dtype=torch.bfloat16, device=self.dev)
+
+        stack = _Persistent(spec, weights, dev)
+    else:
+        stack = LinearStack(spec, weights, dev)
     x_dev, attn = make_inputs(spec, dev)
     x_host = x_dev.cpu().pin_memory()
     out_host = torch.empty(spec.M, spec.hidden, dtype=stack.res.dtype).pin_memory()
@@ -381,6 +413,19 @@ def main():
                     "traffic": None, "kernel": f"gemm_fp8_tc5_kernel {spec.M}x{n_dom}x{k_dom} ({name})",
                     "peak_source": f"hbm_gbs of MEASURED_PEAKS.json ({peaks['source']})",
                     "frac_of_nominal_8000": achieved / NOMINAL_HBM_GBS, "ms_per_launch": dom_ms}
+    if persistent:
+        # the step is one launch of the persistent kernel: its algorithmic bytes are every weight
+        # matrix once per layer and flow step plus the activations each operator reads and writes
+        lin = spec.linears()
+        act = sum(spec.M * k + 2.0 * spec.M * n for _, n, k in lin) + spec.M * spec.ffn * 5.0 + spec.M * spec.hidden * 11.0
+        step_bytes = (spec.weight_bytes() + act * spec.layers) * spec.steps
+        achieved = step_bytes / (ms / args.steps * 1e-3) / 1e9
+        roofline = {"bound": "hbm", "achieved": achieved, "peak": peaks["hbm_gbs"], "unit": "GB/s",
+                    "frac": achieved / peaks["hbm_gbs"], "traffic": None,
+                    "kernel": f"stack_persistent_kernel ({spec.layers} layers x {spec.steps} steps, M={spec.M})",
+                    "peak_source": f"hbm_gbs of MEASURED_PEAKS.json ({peaks['source']})",
+                    "frac_of_nominal_8000": achieved / NOMINAL_HBM_GBS, "ms_per_launch": ms / args.steps,
+                    "note": "bound by the chain of grid-wide dependencies (4 per layer and step), not by bandwidth"}
     traffic_file = ROOT / "profiles" / "traffic.json"
     if traffic_file.exists():
         roofline["traffic"] = json.loads(traffic_file.read_text()).get(f"{spec.name}:{name}")
@@ -415,7 +460,9 @@ def main():
             "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
             "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
             "dtype": "e4m3 x e4m3 -> f32", "data": "synthetic",
-            "config": {"workload": workload_name(spec), "parallelism": f"dp{world} (independent stacks, no collective)",
+            "config": {"workload": workload_name(spec) + (f", {args.episodes} episodes stacked along M (M={spec.M})" if args.episodes > 1 else ""),
+                       "execution": "persistent whole-stack kernel (one cooperative launch per step)" if persistent else "one launch per operator, CUDA graph",
+                       "parallelism": f"dp{world} (independent stacks, no collective)",
                        "l2": f"weights streamed per step ({spec.weight_bytes() / 1e9:.2f} GB) exceed the 126 MB L2",
                        "timing": "one CUDA-graph replay per step, CUDA events on the launching stream"},
             "roofline": roofline, "cpu_baseline": cpu,

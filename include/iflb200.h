@@ -210,6 +210,51 @@ IFLB200_API int iflb200_dynamic_pack_bf16_e4m3_noalloc(const void* x, int64_t n,
 IFLB200_API int iflb200_pack_bf16_e4m3(const void* x, int64_t n, const float* scale, void* q, void* stream);
 
 /*
+ * Persistent whole-stack execution for skinny activations (M <= 128): ONE cooperative launch
+ * runs a program of operators over all layers and flow steps, with grid-wide dependency
+ * counters between them and weights prefetched across operator boundaries.
+ * Replaces the per-operator launch sequence of the reference's action-expert loop
+ * (instinctflash/engines/pi05/engine.py:225-253: gemm / gated_act_quant / gemm /
+ * residual_norm_quant per layer and flow step) for the operators listed below; arithmetic per
+ * operator is that of the stand-alone entry points (a split-K GEMM sums its fp32 partials in
+ * split order before the bf16 rounding point).
+ *
+ * `ops`, `tensor_maps` (128 bytes each, 64-byte aligned, written by
+ * iflb200_encode_operand_map), `barriers` (num_barriers uint32) and `status2` (2 uint32) are
+ * device buffers owned by the caller; barriers and status2[1] are zeroed by the call itself.
+ * status2[0] != 0 after completion: a wait ran out of its time budget (role<<24 | kind<<16 | op).
+ */
+#define IFLB200_STACK_GEMM 1    /* out[M,N] = a[M,K] x w[N,K]^T: raw bf16 (split_k = 1) or fp32 partials [split_k][M][N] */
+#define IFLB200_STACK_GATED 2   /* gated_act_quant of raw [M, 2N] -> codes [M,N] + row scales */
+#define IFLB200_STACK_RESNORM 3 /* res += acc*row*col; RMS norm; quantiser -> codes [M,N] + row scales */
+typedef struct {
+  int32_t type;        /* IFLB200_STACK_* */
+  int32_t wait_bar;    /* counter that must reach the grid size before activations are read; -1: none */
+  int32_t arrive_bar;  /* counter this operator's CTAs bump when their outputs are visible; -1: none */
+  int32_t tile_offset; /* GEMM: rotation of the work-item -> CTA assignment */
+  int32_t N, K;        /* GEMM: output columns, reduction length; row operators: N = width */
+  int32_t split_k;     /* GEMM: K splits (each at least one 128-byte step); RESNORM: partials to sum (1: raw bf16 in) */
+  int32_t act;         /* GATED: IFLB200_ACT_* */
+  int32_t tm_a, tm_w;  /* GEMM: indices into tensor_maps (activation box, weight box) */
+  int32_t pad0, pad1;
+  void* out;           /* GEMM: raw bf16 / fp32 partials; row operators: e4m3 codes */
+  const void* in;      /* GATED: raw bf16 [M, 2N]; RESNORM: raw bf16 [M,N] or fp32 partials */
+  const float* row_scale; /* GATED: row scales of the GEMM input; RESNORM: delta_row */
+  const float* col_scale; /* GATED: [2N]; RESNORM: [N] */
+  float* out_scale;    /* row operators: row scales out [M] */
+  float* res;          /* RESNORM: residual stream fp32 [M,N], in place */
+  int64_t ld_out, ld_in;
+  float eps;           /* RESNORM */
+  int32_t pad2;
+  int64_t pad3;
+} iflb200_stack_op;
+IFLB200_API int iflb200_encode_operand_map(void* out128, const void* ptr, int rows, int K, int64_t ld, int box_rows);
+IFLB200_API int iflb200_stack_activation_box_rows(int M);
+IFLB200_API int iflb200_stack_weight_box_rows(void);
+IFLB200_API int iflb200_stack_run(const void* ops, int num_ops, const void* tensor_maps, void* barriers,
+                      int num_barriers, int M, void* status2, void* stream);
+
+/*
  * Diagnostics of the tcgen05 GEMM: every wait inside the kernel is bounded; a wait that
  * runs out records (role, barrier, tile) in a device word and the kernel drains and
  * returns.  This reads the word (synchronises the given stream) and clears it.

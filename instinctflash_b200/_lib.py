@@ -42,6 +42,10 @@ SIGNATURES = {
     "iflb200_dynamic_pack_bf16_e4m3": (_i, [_p, _l, _p, _p, _p, _z, _p]),
     "iflb200_dynamic_pack_bf16_e4m3_noalloc": (_i, [_p, _l, _p, _p, _p]),
     "iflb200_pack_bf16_e4m3": (_i, [_p, _l, _p, _p, _p]),
+    "iflb200_encode_operand_map": (_i, [_p, _p, _i, _i, _l, _i]),
+    "iflb200_stack_activation_box_rows": (_i, [_i]),
+    "iflb200_stack_weight_box_rows": (_i, []),
+    "iflb200_stack_run": (_i, [_p, _i, _p, _p, _i, _i, _p, _p]),
     "iflb200_gemm_take_timeout_record": (_i, [ctypes.POINTER(ctypes.c_uint32), _p]),
     "iflb200_gemm_set_config": (_i, [_i, _i, _i]),
     "iflb200_gemm_set_mode": (_i, [_i]),
