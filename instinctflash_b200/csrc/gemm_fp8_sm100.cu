@@ -29,10 +29,11 @@ namespace iflb200 {
 
 constexpr int BM = 128;
 constexpr int BK = 128;  // bytes == e4m3 elements per stage along K
-constexpr int kGemmThreads = 192;
+constexpr int kGemmThreads = 320;  // TMA warp, MMA warp, eight epilogue warps
+constexpr int kEpilogueWarps = 8;   // two per TMEM lane quadrant, each draining half of the columns
 constexpr uint64_t kWaitBudgetNs = 2000000000ull;  // 2 s per wait, then abort
 
-constexpr int kStagingBytes = 4 * 2 * 32 * 128;  // 4 epilogue warps x 2 buffers x 32 rows x 128 B
+constexpr int kStagingBytes = kEpilogueWarps * 32 * 128;  // one 32-row x 128-byte buffer per epilogue warp
 
 enum : int { EPI_RAW = 0, EPI_DEQUANT = 1, EPI_RESIDUAL = 2 };
 
@@ -52,11 +53,24 @@ struct GemmParams {
   void* out;
   int out_dtype;
   int64_t ld_out;
+  int split_k;     // > 1: the CTAs of a cluster share one tile, each a K range; partials are summed over DSMEM
+  int debug_skip;  // experiments: 1 skip the whole epilogue body, 2 load TMEM but do not store
   int tma_store;  // 1: the epilogue stages 128-byte row pieces in shared memory and TMA-stores them
 };
 
 // role << 24 | barrier kind << 16 | low 16 bits of the tile counter; 0 = no timeout.
 __device__ uint32_t g_timeout_record[4];
+
+__device__ __forceinline__ uint32_t map_to_cta(uint32_t smem_addr, uint32_t rank) {
+  uint32_t r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(smem_addr), "r"(rank));
+  return r;
+}
+__device__ __forceinline__ float ld_dsmem_f32(uint32_t addr) {
+  float v;
+  asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(addr));
+  return v;
+}
 
 template <int BN, int STAGES>
 struct SmemLayout {
@@ -198,14 +212,29 @@ __device__ __forceinline__ void epilogue_chunk(const GemmParams& p, const uint32
   }
 }
 
+__device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
+  const __nv_bfloat162 h = __floats2bfloat162_rn(lo, hi);  // one cvt.rn.bf16x2.f32
+  return *reinterpret_cast<const uint32_t*>(&h);
+}
+__device__ __forceinline__ uint32_t pack_f16x2(float lo, float hi) {
+  const __half2 h = __floats2half2_rn(lo, hi);
+  return *reinterpret_cast<const uint32_t*>(&h);
+}
+
 // Consumer arithmetic on 32 consecutive columns of one accumulator row (y in fp32, before the
 // cast to the output type).  Scale / bias vectors are read with warp-uniform addresses.
 __device__ __forceinline__ void epilogue_values(const GemmParams& p, const uint32_t (&acc)[32], int n0, float rs,
                                                 float (&y)[32]) {
+  if (p.exact) {
 #pragma unroll
-  for (int i = 0; i < 32; ++i) {
-    const float a = __uint_as_float(acc[i]);
-    y[i] = p.exact ? a : __bfloat162float(__float2bfloat16_rn(a));
+    for (int i = 0; i < 32; ++i) y[i] = __uint_as_float(acc[i]);
+  } else {
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {  // the bf16 rounding point of the accumulator, two at a time
+      const uint32_t w = pack_bf16x2(__uint_as_float(acc[2 * i]), __uint_as_float(acc[2 * i + 1]));
+      y[2 * i] = __uint_as_float(w << 16);
+      y[2 * i + 1] = __uint_as_float(w & 0xFFFF0000u);
+    }
   }
   if (p.epilogue == EPI_RAW) return;
 #pragma unroll
@@ -232,50 +261,69 @@ __device__ __forceinline__ void epilogue_values(const GemmParams& p, const uint3
   }
 }
 
-// Epilogue of one accumulator (BN columns) for one warp's 32 rows through shared memory:
-// 128 bytes of each output row (64 two-byte or 32 four-byte columns) are staged with the
-// 128-byte swizzle and written by one TMA store, so global memory sees whole 128-byte lines
-// instead of 16-byte pieces of 32 different rows.  Two staging buffers per warp alternate.
+// Epilogue of one warp: its 32 accumulator rows x its half of the tile's columns, through shared
+// memory.  128 bytes of each output row (64 two-byte or 32 four-byte columns) are staged with
+// the 128-byte swizzle and written by one TMA store, so global memory sees whole 128-byte lines
+// instead of 16-byte pieces of 32 different rows.
 template <int BN>
 __device__ __forceinline__ void epilogue_tma_store(const GemmParams& p, const CUtensorMap* tm_out, uint32_t t_row,
-                                                   uint32_t staging, uint8_t* staging_ptr, int row0, int m, int n_base,
-                                                   float rs, int lane, uint32_t& buf) {
+                                                   uint32_t staging, uint8_t* staging_ptr, int row0, int n_base,
+                                                   int col_begin, int col_end, float rs, int lane) {
   const int es = (p.out_dtype == IFLB200_F32) ? 4 : 2;
   const int cols_per_store = 128 / es;  // 64 or 32
+  uint8_t* mine = staging_ptr + lane * 128;
 #pragma unroll 1
-  for (int c = 0; c < BN; c += cols_per_store) {
+  for (int c = col_begin; c < col_end; c += cols_per_store) {
     const int n0 = n_base + c;
     if (n0 >= p.N) break;  // uniform
-    if (lane == 0) bulk_wait_group_read<1>();  // the buffer written two stores ago has been read
+    if (p.debug_skip == 1) continue;
+    if (lane == 0) bulk_wait_group_read<0>();  // the previous store has read the buffer
     __syncwarp();
-    uint8_t* mine = staging_ptr + buf * 4096 + lane * 128;
 #pragma unroll 1
     for (int sub = 0; sub < cols_per_store; sub += 32) {
       uint32_t r[32];
       tmem_ld_32x32b_x32(t_row + c + sub, r);
       tmem_ld_wait();
-      float y[32];
-      epilogue_values(p, r, n0 + sub, rs, y);
+      if (p.debug_skip == 2) {
+        if (r[0] == 0x7fc12345u) mine[0] = 1;  // keep the load alive
+        continue;
+      }
       if (es == 2) {
         // 32 values = 64 bytes = four 16-byte chunks; chunk index within the 128-byte row
         const int first = sub / 8;  // 0 or 4
+        if (p.epilogue == EPI_RAW) {
 #pragma unroll
-        for (int j = 0; j < 4; ++j) {
-          uint4 u;
-          if (p.out_dtype == IFLB200_BF16) {
-            u.x = f32_to_bf16_bits(y[8 * j + 0]) | (f32_to_bf16_bits(y[8 * j + 1]) << 16);
-            u.y = f32_to_bf16_bits(y[8 * j + 2]) | (f32_to_bf16_bits(y[8 * j + 3]) << 16);
-            u.z = f32_to_bf16_bits(y[8 * j + 4]) | (f32_to_bf16_bits(y[8 * j + 5]) << 16);
-            u.w = f32_to_bf16_bits(y[8 * j + 6]) | (f32_to_bf16_bits(y[8 * j + 7]) << 16);
-          } else {
-            u.x = f32_to_f16_bits(y[8 * j + 0]) | (f32_to_f16_bits(y[8 * j + 1]) << 16);
-            u.y = f32_to_f16_bits(y[8 * j + 2]) | (f32_to_f16_bits(y[8 * j + 3]) << 16);
-            u.z = f32_to_f16_bits(y[8 * j + 4]) | (f32_to_f16_bits(y[8 * j + 5]) << 16);
-            u.w = f32_to_f16_bits(y[8 * j + 6]) | (f32_to_f16_bits(y[8 * j + 7]) << 16);
+          for (int j = 0; j < 4; ++j) {
+            uint4 u;
+            u.x = pack_bf16x2(__uint_as_float(r[8 * j + 0]), __uint_as_float(r[8 * j + 1]));
+            u.y = pack_bf16x2(__uint_as_float(r[8 * j + 2]), __uint_as_float(r[8 * j + 3]));
+            u.z = pack_bf16x2(__uint_as_float(r[8 * j + 4]), __uint_as_float(r[8 * j + 5]));
+            u.w = pack_bf16x2(__uint_as_float(r[8 * j + 6]), __uint_as_float(r[8 * j + 7]));
+            *reinterpret_cast<uint4*>(mine + (((first + j) ^ (lane & 7)) * 16)) = u;
           }
-          *reinterpret_cast<uint4*>(mine + (((first + j) ^ (lane & 7)) * 16)) = u;
+        } else {
+          float y[32];
+          epilogue_values(p, r, n0 + sub, rs, y);
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            uint4 u;
+            if (p.out_dtype == IFLB200_BF16) {
+              u.x = pack_bf16x2(y[8 * j + 0], y[8 * j + 1]);
+              u.y = pack_bf16x2(y[8 * j + 2], y[8 * j + 3]);
+              u.z = pack_bf16x2(y[8 * j + 4], y[8 * j + 5]);
+              u.w = pack_bf16x2(y[8 * j + 6], y[8 * j + 7]);
+            } else {
+              u.x = pack_f16x2(y[8 * j + 0], y[8 * j + 1]);
+              u.y = pack_f16x2(y[8 * j + 2], y[8 * j + 3]);
+              u.z = pack_f16x2(y[8 * j + 4], y[8 * j + 5]);
+              u.w = pack_f16x2(y[8 * j + 6], y[8 * j + 7]);
+            }
+            *reinterpret_cast<uint4*>(mine + (((first + j) ^ (lane & 7)) * 16)) = u;
+          }
         }
       } else {
+        float y[32];
+        epilogue_values(p, r, n0 + sub, rs, y);
 #pragma unroll
         for (int j = 0; j < 8; ++j)
           *reinterpret_cast<float4*>(mine + ((j ^ (lane & 7)) * 16)) =
@@ -284,13 +332,11 @@ __device__ __forceinline__ void epilogue_tma_store(const GemmParams& p, const CU
     }
     fence_proxy_async_smem();  // generic-proxy writes visible to the TMA unit
     __syncwarp();
-    if (lane == 0) {
-      tma_store_2d(tm_out, staging + buf * 4096, n0, row0);
+    if (lane == 0 && p.debug_skip == 0) {
+      tma_store_2d(tm_out, staging, n0, row0);
       bulk_commit_group();
     }
-    buf ^= 1u;
   }
-  (void)m;
 }
 
 template <int BN, int STAGES>
@@ -316,6 +362,14 @@ gemm_fp8_tc5_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
+  // Split-K: the S CTAs of a cluster work on the same tile, CTA r on K steps [kb0, kb1); one
+  // tile per CTA (the host launches tiles x S CTAs, at most one wave).
+  const bool split = p.split_k > 1;
+  const int split_rank = split ? (int)cluster_ctarank() : 0;
+  const int tile_first = split ? (int)blockIdx.x / p.split_k : (int)blockIdx.x;
+  const int tile_stride = split ? p.num_tiles : (int)gridDim.x;
+  const int kb0 = split ? (int)(((int64_t)p.num_k * split_rank) / p.split_k) : 0;
+  const int kb1 = split ? (int)(((int64_t)p.num_k * (split_rank + 1)) / p.split_k) : p.num_k;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) {
@@ -324,7 +378,7 @@ gemm_fp8_tc5_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
     }
     for (int a = 0; a < 2; ++a) {
       mbar_init(tfull_bar(a), 1);
-      mbar_init(tempty_bar(a), 4);  // one arrival per epilogue warp
+      mbar_init(tempty_bar(a), kEpilogueWarps);  // one arrival per epilogue warp
     }
     tmem_slot[1] = 0;
     fence_barrier_init();
@@ -351,10 +405,10 @@ gemm_fp8_tc5_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
     uint32_t last_parity = 0;  // parity of the last arming per stage
     bool ok = true;
     uint32_t it = 0;
-    for (int tile = blockIdx.x; ok && tile < p.num_tiles; tile += gridDim.x, ++it) {
+    for (int tile = tile_first; ok && tile < p.num_tiles; tile += tile_stride, ++it) {
       int m_blk, n_blk;
       tile_coords(p, tile, m_blk, n_blk);
-      for (int kb = 0; kb < p.num_k; ++kb) {
+      for (int kb = kb0; kb < kb1; ++kb) {
         ok = __all_sync(0xFFFFFFFFu, wait_bounded(empty_bar(stage), phase ^ 1, abort_flag,
                                                   (1u << 24) | (1u << 16) | (it & 0xFFFF)));
         if (!ok) break;
@@ -389,7 +443,7 @@ gemm_fp8_tc5_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
     uint32_t phase = 0;
     bool ok = true;
     uint32_t it = 0;
-    for (int tile = blockIdx.x; ok && tile < p.num_tiles; tile += gridDim.x, ++it) {
+    for (int tile = tile_first; ok && tile < p.num_tiles; tile += tile_stride, ++it) {
       const uint32_t acc = it & 1u;
       const uint32_t acc_phase = (it >> 1) & 1u;
       ok = __all_sync(0xFFFFFFFFu, wait_bounded(tempty_bar(acc), acc_phase ^ 1, abort_flag,
@@ -397,7 +451,7 @@ gemm_fp8_tc5_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
       if (!ok) break;
       tc_fence_after();
       const uint32_t d_tmem = tmem_base + acc * BN;
-      for (int kb = 0; kb < p.num_k; ++kb) {
+      for (int kb = kb0; kb < kb1; ++kb) {
         ok = __all_sync(0xFFFFFFFFu, wait_bounded(full_bar(stage), phase, abort_flag,
                                                   (2u << 24) | (3u << 16) | (it & 0xFFFF)));
         if (!ok) break;
@@ -409,7 +463,7 @@ gemm_fp8_tc5_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
 #pragma unroll
           for (int j = 0; j < BK / 32; ++j) {
             // 32 bytes further along K inside the swizzled 128-byte row: +2 in 16-byte units.
-            mma_f8f6f4(d_tmem, da + 2 * j, db + 2 * j, kIdesc, (kb | j) != 0 ? 1u : 0u);
+            mma_f8f6f4(d_tmem, da + 2 * j, db + 2 * j, kIdesc, (kb > kb0 || j > 0) ? 1u : 0u);
           }
           mma_commit(empty_bar(stage));  // stage reusable once these MMAs have read it
         }
@@ -426,12 +480,19 @@ gemm_fp8_tc5_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
   } else {
     // ------------------------------------------------------------------ epilogue warps
     const int quad = warp & 3;  // TMEM lanes [32*quad, 32*quad+32) are this warp's
-    const uint32_t staging = base + L::kStagingOffset + (uint32_t)(warp - 2) * 8192u;
-    uint8_t* staging_ptr = smem + L::kStagingOffset + (warp - 2) * 8192;
-    uint32_t store_buf = 0;
+    const int half = (warp - 2) >> 2;  // which half of the tile's columns this warp drains
+    int col_begin = half * (BN / 2), col_end = col_begin + BN / 2;
+    if (p.tma_store && BN / 2 < 128 / ((p.out_dtype == IFLB200_F32) ? 4 : 2)) {
+      // a 64-wide tile of two-byte outputs is a single 128-byte store: the first warp of the
+      // quadrant takes it all
+      col_begin = 0;
+      col_end = half == 0 ? BN : 0;
+    }
+    const uint32_t staging = base + L::kStagingOffset + (uint32_t)(warp - 2) * 4096u;
+    uint8_t* staging_ptr = smem + L::kStagingOffset + (warp - 2) * 4096;
     bool ok = true;
     uint32_t it = 0;
-    for (int tile = blockIdx.x; ok && tile < p.num_tiles; tile += gridDim.x, ++it) {
+    for (int tile = tile_first; ok && tile < p.num_tiles; tile += tile_stride, ++it) {
       int m_blk, n_blk;
       tile_coords(p, tile, m_blk, n_blk);
       const uint32_t acc = it & 1u;
@@ -445,12 +506,25 @@ gemm_fp8_tc5_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
       const float rs = (row_ok && p.row) ? __ldg(p.row + (int64_t)m * p.row_stride) : 1.0f;
       const int64_t gofs = (row_ok && p.gate_index) ? (int64_t)p.gate_index[m] * p.N : 0;
       const uint32_t t_row = tmem_base + ((uint32_t)(quad * 32) << 16) + acc * BN;
-      if (p.tma_store) {
-        epilogue_tma_store<BN>(p, &tm_out, t_row, staging, staging_ptr, m_blk * BM + quad * 32, m, n_blk * BN, rs,
-                               lane, store_buf);
+      if (split) {
+        // park this CTA's partial accumulator in shared memory (the stage ring is free: every
+        // load has been consumed), column-major so that lanes hit consecutive banks
+        float* part = reinterpret_cast<float*>(smem);
+        const int row = quad * 32 + lane;
+#pragma unroll 1
+        for (int c = half * (BN / 2); c < (half + 1) * (BN / 2); c += 32) {
+          uint32_t r[32];
+          tmem_ld_32x32b_x32(t_row + c, r);
+          tmem_ld_wait();
+#pragma unroll
+          for (int i = 0; i < 32; ++i) part[(c + i) * BM + row] = __uint_as_float(r[i]);
+        }
+      } else if (p.tma_store) {
+        epilogue_tma_store<BN>(p, &tm_out, t_row, staging, staging_ptr, m_blk * BM + quad * 32, n_blk * BN,
+                               col_begin, col_end, rs, lane);
       } else {
 #pragma unroll 1
-        for (int c = 0; c < BN / 32; ++c) {
+        for (int c = col_begin / 32; c < col_end / 32; ++c) {
           const int n0 = n_blk * BN + c * 32;
           if (n0 >= p.N) break;  // uniform
           uint32_t r[32];
@@ -467,6 +541,61 @@ gemm_fp8_tc5_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
     __syncwarp();
   }
 
+  if (split) {
+    // Every CTA of the cluster has parked its partial: CTA r now reduces columns
+    // [r*BN/S, (r+1)*BN/S) of the tile over all partials, in rank order (fixed, so the sum does
+    // not depend on timing), and runs the consumer arithmetic on the sums.
+    cluster_sync_all();
+    if (warp >= 2 && !*abort_flag) {
+      const int quad = warp & 3;
+      const int half = (warp - 2) >> 2;
+      const int own = BN / p.split_k;                 // columns this CTA reduces (>= 32)
+      const int per_warp = own >= 64 ? own / 2 : own;  // two warps per quadrant share them
+      const int c_begin = split_rank * own + (own >= 64 ? half * per_warp : 0);
+      const int c_end = (own >= 64 || half == 0) ? c_begin + per_warp : c_begin;
+      int m_blk, n_blk;
+      tile_coords(p, tile_first, m_blk, n_blk);
+      const int row = quad * 32 + lane;
+      const int m = m_blk * BM + row;
+      const bool row_ok = m < p.M && tile_first < p.num_tiles;
+      const float rs = (row_ok && p.row) ? __ldg(p.row + (int64_t)m * p.row_stride) : 1.0f;
+      const int64_t gofs = (row_ok && p.gate_index) ? (int64_t)p.gate_index[m] * p.N : 0;
+      uint32_t peer[8];
+#pragma unroll
+      for (int r = 0; r < 8; ++r) peer[r] = map_to_cta(base, (uint32_t)(r < p.split_k ? r : 0));
+#pragma unroll 1
+      for (int c = c_begin; c < c_end; c += 32) {
+        const int n0 = n_blk * BN + c;
+        if (n0 >= p.N) break;
+        uint32_t acc[32];
+        // eight columns at a time: every partial of the group is requested before the first
+        // is used (a distributed-shared-memory load takes hundreds of cycles), then summed in
+        // rank order
+#pragma unroll
+        for (int g = 0; g < 4; ++g) {
+          float part[8][8];
+#pragma unroll
+          for (int r = 0; r < 8; ++r) {
+            if (r < p.split_k) {
+#pragma unroll
+              for (int i = 0; i < 8; ++i)
+                part[r][i] = ld_dsmem_f32(peer[r] + (uint32_t)(((c + 8 * g + i) * BM + row) * 4));
+            }
+          }
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            float v = part[0][i];
+#pragma unroll
+            for (int r = 1; r < 8; ++r)
+              if (r < p.split_k) v = __fadd_rn(v, part[r][i]);
+            acc[8 * g + i] = __float_as_uint(v);
+          }
+        }
+        epilogue_chunk<BN>(p, acc, m, n0, row_ok, rs, gofs);
+      }
+    }
+    cluster_sync_all();  // peers may still be reading this CTA's partial
+  }
   tc_fence_before();
   __syncthreads();
   if (warp == 1) {
@@ -537,7 +666,7 @@ gemm_fp8_tc5_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_
     }
     for (int a = 0; a < 2; ++a) {
       mbar_init(tfull_bar(a), 1);
-      mbar_init(tempty_bar(a), 8);  // four epilogue warps in each of the two CTAs
+      mbar_init(tempty_bar(a), 2 * kEpilogueWarps);  // the epilogue warps of both CTAs
     }
     tmem_slot[1] = 0;
     fence_barrier_init();
@@ -629,9 +758,16 @@ gemm_fp8_tc5_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_
   } else {
     // ------------------------------------------------------------------ epilogue warps (both CTAs)
     const int quad = warp & 3;
-    const uint32_t staging = base + L::kStagingOffset + (uint32_t)(warp - 2) * 8192u;
-    uint8_t* staging_ptr = smem + L::kStagingOffset + (warp - 2) * 8192;
-    uint32_t store_buf = 0;
+    const int half = (warp - 2) >> 2;
+    int col_begin = half * (BN / 2), col_end = col_begin + BN / 2;
+    if (p.tma_store && BN / 2 < 128 / ((p.out_dtype == IFLB200_F32) ? 4 : 2)) {
+      // a 64-wide tile of two-byte outputs is a single 128-byte store: the first warp of the
+      // quadrant takes it all
+      col_begin = 0;
+      col_end = half == 0 ? BN : 0;
+    }
+    const uint32_t staging = base + L::kStagingOffset + (uint32_t)(warp - 2) * 4096u;
+    uint8_t* staging_ptr = smem + L::kStagingOffset + (warp - 2) * 4096;
     bool ok = true;
     uint32_t it = 0;
     for (int tile = pair_id; ok && tile < p.num_tiles; tile += pair_stride, ++it) {
@@ -650,10 +786,10 @@ gemm_fp8_tc5_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_
       const uint32_t t_row = tmem_base + ((uint32_t)(quad * 32) << 16) + acc * BN;
       if (p.tma_store) {
         epilogue_tma_store<BN>(p, &tm_out, t_row, staging, staging_ptr,
-                               m_blk * 2 * BM + (int)rank * BM + quad * 32, m, n_blk * BN, rs, lane, store_buf);
+                               m_blk * 2 * BM + (int)rank * BM + quad * 32, n_blk * BN, col_begin, col_end, rs, lane);
       } else {
 #pragma unroll 1
-        for (int c = 0; c < BN / 32; ++c) {
+        for (int c = col_begin / 32; c < col_end / 32; ++c) {
           const int n0 = n_blk * BN + c * 32;
           if (n0 >= p.N) break;
           uint32_t r[32];
@@ -761,6 +897,8 @@ static int device_info(DeviceInfo** out) {
 }
 
 static int g_cfg_tile_n = 0, g_cfg_stages = 0, g_cfg_group_m = 0;
+static int g_cfg_split_k = 0;  // 0: cost model, 1: never split K, 2/4/8: forced
+static int g_cfg_debug_skip = 0;
 static int g_cfg_direct_store = 0;  // 1: epilogue stores straight from registers (experiments)
 static int g_cfg_mode = 0;  // 0 auto, 1 single-CTA tiles only, 2 CTA pairs with one accumulator, 3 CTA pairs with two
 
@@ -776,6 +914,22 @@ static int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tw, const CUten
                                          cudaFuncAttributeMaxDynamicSharedMemorySize, L::kDynamic);
     if (e != cudaSuccess) return (int)e;
     attr_set[dev] = true;
+  }
+  if (p.split_k > 1) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(grid);
+    cfg.blockDim = dim3(kGemmThreads);
+    cfg.dynamicSmemBytes = L::kDynamic;
+    cfg.stream = s;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = p.split_k;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    const cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_fp8_tc5_kernel<BN, STAGES>, ta, tw, to, p);
+    return e != cudaSuccess ? (int)e : (int)cudaGetLastError();
   }
   gemm_fp8_tc5_kernel<BN, STAGES><<<grid, kGemmThreads, L::kDynamic, s>>>(ta, tw, to, p);
   return (int)cudaGetLastError();
@@ -817,6 +971,7 @@ static int run_gemm(const void* a, int64_t ld_a, const void* w, int64_t ld_w, Ge
   // updates its operand in place with plain loads and stores.
   CUtensorMap to;
   p.tma_store = (p.epilogue != EPI_RESIDUAL && g_cfg_direct_store == 0) ? 1 : 0;
+  p.debug_skip = g_cfg_debug_skip;
   if (p.tma_store) {
     st = make_out_map(&to, p.out, p.M, p.N, p.ld_out, oes);
     if (st != IFLB200_OK) return st;
@@ -848,27 +1003,43 @@ static int run_gemm(const void* a, int64_t ld_a, const void* w, int64_t ld_w, Ge
   // waves x steps x that, plus a fixed cost per wave for prologue and the exposed epilogue.
   p.num_m = (p.M + BM - 1) / BM;
   int bn = g_cfg_tile_n;
-  if (bn == 0) {
+  int split = 1;
+  {
     const int widths[3] = {256, 128, 64};
     const int64_t step_cycles[3] = {830, 690, 590};
     const int64_t steps = (p.K + BK - 1) / BK;
     int64_t best = 0;
+    int best_bn = 0;
     for (int i = 0; i < 3; ++i) {
-      if (widths[i] > 64 && p.N < widths[i]) continue;
+      if (g_cfg_tile_n && widths[i] != g_cfg_tile_n) continue;
+      if (!g_cfg_tile_n && widths[i] > 64 && p.N < widths[i]) continue;
       const int64_t tiles = (int64_t)p.num_m * ((p.N + widths[i] - 1) / widths[i]);
-      const int64_t waves = (tiles + dev->sm_count - 1) / dev->sm_count;
-      const int64_t cost = waves * (steps * step_cycles[i] + 2500);
-      if (bn == 0 || cost < best) {
-        best = cost;
-        bn = widths[i];
+      // split-K over a cluster: one wave of tiles x S CTAs, S a power of two that leaves each
+      // CTA >= 8 K steps and >= 32 columns to reduce.  Parking the partial accumulators, the
+      // cluster barrier and the reduction over distributed shared memory cost about 9-10 us
+      // (measured for S = 2 and 4; S = 8 costs three times that and is only used when forced).
+      for (int sk = 1; sk <= 8; sk *= 2) {
+        if (g_cfg_split_k && sk != g_cfg_split_k) continue;
+        if (sk > 1 && (tiles * sk > dev->sm_count || steps / sk < 8 || widths[i] / sk < 32)) continue;
+        if (sk == 8 && g_cfg_split_k == 0) continue;
+        const int64_t waves = sk > 1 ? 1 : (tiles + dev->sm_count - 1) / dev->sm_count;
+        const int64_t cost = waves * ((steps / sk) * step_cycles[i] + 2500 + (sk > 1 ? 18000 : 0));
+        if (best_bn == 0 || cost < best) {
+          best = cost;
+          best_bn = widths[i];
+          split = sk;
+        }
       }
     }
+    if (best_bn == 0) return IFLB200_ERR_ARG;  // the forced configuration does not fit this problem
+    bn = best_bn;
   }
+  p.split_k = split;
   p.num_n = (p.N + bn - 1) / bn;
   p.num_k = (p.K + BK - 1) / BK;
   p.num_tiles = p.num_m * p.num_n;
   p.group_m = g_cfg_group_m > 0 ? g_cfg_group_m : 8;
-  const int grid = p.num_tiles < dev->sm_count ? p.num_tiles : dev->sm_count;
+  const int grid = split > 1 ? p.num_tiles * split : (p.num_tiles < dev->sm_count ? p.num_tiles : dev->sm_count);
 
   CUtensorMap ta, tw;
   st = make_tensor_map(&ta, a, p.M, p.K, ld_a, BM);
@@ -897,12 +1068,19 @@ extern "C" int iflb200_gemm_set_config(int tile_n, int stages, int group_m) {
   return IFLB200_OK;
 }
 
+extern "C" int iflb200_gemm_set_split_k(int split_k) {
+  if (split_k != 0 && split_k != 1 && split_k != 2 && split_k != 4 && split_k != 8) return IFLB200_ERR_ARG;
+  g_cfg_split_k = split_k;
+  return IFLB200_OK;
+}
+
 extern "C" int iflb200_gemm_set_mode(int mode) {
   // bit 4 (value 16) selects the direct-store epilogue; the low bits the kernel family
   const int family = mode & 15;
-  if (mode < 0 || family > 3 || (mode & ~31)) return IFLB200_ERR_ARG;
+  if (mode < 0 || family > 3 || (mode & ~127)) return IFLB200_ERR_ARG;
   g_cfg_mode = family;
   g_cfg_direct_store = (mode & 16) ? 1 : 0;
+  g_cfg_debug_skip = (mode >> 5) & 3;  // timing experiments only: outputs are not written
   return IFLB200_OK;
 }
 

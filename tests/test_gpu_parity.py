@@ -27,7 +27,12 @@ def ops():
     from instinctflash_b200.kernels import activation, fp8, norm
     from instinctflash_b200.runtime import fp8_pack, torch_fp8_linear
     lib = _lib.lib()   # raises if the CUDA library is missing: no fallback
-    return dict(lib=lib, _lib=_lib, fp8=fp8, norm=norm, act=activation, pack=fp8_pack, lin=torch_fp8_linear)
+    # The bit-exact claims of this module (raw accumulator == the reference's cuBLASLt output,
+    # column shards == full matrix) hold for the unsplit K loop; cluster split-K, which the cost
+    # model picks for deep reductions with few tiles, is tested on its own below.
+    assert lib.iflb200_gemm_set_split_k(1) == 0
+    yield dict(lib=lib, _lib=_lib, fp8=fp8, norm=norm, act=activation, pack=fp8_pack, lin=torch_fp8_linear)
+    lib.iflb200_gemm_set_split_k(0)
 
 
 @pytest.fixture(scope="module")
@@ -340,6 +345,51 @@ def test_gemm_rejects_bad_shapes(ops):
     fp8.gemm(torch.zeros(0, 32, device=DEV, dtype=torch.uint8).view(E4M3),
              fp8.Fp8Weight(torch.zeros(16, 32, device=DEV, dtype=torch.uint8).view(E4M3), torch.ones(16, device=DEV), None),
              torch.empty(0, 16, device=DEV, dtype=torch.bfloat16))       # empty input is a no-op
+
+
+SPLIT_CASES = [("c2_down_slice", 0), ("c2_down_slice", 2), ("c2_down_slice", 8), ("c4_ff2_slice", 0), ("c4_ff2_slice", 4),
+               ("c3_down", 0), ("c3_down", 2), ("siglip", 0)]
+
+
+@pytest.mark.parametrize("name,forced", SPLIT_CASES)
+def test_gemm_cluster_split_k(ops, oracle, name, forced):
+    """Deep-K, few-tile shapes: the CTAs of a cluster each take a K range and sum their fp32
+    partials over distributed shared memory in rank order.  Only the summation order differs from
+    the unsplit kernel: same tolerance class as the GEMM bar, deterministic, and the fused
+    epilogues stay bit-identical to the unfused operators run on the same (split) raw output."""
+    c = dict(cases.gemm_cases())[name]
+    fp8, norm, lib = ops["fp8"], ops["norm"], ops["lib"]
+    a, s = quantise(ops, dev(c["x"]))
+    W = fp8.Fp8Weight(dev(c["wq"]), dev(c["wscale"]), dev(c["bias"]))
+    M, N = a.shape[0], W.w.shape[0]
+    unsplit = torch.empty(M, N, device=DEV, dtype=torch.bfloat16)
+    fp8.gemm(a, W, unsplit)
+    try:
+        assert lib.iflb200_gemm_set_split_k(forced) == 0
+        raw = torch.full((M, N), float("nan"), device=DEV, dtype=torch.bfloat16)
+        fp8.gemm(a, W, raw)
+        no_timeout(ops)
+        again = torch.empty_like(raw)
+        fp8.gemm(a, W, again)
+        assert torch.equal(raw, again)                          # fixed-order reduction: deterministic
+        exact = oracle.gemm_acc(a.cpu(), c["wq"]).to(torch.bfloat16)
+        assert (raw.cpu() != exact).float().mean().item() < 2e-3
+        assert rel_frobenius(raw.float(), exact.float()) < 1e-4
+        assert rel_frobenius(raw.float(), unsplit.float()) < 1e-4
+        y = torch.empty(M, N, device=DEV, dtype=torch.bfloat16)
+        fp8.fp8_linear(a, s, W, y)
+        y_unfused = torch.empty_like(y)
+        norm.dequant_rows(raw, y_unfused, row=s, col=W.scale, bias=W.bias)
+        assert torch.equal(y, y_unfused)
+        assert_gemm_parity(y.float(), oracle.fp8_linear(a.cpu(), s.cpu(), c["wq"], c["wscale"], c["bias"]).float(), name)
+        res = dev(cases.activations(M, N, 79, dtype=torch.float32))
+        r1, r2 = res.clone(), res.clone()
+        norm.residual_norm_quant(r1, delta=raw, delta_row=s, delta_col=W.scale)
+        fp8.fp8_linear_residual(a, s, W, r2)
+        assert torch.equal(r1, r2)
+        no_timeout(ops)
+    finally:
+        lib.iflb200_gemm_set_split_k(1)
 
 
 FULL_SIZE = [("c2_gate_up", 816, 32768, 2048, 1), ("c2_down", 816, 2048, 16384, 1), ("c4_qkv", 4680, 9216, 3072, 3),

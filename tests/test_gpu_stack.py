@@ -41,13 +41,18 @@ def test_stack_matches_cpu_oracle_stack(kind, M):
 
 @pytest.mark.parametrize("M,split", [(50, 1), (7, 1), (100, 1), (50, 8), (64, 3)])
 def test_persistent_stack_against_per_operator_stack(M, split):
+    from instinctflash_b200 import _lib
     from instinctflash_b200.stack_persistent import PersistentExpertStack
     spec = StackSpec("expert", "gemma", 3, M, 1024, 4096, 1536, steps=2, seed=2)
     weights = make_weights(spec, DEV)
     x, attn = make_inputs(spec, DEV)
     ref = LinearStack(spec, weights, DEV)
     ref.load(x, attn)
-    ref.forward()
+    _lib.lib().iflb200_gemm_set_split_k(1)   # the per-operator arm with the unsplit K loop
+    try:
+        ref.forward()
+    finally:
+        _lib.lib().iflb200_gemm_set_split_k(0)
     ps = PersistentExpertStack(spec, weights, DEV, down_split_k=split)
     ps.load(x)
     ps.forward()
