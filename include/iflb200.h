@@ -272,6 +272,13 @@ IFLB200_API int iflb200_gemm_set_split_k(int split_k);
 /* Row kernels: force the number of threads that share one row (power of two, 32..1024;
  * 0 = heuristic).  For experiments and tests.  No reference counterpart. */
 IFLB200_API int iflb200_row_set_group(int threads_per_row);
+/* Programmatic dependent launch: a kernel launched this way may be scheduled while its
+ * predecessor in the stream drains; it waits for the predecessor's results before its first
+ * access to memory a kernel can write, and the GEMM warms L2 with its first weight boxes
+ * meanwhile.  1 (default) = for calls over at most 2048 activation rows (short kernels, where
+ * it shortens a layer stack; with thousands of rows it was measured slower), 0 = never,
+ * 2 = always.  Results are identical in every mode.  No reference counterpart. */
+IFLB200_API int iflb200_set_dependent_launch(int enable);
 /* Kernel family: 0 = heuristic, 1 = single-CTA tiles only, 2 / 3 = 256x256 tiles on CTA pairs
  * (cta_group::2) with one / two tensor-memory accumulators; add 16 to store the epilogue
  * straight from registers instead of through shared memory and TMA.  For experiments and

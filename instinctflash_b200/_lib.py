@@ -49,6 +49,7 @@ SIGNATURES = {
     "iflb200_gemm_take_timeout_record": (_i, [ctypes.POINTER(ctypes.c_uint32), _p]),
     "iflb200_gemm_set_config": (_i, [_i, _i, _i]),
     "iflb200_gemm_set_mode": (_i, [_i]),
+    "iflb200_set_dependent_launch": (_i, [_i]),
     "iflb200_gemm_set_split_k": (_i, [_i]),
     "iflb200_row_set_group": (_i, [_i]),
     "iflb200_gemm_debug_words": (_i, [ctypes.POINTER(ctypes.c_uint32), _p]),

@@ -23,6 +23,7 @@
 #include <string.h>
 
 #include "../../include/iflb200.h"
+#include "launch.cuh"
 #include "rowmath.cuh"
 
 namespace iflb200 {
@@ -30,6 +31,7 @@ namespace iflb200 {
 constexpr int BM = 128;
 constexpr int BK = 128;  // bytes == e4m3 elements per stage along K
 constexpr int kGemmThreads = 320;  // TMA warp, MMA warp, eight epilogue warps
+constexpr int kPrefetchSteps = 8;  // W boxes warmed in L2 ahead of the grid dependency wait
 constexpr int kEpilogueWarps = 8;   // two per TMEM lane quadrant, each draining half of the columns
 constexpr uint64_t kWaitBudgetNs = 2000000000ull;  // 2 s per wait, then abort
 
@@ -397,8 +399,25 @@ gemm_fp8_tc5_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
 
+  // Everything above touched no global memory.  While the kernel before this one in the stream
+  // drains, pull the first W boxes of this CTA's first tile towards L2 (a prefetch cannot read
+  // stale data into the kernel: the loads proper are issued after the dependency wait and L2 is
+  // the coherence point), then wait for that kernel's results.
+  if (warp == 0 && lane == 0 && tile_first < p.num_tiles) {
+    int m_blk, n_blk;
+    tile_coords(p, tile_first, m_blk, n_blk);
+    const int kb_end = kb1 < kb0 + kPrefetchSteps ? kb1 : kb0 + kPrefetchSteps;
+    for (int kb = kb0; kb < kb_end; ++kb) tma_prefetch_l2_2d(&tm_w, kb * BK, n_blk * BN);
+  }
+
   if (warp == 0) {
     // ------------------------------------------------------------------ TMA producer
+    // The one thread that issues loads waits for the kernel before this one; the epilogue warps
+    // are ordered behind it through the barriers (and re-check below), the MMA warp touches no
+    // global memory.  Fewer waiting threads matter: a CTA that became resident early sits beside
+    // a kernel that is still running.
+    if (lane == 0) grid_dependency_wait();
+    __syncwarp();
     int stage = 0;
     uint32_t phase = 0;
     uint32_t armed = 0;        // stages armed at least once
@@ -427,6 +446,10 @@ gemm_fp8_tc5_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
         }
       }
     }
+    // This CTA's last loads are in flight: the next kernel in the stream may be scheduled now
+    // (it becomes resident as CTAs of this grid leave and waits for the grid to complete).
+    // Not earlier: CTAs parked at their dependency wait for the length of a long GEMM slow it.
+    grid_launch_dependents();
     // Drain: every load this warp issued must have landed before the CTA's shared memory can
     // go away.  Normal exit: the consumer has already waited on all of them, these return at
     // once.  Abort: bounded.
@@ -501,6 +524,7 @@ gemm_fp8_tc5_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
                                                 (3u << 24) | (4u << 16) | (it & 0xFFFF)));
       if (!ok) break;
       tc_fence_after();
+      if (it == 0) grid_dependency_wait();  // returns at once: the loads behind this tile waited already
       const int m = m_blk * BM + quad * 32 + lane;
       const bool row_ok = m < p.M;
       const float rs = (row_ok && p.row) ? __ldg(p.row + (int64_t)m * p.row_stride) : 1.0f;
@@ -684,6 +708,7 @@ gemm_fp8_tc5_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_
   cluster_sync_all();  // barriers of both CTAs initialised before any remote signal
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
+  grid_dependency_wait();
   if (pair_id == 0 && threadIdx.x == 0) g_pair_debug[rank] = tmem_base;
 
   if (warp == 0) {
@@ -715,6 +740,7 @@ gemm_fp8_tc5_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_
         }
       }
     }
+    grid_launch_dependents();  // last loads issued: the next kernel may be scheduled
   } else if (warp == 1) {
     // ------------------------------------------------------------------ MMA issuer (leader only)
     if (leader) {
@@ -896,6 +922,7 @@ static int device_info(DeviceInfo** out) {
   return IFLB200_OK;
 }
 
+int g_dependent_launch = 1;
 static int g_cfg_tile_n = 0, g_cfg_stages = 0, g_cfg_group_m = 0;
 static int g_cfg_split_k = 0;  // 0: cost model, 1: never split K, 2/4/8: forced
 static int g_cfg_debug_skip = 0;
@@ -915,24 +942,9 @@ static int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tw, const CUten
     if (e != cudaSuccess) return (int)e;
     attr_set[dev] = true;
   }
-  if (p.split_k > 1) {
-    cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3(grid);
-    cfg.blockDim = dim3(kGemmThreads);
-    cfg.dynamicSmemBytes = L::kDynamic;
-    cfg.stream = s;
-    cudaLaunchAttribute attr[1];
-    attr[0].id = cudaLaunchAttributeClusterDimension;
-    attr[0].val.clusterDim.x = p.split_k;
-    attr[0].val.clusterDim.y = 1;
-    attr[0].val.clusterDim.z = 1;
-    cfg.attrs = attr;
-    cfg.numAttrs = 1;
-    const cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_fp8_tc5_kernel<BN, STAGES>, ta, tw, to, p);
-    return e != cudaSuccess ? (int)e : (int)cudaGetLastError();
-  }
-  gemm_fp8_tc5_kernel<BN, STAGES><<<grid, kGemmThreads, L::kDynamic, s>>>(ta, tw, to, p);
-  return (int)cudaGetLastError();
+  const cudaError_t e = launch_dep(gemm_fp8_tc5_kernel<BN, STAGES>, dim3(grid), dim3(kGemmThreads), L::kDynamic, s,
+                                   p.split_k, dependent_launch_for(p.M), ta, tw, to, p);
+  return e != cudaSuccess ? (int)e : (int)cudaGetLastError();
 }
 
 template <int BN, int STAGES, int ACC>
@@ -948,8 +960,9 @@ static int launch_gemm_pair(const CUtensorMap& ta, const CUtensorMap& tw, const 
     if (e != cudaSuccess) return (int)e;
     attr_set[dev] = true;
   }
-  gemm_fp8_tc5_pair_kernel<BN, STAGES, ACC><<<grid, kGemmThreads, L::kDynamic, s>>>(ta, tw, to, p);
-  return (int)cudaGetLastError();
+  const cudaError_t e = launch_dep(gemm_fp8_tc5_pair_kernel<BN, STAGES, ACC>, dim3(grid), dim3(kGemmThreads),
+                                   L::kDynamic, s, 1, dependent_launch_for(p.M), ta, tw, to, p);
+  return e != cudaSuccess ? (int)e : (int)cudaGetLastError();
 }
 
 static int run_gemm(const void* a, int64_t ld_a, const void* w, int64_t ld_w, GemmParams p, void* stream) {
@@ -1071,6 +1084,12 @@ extern "C" int iflb200_gemm_set_config(int tile_n, int stages, int group_m) {
 extern "C" int iflb200_gemm_set_split_k(int split_k) {
   if (split_k != 0 && split_k != 1 && split_k != 2 && split_k != 4 && split_k != 8) return IFLB200_ERR_ARG;
   g_cfg_split_k = split_k;
+  return IFLB200_OK;
+}
+
+extern "C" int iflb200_set_dependent_launch(int enable) {
+  if (enable < 0 || enable > 2) return IFLB200_ERR_ARG;
+  g_dependent_launch = enable;
   return IFLB200_OK;
 }
 

@@ -120,6 +120,26 @@ __device__ __forceinline__ void prefetch_tensormap(const void* tensor_map) {
   asm volatile("prefetch.tensormap [%0];" ::"l"(tensor_map) : "memory");
 }
 
+// Warm L2 with one box of a tiled tensor.  L2 is the coherence point of device memory, so a
+// line prefetched before its producer has finished is updated by the producer's later writes:
+// safe to issue ahead of a grid dependency.
+__device__ __forceinline__ void tma_prefetch_l2_2d(const void* tensor_map, int x, int y) {
+  asm volatile("cp.async.bulk.prefetch.tensor.2d.L2.global.tile [%0, {%1, %2}];" ::"l"(tensor_map), "r"(x), "r"(y)
+               : "memory");
+}
+
+// ---------------------------------------------------------------------------------------------
+// Programmatic dependent launch.  A kernel launched with the programmatic-stream-serialization
+// attribute may start while its predecessor in the stream still runs; grid_dependency_wait()
+// returns once the predecessor has completed and its writes are visible.  Every global access
+// that can alias anything another kernel writes must come after it.  Both are no-ops in a
+// kernel launched without the attribute.
+// ---------------------------------------------------------------------------------------------
+__device__ __forceinline__ void grid_dependency_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void grid_launch_dependents() {
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+}
+
 // ---------------------------------------------------------------------------------------------
 // tcgen05: tensor memory and the 5th-generation MMA (cta_group::1 forms)
 // ---------------------------------------------------------------------------------------------

@@ -5,6 +5,7 @@
 #include <cuda_runtime.h>
 
 #include "../../include/iflb200.h"
+#include "launch.cuh"
 #include "rowmath.cuh"
 
 // The file compiles as one translation unit, or as three (IFLB200_ROW_PART = 0, 1, 2) so that
@@ -15,6 +16,16 @@
 #endif
 
 namespace iflb200 {
+
+// One thread waits for the kernel before this one in the stream, the others park at the CTA
+// barrier: a CTA that became resident early costs the still-running kernel next to it nothing.
+__device__ __forceinline__ void row_dependency_wait() {
+  if (threadIdx.x == 0) grid_dependency_wait();
+  __syncthreads();
+}
+
+// Row kernels let the next kernel in the stream be scheduled as soon as their last CTAs start.
+__device__ __forceinline__ void row_trigger() { grid_launch_dependents(); }
 
 // CTAs have 256 threads.  A row is owned by a group of TPR threads, each holding IT chunks of 8
 // elements: narrow rows share a CTA (TPR = 32 / 64 / 128, one chunk per thread), wide rows take
@@ -243,6 +254,8 @@ struct RowQuantArgs {
 template <typename XT, int TPR, int IT, bool PLAIN, bool FAST>
 __global__ void __launch_bounds__(kRowThreads, PLAIN ? (IT <= 2 ? 4 : 3) : row_min_blocks<IT>())
 row_quant_kernel(const RowQuantArgs a) {
+  row_dependency_wait();  // inputs may come from the kernel before this one in the stream
+  row_trigger();
   __shared__ float red[kRowThreads / 32];
   const int t = threadIdx.x % TPR;
   const int m = blockIdx.x * (kRowThreads / TPR) + threadIdx.x / TPR;
@@ -347,6 +360,8 @@ struct GatedArgs {
 template <typename XT, int TPR, int IT, bool FAST>
 __global__ void __launch_bounds__(kRowThreads, row_min_blocks<IT>())
 gated_act_quant_kernel(const GatedArgs a) {
+  row_dependency_wait();  // inputs may come from the kernel before this one in the stream
+  row_trigger();
   __shared__ float red[kRowThreads / 32];
   const int t = threadIdx.x % TPR;
   const int m = blockIdx.x * (kRowThreads / TPR) + threadIdx.x / TPR;
@@ -433,6 +448,8 @@ struct DequantArgs {
 
 template <typename XT, bool FAST>
 __global__ void __launch_bounds__(256) dequant_rows_kernel(const DequantArgs a) {
+  row_dependency_wait();  // inputs may come from the kernel before this one in the stream
+  row_trigger();
   const int m = blockIdx.y;
   const int c0 = (blockIdx.x * 256 + threadIdx.x) * 8;
   if (c0 >= a.D) return;
@@ -491,6 +508,8 @@ __device__ __forceinline__ float round_through<__nv_bfloat16>(float x) {
 template <typename RT, int TPR, int IT, bool FAST>
 __global__ void __launch_bounds__(kRowThreads, row_min_blocks<IT>())
 residual_norm_quant_kernel(const ResNormArgs a) {
+  row_dependency_wait();  // inputs may come from the kernel before this one in the stream
+  row_trigger();
   __shared__ float red[3][kRowThreads / 32];
   const int t = threadIdx.x % TPR;
   const int m = blockIdx.x * (kRowThreads / TPR) + threadIdx.x / TPR;
@@ -622,6 +641,8 @@ constexpr int kPackMaxCtas = 1024;
 // their bits, and every NaN pattern is larger than infinity, so NaN propagates.
 __global__ void __launch_bounds__(kPackThreads)
 amax_partial_kernel(const uint16_t* __restrict__ x, int64_t n, uint32_t* __restrict__ partial) {
+  row_dependency_wait();  // inputs may come from the kernel before this one in the stream
+  row_trigger();
   __shared__ uint32_t red[kPackThreads / 32];
   uint32_t best = 0;
   const int64_t nvec = n / 8;
@@ -665,6 +686,8 @@ __global__ void __launch_bounds__(kPackThreads)
 pack_kernel(const uint16_t* __restrict__ x, int64_t n, const uint32_t* __restrict__ partial,
             int n_partial, const float* __restrict__ scale_in, float* __restrict__ scale_out,
             uint8_t* __restrict__ q) {
+  row_dependency_wait();  // inputs may come from the kernel before this one in the stream
+  row_trigger();
   __shared__ uint32_t red[kPackThreads / 32];
   __shared__ float s_scale;
   if (n_partial > 0) {
@@ -786,8 +809,8 @@ static void launch_row_quant(RowQuantArgs a, bool fast, cudaStream_t s) {
   const bool plain = !(a.row || a.col || a.bias || a.gelu);
   if (!fast) {
     a.iters = slow_geom(a.K).iters;
-    if (plain) row_quant_kernel<XT, kRowThreads, 8, true, false><<<a.M, kRowThreads, 0, s>>>(a);
-    else row_quant_kernel<XT, kRowThreads, 8, false, false><<<a.M, kRowThreads, 0, s>>>(a);
+    if (plain) launch_dep(row_quant_kernel<XT, kRowThreads, 8, true, false>, dim3(a.M), dim3(kRowThreads), 0, s, 1, dependent_launch_for(a.M), a);
+    else launch_dep(row_quant_kernel<XT, kRowThreads, 8, false, false>, dim3(a.M), dim3(kRowThreads), 0, s, 1, dependent_launch_for(a.M), a);
     return;
   }
   const RowGeom g = pick_geom(a.K);
@@ -795,15 +818,15 @@ static void launch_row_quant(RowQuantArgs a, bool fast, cudaStream_t s) {
   dispatch_geom(g, [&](auto tpr, auto it) {
     constexpr int TPR = decltype(tpr)::value, IT = decltype(it)::value;
     const int grid = (a.M + kRowThreads / TPR - 1) / (kRowThreads / TPR);
-    if (plain) row_quant_kernel<XT, TPR, IT, true, true><<<grid, kRowThreads, 0, s>>>(a);
-    else row_quant_kernel<XT, TPR, IT, false, true><<<grid, kRowThreads, 0, s>>>(a);
+    if (plain) launch_dep(row_quant_kernel<XT, TPR, IT, true, true>, dim3(grid), dim3(kRowThreads), 0, s, 1, dependent_launch_for(a.M), a);
+    else launch_dep(row_quant_kernel<XT, TPR, IT, false, true>, dim3(grid), dim3(kRowThreads), 0, s, 1, dependent_launch_for(a.M), a);
   });
 }
 template <typename XT>
 static void launch_gated(GatedArgs a, bool fast, cudaStream_t s) {
   if (!fast) {
     a.iters = slow_geom(a.F).iters;
-    gated_act_quant_kernel<XT, kRowThreads, 8, false><<<a.M, kRowThreads, 0, s>>>(a);
+    launch_dep(gated_act_quant_kernel<XT, kRowThreads, 8, false>, dim3(a.M), dim3(kRowThreads), 0, s, 1, dependent_launch_for(a.M), a);
     return;
   }
   const RowGeom g = pick_geom(a.F);
@@ -811,14 +834,14 @@ static void launch_gated(GatedArgs a, bool fast, cudaStream_t s) {
   dispatch_geom(g, [&](auto tpr, auto it) {
     constexpr int TPR = decltype(tpr)::value, IT = decltype(it)::value;
     const int grid = (a.M + kRowThreads / TPR - 1) / (kRowThreads / TPR);
-    gated_act_quant_kernel<XT, TPR, IT, true><<<grid, kRowThreads, 0, s>>>(a);
+    launch_dep(gated_act_quant_kernel<XT, TPR, IT, true>, dim3(grid), dim3(kRowThreads), 0, s, 1, dependent_launch_for(a.M), a);
   });
 }
 template <typename RT>
 static void launch_resnorm(ResNormArgs a, bool fast, cudaStream_t s) {
   if (!fast) {
     a.iters = slow_geom(a.D).iters;
-    residual_norm_quant_kernel<RT, kRowThreads, 8, false><<<a.M, kRowThreads, 0, s>>>(a);
+    launch_dep(residual_norm_quant_kernel<RT, kRowThreads, 8, false>, dim3(a.M), dim3(kRowThreads), 0, s, 1, dependent_launch_for(a.M), a);
     return;
   }
   const RowGeom g = pick_geom(a.D);
@@ -826,7 +849,7 @@ static void launch_resnorm(ResNormArgs a, bool fast, cudaStream_t s) {
   dispatch_geom(g, [&](auto tpr, auto it) {
     constexpr int TPR = decltype(tpr)::value, IT = decltype(it)::value;
     const int grid = (a.M + kRowThreads / TPR - 1) / (kRowThreads / TPR);
-    residual_norm_quant_kernel<RT, TPR, IT, true><<<grid, kRowThreads, 0, s>>>(a);
+    launch_dep(residual_norm_quant_kernel<RT, TPR, IT, true>, dim3(grid), dim3(kRowThreads), 0, s, 1, dependent_launch_for(a.M), a);
   });
 }
 
@@ -938,13 +961,13 @@ extern "C" int iflb200_dequant_rows(const void* x, int x_dtype, int64_t ld_x, in
     b.row = row ? row + m0 : nullptr;
     const dim3 grid(chunks, rows);
     if (fast) {
-      if (x_dtype == IFLB200_BF16) dequant_rows_kernel<__nv_bfloat16, true><<<grid, 256, 0, s>>>(b);
-      else if (x_dtype == IFLB200_F16) dequant_rows_kernel<__half, true><<<grid, 256, 0, s>>>(b);
-      else dequant_rows_kernel<float, true><<<grid, 256, 0, s>>>(b);
+      if (x_dtype == IFLB200_BF16) launch_dep(dequant_rows_kernel<__nv_bfloat16, true>, dim3(grid), dim3(256), 0, s, 1, dependent_launch_for(b.M), b);
+      else if (x_dtype == IFLB200_F16) launch_dep(dequant_rows_kernel<__half, true>, dim3(grid), dim3(256), 0, s, 1, dependent_launch_for(b.M), b);
+      else launch_dep(dequant_rows_kernel<float, true>, dim3(grid), dim3(256), 0, s, 1, dependent_launch_for(b.M), b);
     } else {
-      if (x_dtype == IFLB200_BF16) dequant_rows_kernel<__nv_bfloat16, false><<<grid, 256, 0, s>>>(b);
-      else if (x_dtype == IFLB200_F16) dequant_rows_kernel<__half, false><<<grid, 256, 0, s>>>(b);
-      else dequant_rows_kernel<float, false><<<grid, 256, 0, s>>>(b);
+      if (x_dtype == IFLB200_BF16) launch_dep(dequant_rows_kernel<__nv_bfloat16, false>, dim3(grid), dim3(256), 0, s, 1, dependent_launch_for(b.M), b);
+      else if (x_dtype == IFLB200_F16) launch_dep(dequant_rows_kernel<__half, false>, dim3(grid), dim3(256), 0, s, 1, dependent_launch_for(b.M), b);
+      else launch_dep(dequant_rows_kernel<float, false>, dim3(grid), dim3(256), 0, s, 1, dependent_launch_for(b.M), b);
     }
   }
   return (int)cudaGetLastError();
@@ -1019,8 +1042,8 @@ extern "C" int iflb200_dynamic_pack_bf16_e4m3(const void* x, int64_t n, void* q,
   const int grid = pack_grid(n);
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
   uint32_t* partial = reinterpret_cast<uint32_t*>(workspace);
-  amax_partial_kernel<<<grid, kPackThreads, 0, s>>>(reinterpret_cast<const uint16_t*>(x), n, partial);
-  pack_kernel<<<grid, kPackThreads, 0, s>>>(reinterpret_cast<const uint16_t*>(x), n, partial, grid,
+  launch_dep(amax_partial_kernel, dim3(grid), dim3(kPackThreads), 0, s, 1, dependent_launch_for(n >> 12), reinterpret_cast<const uint16_t*>(x), n, partial);
+  launch_dep(pack_kernel, dim3(grid), dim3(kPackThreads), 0, s, 1, dependent_launch_for(n >> 12), reinterpret_cast<const uint16_t*>(x), n, partial, grid,
                                             nullptr, scale, reinterpret_cast<uint8_t*>(q));
   return (int)cudaGetLastError();
 }
@@ -1031,7 +1054,7 @@ extern "C" int iflb200_pack_bf16_e4m3(const void* x, int64_t n, const float* sca
   if (n == 0) return IFLB200_OK;
   if (!x || !q) return IFLB200_ERR_ARG;
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
-  pack_kernel<<<pack_grid(n), kPackThreads, 0, s>>>(reinterpret_cast<const uint16_t*>(x), n, nullptr,
+  launch_dep(pack_kernel, dim3(pack_grid(n)), dim3(kPackThreads), 0, s, 1, dependent_launch_for(n >> 12), reinterpret_cast<const uint16_t*>(x), n, nullptr,
                                                     0, scale, nullptr, reinterpret_cast<uint8_t*>(q));
   return (int)cudaGetLastError();
 }
@@ -1083,8 +1106,8 @@ extern "C" int iflb200_dynamic_pack_bf16_e4m3_noalloc(const void* x, int64_t n, 
   if (st != IFLB200_OK) return st;
   const int grid = pack_grid(n);  // <= kPackMaxCtas words of scratch, all written before they are read
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
-  amax_partial_kernel<<<grid, kPackThreads, 0, s>>>(reinterpret_cast<const uint16_t*>(x), n, partial);
-  pack_kernel<<<grid, kPackThreads, 0, s>>>(reinterpret_cast<const uint16_t*>(x), n, partial, grid, nullptr,
+  launch_dep(amax_partial_kernel, dim3(grid), dim3(kPackThreads), 0, s, 1, dependent_launch_for(n >> 12), reinterpret_cast<const uint16_t*>(x), n, partial);
+  launch_dep(pack_kernel, dim3(grid), dim3(kPackThreads), 0, s, 1, dependent_launch_for(n >> 12), reinterpret_cast<const uint16_t*>(x), n, partial, grid, nullptr,
                                             scale, reinterpret_cast<uint8_t*>(q));
   return (int)cudaGetLastError();
 }
