@@ -110,6 +110,44 @@ IFLB200_API int iflb200_gated_act_quant(const void* gu, int gu_dtype, int64_t ld
                             void* q, int64_t ld_q, float* qs, void* stream);
 
 /*
+ * Split of a raw fused QKV accumulator [Q heads | K heads | V heads] (head_dim wide each):
+ * dequantisation (row, col, bias; each optional), per-head RMS norm of Q and K (q_norm and
+ * k_norm [head_dim], both or neither), rotary embedding of Q and K with pairs (i, i + head_dim/2)
+ * and angle pos[t, sections[i]] * inv_freq[i] (inv_freq null: no rotation; sections null:
+ * column 0), and the store: Q at q_out[t, h], K and V at row kv_base + t of their caches, where
+ * kv_base is read from the device when kv_base_dev is given.  Strides are in elements; pos is
+ * a float32 table with row stride ld_pos.  head_dim even, <= 512.
+ * Replaces: instinctflash/kernels/rope.py:22-114 (_qkv_split_kernel, qkv_split).
+ */
+IFLB200_API int iflb200_qkv_split(const void* qkv, int qkv_dtype, int64_t ld_qkv, int T, int heads_q,
+                      int heads_kv, int head_dim, const float* row, const float* col,
+                      const float* bias, const float* q_norm, const float* k_norm, float eps,
+                      const float* inv_freq, const float* pos, int64_t ld_pos,
+                      const int32_t* sections, const int32_t* kv_base_dev, int kv_base,
+                      void* q_out, int64_t q_stride_t, int64_t q_stride_h,
+                      void* k_out, int64_t k_stride_t, int64_t k_stride_h,
+                      void* v_out, int64_t v_stride_t, int64_t v_stride_h, int out_dtype,
+                      void* stream);
+
+/*
+ * Wan-DiT projection consumer on a raw accumulator [Q | K | V] (each heads*head_dim wide; K and
+ * V present when their pools are given): dequantisation, RMS norm of Q and of K over the FULL
+ * width (q_norm / k_norm [heads*head_dim], each optional), rotary embedding of adjacent pairs
+ * (2j, 2j+1) of every head by pos[row % tokens, sections[j]] * inv_freq[j], dense store of Q
+ * and scatter of K and V to pool[row / tokens, slots[row % tokens]] (slots null: the token).
+ * heads*head_dim <= 8192, head_dim even, <= 512.
+ * Replaces: instinctflash/kernels/wan.py:20-104 (_part, _wan_qkv_kernel, wan_qkv).
+ */
+IFLB200_API int iflb200_wan_qkv(const void* raw, int raw_dtype, int64_t ld_raw, int rows, int tokens,
+                    int heads, int head_dim, const float* row, const float* col,
+                    const float* bias, const float* q_norm, const float* k_norm, float eps,
+                    const float* inv_freq, const float* pos, int64_t ld_pos,
+                    const int32_t* sections, const int32_t* slots,
+                    void* q_out, int64_t ld_q, void* k_pool, int64_t k_stride_b, int64_t k_stride_s,
+                    void* v_pool, int64_t v_stride_b, int64_t v_stride_s, int out_dtype,
+                    void* stream);
+
+/*
  * Residual update + RMS/LayerNorm + affine + adaptive modulation + per-token quantiser,
  * one row per thread group (the MoE router tail of the reference kernel is not part of
  * this path).

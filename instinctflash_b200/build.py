@@ -20,6 +20,7 @@ LIBRARY = PKG / "libiflb200.so"
 # (source, extra defines, object stem): row_ops.cu is compiled as three translation units in parallel
 SOURCES = (("gemm_fp8_sm100.cu", (), "gemm_fp8_sm100"),
            ("stack_persistent.cu", (), "stack_persistent"),
+           ("qkv_ops.cu", (), "qkv_ops"),
            ("row_ops.cu", ("-DIFLB200_ROW_PART=0",), "row_ops_quant"),
            ("row_ops.cu", ("-DIFLB200_ROW_PART=1",), "row_ops_gated_pack"),
            ("row_ops.cu", ("-DIFLB200_ROW_PART=2",), "row_ops_resnorm"))

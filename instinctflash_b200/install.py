@@ -12,7 +12,7 @@ from __future__ import annotations
 import importlib
 import sys
 
-from .kernels import activation, fp8, norm
+from .kernels import activation, fp8, norm, rope, wan
 
 REPLACEMENTS = {
     "gemm": fp8.gemm,
@@ -22,10 +22,15 @@ REPLACEMENTS = {
     "dequant_rows": norm.dequant_rows,
     "residual_norm_quant": norm.residual_norm_quant,
     "gated_act_quant": activation.gated_act_quant,
+    "qkv_split": rope.qkv_split,
+    "rope_inv_freq": rope.rope_inv_freq,
+    "wan_qkv": wan.wan_qkv,
 }
 KERNEL_MODULES = {"instinctflash.kernels.fp8": ("gemm", "quantize_weight", "Fp8Weight"),
                   "instinctflash.kernels.norm": ("row_quant", "dequant_rows", "residual_norm_quant"),
-                  "instinctflash.kernels.activation": ("gated_act_quant",)}
+                  "instinctflash.kernels.activation": ("gated_act_quant",),
+                  "instinctflash.kernels.rope": ("qkv_split", "rope_inv_freq"),
+                  "instinctflash.kernels.wan": ("wan_qkv",)}
 ENGINE_MODULES = tuple(f"instinctflash.engines.{fam}.engine" for fam in ("pi05", "vla4", "vla2", "groot_n17", "wan_va"))
 
 

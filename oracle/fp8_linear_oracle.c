@@ -13,6 +13,8 @@
  *   oracle_fp8_linear           fp8.py:50-53 + norm.py:162-175 (and the exact-rounding form)
  *   oracle_pack_tensor          instinctflash/runtime/fp8_pack.py:27-92
  *   oracle_e4m3_encode          instinctflash/runtime/fp8_pack.py:12-23 (integer RNE cast)
+ *   oracle_qkv_split            instinctflash/kernels/rope.py:22-83
+ *   oracle_wan_qkv              instinctflash/kernels/wan.py:20-82
  *
  * Known, documented differences from the GPU reference: the GPU uses the approximate PTX
  * instructions div.full.f32, ex2.approx.f32 and rsqrt.approx.ftz.f32; here they are IEEE
@@ -21,7 +23,9 @@
  * kernels with this oracle allow exactly that and count it, while the bit-exact comparison is
  * made against vectors recorded from the reference's own kernels on a B200 (tests/golden).
  * The row sums of the normalisation are accumulated in double here (the GPU order is
- * layout-specific), so normalised outputs are tolerance-class by construction.
+ * layout-specific), so normalised outputs are tolerance-class by construction.  The rotary
+ * consumers take sine and cosine from the C library where the GPU has its own single-precision
+ * routines (both within a few ulp of the true value): rotated outputs are tolerance-class too.
  */
 #include <math.h>
 #include <stdint.h>
@@ -349,5 +353,110 @@ ORACLE_API void oracle_pack_tensor(const uint16_t* x, int64_t n, int dynamic, fl
     float d = u2f((uint32_t)x[i] << 16) / s;
     if (d == d) d = d < -448.0f ? -448.0f : (d > 448.0f ? 448.0f : d);
     q[i] = oracle_e4m3_encode(d);
+  }
+}
+
+/* ------------------------------------------------------------------ QKV consumers */
+static inline float rms_scale(double sum_sq, int n, float eps) {
+  const float mean = (float)sum_sq / (float)n;
+  return 1.0f / sqrtf(mean + eps);
+}
+
+/* (a, b) <- (a cos - b sin, b cos + a sin); the sine products are rounded, the cosine products
+ * fused, as the reference's kernels compile (rope.py:67-69, wan.py:41-43). */
+static inline void rotate_pair(float* a, float* b, float cs, float sn) {
+  const float bs = *b * sn, as = *a * sn;
+  const float na = fmaf(*a, cs, -bs), nb = fmaf(*b, cs, as);
+  *a = na; *b = nb;
+}
+
+static inline float dequant_elem(float raw, const float* row_scale, const float* col, const float* bias,
+                                 int64_t c) {
+  chain_t ch; ch_init(&ch, raw);
+  if (row_scale) ch_mul(&ch, *row_scale);
+  if (col) ch_mul(&ch, col[c]);
+  if (bias) ch_add(&ch, bias[c]);
+  return ch_done(&ch);
+}
+
+/* instinctflash/kernels/rope.py:22-83.  qkv [T, (HQ+2*HKV)*HD] fp32 (widened); q [T,HQ,HD],
+ * k/v [S,HKV,HD] dense fp32 holding values rounded to out_dtype; rows kv_base + t written. */
+ORACLE_API void oracle_qkv_split(const float* qkv, int64_t ld, int T, int HQ, int HKV, int HD,
+                                 const float* row, const float* col, const float* bias,
+                                 const float* q_norm, const float* k_norm, float eps,
+                                 const float* inv_freq, const float* pos, int64_t ld_pos,
+                                 const int32_t* sections, int kv_base, float* q, float* k, float* v,
+                                 int out_dtype) {
+  const int half = HD / 2, heads = HQ + 2 * HKV;
+#pragma omp parallel for schedule(static)
+  for (int t = 0; t < T; ++t) {
+    float* x = (float*)malloc(sizeof(float) * (size_t)HD);
+    for (int h = 0; h < heads; ++h) {
+      const float* src = qkv + (int64_t)t * ld + (int64_t)h * HD;
+      for (int i = 0; i < HD; ++i)
+        x[i] = dequant_elem(src[i], row ? row + t : NULL, col, bias, (int64_t)h * HD + i);
+      if (h < HQ + HKV) {
+        const float* nw = h < HQ ? q_norm : k_norm;
+        if (nw) {
+          double ss = 0.0;
+          for (int i = 0; i < HD; ++i) ss += (double)x[i] * x[i];
+          const float rs = rms_scale(ss, HD, eps);
+          for (int i = 0; i < HD; ++i) x[i] = (x[i] * rs) * nw[i];
+        }
+        if (inv_freq) {
+          for (int i = 0; i < half; ++i) {
+            const float ang = pos[(int64_t)t * ld_pos + (sections ? sections[i] : 0)] * inv_freq[i];
+            rotate_pair(&x[i], &x[half + i], cosf(ang), sinf(ang));
+          }
+        }
+      }
+      float* dst;
+      if (h < HQ) dst = q + ((int64_t)t * HQ + h) * HD;
+      else if (h < HQ + HKV) dst = k + ((int64_t)(kv_base + t) * HKV + (h - HQ)) * HD;
+      else dst = v + ((int64_t)(kv_base + t) * HKV + (h - HQ - HKV)) * HD;
+      for (int i = 0; i < HD; ++i) dst[i] = round_to(x[i], out_dtype);
+    }
+    free(x);
+  }
+}
+
+/* instinctflash/kernels/wan.py:20-82.  raw [rows, parts*D] fp32; q [rows, D]; pools [B, S, D]
+ * dense fp32 (values rounded to out_dtype), written at pool[row / tokens, slots[row % tokens]]. */
+ORACLE_API void oracle_wan_qkv(const float* raw, int64_t ld, int rows, int tokens, int H, int HD, int parts,
+                               const float* row, const float* col, const float* bias,
+                               const float* q_norm, const float* k_norm, float eps,
+                               const float* inv_freq, const float* pos, int64_t ld_pos,
+                               const int32_t* sections, const int32_t* slots, int S, float* q,
+                               float* kp, float* vp, int out_dtype) {
+  const int D = H * HD, half = HD / 2;
+#pragma omp parallel for schedule(static)
+  for (int r = 0; r < rows; ++r) {
+    float* x = (float*)malloc(sizeof(float) * (size_t)D);
+    const int b = r / tokens, t = r % tokens;
+    for (int part = 0; part < parts; ++part) {
+      const int64_t col0 = (int64_t)part * D;
+      const float* src = raw + (int64_t)r * ld + col0;
+      for (int d = 0; d < D; ++d)
+        x[d] = dequant_elem(src[d], row ? row + r : NULL, col ? col + col0 : NULL, bias ? bias + col0 : NULL, d);
+      const float* nw = part == 0 ? q_norm : (part == 1 ? k_norm : NULL);
+      if (nw) {
+        double ss = 0.0;
+        for (int d = 0; d < D; ++d) ss += (double)x[d] * x[d];
+        const float rs = rms_scale(ss, D, eps);
+        for (int d = 0; d < D; ++d) x[d] = (x[d] * rs) * nw[d];
+      }
+      if (inv_freq && part < 2) {
+        for (int h = 0; h < H; ++h)
+          for (int j = 0; j < half; ++j) {
+            const float ang = pos[(int64_t)t * ld_pos + sections[j]] * inv_freq[j];
+            rotate_pair(&x[h * HD + 2 * j], &x[h * HD + 2 * j + 1], cosf(ang), sinf(ang));
+          }
+      }
+      const int slot = slots ? slots[t] : t;
+      float* dst = part == 0 ? q + (int64_t)r * D
+                             : (part == 1 ? kp : vp) + ((int64_t)b * S + slot) * D;
+      for (int d = 0; d < D; ++d) dst[d] = round_to(x[d], out_dtype);
+    }
+    free(x);
   }
 }

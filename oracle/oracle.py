@@ -150,6 +150,50 @@ def residual_norm_quant(res, *, delta=None, delta_row=None, delta_col=None, bias
                 y=None if y is None else torch.from_numpy(y).to(y_dtype))
 
 
+def _i32(t):
+    return None if t is None else np.ascontiguousarray(t.detach().cpu().numpy().astype(np.int32))
+
+
+def qkv_split(qkv, *, heads_q, heads_kv, head_dim, kv_rows, row=None, col=None, bias=None, inv_freq=None,
+              pos=None, sections=None, q_norm=None, k_norm=None, norm_eps=1e-6, kv_base=0,
+              out_dtype=torch.float16):
+    """instinctflash/kernels/rope.py:22-83 -> (q [T,HQ,HD], k [kv_rows,HKV,HD], v likewise), rows
+    outside ``kv_base .. kv_base+T`` of k and v left at zero."""
+    xf = _f32(qkv)
+    T = xf.shape[0]
+    q = np.zeros((T, heads_q, head_dim), np.float32)
+    k = np.zeros((kv_rows, heads_kv, head_dim), np.float32)
+    v = np.zeros_like(k)
+    pf = _f32(pos)
+    _lib().oracle_qkv_split(_p(xf), ctypes.c_int64(xf.shape[1]), T, heads_q, heads_kv, head_dim, _p(_f32(row)),
+                            _p(_f32(col)), _p(_f32(bias)), _p(_f32(q_norm)), _p(_f32(k_norm)),
+                            ctypes.c_float(norm_eps), _p(_f32(inv_freq)), _p(pf),
+                            ctypes.c_int64(0 if pf is None else pf.shape[1]), _p(_i32(sections)), int(kv_base),
+                            _p(q), _p(k), _p(v), _DT[out_dtype])
+    return tuple(torch.from_numpy(a).to(out_dtype) for a in (q, k, v))
+
+
+def wan_qkv(raw, *, heads, head_dim, tokens, parts, pool_rows=None, slots=None, row=None, col=None, bias=None,
+            q_norm=None, k_norm=None, pos=None, sections=None, inv_freq=None, eps=1e-6,
+            out_dtype=torch.bfloat16):
+    """instinctflash/kernels/wan.py:20-82 -> (q [rows,D], k_pool [B,S,D] or None, v_pool or None)."""
+    xf = _f32(raw)
+    n_rows = xf.shape[0]
+    D = heads * head_dim
+    B = n_rows // tokens
+    S = pool_rows if pool_rows is not None else tokens
+    q = np.zeros((n_rows, D), np.float32)
+    kp = np.zeros((B, S, D), np.float32) if parts >= 2 else None
+    vp = np.zeros((B, S, D), np.float32) if parts >= 3 else None
+    pf = _f32(pos)
+    _lib().oracle_wan_qkv(_p(xf), ctypes.c_int64(xf.shape[1]), n_rows, tokens, heads, head_dim, parts,
+                          _p(_f32(row)), _p(_f32(col)), _p(_f32(bias)), _p(_f32(q_norm)), _p(_f32(k_norm)),
+                          ctypes.c_float(eps), _p(_f32(inv_freq)), _p(pf),
+                          ctypes.c_int64(0 if pf is None else pf.shape[1]), _p(_i32(sections)), _p(_i32(slots)),
+                          S, _p(q), _p(kp), _p(vp), _DT[out_dtype])
+    return tuple(None if a is None else torch.from_numpy(a).to(out_dtype) for a in (q, kp, vp))
+
+
 def gemm_acc(a, w):
     """fp32_rn of the exact sum_k a[m,k]*w[n,k] over e4m3 codes -> float32 [M,N]."""
     ac, wc = _codes(a), _codes(w)

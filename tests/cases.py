@@ -153,6 +153,69 @@ def resnorm_cases():
             mod_index=(torch.arange(M, dtype=torch.int32) % ntab) if idx else None)
 
 
+def rope_inv_freq(head_dim, theta=10000.0):
+    exponent = torch.arange(0, head_dim, 2, dtype=torch.int64).float() / head_dim
+    return (1.0 / (theta ** exponent)).float()
+
+
+def qkv_split_cases():
+    """(name, kwargs) for the split of a fused QKV accumulator; flag sets follow the reference's
+    call sites (instinctflash/engines/pi05/engine.py:200-201,231-233, vla4/engine.py:124-126,
+    vla2/engine.py:158-160) plus ragged and float32 variants."""
+    table = [  # name, T, HQ, HKV, HD, xdt, odt, row, bias, norm, rope, sections, kv_rows, kv_base, dynamic
+        ("pi05_prefix", 96, 8, 1, 256, torch.bfloat16, torch.float16, True, False, False, True, 0, 128, 0, False),
+        ("pi05_expert", 50, 8, 1, 256, torch.bfloat16, torch.float16, True, False, False, True, 0, 128, 37, True),
+        ("vla4_bias", 64, 4, 2, 128, torch.bfloat16, torch.float16, True, True, False, True, 0, 64, 0, False),
+        ("vla2_mrope_norm", 33, 6, 2, 128, torch.bfloat16, torch.bfloat16, True, False, True, True, 3, 48, 9, True),
+        ("ragged_plain", 5, 3, 1, 80, torch.bfloat16, torch.bfloat16, False, True, False, False, 0, 8, 2, False),
+        ("f32_norm", 7, 2, 2, 64, torch.float32, torch.float32, True, True, True, True, 2, 16, 4, False),
+    ]
+    for j, (name, T, HQ, HKV, HD, xdt, odt, use_row, use_bias, norm, rope, nsec, kv_rows, kv_base, dyn) in enumerate(table):
+        width = (HQ + 2 * HKV) * HD
+        S = max(nsec, 1)
+        pos = None
+        if rope:
+            g = gen(760 + j)
+            pos = (torch.rand(T, S, generator=g) * 800.0).floor()
+        yield name, dict(
+            qkv=raw_like(T, width, 700 + j).to(xdt), heads_q=HQ, heads_kv=HKV, head_dim=HD, out_dtype=odt,
+            row=vector(T, 710 + j, lo=0.001, hi=0.02) if use_row else None,
+            col=vector(width, 720 + j, lo=0.05, hi=0.5), bias=vector(width, 730 + j, sigma=0.3) if use_bias else None,
+            q_norm=vector(HD, 740 + j, lo=0.5, hi=1.5) if norm else None,
+            k_norm=vector(HD, 750 + j, lo=0.5, hi=1.5) if norm else None,
+            inv_freq=rope_inv_freq(HD) if rope else None, pos=pos,
+            sections=(torch.arange(HD // 2, dtype=torch.int32) % nsec) if nsec else None,
+            kv_rows=kv_rows, kv_base=kv_base, dynamic_base=dyn)
+
+
+def wan_qkv_cases():
+    """Wan projection consumer; flag sets of instinctflash/engines/wan_va/engine.py:183-184 (text
+    K from a [K | V] accumulator), :215-217 (self-attention Q/K/V with pooled K/V) and :226-227
+    (cross-attention Q), plus a ragged width and the 14B width."""
+    table = [  # name, B, T, H, HD, parts, raw_parts, odt, row, col, bias, qn, kn, rope, slots, S
+        ("self_attn", 2, 40, 24, 128, 3, 3, torch.float16, True, True, True, True, True, True, True, 64),
+        ("cross_q", 2, 24, 24, 128, 1, 1, torch.float16, True, True, True, True, False, False, False, 0),
+        ("text_k", 2, 16, 24, 128, 1, 2, torch.float16, True, True, True, True, False, False, False, 0),
+        ("ragged_kv", 1, 9, 5, 4, 2, 2, torch.bfloat16, False, False, True, False, True, True, False, 9),
+        ("wide_14b", 1, 16, 40, 128, 3, 3, torch.bfloat16, True, True, True, True, True, True, False, 16),
+    ]
+    for j, (name, B, T, H, HD, parts, raw_parts, odt, use_row, use_col, use_bias, qn, kn, rope, use_slots, S) in enumerate(table):
+        D = H * HD
+        rows_n = B * T
+        g = gen(860 + j)
+        yield name, dict(
+            raw=raw_like(rows_n, raw_parts * D, 800 + j), heads=H, head_dim=HD, tokens=T, parts=parts, out_dtype=odt,
+            row=vector(rows_n, 810 + j, lo=0.001, hi=0.02) if use_row else None,
+            col=vector(parts * D, 820 + j, lo=0.05, hi=0.5) if use_col else None,
+            bias=vector(parts * D, 830 + j, sigma=0.3) if use_bias else None,
+            q_norm=vector(D, 840 + j, lo=0.5, hi=1.5) if qn else None,
+            k_norm=vector(D, 850 + j, lo=0.5, hi=1.5) if kn else None,
+            inv_freq=rope_inv_freq(HD) if rope else None,
+            pos=(torch.rand(T, 3, generator=g) * 60.0).floor() if rope else None,
+            sections=(torch.arange(HD // 2, dtype=torch.int32) % 3) if rope else None,
+            slots=torch.randperm(S, generator=g)[:T].to(torch.int32) if use_slots else None, pool_rows=S)
+
+
 def pack_weight_cpu(wf: torch.Tensor):
     """Per-channel pack with CPU arithmetic (true division), the form every arm is fed."""
     amax = wf.abs().amax(dim=1).clamp_min(1e-12)

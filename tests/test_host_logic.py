@@ -101,3 +101,19 @@ def test_install_rebinds_engine_and_kernel_modules():
 
 def test_install_default_patches_only_imported_modules():
     assert isinstance(inst.install(), dict)
+
+
+def test_qkv_consumers_reject_bad_arguments_before_launch():
+    from instinctflash_b200.kernels import rope, wan
+    x = torch.zeros(4, 3 * 64, dtype=torch.bfloat16)
+    q = torch.zeros(4, 1, 64, dtype=torch.float16)
+    kv = torch.zeros(8, 1, 64, dtype=torch.float16)
+    with pytest.raises(ValueError, match="CUDA"):          # no CPU implementation
+        rope.qkv_split(x, q, kv, kv.clone(), heads_q=1, heads_kv=1, head_dim=64)
+    with pytest.raises(ValueError, match="share a dtype"):
+        rope.qkv_split(x, q, kv, kv.float(), heads_q=1, heads_kv=1, head_dim=64)
+    with pytest.raises(ValueError, match="position table"):
+        rope.qkv_split(x, q, kv, kv.clone(), heads_q=1, heads_kv=1, head_dim=64, inv_freq=torch.ones(32))
+    with pytest.raises(ValueError, match="CUDA"):
+        wan.wan_qkv(x, torch.zeros(4, 64, dtype=torch.float16), heads=1, head_dim=64, tokens=4)
+    assert rope.rope_inv_freq(8, 10000.0, "cpu").tolist() == pytest.approx([1.0, 0.1, 0.01, 0.001])

@@ -184,3 +184,112 @@ def test_gemm_oracle_vs_b200_cublaslt(name):
     head = raw[0, :64].view(torch.int16).to(torch.int32)
     ref = torch.tensor(g["raw_head"], dtype=torch.int32)
     assert (head - ref).abs().max().item() <= 1
+
+
+# ---------------------------------------------------------------------------------------------
+# QKV consumers: the oracle against the reference's kernels recorded on a B200, and against the
+# closed-form check the reference's own test uses (tests/test_gi_kernels.py:58-91, 1e-2).
+# ---------------------------------------------------------------------------------------------
+QKV = golden("golden_b200_qkv.json")
+
+
+def _close_to_recording(got, rec, what, stride=97):
+    min_same = 0.9 if got.dtype != torch.float32 else 0.0   # float32 outputs expose every last-place difference
+    flat = got.float().flatten()
+    ref = torch.tensor(rec["sample"], dtype=torch.int32).view(torch.float32)
+    mine = flat[::stride]
+    scale = ref.abs().max().clamp_min(1e-30)
+    assert ((mine - ref).abs().max() / scale).item() <= 2.0 ** -7, what
+    assert ((mine - ref).norm() / ref.norm().clamp_min(1e-30)).item() <= 1e-3, what
+    # rounding differences only: all but a few samples are the reference's very bits
+    same = (mine.view(torch.int32) == ref.view(torch.int32)).float().mean().item()
+    assert same >= min_same, f"{what}: only {same:.1%} of the samples match the reference bit for bit"
+
+
+@pytest.mark.parametrize("name", [n for n, _ in cases.qkv_split_cases()])
+def test_qkv_split_oracle_vs_b200_reference(name):
+    c = dict(cases.qkv_split_cases())[name]
+    q, k, v = O.qkv_split(c["qkv"], heads_q=c["heads_q"], heads_kv=c["heads_kv"], head_dim=c["head_dim"],
+                          kv_rows=c["kv_rows"], row=c["row"], col=c["col"], bias=c["bias"], inv_freq=c["inv_freq"],
+                          pos=c["pos"], sections=c["sections"], q_norm=c["q_norm"], k_norm=c["k_norm"],
+                          kv_base=c["kv_base"], out_dtype=c["out_dtype"])
+    rec = QKV[f"qkv_split/{name}"]
+    _close_to_recording(q, rec["q"], f"{name}/q")
+    _close_to_recording(k, rec["k"], f"{name}/k")
+    assert sha(v) == rec["v"]["sha"], f"{name}/v: dequantisation alone is exact arithmetic"
+
+
+@pytest.mark.parametrize("name", [n for n, _ in cases.wan_qkv_cases()])
+def test_wan_qkv_oracle_vs_b200_reference(name):
+    c = dict(cases.wan_qkv_cases())[name]
+    q, k, v = O.wan_qkv(c["raw"], heads=c["heads"], head_dim=c["head_dim"], tokens=c["tokens"], parts=c["parts"],
+                        pool_rows=c["pool_rows"], slots=c["slots"], row=c["row"], col=c["col"], bias=c["bias"],
+                        q_norm=c["q_norm"], k_norm=c["k_norm"], pos=c["pos"], sections=c["sections"],
+                        inv_freq=c["inv_freq"], out_dtype=c["out_dtype"])
+    rec = QKV[f"wan_qkv/{name}"]
+    _close_to_recording(q, rec["q"], f"{name}/q")
+    if k is not None:
+        _close_to_recording(k, rec["k"], f"{name}/k")
+    if v is not None:
+        assert sha(v) == rec["v"]["sha"], f"{name}/v"
+
+
+def test_qkv_split_oracle_closed_form():
+    torch.manual_seed(2)
+    T, HQ, HKV, HD = 7, 4, 2, 128
+    raw = torch.randn(T, (HQ + 2 * HKV) * HD).to(torch.bfloat16)
+    row, col, bias = torch.rand(T) + 0.5, torch.rand(raw.shape[1]) + 0.5, torch.randn(raw.shape[1])
+    qn, kn = torch.rand(HD) + 0.5, torch.rand(HD) + 0.5
+    inv = cases.rope_inv_freq(HD, 1e6)
+    pos = torch.stack([torch.arange(T), torch.arange(T) * 2, torch.arange(T) * 3], 1).float()
+    sec = (torch.arange(HD // 2) % 3).int()
+    q, kc, vc = O.qkv_split(raw, heads_q=HQ, heads_kv=HKV, head_dim=HD, kv_rows=20, row=row, col=col, bias=bias,
+                            inv_freq=inv, pos=pos, sections=sec, q_norm=qn, k_norm=kn, kv_base=9)
+    x = raw.float() * row[:, None] * col + bias
+    xq = x[:, :HQ * HD].view(T, HQ, HD)
+    xk = x[:, HQ * HD:(HQ + HKV) * HD].view(T, HKV, HD)
+    xv = x[:, (HQ + HKV) * HD:].view(T, HKV, HD)
+
+    def rms(t, w):
+        return t * torch.rsqrt(t.pow(2).mean(-1, keepdim=True) + 1e-6) * w
+
+    ang = pos.gather(1, sec.long()[None].expand(T, -1)) * inv
+
+    def rope(t):
+        c, s = ang.cos()[:, None], ang.sin()[:, None]
+        lo, hi = t[..., :HD // 2], t[..., HD // 2:]
+        return torch.cat([lo * c - hi * s, hi * c + lo * s], -1)
+    assert (q.float() - rope(rms(xq, qn))).abs().max() < 1e-2
+    assert (kc[9:16].float() - rope(rms(xk, kn))).abs().max() < 1e-2
+    assert (vc[9:16].float() - xv).abs().max() < 1e-2
+    assert kc[:9].abs().max() == 0 and kc[16:].abs().max() == 0
+
+
+def test_wan_qkv_oracle_closed_form():
+    torch.manual_seed(5)
+    B, T, H, HD = 2, 6, 4, 32
+    D = H * HD
+    raw = torch.randn(B * T, 3 * D).to(torch.bfloat16)
+    row, col, bias = torch.rand(B * T) + 0.5, torch.rand(3 * D) + 0.5, torch.randn(3 * D)
+    qn, kn = torch.rand(D) + 0.5, torch.rand(D) + 0.5
+    inv = cases.rope_inv_freq(HD)
+    pos = (torch.rand(T, 3) * 20).floor()
+    sec = (torch.arange(HD // 2) % 3).int()
+    slots = torch.randperm(10)[:T].int()
+    q, kp, vp = O.wan_qkv(raw, heads=H, head_dim=HD, tokens=T, parts=3, pool_rows=10, slots=slots, row=row, col=col,
+                          bias=bias, q_norm=qn, k_norm=kn, pos=pos, sections=sec, inv_freq=inv, out_dtype=torch.float32)
+    x = raw.float() * row[:, None] * col + bias
+    ang = (pos.gather(1, sec.long()[None].expand(T, -1)) * inv).repeat(B, 1)   # [B*T, HD/2]
+
+    def part(xp, w):
+        y = xp * torch.rsqrt(xp.pow(2).mean(-1, keepdim=True) + 1e-6) * w
+        y = y.view(B * T, H, HD // 2, 2)
+        e, o = y[..., 0], y[..., 1]
+        c, s = ang.cos()[:, None], ang.sin()[:, None]
+        return torch.stack([e * c - o * s, e * s + o * c], -1).reshape(B * T, D)
+    assert (q - part(x[:, :D], qn)).abs().max() < 1e-4
+    want_k = part(x[:, D:2 * D], kn).view(B, T, D)
+    assert (kp[:, slots.long()] - want_k).abs().max() < 1e-4
+    assert (vp[:, slots.long()] - x[:, 2 * D:].view(B, T, D)).abs().max() < 1e-4
+    untouched = [s for s in range(10) if s not in slots.tolist()]
+    assert kp[:, untouched].abs().max() == 0
