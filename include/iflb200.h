@@ -305,7 +305,7 @@ IFLB200_API int iflb200_gemm_set_config(int tile_n, int stages, int group_m);
 /* Split-K of the GEMM over a thread-block cluster (partials summed over distributed shared
  * memory in rank order): 0 = cost model (deep reductions with too few tiles to fill the GPU),
  * 1 = never (the K loop is then a function of K alone and outputs are bit-identical to the
- * unsplit kernel), 2 / 4 / 8 = forced.  No reference counterpart. */
+ * unsplit kernel), 2 / 4 = forced.  No reference counterpart. */
 IFLB200_API int iflb200_gemm_set_split_k(int split_k);
 /* Row kernels: force the number of threads that share one row (power of two, 32..1024;
  * 0 = heuristic).  For experiments and tests.  No reference counterpart. */

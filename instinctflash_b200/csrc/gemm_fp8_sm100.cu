@@ -68,6 +68,9 @@ __device__ __forceinline__ uint32_t map_to_cta(uint32_t smem_addr, uint32_t rank
   asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(smem_addr), "r"(rank));
   return r;
 }
+__device__ __forceinline__ void st_dsmem_f32(uint32_t addr, float v) {
+  asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(addr), "f"(v) : "memory");
+}
 __device__ __forceinline__ float ld_dsmem_f32(uint32_t addr) {
   float v;
   asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(addr));
@@ -150,29 +153,40 @@ __device__ __forceinline__ void epilogue_chunk(const GemmParams& p, const uint32
     return;
   }
   // Consumer arithmetic.  Column vectors are read with warp-uniform addresses (every thread
-  // of the warp has the same columns), which the L1 serves as broadcasts.
+  // of the warp has the same columns), which the L1 serves as broadcasts.  The residual operand
+  // is updated in place, so its loads cannot move above the stores of an earlier piece: all 32
+  // columns are requested before the first is used (one memory round trip, not four).
+  float res_all[32];
+  if (p.epilogue == EPI_RESIDUAL) {
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      if (j * 8 < valid) {
+        const int64_t off = (int64_t)m * p.ld_out + n0 + 8 * j;
+        if (p.out_dtype == IFLB200_F32) {
+          const float* o = reinterpret_cast<const float*>(p.out) + off;
+          const float4 a = *reinterpret_cast<const float4*>(o);
+          const float4 b = *reinterpret_cast<const float4*>(o + 4);
+          res_all[8 * j + 0] = a.x; res_all[8 * j + 1] = a.y; res_all[8 * j + 2] = a.z; res_all[8 * j + 3] = a.w;
+          res_all[8 * j + 4] = b.x; res_all[8 * j + 5] = b.y; res_all[8 * j + 6] = b.z; res_all[8 * j + 7] = b.w;
+        } else {
+          const uint4 u = *reinterpret_cast<const uint4*>(reinterpret_cast<const __nv_bfloat16*>(p.out) + off);
+          const uint32_t w[4] = {u.x, u.y, u.z, u.w};
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            res_all[8 * j + 2 * i] = __uint_as_float(w[i] << 16);
+            res_all[8 * j + 2 * i + 1] = __uint_as_float(w[i] & 0xFFFF0000u);
+          }
+        }
+      }
+    }
+  }
 #pragma unroll
   for (int j = 0; j < 4; ++j) {
     if (j * 8 >= valid) break;
     const int64_t off = (int64_t)m * p.ld_out + n0 + 8 * j;
     float res[8];
-    if (p.epilogue == EPI_RESIDUAL) {
-      if (p.out_dtype == IFLB200_F32) {
-        const float* o = reinterpret_cast<const float*>(p.out) + off;
-        const float4 a = *reinterpret_cast<const float4*>(o);
-        const float4 b = *reinterpret_cast<const float4*>(o + 4);
-        res[0] = a.x; res[1] = a.y; res[2] = a.z; res[3] = a.w;
-        res[4] = b.x; res[5] = b.y; res[6] = b.z; res[7] = b.w;
-      } else {
-        const uint4 u = *reinterpret_cast<const uint4*>(reinterpret_cast<const __nv_bfloat16*>(p.out) + off);
-        const uint32_t w[4] = {u.x, u.y, u.z, u.w};
 #pragma unroll
-        for (int i = 0; i < 4; ++i) {
-          res[2 * i] = __uint_as_float(w[i] << 16);
-          res[2 * i + 1] = __uint_as_float(w[i] & 0xFFFF0000u);
-        }
-      }
-    }
+    for (int i = 0; i < 8; ++i) res[i] = p.epilogue == EPI_RESIDUAL ? res_all[8 * j + i] : 0.0f;
     float y[8];
 #pragma unroll
     for (int i = 0; i < 8; ++i) {
@@ -263,6 +277,55 @@ __device__ __forceinline__ void epilogue_values(const GemmParams& p, const uint3
   }
 }
 
+// Consumer arithmetic and output cast of 32 consecutive columns of this lane's row, written into
+// the lane's 128-byte staging row (128-byte swizzle: 16-byte chunk index ^ (lane & 7)).  `sub` is
+// the column offset inside the staged piece: 0 or 32 for two-byte outputs, 0 for four-byte ones.
+__device__ __forceinline__ void stage_columns(const GemmParams& p, const uint32_t (&r)[32], int n_abs, float rs,
+                                              uint8_t* mine, int sub, int lane) {
+  const int es = (p.out_dtype == IFLB200_F32) ? 4 : 2;
+  if (es == 2) {
+    // 32 values = 64 bytes = four 16-byte chunks; chunk index within the 128-byte row
+    const int first = sub / 8;  // 0 or 4
+    if (p.epilogue == EPI_RAW) {
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        uint4 u;
+        u.x = pack_bf16x2(__uint_as_float(r[8 * j + 0]), __uint_as_float(r[8 * j + 1]));
+        u.y = pack_bf16x2(__uint_as_float(r[8 * j + 2]), __uint_as_float(r[8 * j + 3]));
+        u.z = pack_bf16x2(__uint_as_float(r[8 * j + 4]), __uint_as_float(r[8 * j + 5]));
+        u.w = pack_bf16x2(__uint_as_float(r[8 * j + 6]), __uint_as_float(r[8 * j + 7]));
+        *reinterpret_cast<uint4*>(mine + (((first + j) ^ (lane & 7)) * 16)) = u;
+      }
+    } else {
+      float y[32];
+      epilogue_values(p, r, n_abs, rs, y);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        uint4 u;
+        if (p.out_dtype == IFLB200_BF16) {
+          u.x = pack_bf16x2(y[8 * j + 0], y[8 * j + 1]);
+          u.y = pack_bf16x2(y[8 * j + 2], y[8 * j + 3]);
+          u.z = pack_bf16x2(y[8 * j + 4], y[8 * j + 5]);
+          u.w = pack_bf16x2(y[8 * j + 6], y[8 * j + 7]);
+        } else {
+          u.x = pack_f16x2(y[8 * j + 0], y[8 * j + 1]);
+          u.y = pack_f16x2(y[8 * j + 2], y[8 * j + 3]);
+          u.z = pack_f16x2(y[8 * j + 4], y[8 * j + 5]);
+          u.w = pack_f16x2(y[8 * j + 6], y[8 * j + 7]);
+        }
+        *reinterpret_cast<uint4*>(mine + (((first + j) ^ (lane & 7)) * 16)) = u;
+      }
+    }
+  } else {
+    float y[32];
+    epilogue_values(p, r, n_abs, rs, y);
+#pragma unroll
+    for (int j = 0; j < 8; ++j)
+      *reinterpret_cast<float4*>(mine + ((j ^ (lane & 7)) * 16)) =
+          make_float4(y[4 * j + 0], y[4 * j + 1], y[4 * j + 2], y[4 * j + 3]);
+  }
+}
+
 // Epilogue of one warp: its 32 accumulator rows x its half of the tile's columns, through shared
 // memory.  128 bytes of each output row (64 two-byte or 32 four-byte columns) are staged with
 // the 128-byte swizzle and written by one TMA store, so global memory sees whole 128-byte lines
@@ -290,47 +353,7 @@ __device__ __forceinline__ void epilogue_tma_store(const GemmParams& p, const CU
         if (r[0] == 0x7fc12345u) mine[0] = 1;  // keep the load alive
         continue;
       }
-      if (es == 2) {
-        // 32 values = 64 bytes = four 16-byte chunks; chunk index within the 128-byte row
-        const int first = sub / 8;  // 0 or 4
-        if (p.epilogue == EPI_RAW) {
-#pragma unroll
-          for (int j = 0; j < 4; ++j) {
-            uint4 u;
-            u.x = pack_bf16x2(__uint_as_float(r[8 * j + 0]), __uint_as_float(r[8 * j + 1]));
-            u.y = pack_bf16x2(__uint_as_float(r[8 * j + 2]), __uint_as_float(r[8 * j + 3]));
-            u.z = pack_bf16x2(__uint_as_float(r[8 * j + 4]), __uint_as_float(r[8 * j + 5]));
-            u.w = pack_bf16x2(__uint_as_float(r[8 * j + 6]), __uint_as_float(r[8 * j + 7]));
-            *reinterpret_cast<uint4*>(mine + (((first + j) ^ (lane & 7)) * 16)) = u;
-          }
-        } else {
-          float y[32];
-          epilogue_values(p, r, n0 + sub, rs, y);
-#pragma unroll
-          for (int j = 0; j < 4; ++j) {
-            uint4 u;
-            if (p.out_dtype == IFLB200_BF16) {
-              u.x = pack_bf16x2(y[8 * j + 0], y[8 * j + 1]);
-              u.y = pack_bf16x2(y[8 * j + 2], y[8 * j + 3]);
-              u.z = pack_bf16x2(y[8 * j + 4], y[8 * j + 5]);
-              u.w = pack_bf16x2(y[8 * j + 6], y[8 * j + 7]);
-            } else {
-              u.x = pack_f16x2(y[8 * j + 0], y[8 * j + 1]);
-              u.y = pack_f16x2(y[8 * j + 2], y[8 * j + 3]);
-              u.z = pack_f16x2(y[8 * j + 4], y[8 * j + 5]);
-              u.w = pack_f16x2(y[8 * j + 6], y[8 * j + 7]);
-            }
-            *reinterpret_cast<uint4*>(mine + (((first + j) ^ (lane & 7)) * 16)) = u;
-          }
-        }
-      } else {
-        float y[32];
-        epilogue_values(p, r, n0 + sub, rs, y);
-#pragma unroll
-        for (int j = 0; j < 8; ++j)
-          *reinterpret_cast<float4*>(mine + ((j ^ (lane & 7)) * 16)) =
-              make_float4(y[4 * j + 0], y[4 * j + 1], y[4 * j + 2], y[4 * j + 3]);
-      }
+      stage_columns(p, r, n0 + sub, rs, mine, sub, lane);
     }
     fence_proxy_async_smem();  // generic-proxy writes visible to the TMA unit
     __syncwarp();
@@ -341,12 +364,20 @@ __device__ __forceinline__ void epilogue_tma_store(const GemmParams& p, const CU
   }
 }
 
-template <int BN, int STAGES>
+// SPLIT: 0 = never a cluster split-K, 1 = always (p.split_k > 1), 2 = decided by p.split_k.  The
+// wide-tile kernels of the large-M regime exist in forms 0 and 1: measured inside the M = 816 layer
+// stack, a kernel that carries both code paths ran the stack 5 % slower than the two specialised
+// ones.  The 64-wide kernel of the skinny-M regime exists only in form 2, so that the launches of a
+// layer, split or not, run the same code: there a second GEMM kernel per layer cost about 1 us per
+// launch in instruction fetch (0.2 ms per pass of the M = 50 stack).
+template <int BN, int STAGES, int SPLIT>
 __global__ void __launch_bounds__(kGemmThreads, 1)
 gemm_fp8_tc5_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_w,
                     const __grid_constant__ CUtensorMap tm_out, const GemmParams p) {
   using L = SmemLayout<BN, STAGES>;
-  constexpr uint32_t kTmemCols = (2 * BN < 32) ? 32 : 2 * BN;  // BN in {32,64,128,256}
+  // two accumulators, each at a power-of-two column offset; BN in {64, 128, 192, 224, 256}
+  constexpr uint32_t kAccStride = BN <= 64 ? 64 : (BN <= 128 ? 128 : 256);
+  constexpr uint32_t kTmemCols = 2 * kAccStride;
   constexpr uint32_t kIdesc = make_idesc_e4m3_f32(BM, BN);
 
   extern __shared__ uint8_t smem_raw[];
@@ -366,7 +397,7 @@ gemm_fp8_tc5_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
   const int lane = threadIdx.x & 31;
   // Split-K: the S CTAs of a cluster work on the same tile, CTA r on K steps [kb0, kb1); one
   // tile per CTA (the host launches tiles x S CTAs, at most one wave).
-  const bool split = p.split_k > 1;
+  const bool split = SPLIT == 1 || (SPLIT == 2 && p.split_k > 1);
   const int split_rank = split ? (int)cluster_ctarank() : 0;
   const int tile_first = split ? (int)blockIdx.x / p.split_k : (int)blockIdx.x;
   const int tile_stride = split ? p.num_tiles : (int)gridDim.x;
@@ -374,6 +405,8 @@ gemm_fp8_tc5_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
   const int kb1 = split ? (int)(((int64_t)p.num_k * (split_rank + 1)) / p.split_k) : p.num_k;
 
   if (threadIdx.x == 0) {
+    prefetch_tensormap(&tm_a);
+    prefetch_tensormap(&tm_w);
     for (int s = 0; s < STAGES; ++s) {
       mbar_init(full_bar(s), 1);
       mbar_init(empty_bar(s), 1);
@@ -389,10 +422,6 @@ gemm_fp8_tc5_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
   if (warp == 1) {
     tmem_alloc(smem_u32(tmem_slot), kTmemCols);
     tmem_relinquish();
-  }
-  if (warp == 0 && lane == 0) {
-    prefetch_tensormap(&tm_a);
-    prefetch_tensormap(&tm_w);
   }
   tc_fence_before();
   __syncthreads();
@@ -473,7 +502,7 @@ gemm_fp8_tc5_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
                                                 (2u << 24) | (2u << 16) | (it & 0xFFFF)));
       if (!ok) break;
       tc_fence_after();
-      const uint32_t d_tmem = tmem_base + acc * BN;
+      const uint32_t d_tmem = tmem_base + acc * kAccStride;
       for (int kb = kb0; kb < kb1; ++kb) {
         ok = __all_sync(0xFFFFFFFFu, wait_bounded(full_bar(stage), phase, abort_flag,
                                                   (2u << 24) | (3u << 16) | (it & 0xFFFF)));
@@ -504,12 +533,13 @@ gemm_fp8_tc5_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
     // ------------------------------------------------------------------ epilogue warps
     const int quad = warp & 3;  // TMEM lanes [32*quad, 32*quad+32) are this warp's
     const int half = (warp - 2) >> 2;  // which half of the tile's columns this warp drains
-    int col_begin = half * (BN / 2), col_end = col_begin + BN / 2;
-    if (p.tma_store && BN / 2 < 128 / ((p.out_dtype == IFLB200_F32) ? 4 : 2)) {
-      // a 64-wide tile of two-byte outputs is a single 128-byte store: the first warp of the
-      // quadrant takes it all
-      col_begin = 0;
-      col_end = half == 0 ? BN : 0;
+    // the two warps of a quadrant split the tile's columns at a multiple of 64 (one 128-byte
+    // store of two-byte outputs): 128 | rest for wide tiles, half | half for 128, all | none for 64
+    constexpr int kColSplit = BN > 128 ? 128 : (BN == 128 ? 64 : BN);
+    int col_begin = half == 0 ? 0 : kColSplit, col_end = half == 0 ? kColSplit : BN;
+    if (BN == 64 && p.tma_store && p.out_dtype == IFLB200_F32) {  // 32 four-byte columns per store
+      col_begin = half * 32;
+      col_end = col_begin + 32;
     }
     const uint32_t staging = base + L::kStagingOffset + (uint32_t)(warp - 2) * 4096u;
     uint8_t* staging_ptr = smem + L::kStagingOffset + (warp - 2) * 4096;
@@ -529,23 +559,26 @@ gemm_fp8_tc5_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
       const bool row_ok = m < p.M;
       const float rs = (row_ok && p.row) ? __ldg(p.row + (int64_t)m * p.row_stride) : 1.0f;
       const int64_t gofs = (row_ok && p.gate_index) ? (int64_t)p.gate_index[m] * p.N : 0;
-      const uint32_t t_row = tmem_base + ((uint32_t)(quad * 32) << 16) + acc * BN;
+      const uint32_t t_row = tmem_base + ((uint32_t)(quad * 32) << 16) + acc * kAccStride;
       if (split) {
-        // park this CTA's partial accumulator in shared memory (the stage ring is free: every
-        // load has been consumed), column-major so that lanes hit consecutive banks
-        float* part = reinterpret_cast<float*>(smem);
-        const int row = quad * 32 + lane;
-#pragma unroll 1
-        for (int c = half * (BN / 2); c < (half + 1) * (BN / 2); c += 32) {
-          uint32_t r[32];
-          tmem_ld_32x32b_x32(t_row + c, r);
-          tmem_ld_wait();
-#pragma unroll
-          for (int i = 0; i < 32; ++i) part[(c + i) * BM + row] = __uint_as_float(r[i]);
-        }
+        // one tile per CTA: the partial accumulator stays in tensor memory; the exchange with
+        // the other CTAs of the cluster follows the role loops
       } else if (p.tma_store) {
+        // whole 128-byte pieces through shared memory and TMA; a 32-column remainder of a
+        // 224-wide tile (two-byte outputs) straight from registers
+        const int per_store = (p.out_dtype == IFLB200_F32) ? 32 : 64;
+        const int col_tma_end = col_begin + (col_end - col_begin) / per_store * per_store;
         epilogue_tma_store<BN>(p, &tm_out, t_row, staging, staging_ptr, m_blk * BM + quad * 32, n_blk * BN,
-                               col_begin, col_end, rs, lane);
+                               col_begin, col_tma_end, rs, lane);
+        if (BN % 64 != 0 && col_tma_end < col_end) {
+          const int n0 = n_blk * BN + col_tma_end;
+          if (n0 < p.N && p.debug_skip == 0) {
+            uint32_t r[32];
+            tmem_ld_32x32b_x32(t_row + col_tma_end, r);
+            tmem_ld_wait();
+            epilogue_chunk<BN>(p, r, m, n0, row_ok, rs, gofs);
+          }
+        }
       } else {
 #pragma unroll 1
         for (int c = col_begin / 32; c < col_end / 32; ++c) {
@@ -566,59 +599,121 @@ gemm_fp8_tc5_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
   }
 
   if (split) {
-    // Every CTA of the cluster has parked its partial: CTA r now reduces columns
-    // [r*BN/S, (r+1)*BN/S) of the tile over all partials, in rank order (fixed, so the sum does
-    // not depend on timing), and runs the consumer arithmetic on the sums.
-    cluster_sync_all();
-    if (warp >= 2 && !*abort_flag) {
-      const int quad = warp & 3;
-      const int half = (warp - 2) >> 2;
-      const int own = BN / p.split_k;                 // columns this CTA reduces (>= 32)
-      const int per_warp = own >= 64 ? own / 2 : own;  // two warps per quadrant share them
-      const int c_begin = split_rank * own + (own >= 64 ? half * per_warp : 0);
-      const int c_end = (own >= 64 || half == 0) ? c_begin + per_warp : c_begin;
-      int m_blk, n_blk;
-      tile_coords(p, tile_first, m_blk, n_blk);
-      const int row = quad * 32 + lane;
-      const int m = m_blk * BM + row;
-      const bool row_ok = m < p.M && tile_first < p.num_tiles;
-      const float rs = (row_ok && p.row) ? __ldg(p.row + (int64_t)m * p.row_stride) : 1.0f;
-      const int64_t gofs = (row_ok && p.gate_index) ? (int64_t)p.gate_index[m] * p.N : 0;
-      uint32_t peer[8];
-#pragma unroll
-      for (int r = 0; r < 8; ++r) peer[r] = map_to_cta(base, (uint32_t)(r < p.split_k ? r : 0));
+    // CTA r of the cluster reduces columns [r*BN/S, (r+1)*BN/S) of the tile: its own partial
+    // comes from tensor memory, the peers write theirs into its shared memory, and the sum runs
+    // in rank order (fixed, so the result does not depend on timing); then the consumer
+    // arithmetic on the sums.  Nothing touches another CTA's memory after the second barrier, so
+    // CTAs leave independently.
+    const int quad = warp & 3;
+    const int half = (warp - 2) >> 2;
+    const int row = quad * 32 + lane;
+    const bool reducing = warp >= 2 && !*abort_flag && tile_first < p.num_tiles;
+    cluster_arrive();
+    cluster_wait();  // every CTA of the cluster has finished its main loop: the stage rings are free
+    if (reducing) {
+      // Hand every column range to the CTA that reduces it: the values go straight into the
+      // owner's shared memory (slot = this CTA's position among the owner's peers, column-major
+      // so that lanes hit consecutive banks).  Remote stores are posted, no round trip per value.
+      const int own = BN / p.split_k;
+      const uint32_t t_row = tmem_base + ((uint32_t)(quad * 32) << 16);  // accumulator 0: the only tile
 #pragma unroll 1
-      for (int c = c_begin; c < c_end; c += 32) {
-        const int n0 = n_blk * BN + c;
-        if (n0 >= p.N) break;
-        uint32_t acc[32];
-        // eight columns at a time: every partial of the group is requested before the first
-        // is used (a distributed-shared-memory load takes hundreds of cycles), then summed in
-        // rank order
+      for (int c = half * (BN / 2); c < (half + 1) * (BN / 2); c += 32) {
+        const int owner = c / own;
+        if (owner == split_rank) continue;  // reduced here, from tensor memory
+        const int slot = split_rank < owner ? split_rank : split_rank - 1;
+        uint32_t r[32];
+        tmem_ld_32x32b_x32(t_row + c, r);
+        tmem_ld_wait();
+        const uint32_t dst = map_to_cta(base, (uint32_t)owner) +
+                             (uint32_t)(((slot * own + (c - owner * own)) * BM + row) * 4);
 #pragma unroll
-        for (int g = 0; g < 4; ++g) {
-          float part[8][8];
-#pragma unroll
-          for (int r = 0; r < 8; ++r) {
-            if (r < p.split_k) {
-#pragma unroll
-              for (int i = 0; i < 8; ++i)
-                part[r][i] = ld_dsmem_f32(peer[r] + (uint32_t)(((c + 8 * g + i) * BM + row) * 4));
-            }
-          }
-#pragma unroll
-          for (int i = 0; i < 8; ++i) {
-            float v = part[0][i];
-#pragma unroll
-            for (int r = 1; r < 8; ++r)
-              if (r < p.split_k) v = __fadd_rn(v, part[r][i]);
-            acc[8 * g + i] = __float_as_uint(v);
-          }
-        }
-        epilogue_chunk<BN>(p, acc, m, n0, row_ok, rs, gofs);
+        for (int i = 0; i < 32; ++i) st_dsmem_f32(dst + (uint32_t)(i * BM * 4), __uint_as_float(r[i]));
       }
     }
-    cluster_sync_all();  // peers may still be reading this CTA's partial
+    cluster_arrive();
+    cluster_wait();  // the peers' columns have landed here
+    uint32_t sum[2][32];
+    int my_chunks = 0, c_first = 0;
+    int m_blk = 0, n_blk = 0;
+    if (reducing) {
+      tile_coords(p, tile_first, m_blk, n_blk);
+      const int own = BN / p.split_k;  // columns this CTA reduces (a multiple of 32, at most 128)
+      const int n_chunks = own / 32;   // 1, 2 or 4: the two warps of a quadrant take adjacent halves
+      my_chunks = n_chunks >= 2 ? n_chunks / 2 : (half == 0 ? 1 : 0);
+      c_first = split_rank * own + (n_chunks >= 2 ? half * my_chunks * 32 : 0);
+      const uint32_t t_row = tmem_base + ((uint32_t)(quad * 32) << 16);  // accumulator 0: the only tile
+#pragma unroll
+      for (int k = 0; k < 2; ++k) {
+        if (k < my_chunks) {
+          const int c = c_first + 32 * k;
+          uint32_t mine[32];
+          tmem_ld_32x32b_x32(t_row + c, mine);
+          float rem[3][32];  // the peers in rank order (this CTA's own rank left out)
+          const float* slots = reinterpret_cast<const float*>(smem);
+#pragma unroll
+          for (int q = 0; q < 3; ++q) {
+            if (q + 1 < p.split_k) {
+#pragma unroll
+              for (int i = 0; i < 32; ++i) rem[q][i] = slots[(q * own + (c - split_rank * own) + i) * BM + row];
+            }
+          }
+          tmem_ld_wait();
+#pragma unroll
+          for (int i = 0; i < 32; ++i) {
+            float v = 0.0f;
+#pragma unroll
+            for (int r = 0; r < 4; ++r) {
+              if (r < p.split_k) {
+                const float before = r <= 2 ? rem[r <= 2 ? r : 0][i] : 0.0f;      // peer r when r < own rank
+                const float after = r >= 1 ? rem[r >= 1 ? r - 1 : 0][i] : 0.0f;   // peer r when r > own rank
+                const float t = r == split_rank ? __uint_as_float(mine[i]) : (r < split_rank ? before : after);
+                v = r == 0 ? t : __fadd_rn(v, t);
+              }
+            }
+            sum[k][i] = __float_as_uint(v);
+          }
+        }
+      }
+    }
+    if (reducing && my_chunks > 0) {
+      const int m = m_blk * BM + row;
+      const bool row_ok = m < p.M;
+      const float rs = (row_ok && p.row) ? __ldg(p.row + (int64_t)m * p.row_stride) : 1.0f;
+      const int64_t gofs = (row_ok && p.gate_index) ? (int64_t)p.gate_index[m] * p.N : 0;
+      const int per_store = (p.out_dtype == IFLB200_F32) ? 32 : 64;
+      const int n_first = n_blk * BN + c_first;
+      if (p.tma_store && my_chunks * 32 >= per_store && n_first < p.N) {
+        uint8_t* mine_row = smem + L::kStagingOffset + (warp - 2) * 4096 + lane * 128;
+        const uint32_t staging = base + L::kStagingOffset + (uint32_t)(warp - 2) * 4096u;
+#pragma unroll
+        for (int k = 0; k < 2; ++k) {
+          if (k < my_chunks) {
+            const int sub = (32 * k) % per_store;
+            if (sub == 0 && k > 0) {
+              if (lane == 0) bulk_wait_group_read<0>();  // the previous store has read the buffer
+              __syncwarp();
+            }
+            stage_columns(p, sum[k], n_first + 32 * k, rs, mine_row, sub, lane);
+            if (sub + 32 == per_store) {
+              fence_proxy_async_smem();
+              __syncwarp();
+              if (lane == 0) {
+                tma_store_2d(&tm_out, staging, n_first + 32 * k - sub, m_blk * BM + quad * 32);
+                bulk_commit_group();
+              }
+            }
+          }
+        }
+        if (lane == 0) bulk_wait_group_read<0>();
+        __syncwarp();
+      } else {
+#pragma unroll
+        for (int k = 0; k < 2; ++k) {
+          const int n0 = n_first + 32 * k;
+          if (k < my_chunks && n0 < p.N) epilogue_chunk<BN>(p, sum[k], m, n0, row_ok, rs, gofs);
+        }
+      }
+    }
   }
   tc_fence_before();
   __syncthreads();
@@ -929,22 +1024,35 @@ static int g_cfg_debug_skip = 0;
 static int g_cfg_direct_store = 0;  // 1: epilogue stores straight from registers (experiments)
 static int g_cfg_mode = 0;  // 0 auto, 1 single-CTA tiles only, 2 CTA pairs with one accumulator, 3 CTA pairs with two
 
-template <int BN, int STAGES>
-static int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tw, const CUtensorMap& to, const GemmParams& p,
-                       int grid, cudaStream_t s) {
+template <int BN, int STAGES, int SPLIT>
+static int launch_gemm_form(const CUtensorMap& ta, const CUtensorMap& tw, const CUtensorMap& to, const GemmParams& p,
+                            int grid, cudaStream_t s) {
   using L = SmemLayout<BN, STAGES>;
   static bool attr_set[64] = {};
   int dev = 0;
   cudaGetDevice(&dev);
   if (!attr_set[dev]) {
-    cudaError_t e = cudaFuncSetAttribute(gemm_fp8_tc5_kernel<BN, STAGES>,
+    cudaError_t e = cudaFuncSetAttribute(gemm_fp8_tc5_kernel<BN, STAGES, SPLIT>,
                                          cudaFuncAttributeMaxDynamicSharedMemorySize, L::kDynamic);
     if (e != cudaSuccess) return (int)e;
     attr_set[dev] = true;
   }
-  const cudaError_t e = launch_dep(gemm_fp8_tc5_kernel<BN, STAGES>, dim3(grid), dim3(kGemmThreads), L::kDynamic, s,
-                                   p.split_k, dependent_launch_for(p.M), ta, tw, to, p);
+  const cudaError_t e = launch_dep(gemm_fp8_tc5_kernel<BN, STAGES, SPLIT>, dim3(grid), dim3(kGemmThreads), L::kDynamic,
+                                   s, p.split_k, dependent_launch_for(p.M), ta, tw, to, p);
   return e != cudaSuccess ? (int)e : (int)cudaGetLastError();
+}
+
+template <int BN, int STAGES>
+static int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tw, const CUtensorMap& to, const GemmParams& p,
+                       int grid, cudaStream_t s) {
+  if constexpr (BN == 64) {
+    return launch_gemm_form<BN, STAGES, 2>(ta, tw, to, p, grid, s);
+  } else {
+    if constexpr ((BN & (BN - 1)) == 0) {  // the reduction splits power-of-two widths
+      if (p.split_k > 1) return launch_gemm_form<BN, STAGES, 1>(ta, tw, to, p, grid, s);
+    }
+    return launch_gemm_form<BN, STAGES, 0>(ta, tw, to, p, grid, s);
+  }
 }
 
 template <int BN, int STAGES, int ACC>
@@ -1010,31 +1118,35 @@ static int run_gemm(const void* a, int64_t ld_a, const void* w, int64_t ld_w, Ge
                            : launch_gemm_pair<PBN, 6, 2>(ta, tw, to, p, grid, s);
   }
 
-  // Tile width by a measured cost model: a CTA's main loop is bound by the rate at which its
-  // TMA unit turns 128-byte rows into requests, so one 128-byte K step costs about 590 / 690 /
-  // 830 cycles for a 64 / 128 / 256 wide tile (24 / 32 / 48 KB per step); the kernel takes
-  // waves x steps x that, plus a fixed cost per wave for prologue and the exposed epilogue.
+  // Tile width by a measured cost model: one 128-byte K step of a CTA costs about 590 / 690 /
+  // 830 cycles for a 64 / 128 / 256 wide tile (24 / 32 / 48 KB through the SM's L2 port per
+  // step; 192 and 224 interpolate), the kernel takes waves x steps x that, plus a fixed cost per
+  // wave for prologue and the exposed epilogue.  The widths that are not powers of two are for
+  // wave quantisation (7 row blocks x 32768 columns: 896 tiles of 256 = 6.05 waves of 148 SMs, i.e.
+  // 7, but 1029 tiles of 224 = 6.95 waves of narrower tiles).  Timed alone the 224-wide kernel is
+  // 2 % faster on that shape, inside the layer stack it was 4 us per launch slower (its 448-byte
+  // tile rows start off the 128-byte line grid), so the model does not choose them by itself.
   p.num_m = (p.M + BM - 1) / BM;
   int bn = g_cfg_tile_n;
   int split = 1;
   {
-    const int widths[3] = {256, 128, 64};
-    const int64_t step_cycles[3] = {830, 690, 590};
+    const int widths[5] = {256, 224, 192, 128, 64};
+    const int64_t step_cycles[5] = {830, 790, 750, 690, 590};
     const int64_t steps = (p.K + BK - 1) / BK;
     int64_t best = 0;
     int best_bn = 0;
-    for (int i = 0; i < 3; ++i) {
+    for (int i = 0; i < 5; ++i) {
       if (g_cfg_tile_n && widths[i] != g_cfg_tile_n) continue;
+      if (!g_cfg_tile_n && (widths[i] & (widths[i] - 1))) continue;  // 192 / 224: only when asked for (see above)
       if (!g_cfg_tile_n && widths[i] > 64 && p.N < widths[i]) continue;
       const int64_t tiles = (int64_t)p.num_m * ((p.N + widths[i] - 1) / widths[i]);
-      // split-K over a cluster: one wave of tiles x S CTAs, S a power of two that leaves each
-      // CTA >= 8 K steps and >= 32 columns to reduce.  Parking the partial accumulators, the
-      // cluster barrier and the reduction over distributed shared memory cost about 9-10 us
-      // (measured for S = 2 and 4; S = 8 costs three times that and is only used when forced).
-      for (int sk = 1; sk <= 8; sk *= 2) {
+      // split-K over a cluster: one wave of tiles x S CTAs, S in {2, 4}, leaving each CTA >= 8 K
+      // steps and >= 32 columns to reduce; the exchange of partials over distributed shared
+      // memory, two cluster barriers and the reduction are a fixed cost per launch.
+      for (int sk = 1; sk <= 4; sk *= 2) {
         if (g_cfg_split_k && sk != g_cfg_split_k) continue;
         if (sk > 1 && (tiles * sk > dev->sm_count || steps / sk < 8 || widths[i] / sk < 32)) continue;
-        if (sk == 8 && g_cfg_split_k == 0) continue;
+        if (sk > 1 && (widths[i] & (widths[i] - 1))) continue;  // the reduction splits power-of-two widths
         const int64_t waves = sk > 1 ? 1 : (tiles + dev->sm_count - 1) / dev->sm_count;
         const int64_t cost = waves * ((steps / sk) * step_cycles[i] + 2500 + (sk > 1 ? 18000 : 0));
         if (best_bn == 0 || cost < best) {
@@ -1062,6 +1174,8 @@ static int run_gemm(const void* a, int64_t ld_a, const void* w, int64_t ld_w, Ge
   const int stages = g_cfg_stages;
   switch (bn) {
     case 256: return (stages == 3) ? launch_gemm<256, 3>(ta, tw, to, p, grid, s) : launch_gemm<256, 4>(ta, tw, to, p, grid, s);
+    case 224: return launch_gemm<224, 4>(ta, tw, to, p, grid, s);
+    case 192: return launch_gemm<192, 4>(ta, tw, to, p, grid, s);
     case 128: return (stages == 4) ? launch_gemm<128, 4>(ta, tw, to, p, grid, s) : launch_gemm<128, 6>(ta, tw, to, p, grid, s);
     case 64: return (stages == 4) ? launch_gemm<64, 4>(ta, tw, to, p, grid, s) : launch_gemm<64, 8>(ta, tw, to, p, grid, s);
     default: return IFLB200_ERR_ARG;
@@ -1073,7 +1187,8 @@ static int run_gemm(const void* a, int64_t ld_a, const void* w, int64_t ld_w, Ge
 using namespace iflb200;
 
 extern "C" int iflb200_gemm_set_config(int tile_n, int stages, int group_m) {
-  if (tile_n != 0 && tile_n != 64 && tile_n != 128 && tile_n != 256) return IFLB200_ERR_ARG;
+  if (tile_n != 0 && tile_n != 64 && tile_n != 128 && tile_n != 192 && tile_n != 224 && tile_n != 256)
+    return IFLB200_ERR_ARG;
   if (stages < 0 || group_m < 0) return IFLB200_ERR_ARG;
   g_cfg_tile_n = tile_n;
   g_cfg_stages = stages;
@@ -1082,7 +1197,7 @@ extern "C" int iflb200_gemm_set_config(int tile_n, int stages, int group_m) {
 }
 
 extern "C" int iflb200_gemm_set_split_k(int split_k) {
-  if (split_k != 0 && split_k != 1 && split_k != 2 && split_k != 4 && split_k != 8) return IFLB200_ERR_ARG;
+  if (split_k != 0 && split_k != 1 && split_k != 2 && split_k != 4) return IFLB200_ERR_ARG;
   g_cfg_split_k = split_k;
   return IFLB200_OK;
 }

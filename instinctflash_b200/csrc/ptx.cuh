@@ -128,6 +128,15 @@ __device__ __forceinline__ void tma_prefetch_l2_2d(const void* tensor_map, int x
                : "memory");
 }
 
+// Named CTA barrier split into its two halves: threads that only publish (arrive) do not wait
+// for the others.  `threads` counts arrivals and waiters together.
+__device__ __forceinline__ void named_bar_sync(uint32_t id, uint32_t threads) {
+  asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(threads) : "memory");
+}
+__device__ __forceinline__ void named_bar_arrive(uint32_t id, uint32_t threads) {
+  asm volatile("bar.arrive %0, %1;" ::"r"(id), "r"(threads) : "memory");
+}
+
 // ---------------------------------------------------------------------------------------------
 // Programmatic dependent launch.  A kernel launched with the programmatic-stream-serialization
 // attribute may start while its predecessor in the stream still runs; grid_dependency_wait()
@@ -205,6 +214,14 @@ __device__ __forceinline__ uint32_t cluster_ctarank() {
   uint32_t r;
   asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
   return r;
+}
+// The two halves of the cluster barrier (every thread of every CTA of the cluster executes both,
+// in this order, each warp converged).
+__device__ __forceinline__ void cluster_arrive() {
+  asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void cluster_wait() {
+  asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
 }
 __device__ __forceinline__ void cluster_sync_all() {
   asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
