@@ -265,7 +265,10 @@ def main():
     ap.add_argument("--episodes", type=int, default=1,
                     help="c3 only: independent episodes stacked along M on each GPU (rows are independent: "
                          "per-token scales and per-row norms, so this is arithmetically the same as separate runs)")
-    ap.add_argument("--per-op", action="store_true", help="c3: one launch per operator instead of the persistent kernel")
+    ap.add_argument("--persistent", action="store_true",
+                    help="c3: the whole stack as one cooperative launch (stack_persistent_kernel) instead of one "
+                         "launch per operator (the default: with dependent launches it is the faster of the two)")
+    ap.add_argument("--per-op", action="store_true", help="accepted for compatibility: one launch per operator is the default")
     ap.add_argument("--parallel", default="dp", choices=["dp", "tp"],
                     help="dp: every rank runs its own stack (default); tp: the Wan-shape stacks (c4, c5) are "
                          "column/row split over the ranks with NCCL all-gather / reduce-scatter")
@@ -302,7 +305,7 @@ def main():
         return
 
     weights = make_weights(spec, dev)
-    persistent = (spec.kind == "gemma" and not spec.o_in and spec.M <= 128 and not args.per_op)
+    persistent = (spec.kind == "gemma" and not spec.o_in and spec.M <= 128 and args.persistent and not args.per_op)
     if persistent:
         # skinny expert loop: the whole stack is one cooperative launch
         from instinctflash_b200.stack_persistent import PersistentExpertStack

@@ -1099,7 +1099,20 @@ static int run_gemm(const void* a, int64_t ld_a, const void* w, int64_t ld_w, Ge
   } else {
     memset(&to, 0, sizeof(to));
   }
-  if (g_cfg_mode >= 2 && p.N >= 256) {
+  // CTA pairs by choice of the heuristic: in the large-M regime both kernels sit at the tensor
+  // pipe's rate, but a pair moves 32 KB per SM and K step instead of 48 KB, and a layer stack that
+  // runs for milliseconds is power-capped: measured inside the M = 16384 stack the pair kernel is
+  // 3.3 % faster, inside the M = 4680 stack (19 pair row blocks for 18.3 needed, 10 waves for 9)
+  // 2-3 % slower.  It is taken when its wave count (of equal work) is not above the single-CTA one.
+  bool pair_by_heuristic = false;
+  if (g_cfg_mode == 0 && g_cfg_tile_n == 0 && g_cfg_split_k == 0 && p.M >= 4096 && p.N >= 256) {
+    const int64_t single_tiles = (int64_t)((p.M + BM - 1) / BM) * ((p.N + 255) / 256);
+    const int64_t pair_tiles = (int64_t)((p.M + 2 * BM - 1) / (2 * BM)) * ((p.N + 255) / 256);
+    const int64_t single_waves = (single_tiles + dev->sm_count - 1) / dev->sm_count;
+    const int64_t pair_waves = (pair_tiles + dev->sm_count / 2 - 1) / (dev->sm_count / 2);
+    pair_by_heuristic = pair_waves <= single_waves;
+  }
+  if ((g_cfg_mode >= 2 || pair_by_heuristic) && p.N >= 256) {
     // CTA pairs: 256 x 256 tiles, each CTA loads 128 rows of A and 128 rows of W per K step.
     constexpr int PBN = 256;
     p.num_m = (p.M + 2 * BM - 1) / (2 * BM);
@@ -1115,7 +1128,7 @@ static int run_gemm(const void* a, int64_t ld_a, const void* w, int64_t ld_w, Ge
     st = make_tensor_map(&tw, w, p.N, p.K, ld_w, PBN / 2);
     if (st != IFLB200_OK) return st;
     return g_cfg_mode == 2 ? launch_gemm_pair<PBN, 6, 1>(ta, tw, to, p, grid, s)
-                           : launch_gemm_pair<PBN, 6, 2>(ta, tw, to, p, grid, s);
+                           : launch_gemm_pair<PBN, 6, 2>(ta, tw, to, p, grid, s);  // two accumulators
   }
 
   // Tile width by a measured cost model: one 128-byte K step of a CTA costs about 590 / 690 /

@@ -145,10 +145,12 @@ __device__ __forceinline__ void mask_tail(float (&v)[8], int c0, int width) {
 }
 template <bool FAST>
 __device__ __forceinline__ void store_codes(uint8_t* row_ptr, int c0, int width, const float (&v)[8], float inv) {
-  const uint32_t lo = cvt_e4m3x4(__fmul_rn(v[0], inv), __fmul_rn(v[1], inv), __fmul_rn(v[2], inv),
-                                 __fmul_rn(v[3], inv));
-  const uint32_t hi = cvt_e4m3x4(__fmul_rn(v[4], inv), __fmul_rn(v[5], inv), __fmul_rn(v[6], inv),
-                                 __fmul_rn(v[7], inv));
+  float s[8];
+  const uint64_t inv2 = pack2(inv, inv);
+#pragma unroll
+  for (int i = 0; i < 8; i += 2) unpack2(mul2(pack2(v[i], v[i + 1]), inv2), s[i], s[i + 1]);
+  const uint32_t lo = cvt_e4m3x4(s[0], s[1], s[2], s[3]);
+  const uint32_t hi = cvt_e4m3x4(s[4], s[5], s[6], s[7]);
   if (FAST) {
     *reinterpret_cast<uint2*>(row_ptr + c0) = make_uint2(lo, hi);
   } else {
@@ -316,7 +318,7 @@ row_quant_kernel(const RowQuantArgs a) {
       ch.done(v[it]);
       if (a.gelu) {
 #pragma unroll
-        for (int i = 0; i < 8; ++i) v[it][i] = gelu_tanh_ref(v[it][i]);
+        for (int i = 0; i < 8; i += 2) gelu_tanh_ref2(v[it][i], v[it][i + 1]);
       }
       mask_tail<FAST>(v[it], c0, a.K);
 #pragma unroll
@@ -391,9 +393,10 @@ gated_act_quant_kernel(const GatedArgs a) {
       unpack(ru[it], u);
       if (a.row) {
 #pragma unroll
-        for (int i = 0; i < 8; ++i) {
-          g[i] = __fmul_rn(g[i], rs);
-          u[i] = __fmul_rn(u[i], rs);
+        for (int i = 0; i < 8; i += 2) {
+          const uint64_t rs2 = pack2(rs, rs);
+          unpack2(mul2(pack2(g[i], g[i + 1]), rs2), g[i], g[i + 1]);
+          unpack2(mul2(pack2(u[i], u[i + 1]), rs2), u[i], u[i + 1]);
         }
       }
       if (a.col) {
@@ -401,14 +404,17 @@ gated_act_quant_kernel(const GatedArgs a) {
         load_f32<FAST>(a.col, c0, a.F, cg);
         load_f32<FAST>(a.col + a.F, c0, a.F, cu);
 #pragma unroll
-        for (int i = 0; i < 8; ++i) {
-          g[i] = __fmul_rn(g[i], cg[i]);
-          u[i] = __fmul_rn(u[i], cu[i]);
+        for (int i = 0; i < 8; i += 2) {
+          unpack2(mul2(pack2(g[i], g[i + 1]), pack2(cg[i], cg[i + 1])), g[i], g[i + 1]);
+          unpack2(mul2(pack2(u[i], u[i + 1]), pack2(cu[i], cu[i + 1])), u[i], u[i + 1]);
         }
       }
       if (a.act == IFLB200_ACT_GELU_TANH) {
 #pragma unroll
-        for (int i = 0; i < 8; ++i) h[it][i] = __fmul_rn(u[i], gelu_tanh_ref(g[i]));
+        for (int i = 0; i < 8; i += 2) {
+          gelu_tanh_ref2(g[i], g[i + 1]);
+          unpack2(mul2(pack2(u[i], u[i + 1]), pack2(g[i], g[i + 1])), h[it][i], h[it][i + 1]);
+        }
       } else {
 #pragma unroll
         for (int i = 0; i < 8; ++i) h[it][i] = __fmul_rn(u[i], silu_ref(g[i]));

@@ -8,6 +8,33 @@
 
 namespace iflb200 {
 
+// Two fp32 lanes in one 64-bit register for the packed add / mul / fma of sm_100 (each lane
+// rounds exactly like the scalar instruction, so results are unchanged; the instruction count of
+// the issue-bound row kernels is what they halve).
+__device__ __forceinline__ uint64_t pack2(float a, float b) {
+  uint64_t r;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(a), "f"(b));
+  return r;
+}
+__device__ __forceinline__ void unpack2(uint64_t v, float& a, float& b) {
+  asm("mov.b64 {%0, %1}, %2;" : "=f"(a), "=f"(b) : "l"(v));
+}
+__device__ __forceinline__ uint64_t mul2(uint64_t a, uint64_t b) {
+  uint64_t r;
+  asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
+  return r;
+}
+__device__ __forceinline__ uint64_t add2(uint64_t a, uint64_t b) {
+  uint64_t r;
+  asm("add.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
+  return r;
+}
+__device__ __forceinline__ uint64_t fma2(uint64_t a, uint64_t b, uint64_t c) {
+  uint64_t r;
+  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(r) : "l"(a), "l"(b), "l"(c));
+  return r;
+}
+
 // A value with at most one multiplication not yet rounded, so that a following add can be
 // contracted with it:  x*a*b + c  ->  fma(mul(x, a), b, c).
 struct Chain {
@@ -51,7 +78,7 @@ struct Chain8 {
   __device__ __forceinline__ void flush() {
     if (pending) {
 #pragma unroll
-      for (int i = 0; i < 8; ++i) v[i] = __fmul_rn(v[i], p[i]);
+      for (int i = 0; i < 8; i += 2) unpack2(mul2(pack2(v[i], v[i + 1]), pack2(p[i], p[i + 1])), v[i], v[i + 1]);
     }
   }
   __device__ __forceinline__ void mul(const float (&f)[8]) {
@@ -69,11 +96,12 @@ struct Chain8 {
   __device__ __forceinline__ void add(const float (&c)[8]) {
     if (pending) {
 #pragma unroll
-      for (int i = 0; i < 8; ++i) v[i] = __fmaf_rn(v[i], p[i], c[i]);
+      for (int i = 0; i < 8; i += 2)
+        unpack2(fma2(pack2(v[i], v[i + 1]), pack2(p[i], p[i + 1]), pack2(c[i], c[i + 1])), v[i], v[i + 1]);
       pending = false;
     } else {
 #pragma unroll
-      for (int i = 0; i < 8; ++i) v[i] = __fadd_rn(v[i], c[i]);
+      for (int i = 0; i < 8; i += 2) unpack2(add2(pack2(v[i], v[i + 1]), pack2(c[i], c[i + 1])), v[i], v[i + 1]);
     }
   }
   __device__ __forceinline__ void done(float (&out)[8]) {
@@ -101,6 +129,27 @@ __device__ __forceinline__ float gelu_tanh_ref(float v) {
   const float s1 = __fadd_rn(d, -1.0f);
   const float s2 = __fadd_rn(s1, 1.0f);
   return __fmul_rn(half, s2);
+}
+
+// The same for two elements, with the packed instructions.
+__device__ __forceinline__ void gelu_tanh_ref2(float& x0, float& x1) {
+  const uint64_t v = pack2(x0, x1);
+  const float k1 = __uint_as_float(0x3D372713u), k2 = __uint_as_float(0x3F4C422Au), kl = __uint_as_float(0x3FB8AA3Bu);
+  const uint64_t a1 = mul2(v, pack2(k1, k1));
+  const uint64_t a2 = mul2(v, a1);
+  const uint64_t t = fma2(v, a2, v);
+  const uint64_t inner = mul2(t, pack2(k2, k2));
+  const uint64_t half = mul2(v, pack2(0.5f, 0.5f));
+  const uint64_t m2 = mul2(inner, pack2(-2.0f, -2.0f));
+  const uint64_t z = mul2(m2, pack2(kl, kl));
+  float z0, z1;
+  unpack2(z, z0, z1);
+  const uint64_t den = add2(pack2(ex2_approx(z0), ex2_approx(z1)), pack2(1.0f, 1.0f));
+  float d0, d1;
+  unpack2(den, d0, d1);
+  const uint64_t s1 = add2(pack2(div_full(2.0f, d0), div_full(2.0f, d1)), pack2(-1.0f, -1.0f));
+  const uint64_t s2 = add2(s1, pack2(1.0f, 1.0f));
+  unpack2(mul2(half, s2), x0, x1);
 }
 
 // silu as written in the reference: g / (1 + exp(-g)).
