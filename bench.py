@@ -269,9 +269,11 @@ def main():
                     help="c3: the whole stack as one cooperative launch (stack_persistent_kernel) instead of one "
                          "launch per operator (the default: with dependent launches it is the faster of the two)")
     ap.add_argument("--per-op", action="store_true", help="accepted for compatibility: one launch per operator is the default")
-    ap.add_argument("--parallel", default="dp", choices=["dp", "tp"],
-                    help="dp: every rank runs its own stack (default); tp: the Wan-shape stacks (c4, c5) are "
-                         "column/row split over the ranks with NCCL all-gather / reduce-scatter")
+    ap.add_argument("--parallel", default="dp", choices=["dp", "tp", "tokens"],
+                    help="dp: every rank runs its own stack (default, weak scaling); tp: the Wan-shape stacks "
+                         "(c4, c5) are column/row split over the ranks with NCCL all-gather / reduce-scatter; "
+                         "tokens: the rows of one stack are split over the ranks (every linear and every row "
+                         "operator of the path is row-independent: no collective, strong scaling)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "native" else args.warmup
 
@@ -284,6 +286,12 @@ def main():
     if args.episodes > 1:
         from instinctflash_b200.stack import StackSpec
         spec = StackSpec(**{**spec.__dict__, "M": spec.M * args.episodes})
+    total_flops_all_ranks = None
+    if args.parallel == "tokens":
+        # strong scaling over tokens: rank r owns rows [r*M/p, (r+1)*M/p) (ceil), full weights everywhere
+        from instinctflash_b200.stack import StackSpec
+        total_flops_all_ranks = spec.flops()
+        spec = StackSpec(**{**spec.__dict__, "M": -(-spec.M // world)})
 
     if args.impl == "reference":
         run_reference(args, spec, rank, world)
@@ -457,15 +465,19 @@ def main():
                          f"best of repeats within 12 s"}
 
     if rank == 0:
-        value = world * flops * args.steps / (ms * 1e-3) / 1e12
-        e2e_value = world * flops * args.steps / (ms_e2e * 1e-3) / 1e12
+        tokens = args.parallel == "tokens"
+        job_flops = total_flops_all_ranks if tokens else world * flops   # rows actually asked for, padding not counted
+        value = job_flops * args.steps / (ms * 1e-3) / 1e12
+        e2e_value = job_flops * args.steps / (ms_e2e * 1e-3) / 1e12
         line = {
             "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
-            "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
-            "dtype": "e4m3 x e4m3 -> f32", "data": "synthetic",
+            "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "strong" if tokens else "weak",
+            "vs_baseline": None, "dtype": "e4m3 x e4m3 -> f32", "data": "synthetic",
             "config": {"workload": workload_name(spec) + (f", {args.episodes} episodes stacked along M (M={spec.M})" if args.episodes > 1 else ""),
                        "execution": "persistent whole-stack kernel (one cooperative launch per step)" if persistent else "one launch per operator, CUDA graph",
-                       "parallelism": f"dp{world} (independent stacks, no collective)",
+                       "parallelism": (f"tokens/{world}: rows of one stack split over the ranks ({spec.M} per rank), full "
+                                       f"weights on every rank, no collective" if tokens
+                                       else f"dp{world} (independent stacks, no collective)"),
                        "l2": f"weights streamed per step ({spec.weight_bytes() / 1e9:.2f} GB) exceed the 126 MB L2",
                        "timing": "one CUDA-graph replay per step, CUDA events on the launching stream"},
             "roofline": roofline, "cpu_baseline": cpu,

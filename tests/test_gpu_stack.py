@@ -105,3 +105,34 @@ def test_persistent_stack_rejects_unsupported_specs():
         PersistentExpertStack(StackSpec("x", "gemma", 1, 50, 1024, 4096, 1536, o_in=2048), w, DEV)
     with pytest.raises(ValueError):
         PersistentExpertStack(StackSpec("x", "wan", 1, 50, 1024, 4096, 1536), w, DEV)
+
+
+@pytest.mark.parametrize("kind,M", [("gemma", 50), ("gemma", 816), ("wan", 300)])
+def test_dependent_launch_modes_give_identical_results(kind, M):
+    """Programmatic dependent launch only changes when a kernel may be scheduled: eager and
+    CUDA-graph runs of a stack give the same bits with it off (0), automatic (1) and forced (2)."""
+    from instinctflash_b200 import _lib
+    lib = _lib.lib()
+    spec = StackSpec("t", kind, 2, M, 1024, 2048, 1536, o_in=1024, cross=kind == "wan", seed=5)
+    weights = make_weights(spec, DEV)
+    x, attn = make_inputs(spec, DEV)
+    results = []
+    try:
+        for mode in (0, 1, 2):
+            assert lib.iflb200_set_dependent_launch(mode) == 0
+            st = LinearStack(spec, weights, DEV)
+            st.load(x, attn)
+            g = st.capture()
+            st.load(x, attn)          # back to the initial residual stream, then one replay
+            g.replay()
+            torch.cuda.synchronize()
+            results.append((st.res.clone(), st._q8(spec.hidden).view(torch.uint8).clone()))
+            st.load(x, attn)
+            eager = st.forward().clone()
+            torch.cuda.synchronize()
+            assert torch.equal(eager, results[-1][0]), f"mode {mode}: eager and graph replay differ"
+    finally:
+        lib.iflb200_set_dependent_launch(1)
+    assert lib.iflb200_set_dependent_launch(3) != 0
+    for res, codes in results[1:]:
+        assert torch.equal(res, results[0][0]) and torch.equal(codes, results[0][1])
