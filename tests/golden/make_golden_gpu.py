@@ -1,7 +1,7 @@
 """Record golden vectors of the reference's OWN FP8 path on a B200.
 
-Runs the unmodified InstinctFlash reference (installed with pip into ``baseline/_ref``, see
-DESIGN.md) on the seeded inputs of ``tests/cases.py`` and writes ``golden_b200.json``:
+Runs the unmodified InstinctFlash reference (installed with pip, unchanged, into the git-ignored
+``baseline/_ref``) on the seeded inputs of ``tests/cases.py`` and writes ``golden_b200.json``:
 per case the sha256 of every output buffer, the full per-row scale vectors (as int32 bit
 patterns) and the first 64 elements of the first row of each buffer.  The Triton kernels of ``instinctflash.kernels`` have no
 capability gate and run on sm_100 as they are; the per-tensor packer does have one
