@@ -319,8 +319,9 @@ IFLB200_API int iflb200_row_set_group(int threads_per_row);
 IFLB200_API int iflb200_set_dependent_launch(int enable);
 /* Kernel family: 0 = heuristic, 1 = single-CTA tiles only, 2 / 3 = 256x256 tiles on CTA pairs
  * (cta_group::2) with one / two tensor-memory accumulators; add 16 to store the epilogue
- * straight from registers instead of through shared memory and TMA.  For experiments and
- * tests.  No reference counterpart. */
+ * straight from registers instead of through shared memory and TMA; add 256 to take the
+ * swapped form (tokens on the MMA's N side, 257..1024 tokens, two-byte raw or dequantised output;
+ * not chosen by the heuristic) wherever it exists, 128 to forbid it, 512 to keep the swapped form off CTA pairs.  For experiments and tests.  No reference counterpart. */
 IFLB200_API int iflb200_gemm_set_mode(int mode);
 /* Diagnostics: tensor-memory base addresses seen by the two CTAs of the first pair of the last
  * CTA-pair launch.  Synchronises the stream.  No reference counterpart. */

@@ -364,13 +364,75 @@ __device__ __forceinline__ void epilogue_tma_store(const GemmParams& p, const CU
   }
 }
 
+// Epilogue of the swapped form (tokens on the MMA's N side): the accumulator holds the tile
+// transposed, lane = output column n, TMEM column = token.  A warp turns 32 tokens x its 32 output
+// columns into a [token][n] block of 32 x 64 bytes in shared memory (one 2-byte store per value:
+// the 32 lanes of a store instruction fill 64 contiguous bytes of one token row, no bank
+// conflict) and writes it with one TMA store; two blocks per warp alternate.  The last chunk of a
+// token tile whose width is not a multiple of 32 starts at width - 32 and rewrites a few tokens of
+// the chunk before it with the same values.  Two-byte outputs, raw or dequantised.
+template <int BT>
+__device__ __forceinline__ void epilogue_swapped(const GemmParams& p, const CUtensorMap* tm_out, uint32_t t_row,
+                                                 uint32_t staging, uint8_t* staging_ptr, int n_row0, int tok0,
+                                                 int half, int lane, int& buf) {
+  constexpr int kChunks = (BT + 31) / 32;
+  constexpr int kFirstHalf = (kChunks + 1) / 2;
+  const int c_begin = half == 0 ? 0 : kFirstHalf, c_end = half == 0 ? kFirstHalf : kChunks;
+  const int n = n_row0 + lane;  // this lane's output column
+  const bool n_ok = n < p.M;    // p.M: rows of the MMA's M side = output columns
+  float cs = 1.0f, bs = 0.0f;
+  if (p.epilogue == EPI_DEQUANT && n_ok) {
+    if (p.col) cs = __ldg(p.col + (int64_t)n * p.col_stride);
+    if (p.bias)
+      bs = (p.bias_dtype == IFLB200_F32) ? __ldg(reinterpret_cast<const float*>(p.bias) + n)
+                                         : __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(p.bias)[n]);
+  }
+  // `buf` lives across tiles: the two blocks alternate over the whole life of the warp, so the
+  // block about to be written is always the one whose store was issued two stores ago
+#pragma unroll 1
+  for (int c = c_begin; c < c_end; ++c) {
+    const int t0 = (c * 32 + 32 <= BT) ? c * 32 : BT - 32;  // chunk start inside the tile
+    const int tok = tok0 + t0;
+    if (tok >= p.N) continue;  // p.N: tokens
+    if (n_row0 >= p.M) continue;
+    if (p.debug_skip == 1) continue;
+    uint32_t r[32];
+    tmem_ld_32x32b_x32(t_row + t0, r);
+    tmem_ld_wait();
+    if (lane == 0) bulk_wait_group_read<1>();  // the store issued two chunks ago has read this block
+    __syncwarp();
+    uint8_t* blk = staging_ptr + buf * 2048 + lane * 2;
+#pragma unroll
+    for (int j = 0; j < 32; ++j) {
+      float v = __uint_as_float(r[j]);
+      if (p.epilogue == EPI_DEQUANT) {
+        if (!p.exact) v = __bfloat162float(__float2bfloat16_rn(v));
+        Chain ch(v);
+        if (p.row) ch.mul(__ldg(p.row + (int64_t)min(tok + j, p.N - 1) * p.row_stride));
+        if (p.col) ch.mul(cs);
+        if (p.bias) ch.add(bs);
+        v = ch.done();
+      }
+      const uint16_t h = p.out_dtype == IFLB200_F16 ? (uint16_t)f32_to_f16_bits(v) : (uint16_t)f32_to_bf16_bits(v);
+      *reinterpret_cast<uint16_t*>(blk + j * 64) = h;
+    }
+    fence_proxy_async_smem();
+    __syncwarp();
+    if (lane == 0) {
+      tma_store_2d(tm_out, staging + buf * 2048, n_row0, tok);
+      bulk_commit_group();
+    }
+    buf ^= 1;
+  }
+}
+
 // SPLIT: 0 = never a cluster split-K, 1 = always (p.split_k > 1), 2 = decided by p.split_k.  The
 // wide-tile kernels of the large-M regime exist in forms 0 and 1: measured inside the M = 816 layer
 // stack, a kernel that carries both code paths ran the stack 5 % slower than the two specialised
 // ones.  The 64-wide kernel of the skinny-M regime exists only in form 2, so that the launches of a
 // layer, split or not, run the same code: there a second GEMM kernel per layer cost about 1 us per
 // launch in instruction fetch (0.2 ms per pass of the M = 50 stack).
-template <int BN, int STAGES, int SPLIT>
+template <int BN, int STAGES, int SPLIT, bool SWAP = false>
 __global__ void __launch_bounds__(kGemmThreads, 1)
 gemm_fp8_tc5_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_w,
                     const __grid_constant__ CUtensorMap tm_out, const GemmParams p) {
@@ -545,6 +607,7 @@ gemm_fp8_tc5_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
     uint8_t* staging_ptr = smem + L::kStagingOffset + (warp - 2) * 4096;
     bool ok = true;
     uint32_t it = 0;
+    int swap_buf = 0;
     for (int tile = tile_first; ok && tile < p.num_tiles; tile += tile_stride, ++it) {
       int m_blk, n_blk;
       tile_coords(p, tile, m_blk, n_blk);
@@ -557,9 +620,17 @@ gemm_fp8_tc5_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
       if (it == 0) grid_dependency_wait();  // returns at once: the loads behind this tile waited already
       const int m = m_blk * BM + quad * 32 + lane;
       const bool row_ok = m < p.M;
+      const uint32_t t_row = tmem_base + ((uint32_t)(quad * 32) << 16) + acc * kAccStride;
+      if constexpr (SWAP) {
+        epilogue_swapped<BN>(p, &tm_out, t_row, staging, staging_ptr, m_blk * BM + quad * 32, n_blk * BN, half, lane,
+                             swap_buf);
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(tempty_bar(acc));
+        continue;
+      }
       const float rs = (row_ok && p.row) ? __ldg(p.row + (int64_t)m * p.row_stride) : 1.0f;
       const int64_t gofs = (row_ok && p.gate_index) ? (int64_t)p.gate_index[m] * p.N : 0;
-      const uint32_t t_row = tmem_base + ((uint32_t)(quad * 32) << 16) + acc * kAccStride;
       if (split) {
         // one tile per CTA: the partial accumulator stays in tensor memory; the exchange with
         // the other CTAs of the cluster follows the role loops
@@ -750,12 +821,13 @@ struct PairSmemLayout {
 // tensor-memory base addresses seen by the two CTAs of cluster 0 (diagnostics)
 __device__ uint32_t g_pair_debug[4];
 
-template <int BN, int STAGES, int ACC>
+template <int BN, int STAGES, int ACC, bool SWAP = false>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
 gemm_fp8_tc5_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_w,
                          const __grid_constant__ CUtensorMap tm_out, const GemmParams p) {
   using L = PairSmemLayout<BN, STAGES>;
-  constexpr uint32_t kTmemCols = ACC * BN;  // 256 or 512
+  constexpr uint32_t kAccStride = BN <= 128 ? 128 : 256;  // accumulators at power-of-two column offsets
+  constexpr uint32_t kTmemCols = ACC * kAccStride;         // 256 or 512
   constexpr uint32_t kIdesc = make_idesc_e4m3_f32(2 * BM, BN);
 
   extern __shared__ uint8_t smem_raw[];
@@ -850,7 +922,7 @@ gemm_fp8_tc5_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_
                                                   (2u << 24) | (2u << 16) | (it & 0xFFFF)));
         if (!ok) break;
         tc_fence_after();
-        const uint32_t d_tmem = tmem_base + acc * BN;
+        const uint32_t d_tmem = tmem_base + acc * kAccStride;
         for (int kb = 0; kb < p.num_k; ++kb) {
           ok = __all_sync(0xFFFFFFFFu, wait_bounded(full_bar(stage), phase, abort_flag,
                                                     (2u << 24) | (3u << 16) | (it & 0xFFFF)));
@@ -891,6 +963,7 @@ gemm_fp8_tc5_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_
     uint8_t* staging_ptr = smem + L::kStagingOffset + (warp - 2) * 4096;
     bool ok = true;
     uint32_t it = 0;
+    int swap_buf = 0;
     for (int tile = pair_id; ok && tile < p.num_tiles; tile += pair_stride, ++it) {
       int m_blk, n_blk;
       tile_coords(p, tile, m_blk, n_blk);
@@ -902,9 +975,17 @@ gemm_fp8_tc5_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_
       tc_fence_after();
       const int m = m_blk * 2 * BM + (int)rank * BM + quad * 32 + lane;
       const bool row_ok = m < p.M;
+      const uint32_t t_row = tmem_base + ((uint32_t)(quad * 32) << 16) + acc * kAccStride;
+      if constexpr (SWAP) {
+        epilogue_swapped<BN>(p, &tm_out, t_row, staging, staging_ptr, m_blk * 2 * BM + (int)rank * BM + quad * 32,
+                             n_blk * BN, half, lane, swap_buf);
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive_cluster(tempty_bar(acc), 0);
+        continue;
+      }
       const float rs = (row_ok && p.row) ? __ldg(p.row + (int64_t)m * p.row_stride) : 1.0f;
       const int64_t gofs = (row_ok && p.gate_index) ? (int64_t)p.gate_index[m] * p.N : 0;
-      const uint32_t t_row = tmem_base + ((uint32_t)(quad * 32) << 16) + acc * BN;
       if (p.tma_store) {
         epilogue_tma_store<BN>(p, &tm_out, t_row, staging, staging_ptr,
                                m_blk * 2 * BM + (int)rank * BM + quad * 32, n_blk * BN, col_begin, col_end, rs, lane);
@@ -992,6 +1073,21 @@ static int make_out_map(CUtensorMap* tm, void* ptr, int M, int N, int64_t ld, in
   return r == CUDA_SUCCESS ? IFLB200_OK : IFLB200_ERR_DRIVER;
 }
 
+// [tokens, N] output of two-byte elements for the swapped form: box = 32 columns (64 bytes) x 32
+// token rows, no swizzle.
+static int make_out_map_swapped(CUtensorMap* tm, void* ptr, int tokens, int N, int64_t ld) {
+  EncodeTiledFn enc = get_encode_fn();
+  if (!enc) return IFLB200_ERR_DRIVER;
+  const cuuint64_t dims[2] = {(cuuint64_t)N, (cuuint64_t)tokens};
+  const cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
+  const cuuint32_t box[2] = {32u, 32u};
+  const cuuint32_t estr[2] = {1, 1};
+  const CUresult r = enc(tm, CU_TENSOR_MAP_DATA_TYPE_UINT16, 2, ptr, dims, strides, box, estr,
+                         CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_NONE,
+                         CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? IFLB200_OK : IFLB200_ERR_DRIVER;
+}
+
 struct DeviceInfo {
   int sm_count = 0;
   int cc_major = 0;
@@ -1022,9 +1118,11 @@ static int g_cfg_tile_n = 0, g_cfg_stages = 0, g_cfg_group_m = 0;
 static int g_cfg_split_k = 0;  // 0: cost model, 1: never split K, 2/4/8: forced
 static int g_cfg_debug_skip = 0;
 static int g_cfg_direct_store = 0;  // 1: epilogue stores straight from registers (experiments)
+static int g_cfg_pair_swap = 1;  // the swapped form on CTA pairs where the shape allows
+static int g_cfg_swap = 0;  // 0: cost model, 1: never, 2: always where the form exists
 static int g_cfg_mode = 0;  // 0 auto, 1 single-CTA tiles only, 2 CTA pairs with one accumulator, 3 CTA pairs with two
 
-template <int BN, int STAGES, int SPLIT>
+template <int BN, int STAGES, int SPLIT, bool SWAP = false>
 static int launch_gemm_form(const CUtensorMap& ta, const CUtensorMap& tw, const CUtensorMap& to, const GemmParams& p,
                             int grid, cudaStream_t s) {
   using L = SmemLayout<BN, STAGES>;
@@ -1032,13 +1130,13 @@ static int launch_gemm_form(const CUtensorMap& ta, const CUtensorMap& tw, const 
   int dev = 0;
   cudaGetDevice(&dev);
   if (!attr_set[dev]) {
-    cudaError_t e = cudaFuncSetAttribute(gemm_fp8_tc5_kernel<BN, STAGES, SPLIT>,
+    cudaError_t e = cudaFuncSetAttribute(gemm_fp8_tc5_kernel<BN, STAGES, SPLIT, SWAP>,
                                          cudaFuncAttributeMaxDynamicSharedMemorySize, L::kDynamic);
     if (e != cudaSuccess) return (int)e;
     attr_set[dev] = true;
   }
-  const cudaError_t e = launch_dep(gemm_fp8_tc5_kernel<BN, STAGES, SPLIT>, dim3(grid), dim3(kGemmThreads), L::kDynamic,
-                                   s, p.split_k, dependent_launch_for(p.M), ta, tw, to, p);
+  const cudaError_t e = launch_dep(gemm_fp8_tc5_kernel<BN, STAGES, SPLIT, SWAP>, dim3(grid), dim3(kGemmThreads),
+                                   L::kDynamic, s, p.split_k, dependent_launch_for(SWAP ? p.N : p.M), ta, tw, to, p);
   return e != cudaSuccess ? (int)e : (int)cudaGetLastError();
 }
 
@@ -1055,7 +1153,7 @@ static int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tw, const CUten
   }
 }
 
-template <int BN, int STAGES, int ACC>
+template <int BN, int STAGES, int ACC, bool SWAP = false>
 static int launch_gemm_pair(const CUtensorMap& ta, const CUtensorMap& tw, const CUtensorMap& to,
                             const GemmParams& p, int grid, cudaStream_t s) {
   using L = PairSmemLayout<BN, STAGES>;
@@ -1063,13 +1161,13 @@ static int launch_gemm_pair(const CUtensorMap& ta, const CUtensorMap& tw, const 
   int dev = 0;
   cudaGetDevice(&dev);
   if (!attr_set[dev]) {
-    cudaError_t e = cudaFuncSetAttribute(gemm_fp8_tc5_pair_kernel<BN, STAGES, ACC>,
+    cudaError_t e = cudaFuncSetAttribute(gemm_fp8_tc5_pair_kernel<BN, STAGES, ACC, SWAP>,
                                          cudaFuncAttributeMaxDynamicSharedMemorySize, L::kDynamic);
     if (e != cudaSuccess) return (int)e;
     attr_set[dev] = true;
   }
-  const cudaError_t e = launch_dep(gemm_fp8_tc5_pair_kernel<BN, STAGES, ACC>, dim3(grid), dim3(kGemmThreads),
-                                   L::kDynamic, s, 1, dependent_launch_for(p.M), ta, tw, to, p);
+  const cudaError_t e = launch_dep(gemm_fp8_tc5_pair_kernel<BN, STAGES, ACC, SWAP>, dim3(grid), dim3(kGemmThreads),
+                                   L::kDynamic, s, 1, dependent_launch_for(SWAP ? p.N : p.M), ta, tw, to, p);
   return e != cudaSuccess ? (int)e : (int)cudaGetLastError();
 }
 
@@ -1144,6 +1242,7 @@ static int run_gemm(const void* a, int64_t ld_a, const void* w, int64_t ld_w, Ge
   p.num_m = (p.M + BM - 1) / BM;
   int bn = g_cfg_tile_n;
   int split = 1;
+  int64_t best_cost = 0;
   {
     const int widths[5] = {256, 224, 192, 128, 64};
     const int64_t step_cycles[5] = {830, 790, 750, 690, 590};
@@ -1173,6 +1272,63 @@ static int run_gemm(const void* a, int64_t ld_a, const void* w, int64_t ld_w, Ge
     }
     if (best_bn == 0) return IFLB200_ERR_ARG;  // the forced configuration does not fit this problem
     bn = best_bn;
+    best_cost = best;
+  }
+  // Swapped form for a few hundred tokens: the tokens go on the MMA's N side in tiles of the width
+  // that fits them (816 tokens = 4 x 208 with 2 % padding, where 7 row blocks of 128 carry 9 %), the
+  // weight rows on its M side in blocks of 128 (256 on a CTA pair), and the epilogue stores the
+  // tile transposed.  Same K loop, same accumulator bits.  Two-byte raw or dequantised outputs.
+  // Measured on 816 x 32768 x 2048: 54.1 us on CTA pairs, 55.7 on single CTAs, against 53.9 for the
+  // ordinary form (the main loops alone 44.8 / 46.2 / 45.5 us: a 208-wide MMA step is no shorter
+  // than a 256-wide one), so the heuristic does not take it; iflb200_gemm_set_mode(256) does.
+  if (g_cfg_swap != 1 && g_cfg_mode == 0 && g_cfg_tile_n == 0 && g_cfg_split_k == 0 && g_cfg_stages == 0 &&
+      p.M > 256 && p.M <= 1024 && oes == 2 && p.tma_store && (p.epilogue == EPI_RAW || p.epilogue == EPI_DEQUANT)) {
+    const int t_tiles = (p.M + 255) / 256;
+    const int fit = ((p.M + t_tiles - 1) / t_tiles + 15) / 16 * 16;
+    const int bt = fit <= 128 ? 128 : (fit <= 208 ? 208 : 256);  // the widths this form is built for
+    const int64_t steps = (p.K + BK - 1) / BK;
+    const int64_t tiles = (int64_t)((p.N + BM - 1) / BM) * ((p.M + bt - 1) / bt);
+    const int64_t waves = (tiles + dev->sm_count - 1) / dev->sm_count;
+    const int64_t cost = waves * (steps * (350 + 5 * (BM + bt) / 4) + 2500);
+    (void)cost;
+    (void)best_cost;
+    if (g_cfg_swap == 2) {
+      GemmParams q = p;
+      q.M = p.N;  // rows of the MMA's M side: output columns
+      q.N = p.M;  // tokens
+      q.num_m = (p.N + BM - 1) / BM;
+      q.num_n = (p.M + bt - 1) / bt;
+      q.num_k = (int)steps;
+      q.num_tiles = q.num_m * q.num_n;
+      q.group_m = g_cfg_group_m > 0 ? g_cfg_group_m : 8;
+      q.split_k = 1;
+      const int grid = q.num_tiles < dev->sm_count ? q.num_tiles : dev->sm_count;
+      CUtensorMap tw_rows, ta_tokens, to_swapped;
+      st = make_tensor_map(&tw_rows, w, p.N, p.K, ld_w, BM);
+      if (st != IFLB200_OK) return st;
+      st = make_tensor_map(&ta_tokens, a, p.M, p.K, ld_a, bt);
+      if (st != IFLB200_OK) return st;
+      st = make_out_map_swapped(&to_swapped, p.out, p.M, p.N, p.ld_out);
+      if (st != IFLB200_OK) return st;
+      if (p.N >= 2 * BM && bt >= 208 && g_cfg_pair_swap) {
+        // weight rows in blocks of 256 on a CTA pair, each CTA loading half of the token tile
+        q.num_m = (p.N + 2 * BM - 1) / (2 * BM);
+        q.num_tiles = q.num_m * q.num_n;
+        q.group_m = g_cfg_group_m > 0 ? g_cfg_group_m : 4;
+        const int pairs = dev->sm_count / 2;
+        const int pgrid = 2 * (q.num_tiles < pairs ? q.num_tiles : pairs);
+        CUtensorMap ta_half;
+        st = make_tensor_map(&ta_half, a, p.M, p.K, ld_a, bt / 2);
+        if (st != IFLB200_OK) return st;
+        return bt == 208 ? launch_gemm_pair<208, 6, 2, true>(tw_rows, ta_half, to_swapped, q, pgrid, s)
+                         : launch_gemm_pair<256, 6, 2, true>(tw_rows, ta_half, to_swapped, q, pgrid, s);
+      }
+      switch (bt) {
+        case 128: return launch_gemm_form<128, 6, 0, true>(tw_rows, ta_tokens, to_swapped, q, grid, s);
+        case 208: return launch_gemm_form<208, 4, 0, true>(tw_rows, ta_tokens, to_swapped, q, grid, s);
+        default: return launch_gemm_form<256, 4, 0, true>(tw_rows, ta_tokens, to_swapped, q, grid, s);
+      }
+    }
   }
   p.split_k = split;
   p.num_n = (p.N + bn - 1) / bn;
@@ -1226,7 +1382,9 @@ extern "C" int iflb200_set_dependent_launch(int enable) {
 extern "C" int iflb200_gemm_set_mode(int mode) {
   // bit 4 (value 16) selects the direct-store epilogue; the low bits the kernel family
   const int family = mode & 15;
-  if (mode < 0 || family > 3 || (mode & ~127)) return IFLB200_ERR_ARG;
+  if (mode < 0 || family > 3 || (mode & ~1023) || (mode & 384) == 384) return IFLB200_ERR_ARG;
+  g_cfg_swap = (mode & 128) ? 1 : ((mode & 256) ? 2 : 0);  // 128: never the swapped form, 256: wherever it exists
+  g_cfg_pair_swap = (mode & 512) ? 0 : 1;                  // 512: the swapped form on single CTAs only
   g_cfg_mode = family;
   g_cfg_direct_store = (mode & 16) ? 1 : 0;
   g_cfg_debug_skip = (mode >> 5) & 3;  // timing experiments only: outputs are not written

@@ -336,6 +336,45 @@ def test_gemm_odd_tile_widths_all_epilogues(ops, tile_n, out_dtype):
     no_timeout(ops)
 
 
+@pytest.mark.parametrize("M,N,K", [(816, 1040, 512), (300, 640, 256), (1000, 2048, 384), (512, 256, 128), (257, 144, 2048),
+                                   (816, 8192, 256), (600, 20480, 128)])
+def test_gemm_swapped_form_is_bit_identical(ops, M, N, K):
+    """A few hundred tokens: tokens on the MMA's N side, tile stored transposed.  Same K loop, so
+    the raw accumulator and the dequantised outputs equal the ordinary form bit for bit."""
+    fp8, lib = ops["fp8"], ops["lib"]
+    g = torch.Generator().manual_seed(M + N + K)
+    a = dev((torch.randn(M, K, generator=g) * 60).clamp(-448, 448).to(E4M3))
+    w = dev((torch.randn(N, K, generator=g) * 60).clamp(-448, 448).to(E4M3))
+    s = dev(cases.vector(M, 911, lo=0.001, hi=0.02))
+    W = fp8.Fp8Weight(w, dev(cases.vector(N, 912, lo=0.0001, hi=0.001)), dev(cases.vector(N, 913, sigma=0.05)))
+
+    def run():
+        raw = torch.full((M, N), float("nan"), device=DEV, dtype=torch.bfloat16)
+        fp8.gemm(a, W, raw)
+        y16 = torch.full((M, N), float("nan"), device=DEV, dtype=torch.float16)
+        fp8.fp8_linear(a, s, W, y16)
+        ybf = torch.full((M, N), float("nan"), device=DEV, dtype=torch.bfloat16)
+        fp8.fp8_linear(a, s, W, ybf, exact=True)
+        view = torch.full((M, N + 48), float("nan"), device=DEV, dtype=torch.bfloat16)
+        fp8.gemm(a, W, view[:, 16:16 + N])            # a strided output view
+        return raw, y16, ybf, view
+    try:
+        assert lib.iflb200_gemm_set_mode(128) == 0     # never swapped
+        want = run()
+        results = []
+        for mode in (256, 256 + 512):                  # swapped wherever the form exists: CTA pairs, single CTAs
+            assert lib.iflb200_gemm_set_mode(mode) == 0
+            results.append(run())
+    finally:
+        lib.iflb200_gemm_set_mode(0)
+    for got in results:
+        for g_, w_, what in zip(got[:3], want[:3], ("raw", "dequant f16", "dequant exact bf16")):
+            assert torch.equal(g_, w_), what
+        assert torch.equal(got[3][:, 16:16 + N], want[3][:, 16:16 + N])
+        assert torch.isnan(got[3][:, :16]).all() and torch.isnan(got[3][:, 16 + N:]).all()   # nothing outside the view
+    no_timeout(ops)
+
+
 def test_gemm_reference_test_shape(ops):
     """instinctflash tests/test_gi_kernels.py:130-143: M=50, K=1024, N=2560 against x@w.T+b, < 0.05."""
     fp8, norm = ops["fp8"], ops["norm"]
