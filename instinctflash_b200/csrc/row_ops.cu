@@ -228,6 +228,12 @@ template <int IT>
 __host__ __device__ constexpr int row_min_blocks() {
   return IT <= 2 ? 3 : 2;
 }
+// residual_norm_quant: three CTAs per SM for up to three chunks per thread (85 registers; capping
+// at 64 for a fourth CTA spills and was measured slower: 7.7 against 4.9 us at 816 x 2048).
+template <int IT>
+__host__ __device__ constexpr int resnorm_min_blocks() {
+  return IT <= 3 ? 3 : 2;
+}
 
 // --------------------------------------------------------------------------------------------
 // row_quant: 2K (bf16 in) + K (codes out) + 4 bytes per row.
@@ -512,7 +518,7 @@ __device__ __forceinline__ float round_through<__nv_bfloat16>(float x) {
 }
 
 template <typename RT, int TPR, int IT, bool FAST>
-__global__ void __launch_bounds__(kRowThreads, row_min_blocks<IT>())
+__global__ void __launch_bounds__(kRowThreads, resnorm_min_blocks<IT>())
 residual_norm_quant_kernel(const ResNormArgs a) {
   row_dependency_wait();  // inputs may come from the kernel before this one in the stream
   row_trigger();
@@ -580,7 +586,8 @@ residual_norm_quant_kernel(const ResNormArgs a) {
       const int c0 = (it * TPR + t) * 8;
       if (it < a.iters && live && c0 < a.D) {
 #pragma unroll
-        for (int i = 0; i < 8; ++i) x[it][i] = __fsub_rn(x[it][i], mean);
+        for (int i = 0; i < 8; i += 2)  // x - mean == x + (-mean), two lanes per instruction
+          unpack2(add2(pack2(x[it][i], x[it][i + 1]), pack2(-mean, -mean)), x[it][i], x[it][i + 1]);
         mask_tail<FAST>(x[it], c0, a.D);
 #pragma unroll
         for (int i = 0; i < 8; ++i) sq = __fmaf_rn(x[it][i], x[it][i], sq);
@@ -611,7 +618,7 @@ residual_norm_quant_kernel(const ResNormArgs a) {
       if (a.beta) ch.add(bs);
       if (a.mod_scale) {
 #pragma unroll
-        for (int i = 0; i < 8; ++i) ms[i] = __fadd_rn(ms[i], 1.0f);
+        for (int i = 0; i < 8; i += 2) unpack2(add2(pack2(ms[i], ms[i + 1]), pack2(1.0f, 1.0f)), ms[i], ms[i + 1]);
         ch.mul(ms);
         ch.add(mh);
       }
@@ -795,12 +802,14 @@ static void dispatch_geom(const RowGeom& g, F&& launch) {
     case 64: launch(IntTag<64>{}, IntTag<8>{}); return;
     case 128:
       if (g.iters <= 2) launch(IntTag<128>{}, IntTag<2>{});
+      else if (g.iters == 3) launch(IntTag<128>{}, IntTag<3>{});
       else if (g.iters <= 4) launch(IntTag<128>{}, IntTag<4>{});
       else launch(IntTag<128>{}, IntTag<8>{});
       return;
     default: break;
   }
   if (g.iters <= 2) launch(IntTag<256>{}, IntTag<2>{});
+  else if (g.iters == 3) launch(IntTag<256>{}, IntTag<3>{});
   else if (g.iters <= 4) launch(IntTag<256>{}, IntTag<4>{});
   else launch(IntTag<256>{}, IntTag<8>{});
 }
@@ -860,6 +869,12 @@ static void launch_resnorm(ResNormArgs a, bool fast, cudaStream_t s) {
   if (g.tpr == kRowThreads && g.iters == 1 && g_row_tpr_override == 0) {
     g.tpr = 128;
     g.iters = 2;
+  }
+  // 2049..3072 columns: 128 threads x 3 chunks use every chunk slot (256 x 2 leaves a quarter empty)
+  const int chunks = (a.D + 7) / 8;
+  if (g.tpr == kRowThreads && g.iters == 2 && chunks <= 384 && g_row_tpr_override == 0) {
+    g.tpr = 128;
+    g.iters = 3;
   }
   a.iters = g.iters;
   dispatch_geom(g, [&](auto tpr, auto it) {
