@@ -78,3 +78,61 @@ def test_missing_library_is_a_loud_error(monkeypatch, tmp_path):
     monkeypatch.setattr(_lib, "library_candidates", lambda: (tmp_path / "nope.so",))
     with pytest.raises(RuntimeError, match="no CPU or PyTorch fallback"):
         _lib.lib()
+
+
+def test_tuning_switches_validate_their_arguments():
+    """The setters are host-only: they accept the documented values and nothing else, and the
+    defaults are restored afterwards (no device is touched)."""
+    lib = _lib.lib()
+    try:
+        for ok in (0, 1, 2, 3, 16, 32, 64, 128, 256, 256 + 512, 3 + 16 + 64):
+            assert lib.iflb200_gemm_set_mode(ok) == 0, ok
+        for bad in (-1, 4, 128 + 256, 1024, 4096):
+            assert lib.iflb200_gemm_set_mode(bad) != 0, bad
+        for ok in (0, 1, 2, 4):
+            assert lib.iflb200_gemm_set_split_k(ok) == 0
+        for bad in (-1, 3, 8, 16):
+            assert lib.iflb200_gemm_set_split_k(bad) != 0
+        for ok in (0, 1, 2):
+            assert lib.iflb200_set_dependent_launch(ok) == 0
+        for bad in (-1, 3):
+            assert lib.iflb200_set_dependent_launch(bad) != 0
+        for ok in ((0, 0, 0), (64, 0, 0), (128, 4, 2), (192, 0, 0), (224, 0, 0), (256, 3, 16)):
+            assert lib.iflb200_gemm_set_config(*ok) == 0
+        for bad in ((32, 0, 0), (100, 0, 0), (256, -1, 0), (256, 0, -2)):
+            assert lib.iflb200_gemm_set_config(*bad) != 0
+    finally:
+        lib.iflb200_gemm_set_mode(0)
+        lib.iflb200_gemm_set_split_k(0)
+        lib.iflb200_set_dependent_launch(1)
+        lib.iflb200_gemm_set_config(0, 0, 0)
+
+
+def test_qkv_entry_points_reject_bad_arguments_before_any_launch():
+    lib = _lib.lib()
+    buf = ctypes.create_string_buffer(4096)
+    p = ctypes.addressof(buf)
+    BF16, F16 = 1, 2
+    # qkv_split: odd head width, head width above 512, rotary without positions, one norm vector only
+    args = dict(qkv=p, dt=BF16, ld=1024, T=2, hq=1, hkv=1, hd=64)
+
+    def split(**kw):
+        a = {**args, **kw}
+        return lib.iflb200_qkv_split(a["qkv"], a["dt"], a["ld"], a["T"], a["hq"], a["hkv"], a["hd"], None, None, None,
+                                     kw.get("qn"), kw.get("kn"), 1e-6, kw.get("inv"), kw.get("pos"), 0, None, None, 0,
+                                     p, 64, 64, p, 64, 64, p, 64, 64, F16, None)
+    assert split(hd=63) != 0 and split(hd=1024) != 0
+    assert split(inv=p) != 0                      # inv_freq without a position table
+    assert split(qn=p) != 0                       # q_norm without k_norm
+    assert split(dt=7) != 0 and split(ld=10) != 0
+    assert split(T=0) == 0                        # empty input: nothing to do, no launch
+    # wan_qkv: V without K, width above 8192, rotary without sections
+    def wan(**kw):
+        return lib.iflb200_wan_qkv(p, BF16, kw.get("ld", 3 * 256), kw.get("rows", 2), 2, kw.get("heads", 2),
+                                   kw.get("hd", 128), None, None, None, None, None, 1e-6, kw.get("inv"), kw.get("pos"), 0,
+                                   None, None, p, 256, kw.get("kp"), 0, 0, kw.get("vp"), 0, 0, F16, None)
+    assert wan(vp=p) != 0
+    assert wan(heads=80) != 0
+    assert wan(inv=p, pos=p) != 0
+    assert wan(ld=100) != 0
+    assert wan(rows=0) == 0
