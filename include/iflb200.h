@@ -82,6 +82,9 @@ IFLB200_API int iflb200_row_quant(const void* x, int x_dtype, int64_t ld_x, int 
  * and stops.  After an all-reduce-max of amax over the shards, phase 2 quantises the local
  * columns with the global maximum read from amax[m] and writes qs[m] and the codes: they are
  * bit-identical to the codes of the unsharded row.  (col and bias are the local slices.)
+ * Phase 3 is phase 2 that also leaves amax[m] at zero afterwards: the second half of
+ * iflb200_fp8_linear_gated, whose epilogue raises the maxima with atomicMax and needs the words
+ * to start at zero again on the next call.
  * Extends instinctflash/kernels/norm.py:128-158, which is single-GPU; no reference counterpart
  * for the split itself.
  */
@@ -208,6 +211,24 @@ IFLB200_API int iflb200_fp8_linear_residual(const void* a, int64_t ld_a, const v
                                 void* res, int res_dtype, int64_t ld_res, void* stream);
 
 /*
+ * Fused linear + gated activation in the epilogue: w is the [2F, K] matrix [gate rows | up rows];
+ * the kernel pairs the gate and up columns of the same hidden units in one tile and writes
+ *   h[m,f] = (r_u*row_scale[m]*col_scale[F+f]) * act(r_g*row_scale[m]*col_scale[f])     (fp32)
+ * with r_g, r_u the accumulators rounded to bf16 first (the reference's memory round trip) and
+ * the reference's instruction order, and raises amax[m] (a non-negative float's bits, compared as
+ * integers) to max_f |h[m,f]| with atomicMax.  amax[0..M) must be zero on entry;
+ * iflb200_row_quant_sharded(h, IFLB200_F32, ..., phase 3, amax, q, qs) then writes exactly the
+ * codes and scales of gated_act_quant and leaves amax at zero for the next call.  h is never
+ * rounded to 16 bits, as in the reference.  F a multiple of 16.
+ * Replaces: instinctflash/kernels/fp8.py:50-53 followed by the activation part of
+ * instinctflash/kernels/activation.py:20-43 (the call pair at
+ * instinctflash/engines/pi05/engine.py:210-212).
+ */
+IFLB200_API int iflb200_fp8_linear_gated(const void* a, int64_t ld_a, const void* w, int64_t ld_w,
+                             int M, int F, int K, const float* row_scale, const float* col_scale,
+                             int act, float* h, int64_t ld_h, uint32_t* amax, void* stream);
+
+/*
  * Per-tensor dynamic e4m3 pack (the torch-FP8-linear recipe):
  *   amax = max |x| (NaN propagates);  scale = max(amax, 1e-12) * fp32(1/448);
  *   q = e4m3_rn(clamp(x / scale, -448, 448))   (IEEE division, NaN propagates)
@@ -260,6 +281,12 @@ IFLB200_API int iflb200_pack_bf16_e4m3(const void* x, int64_t n, const float* sc
  * `ops`, `tensor_maps` (128 bytes each, 64-byte aligned, written by
  * iflb200_encode_operand_map), `barriers` (num_barriers uint32) and `status2` (2 uint32) are
  * device buffers owned by the caller; barriers and status2[1] are zeroed by the call itself.
+ * The program lives in device memory and is NOT validated by the call.  The caller guarantees:
+ * N a multiple of 8 and row strides / base pointers of every operand 16-byte aligned; row
+ * operators at most 8192 columns wide; every K split of a GEMM at least one 128-byte step
+ * (split_k <= ceil(K / 128)); wait_bar / arrive_bar below num_barriers; every counter that an
+ * operator waits on is the arrive_bar of an earlier operator (a counter nobody arrives on makes
+ * the waiting operator run out of its time budget, see status2).
  * status2[0] != 0 after completion: a wait ran out of its time budget (role<<24 | kind<<16 | op).
  */
 #define IFLB200_STACK_GEMM 1    /* out[M,N] = a[M,K] x w[N,K]^T: raw bf16 (split_k = 1) or fp32 partials [split_k][M][N] */
@@ -300,6 +327,24 @@ IFLB200_API int iflb200_stack_run(const void* ops, int num_ops, const void* tens
  */
 IFLB200_API int iflb200_gemm_take_timeout_record(uint32_t* record, void* stream);
 
+/*
+ * Time budget of the waits inside the tcgen05 GEMM and the persistent stack kernel, in
+ * microseconds (0 restores the default of 2 s).  A wait that outlives it makes the kernel record
+ * where it gave up (iflb200_gemm_take_timeout_record / status2[0] of iflb200_stack_run), drain and
+ * return: the context stays usable.  Applies to the current device and synchronises it; not for
+ * use during stream capture.  No reference counterpart.
+ */
+IFLB200_API int iflb200_set_wait_budget_us(int64_t microseconds);
+
+/*
+ * Which kernel the last GEMM call of this process launched (host-side record, no device access):
+ * family 1 = single-CTA tiles, 2 / 3 = CTA pairs with one / two accumulators, +4 = the swapped
+ * form, +8 = the gated form (paired gate / up columns); the tile width in columns (tokens for the
+ * swapped form); the cluster split-K factor.  Any pointer may be NULL.  For tests that must know
+ * that a given kernel really ran.  No reference counterpart.
+ */
+IFLB200_API int iflb200_gemm_last_launch(int* family, int* tile_n, int* split_k);
+
 /* Tuning overrides for experiments and tests (0 = heuristic). No reference counterpart. */
 IFLB200_API int iflb200_gemm_set_config(int tile_n, int stages, int group_m);
 /* Split-K of the GEMM over a thread-block cluster (partials summed over distributed shared
@@ -321,11 +366,10 @@ IFLB200_API int iflb200_set_dependent_launch(int enable);
  * (cta_group::2) with one / two tensor-memory accumulators; add 16 to store the epilogue
  * straight from registers instead of through shared memory and TMA; add 256 to take the
  * swapped form (tokens on the MMA's N side, 257..1024 tokens, two-byte raw or dequantised output;
- * not chosen by the heuristic) wherever it exists, 128 to forbid it, 512 to keep the swapped form off CTA pairs.  For experiments and tests.  No reference counterpart. */
+ * not chosen by the heuristic) wherever it exists, 128 to forbid it, 512 to keep the swapped form
+ * off CTA pairs.  Any other bit is refused.  Every mode writes the same output bits.  For
+ * experiments and tests.  No reference counterpart. */
 IFLB200_API int iflb200_gemm_set_mode(int mode);
-/* Diagnostics: tensor-memory base addresses seen by the two CTAs of the first pair of the last
- * CTA-pair launch.  Synchronises the stream.  No reference counterpart. */
-IFLB200_API int iflb200_gemm_debug_words(uint32_t* out4, void* stream);
 
 #ifdef __cplusplus
 }

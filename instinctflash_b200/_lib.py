@@ -42,6 +42,7 @@ SIGNATURES = {
     "iflb200_gemm_fp8_raw": (_i, [_p, _l, _p, _l, _i, _i, _i, _p, _l, _p]),
     "iflb200_fp8_linear": (_i, [_p, _l, _p, _l, _i, _i, _i, _p, _i, _p, _i, _p, _i, _i, _p, _i, _l, _p]),
     "iflb200_fp8_linear_residual": (_i, [_p, _l, _p, _l, _i, _i, _i, _p, _p, _p, _p, _p, _p, _i, _l, _p]),
+    "iflb200_fp8_linear_gated": (_i, [_p, _l, _p, _l, _i, _i, _i, _p, _p, _i, _p, _l, _p, _p]),
     "iflb200_pack_workspace_bytes": (_z, [_l]),
     "iflb200_dynamic_pack_bf16_e4m3": (_i, [_p, _l, _p, _p, _p, _z, _p]),
     "iflb200_dynamic_pack_bf16_e4m3_noalloc": (_i, [_p, _l, _p, _p, _p]),
@@ -51,12 +52,13 @@ SIGNATURES = {
     "iflb200_stack_weight_box_rows": (_i, []),
     "iflb200_stack_run": (_i, [_p, _i, _p, _p, _i, _i, _p, _p]),
     "iflb200_gemm_take_timeout_record": (_i, [ctypes.POINTER(ctypes.c_uint32), _p]),
+    "iflb200_set_wait_budget_us": (_i, [_l]),
+    "iflb200_gemm_last_launch": (_i, [ctypes.POINTER(_i), ctypes.POINTER(_i), ctypes.POINTER(_i)]),
     "iflb200_gemm_set_config": (_i, [_i, _i, _i]),
     "iflb200_gemm_set_mode": (_i, [_i]),
     "iflb200_set_dependent_launch": (_i, [_i]),
     "iflb200_gemm_set_split_k": (_i, [_i]),
     "iflb200_row_set_group": (_i, [_i]),
-    "iflb200_gemm_debug_words": (_i, [ctypes.POINTER(ctypes.c_uint32), _p]),
 }
 
 _LIB = None

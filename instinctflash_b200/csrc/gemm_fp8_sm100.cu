@@ -56,12 +56,16 @@ struct GemmParams {
   int out_dtype;
   int64_t ld_out;
   int split_k;     // > 1: the CTAs of a cluster share one tile, each a K range; partials are summed over DSMEM
-  int debug_skip;  // experiments: 1 skip the whole epilogue body, 2 load TMEM but do not store
+  int act;         // gated form: IFLB200_ACT_*
+  uint32_t* amax;  // gated form: per-row maximum of |h| as float bits, raised with atomicMax
   int tma_store;  // 1: the epilogue stages 128-byte row pieces in shared memory and TMA-stores them
 };
 
 // role << 24 | barrier kind << 16 | low 16 bits of the tile counter; 0 = no timeout.
 __device__ uint32_t g_timeout_record[4];
+// Time budget of every wait inside the GEMM kernels (read only on the slow path of a wait).
+__device__ uint64_t g_gemm_wait_budget_ns = kWaitBudgetNs;
+int set_stack_wait_budget_ns(uint64_t ns);  // stack_persistent.cu
 
 __device__ __forceinline__ uint32_t map_to_cta(uint32_t smem_addr, uint32_t rank) {
   uint32_t r;
@@ -116,7 +120,7 @@ __device__ __forceinline__ bool wait_bounded(uint32_t bar, uint32_t parity, vola
     if (++spins > 2048) {
       if (t0 == 0) t0 = globaltimer_ns();
       __nanosleep(128);
-      if (globaltimer_ns() - t0 > kWaitBudgetNs) {
+      if (globaltimer_ns() - t0 > g_gemm_wait_budget_ns) {
         *abort = 1;
         atomicCAS(&g_timeout_record[0], 0u, code);
         return false;
@@ -341,7 +345,6 @@ __device__ __forceinline__ void epilogue_tma_store(const GemmParams& p, const CU
   for (int c = col_begin; c < col_end; c += cols_per_store) {
     const int n0 = n_base + c;
     if (n0 >= p.N) break;  // uniform
-    if (p.debug_skip == 1) continue;
     if (lane == 0) bulk_wait_group_read<0>();  // the previous store has read the buffer
     __syncwarp();
 #pragma unroll 1
@@ -349,19 +352,112 @@ __device__ __forceinline__ void epilogue_tma_store(const GemmParams& p, const CU
       uint32_t r[32];
       tmem_ld_32x32b_x32(t_row + c + sub, r);
       tmem_ld_wait();
-      if (p.debug_skip == 2) {
-        if (r[0] == 0x7fc12345u) mine[0] = 1;  // keep the load alive
-        continue;
-      }
       stage_columns(p, r, n0 + sub, rs, mine, sub, lane);
     }
     fence_proxy_async_smem();  // generic-proxy writes visible to the TMA unit
     __syncwarp();
-    if (lane == 0 && p.debug_skip == 0) {
+    if (lane == 0) {
       tma_store_2d(tm_out, staging, n0, row0);
       bulk_commit_group();
     }
   }
+}
+
+// Epilogue of the gated form.  A tile of BN accumulator columns holds BN/2 gate columns followed
+// by the BN/2 up columns of the same hidden units (the producer loads the two halves of the
+// [gate | up] weight matrix side by side), so the gated activation of
+// instinctflash/kernels/activation.py:26-43 is evaluated on the accumulators in registers, in that
+// kernel's instruction order:  g = (bf16(acc_g) * row) * col_g,  u = (bf16(acc_u) * row) * col_u,
+// h = u * act(g).  h leaves as fp32 (the reference never rounds it to 16 bits before the
+// quantiser), 128 bytes of each row per TMA store, and each row's maximum of |h| is raised in
+// p.amax with an integer atomicMax on the float's bits: a maximum does not depend on the order
+// it is taken in, so the row scale and the codes a later pass derives from it are exactly those of
+// the one-kernel-per-row form.
+template <int BN>
+__device__ __forceinline__ void epilogue_gated(const GemmParams& p, const CUtensorMap* tm_out, uint32_t t_row,
+                                               uint32_t staging, uint8_t* staging_ptr, int row0, int n_base,
+                                               int half, int m, bool row_ok, float rs, int lane) {
+  constexpr int HW = BN / 2;        // hidden units per tile
+  constexpr int kChunks = HW / 32;  // 4, 2 or 1 chunks of 32 columns
+  constexpr int kPerHalf = kChunks >= 2 ? kChunks / 2 : 1;
+  if (kChunks == 1 && half == 1) return;  // a 32-wide tile is one store: the first warp of the quadrant takes it
+  const int c_begin = (kChunks >= 2 ? half * kPerHalf : 0) * 32;
+  uint8_t* mine = staging_ptr + lane * 128;
+  float row_max = 0.0f;
+  bool any = false;
+#pragma unroll 1
+  for (int k = 0; k < kPerHalf; ++k) {
+    const int c = c_begin + 32 * k;
+    const int n0 = n_base + c;
+    if (n0 >= p.N) break;  // uniform
+    any = true;
+    uint32_t rg[32], ru[32];
+    tmem_ld_32x32b_x32(t_row + c, rg);
+    tmem_ld_32x32b_x32(t_row + HW + c, ru);
+    tmem_ld_wait();
+    if (lane == 0) bulk_wait_group_read<0>();  // the previous store has read the buffer
+    __syncwarp();
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      float g[8], u[8], cg[8], cu[8];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {  // the bf16 rounding point of the accumulators
+        const uint32_t wg = pack_bf16x2(__uint_as_float(rg[8 * j + 2 * i]), __uint_as_float(rg[8 * j + 2 * i + 1]));
+        const uint32_t wu = pack_bf16x2(__uint_as_float(ru[8 * j + 2 * i]), __uint_as_float(ru[8 * j + 2 * i + 1]));
+        g[2 * i] = __uint_as_float(wg << 16);
+        g[2 * i + 1] = __uint_as_float(wg & 0xFFFF0000u);
+        u[2 * i] = __uint_as_float(wu << 16);
+        u[2 * i + 1] = __uint_as_float(wu & 0xFFFF0000u);
+      }
+      if (p.row) {
+        const uint64_t rs2 = pack2(rs, rs);
+#pragma unroll
+        for (int i = 0; i < 8; i += 2) {
+          unpack2(mul2(pack2(g[i], g[i + 1]), rs2), g[i], g[i + 1]);
+          unpack2(mul2(pack2(u[i], u[i + 1]), rs2), u[i], u[i + 1]);
+        }
+      }
+      if (p.col) {
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          const int n = n0 + 8 * j + i;
+          const bool in = n < p.N;
+          cg[i] = in ? __ldg(p.col + n) : 0.0f;
+          cu[i] = in ? __ldg(p.col + p.N + n) : 0.0f;
+        }
+#pragma unroll
+        for (int i = 0; i < 8; i += 2) {
+          unpack2(mul2(pack2(g[i], g[i + 1]), pack2(cg[i], cg[i + 1])), g[i], g[i + 1]);
+          unpack2(mul2(pack2(u[i], u[i + 1]), pack2(cu[i], cu[i + 1])), u[i], u[i + 1]);
+        }
+      }
+      float h[8];
+      if (p.act == IFLB200_ACT_GELU_TANH) {
+#pragma unroll
+        for (int i = 0; i < 8; i += 2) {
+          gelu_tanh_ref2(g[i], g[i + 1]);
+          unpack2(mul2(pack2(u[i], u[i + 1]), pack2(g[i], g[i + 1])), h[i], h[i + 1]);
+        }
+      } else {
+#pragma unroll
+        for (int i = 0; i < 8; ++i) h[i] = __fmul_rn(u[i], silu_ref(g[i]));
+      }
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        if (n0 + 8 * j + i >= p.N) h[i] = 0.0f;  // columns past the hidden width: not stored, not in the maximum
+        row_max = max_f32(row_max, fabsf(h[i]));
+      }
+      *reinterpret_cast<float4*>(mine + (((2 * j) ^ (lane & 7)) * 16)) = make_float4(h[0], h[1], h[2], h[3]);
+      *reinterpret_cast<float4*>(mine + (((2 * j + 1) ^ (lane & 7)) * 16)) = make_float4(h[4], h[5], h[6], h[7]);
+    }
+    fence_proxy_async_smem();  // generic-proxy writes visible to the TMA unit
+    __syncwarp();
+    if (lane == 0) {
+      tma_store_2d(tm_out, staging, n0, row0);
+      bulk_commit_group();
+    }
+  }
+  if (any && row_ok) atomicMax(p.amax + m, __float_as_uint(row_max));
 }
 
 // Epilogue of the swapped form (tokens on the MMA's N side): the accumulator holds the tile
@@ -395,7 +491,6 @@ __device__ __forceinline__ void epilogue_swapped(const GemmParams& p, const CUte
     const int tok = tok0 + t0;
     if (tok >= p.N) continue;  // p.N: tokens
     if (n_row0 >= p.M) continue;
-    if (p.debug_skip == 1) continue;
     uint32_t r[32];
     tmem_ld_32x32b_x32(t_row + t0, r);
     tmem_ld_wait();
@@ -432,7 +527,9 @@ __device__ __forceinline__ void epilogue_swapped(const GemmParams& p, const CUte
 // ones.  The 64-wide kernel of the skinny-M regime exists only in form 2, so that the launches of a
 // layer, split or not, run the same code: there a second GEMM kernel per layer cost about 1 us per
 // launch in instruction fetch (0.2 ms per pass of the M = 50 stack).
-template <int BN, int STAGES, int SPLIT, bool SWAP = false>
+// GATED: the gated form (see epilogue_gated): a tile pairs BN/2 gate columns with the BN/2 up
+// columns of the same hidden units; p.N counts hidden units.
+template <int BN, int STAGES, int SPLIT, bool SWAP = false, bool GATED = false>
 __global__ void __launch_bounds__(kGemmThreads, 1)
 gemm_fp8_tc5_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_w,
                     const __grid_constant__ CUtensorMap tm_out, const GemmParams p) {
@@ -498,7 +595,14 @@ gemm_fp8_tc5_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
     int m_blk, n_blk;
     tile_coords(p, tile_first, m_blk, n_blk);
     const int kb_end = kb1 < kb0 + kPrefetchSteps ? kb1 : kb0 + kPrefetchSteps;
-    for (int kb = kb0; kb < kb_end; ++kb) tma_prefetch_l2_2d(&tm_w, kb * BK, n_blk * BN);
+    for (int kb = kb0; kb < kb_end; ++kb) {
+      if constexpr (GATED) {
+        tma_prefetch_l2_2d(&tm_w, kb * BK, n_blk * (BN / 2));
+        tma_prefetch_l2_2d(&tm_w, kb * BK, p.N + n_blk * (BN / 2));
+      } else {
+        tma_prefetch_l2_2d(&tm_w, kb * BK, n_blk * BN);
+      }
+    }
   }
 
   if (warp == 0) {
@@ -526,7 +630,13 @@ gemm_fp8_tc5_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
           mbar_arrive_expect_tx(full_bar(stage), L::kStageBytes);
           const uint32_t sa = base + stage * L::kStageBytes;
           tma_load_2d(sa, &tm_a, full_bar(stage), kb * BK, m_blk * BM);
-          tma_load_2d(sa + L::kABytes, &tm_w, full_bar(stage), kb * BK, n_blk * BN);
+          if constexpr (GATED) {
+            // gate rows, then the up rows of the same hidden units: one B operand of BN rows
+            tma_load_2d(sa + L::kABytes, &tm_w, full_bar(stage), kb * BK, n_blk * (BN / 2));
+            tma_load_2d(sa + L::kABytes + (BN / 2) * BK, &tm_w, full_bar(stage), kb * BK, p.N + n_blk * (BN / 2));
+          } else {
+            tma_load_2d(sa + L::kABytes, &tm_w, full_bar(stage), kb * BK, n_blk * BN);
+          }
         }
         armed |= 1u << stage;
         last_parity = (last_parity & ~(1u << stage)) | (phase << stage);
@@ -630,6 +740,14 @@ gemm_fp8_tc5_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
         continue;
       }
       const float rs = (row_ok && p.row) ? __ldg(p.row + (int64_t)m * p.row_stride) : 1.0f;
+      if constexpr (GATED) {
+        epilogue_gated<BN>(p, &tm_out, t_row, staging, staging_ptr, m_blk * BM + quad * 32, n_blk * (BN / 2), half, m,
+                           row_ok, rs, lane);
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(tempty_bar(acc));
+        continue;
+      }
       const int64_t gofs = (row_ok && p.gate_index) ? (int64_t)p.gate_index[m] * p.N : 0;
       if (split) {
         // one tile per CTA: the partial accumulator stays in tensor memory; the exchange with
@@ -643,7 +761,7 @@ gemm_fp8_tc5_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
                                col_begin, col_tma_end, rs, lane);
         if (BN % 64 != 0 && col_tma_end < col_end) {
           const int n0 = n_blk * BN + col_tma_end;
-          if (n0 < p.N && p.debug_skip == 0) {
+          if (n0 < p.N) {
             uint32_t r[32];
             tmem_ld_32x32b_x32(t_row + col_tma_end, r);
             tmem_ld_wait();
@@ -818,9 +936,6 @@ struct PairSmemLayout {
   static constexpr int kDynamic = kTotal + 1024;
 };
 
-// tensor-memory base addresses seen by the two CTAs of cluster 0 (diagnostics)
-__device__ uint32_t g_pair_debug[4];
-
 template <int BN, int STAGES, int ACC, bool SWAP = false>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
 gemm_fp8_tc5_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_w,
@@ -876,7 +991,6 @@ gemm_fp8_tc5_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
   grid_dependency_wait();
-  if (pair_id == 0 && threadIdx.x == 0) g_pair_debug[rank] = tmem_base;
 
   if (warp == 0) {
     // ------------------------------------------------------------------ TMA producer (both CTAs)
@@ -1114,28 +1228,31 @@ static int device_info(DeviceInfo** out) {
 }
 
 int g_dependent_launch = 1;
+// what the last call of run_gemm launched: {family, tile width, split_k, stages}; family 1 = single-CTA
+// tiles, 2 / 3 = CTA pairs with one / two accumulators, +4 = swapped form, +8 = gated (paired columns)
+static int g_last_launch[4] = {0, 0, 0, 0};
 static int g_cfg_tile_n = 0, g_cfg_stages = 0, g_cfg_group_m = 0;
 static int g_cfg_split_k = 0;  // 0: cost model, 1: never split K, 2/4/8: forced
-static int g_cfg_debug_skip = 0;
 static int g_cfg_direct_store = 0;  // 1: epilogue stores straight from registers (experiments)
 static int g_cfg_pair_swap = 1;  // the swapped form on CTA pairs where the shape allows
 static int g_cfg_swap = 0;  // 0: cost model, 1: never, 2: always where the form exists
 static int g_cfg_mode = 0;  // 0 auto, 1 single-CTA tiles only, 2 CTA pairs with one accumulator, 3 CTA pairs with two
 
-template <int BN, int STAGES, int SPLIT, bool SWAP = false>
+template <int BN, int STAGES, int SPLIT, bool SWAP = false, bool GATED = false>
 static int launch_gemm_form(const CUtensorMap& ta, const CUtensorMap& tw, const CUtensorMap& to, const GemmParams& p,
                             int grid, cudaStream_t s) {
   using L = SmemLayout<BN, STAGES>;
   static bool attr_set[64] = {};
   int dev = 0;
   cudaGetDevice(&dev);
+  if (dev < 0 || dev >= 64) return IFLB200_ERR_DEVICE;
   if (!attr_set[dev]) {
-    cudaError_t e = cudaFuncSetAttribute(gemm_fp8_tc5_kernel<BN, STAGES, SPLIT, SWAP>,
+    cudaError_t e = cudaFuncSetAttribute(gemm_fp8_tc5_kernel<BN, STAGES, SPLIT, SWAP, GATED>,
                                          cudaFuncAttributeMaxDynamicSharedMemorySize, L::kDynamic);
     if (e != cudaSuccess) return (int)e;
     attr_set[dev] = true;
   }
-  const cudaError_t e = launch_dep(gemm_fp8_tc5_kernel<BN, STAGES, SPLIT, SWAP>, dim3(grid), dim3(kGemmThreads),
+  const cudaError_t e = launch_dep(gemm_fp8_tc5_kernel<BN, STAGES, SPLIT, SWAP, GATED>, dim3(grid), dim3(kGemmThreads),
                                    L::kDynamic, s, p.split_k, dependent_launch_for(SWAP ? p.N : p.M), ta, tw, to, p);
   return e != cudaSuccess ? (int)e : (int)cudaGetLastError();
 }
@@ -1190,7 +1307,6 @@ static int run_gemm(const void* a, int64_t ld_a, const void* w, int64_t ld_w, Ge
   // updates its operand in place with plain loads and stores.
   CUtensorMap to;
   p.tma_store = (p.epilogue != EPI_RESIDUAL && g_cfg_direct_store == 0) ? 1 : 0;
-  p.debug_skip = g_cfg_debug_skip;
   if (p.tma_store) {
     st = make_out_map(&to, p.out, p.M, p.N, p.ld_out, oes);
     if (st != IFLB200_OK) return st;
@@ -1227,6 +1343,7 @@ static int run_gemm(const void* a, int64_t ld_a, const void* w, int64_t ld_w, Ge
     if (st != IFLB200_OK) return st;
     st = make_tensor_map(&tw, w, p.N, p.K, ld_w, PBN / 2);
     if (st != IFLB200_OK) return st;
+    g_last_launch[0] = g_cfg_mode == 2 ? 2 : 3; g_last_launch[1] = PBN; g_last_launch[2] = 1; g_last_launch[3] = 6;
     return g_cfg_mode == 2 ? launch_gemm_pair<PBN, 6, 1>(ta, tw, to, p, grid, s)
                            : launch_gemm_pair<PBN, 6, 2>(ta, tw, to, p, grid, s);  // two accumulators
   }
@@ -1242,7 +1359,6 @@ static int run_gemm(const void* a, int64_t ld_a, const void* w, int64_t ld_w, Ge
   p.num_m = (p.M + BM - 1) / BM;
   int bn = g_cfg_tile_n;
   int split = 1;
-  int64_t best_cost = 0;
   {
     const int widths[5] = {256, 224, 192, 128, 64};
     const int64_t step_cycles[5] = {830, 790, 750, 690, 590};
@@ -1272,7 +1388,6 @@ static int run_gemm(const void* a, int64_t ld_a, const void* w, int64_t ld_w, Ge
     }
     if (best_bn == 0) return IFLB200_ERR_ARG;  // the forced configuration does not fit this problem
     bn = best_bn;
-    best_cost = best;
   }
   // Swapped form for a few hundred tokens: the tokens go on the MMA's N side in tiles of the width
   // that fits them (816 tokens = 4 x 208 with 2 % padding, where 7 row blocks of 128 carry 9 %), the
@@ -1287,11 +1402,6 @@ static int run_gemm(const void* a, int64_t ld_a, const void* w, int64_t ld_w, Ge
     const int fit = ((p.M + t_tiles - 1) / t_tiles + 15) / 16 * 16;
     const int bt = fit <= 128 ? 128 : (fit <= 208 ? 208 : 256);  // the widths this form is built for
     const int64_t steps = (p.K + BK - 1) / BK;
-    const int64_t tiles = (int64_t)((p.N + BM - 1) / BM) * ((p.M + bt - 1) / bt);
-    const int64_t waves = (tiles + dev->sm_count - 1) / dev->sm_count;
-    const int64_t cost = waves * (steps * (350 + 5 * (BM + bt) / 4) + 2500);
-    (void)cost;
-    (void)best_cost;
     if (g_cfg_swap == 2) {
       GemmParams q = p;
       q.M = p.N;  // rows of the MMA's M side: output columns
@@ -1320,9 +1430,11 @@ static int run_gemm(const void* a, int64_t ld_a, const void* w, int64_t ld_w, Ge
         CUtensorMap ta_half;
         st = make_tensor_map(&ta_half, a, p.M, p.K, ld_a, bt / 2);
         if (st != IFLB200_OK) return st;
+        g_last_launch[0] = 3 + 4; g_last_launch[1] = bt; g_last_launch[2] = 1; g_last_launch[3] = 6;
         return bt == 208 ? launch_gemm_pair<208, 6, 2, true>(tw_rows, ta_half, to_swapped, q, pgrid, s)
                          : launch_gemm_pair<256, 6, 2, true>(tw_rows, ta_half, to_swapped, q, pgrid, s);
       }
+      g_last_launch[0] = 1 + 4; g_last_launch[1] = bt; g_last_launch[2] = 1; g_last_launch[3] = bt == 128 ? 6 : 4;
       switch (bt) {
         case 128: return launch_gemm_form<128, 6, 0, true>(tw_rows, ta_tokens, to_swapped, q, grid, s);
         case 208: return launch_gemm_form<208, 4, 0, true>(tw_rows, ta_tokens, to_swapped, q, grid, s);
@@ -1343,6 +1455,7 @@ static int run_gemm(const void* a, int64_t ld_a, const void* w, int64_t ld_w, Ge
   st = make_tensor_map(&tw, w, p.N, p.K, ld_w, bn);
   if (st != IFLB200_OK) return st;
   const int stages = g_cfg_stages;
+  g_last_launch[0] = 1; g_last_launch[1] = bn; g_last_launch[2] = split; g_last_launch[3] = stages;
   switch (bn) {
     case 256: return (stages == 3) ? launch_gemm<256, 3>(ta, tw, to, p, grid, s) : launch_gemm<256, 4>(ta, tw, to, p, grid, s);
     case 224: return launch_gemm<224, 4>(ta, tw, to, p, grid, s);
@@ -1350,6 +1463,70 @@ static int run_gemm(const void* a, int64_t ld_a, const void* w, int64_t ld_w, Ge
     case 128: return (stages == 4) ? launch_gemm<128, 4>(ta, tw, to, p, grid, s) : launch_gemm<128, 6>(ta, tw, to, p, grid, s);
     case 64: return (stages == 4) ? launch_gemm<64, 4>(ta, tw, to, p, grid, s) : launch_gemm<64, 8>(ta, tw, to, p, grid, s);
     default: return IFLB200_ERR_ARG;
+  }
+}
+
+// The gated form: W is [2F, K] = [gate rows | up rows]; h [M, F] fp32; amax [M] float bits.
+static int run_gemm_gated(const void* a, int64_t ld_a, const void* w, int64_t ld_w, int M, int F, int K,
+                          const float* row, const float* col, int act, float* h, int64_t ld_h, uint32_t* amax,
+                          void* stream) {
+  if (M < 0 || F < 0 || K < 0) return IFLB200_ERR_ARG;
+  if (M == 0 || F == 0) return IFLB200_OK;
+  if (!a || !w || !h || !amax) return IFLB200_ERR_ARG;
+  if (act != IFLB200_ACT_GELU_TANH && act != IFLB200_ACT_SILU) return IFLB200_ERR_ARG;
+  if (K < 16 || K % 16 || F % 16) return IFLB200_ERR_SHAPE;
+  if (ld_a < K || ld_w < K || ld_h < F) return IFLB200_ERR_ARG;
+  if ((reinterpret_cast<uintptr_t>(a) & 15) || (reinterpret_cast<uintptr_t>(w) & 15) || ld_a % 16 || ld_w % 16 ||
+      (reinterpret_cast<uintptr_t>(h) & 15) || (ld_h * 4) % 16 || (reinterpret_cast<uintptr_t>(amax) & 3))
+    return IFLB200_ERR_ALIGN;
+  DeviceInfo* dev = nullptr;
+  int st = device_info(&dev);
+  if (st != IFLB200_OK) return st;
+  GemmParams p = {};
+  p.M = M; p.N = F; p.K = K;
+  p.epilogue = EPI_RAW;
+  p.row = row; p.row_stride = 1;
+  p.col = col; p.col_stride = 1;
+  p.out = h; p.out_dtype = IFLB200_F32; p.ld_out = ld_h;
+  p.split_k = 1;
+  p.act = act;
+  p.amax = amax;
+  p.tma_store = 1;
+  p.num_m = (M + BM - 1) / BM;
+  p.num_k = (K + BK - 1) / BK;
+  // tile width (gate + up columns) by the cost model of the ordinary form
+  const int widths[3] = {256, 128, 64};
+  const int64_t step_cycles[3] = {830, 690, 590};
+  int bn = g_cfg_tile_n == 256 || g_cfg_tile_n == 128 || g_cfg_tile_n == 64 ? g_cfg_tile_n : 0;
+  if (bn == 0) {
+    int64_t best = 0;
+    for (int i = 0; i < 3; ++i) {
+      const int64_t tiles = (int64_t)p.num_m * ((F + widths[i] / 2 - 1) / (widths[i] / 2));
+      const int64_t waves = (tiles + dev->sm_count - 1) / dev->sm_count;
+      const int64_t cost = waves * (p.num_k * step_cycles[i] + 2500);
+      if (bn == 0 || cost < best) {
+        best = cost;
+        bn = widths[i];
+      }
+    }
+  }
+  p.num_n = (F + bn / 2 - 1) / (bn / 2);
+  p.num_tiles = p.num_m * p.num_n;
+  p.group_m = g_cfg_group_m > 0 ? g_cfg_group_m : 8;
+  const int grid = p.num_tiles < dev->sm_count ? p.num_tiles : dev->sm_count;
+  CUtensorMap ta, tw, to;
+  st = make_tensor_map(&ta, a, M, K, ld_a, BM);
+  if (st != IFLB200_OK) return st;
+  st = make_tensor_map(&tw, w, 2 * F, K, ld_w, bn / 2);
+  if (st != IFLB200_OK) return st;
+  st = make_out_map(&to, h, M, F, ld_h, 4);
+  if (st != IFLB200_OK) return st;
+  cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+  g_last_launch[0] = 1 + 8; g_last_launch[1] = bn; g_last_launch[2] = 1; g_last_launch[3] = 0;
+  switch (bn) {
+    case 256: return launch_gemm_form<256, 4, 0, false, true>(ta, tw, to, p, grid, s);
+    case 128: return launch_gemm_form<128, 6, 0, false, true>(ta, tw, to, p, grid, s);
+    default: return launch_gemm_form<64, 8, 0, false, true>(ta, tw, to, p, grid, s);
   }
 }
 
@@ -1382,21 +1559,27 @@ extern "C" int iflb200_set_dependent_launch(int enable) {
 extern "C" int iflb200_gemm_set_mode(int mode) {
   // bit 4 (value 16) selects the direct-store epilogue; the low bits the kernel family
   const int family = mode & 15;
-  if (mode < 0 || family > 3 || (mode & ~1023) || (mode & 384) == 384) return IFLB200_ERR_ARG;
+  if (mode < 0 || family > 3 || (mode & ~(15 | 16 | 128 | 256 | 512)) || (mode & 384) == 384) return IFLB200_ERR_ARG;
   g_cfg_swap = (mode & 128) ? 1 : ((mode & 256) ? 2 : 0);  // 128: never the swapped form, 256: wherever it exists
   g_cfg_pair_swap = (mode & 512) ? 0 : 1;                  // 512: the swapped form on single CTAs only
   g_cfg_mode = family;
   g_cfg_direct_store = (mode & 16) ? 1 : 0;
-  g_cfg_debug_skip = (mode >> 5) & 3;  // timing experiments only: outputs are not written
   return IFLB200_OK;
 }
 
-extern "C" int iflb200_gemm_debug_words(uint32_t* out4, void* stream) {
-  if (!out4) return IFLB200_ERR_ARG;
-  cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
-  cudaError_t e = cudaMemcpyFromSymbolAsync(out4, g_pair_debug, 4 * sizeof(uint32_t), 0, cudaMemcpyDeviceToHost, s);
+extern "C" int iflb200_set_wait_budget_us(int64_t microseconds) {
+  if (microseconds < 0) return IFLB200_ERR_ARG;
+  const uint64_t ns = microseconds ? (uint64_t)microseconds * 1000ull : kWaitBudgetNs;
+  const cudaError_t e = cudaMemcpyToSymbol(g_gemm_wait_budget_ns, &ns, sizeof(ns));
   if (e != cudaSuccess) return (int)e;
-  return (int)cudaStreamSynchronize(s);
+  return set_stack_wait_budget_ns(ns);
+}
+
+extern "C" int iflb200_gemm_last_launch(int* family, int* tile_n, int* split_k) {
+  if (family) *family = g_last_launch[0];
+  if (tile_n) *tile_n = g_last_launch[1];
+  if (split_k) *split_k = g_last_launch[2];
+  return IFLB200_OK;
 }
 
 extern "C" int iflb200_gemm_take_timeout_record(uint32_t* record, void* stream) {
@@ -1460,6 +1643,12 @@ extern "C" int iflb200_fp8_linear_residual(const void* a, int64_t ld_a, const vo
   p.gate = gate; p.gate_index = gate ? gate_index : nullptr;
   p.out = res; p.out_dtype = res_dtype; p.ld_out = ld_res;
   return run_gemm(a, ld_a, w, ld_w, p, stream);
+}
+
+extern "C" int iflb200_fp8_linear_gated(const void* a, int64_t ld_a, const void* w, int64_t ld_w, int M, int F,
+                                        int K, const float* row_scale, const float* col_scale, int act, float* h,
+                                        int64_t ld_h, uint32_t* amax, void* stream) {
+  return run_gemm_gated(a, ld_a, w, ld_w, M, F, K, row_scale, col_scale, act, h, ld_h, amax, stream);
 }
 
 extern "C" int iflb200_abi_version(void) { return IFLB200_ABI_VERSION; }

@@ -251,7 +251,9 @@ struct RowQuantArgs {
   float* qs;
   // Column-sharded rows (tensor parallel): phase 1 writes the shard's row maximum to `amax` and
   // stops; phase 2 takes the row maximum from `amax` (after an all-reduce-max over the shards)
-  // instead of its own, so the codes equal those of the unsharded row.  0: one pass.
+  // instead of its own, so the codes equal those of the unsharded row.  0: one pass.  Phase 3 is
+  // phase 2 that also leaves amax[m] at zero (the maxima came from a GEMM epilogue's atomicMax,
+  // which needs the words to start at zero the next time).
   int phase;
   float* amax;
 };
@@ -291,7 +293,11 @@ row_quant_kernel(const RowQuantArgs a) {
       if (live && t == 0) a.amax[m] = amax;
       return;
     }
-    if (a.phase == 2 && live) amax = a.amax[m];
+    if (a.phase >= 2 && live) amax = a.amax[m];
+    if (a.phase == 3) {  // every thread of the row has its copy: leave the word at zero for the next producer
+      __syncthreads();
+      if (live && t == 0) a.amax[m] = 0.0f;
+    }
     float scale, inv;
     quant_scales(amax, scale, inv);
     if (!live) return;
@@ -336,7 +342,11 @@ row_quant_kernel(const RowQuantArgs a) {
     if (live && t == 0) a.amax[m] = amax;
     return;
   }
-  if (a.phase == 2 && live) amax = a.amax[m];
+  if (a.phase >= 2 && live) amax = a.amax[m];
+  if (a.phase == 3) {
+    __syncthreads();
+    if (live && t == 0) a.amax[m] = 0.0f;
+  }
   float scale, inv;
   quant_scales(amax, scale, inv);
   if (!live) return;
@@ -933,7 +943,7 @@ extern "C" int iflb200_row_quant_sharded(const void* x, int x_dtype, int64_t ld_
                                          const float* row, const float* col, const float* bias, int gelu,
                                          int phase, float* amax, void* q, int64_t ld_q, float* qs,
                                          void* stream) {
-  if (phase != 1 && phase != 2) return IFLB200_ERR_ARG;
+  if (phase != 1 && phase != 2 && phase != 3) return IFLB200_ERR_ARG;
   return row_quant_impl(x, x_dtype, ld_x, M, K, row, col, bias, gelu, q, ld_q, qs, phase, amax, stream);
 }
 

@@ -42,6 +42,8 @@ constexpr int A_ROWS = 64;    // rows of the activation box actually loaded (M <
 constexpr int A_ROWS_WIDE = 128;  // ... or 128 (64 < M <= 128), with 8 stages
 constexpr int kThreads = 224;
 constexpr uint64_t kWaitBudgetNs = 2000000000ull;
+// Time budget of every wait inside the kernel (read only on the slow path of a wait).
+__device__ uint64_t g_stack_wait_budget_ns = kWaitBudgetNs;
 
 enum : int { OP_GEMM = 1, OP_GATED = 2, OP_RESNORM = 3 };
 
@@ -102,7 +104,7 @@ __device__ __forceinline__ bool wait_mbar(uint32_t bar, uint32_t parity, volatil
         *local_abort = 1;
         return false;
       }
-      if (globaltimer_ns() - t0 > kWaitBudgetNs) {
+      if (globaltimer_ns() - t0 > g_stack_wait_budget_ns) {
         *local_abort = 1;
         atomicCAS(status, 0u, code);
         atomicExch(status + 1, 1u);
@@ -126,7 +128,7 @@ __device__ __forceinline__ bool wait_grid(const uint32_t* bar, uint32_t target, 
         *local_abort = 1;
         return false;
       }
-      if (globaltimer_ns() - t0 > kWaitBudgetNs) {
+      if (globaltimer_ns() - t0 > g_stack_wait_budget_ns) {
         *local_abort = 1;
         atomicCAS(status, 0u, code);
         atomicExch(status + 1, 1u);
@@ -555,6 +557,14 @@ stack_persistent_kernel(const Op* __restrict__ ops, int num_ops, const CUtensorM
 
 using namespace iflb200;
 using namespace iflb200::stackk;
+
+namespace iflb200 {
+// 0 restores the default.  Applies to the current device; synchronises it.
+int set_stack_wait_budget_ns(uint64_t ns) {
+  const uint64_t v = ns ? ns : kWaitBudgetNs;
+  return (int)cudaMemcpyToSymbol(g_stack_wait_budget_ns, &v, sizeof(v));
+}
+}  // namespace iflb200
 
 typedef CUresult (*EncodeTiledFn2)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
                                    const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,

@@ -43,3 +43,42 @@ def ld(t: torch.Tensor) -> int:
 
 def stream(t: torch.Tensor) -> int:
     return _lib.stream_handle(t.device)
+
+
+class on_device:
+    """Make ``t``'s device the current CUDA device around a call into the library.
+
+    The library keys everything on the current device (SM count, kernel attributes, the launch
+    itself), so a call made while another GPU is current would launch there with this GPU's
+    pointers.  The device is switched only when it differs, and restored afterwards."""
+
+    def __init__(self, t: torch.Tensor):
+        self.index = t.device.index if t.device.index is not None else torch.cuda.current_device()
+        self.previous = None
+
+    def __enter__(self):
+        current = torch.cuda.current_device()
+        if current != self.index:
+            self.previous = current
+            torch.cuda.set_device(self.index)
+        return self
+
+    def __exit__(self, *exc):
+        if self.previous is not None:
+            torch.cuda.set_device(self.previous)
+        return False
+
+
+def launch(entry: str, anchor: torch.Tensor, *args) -> None:
+    """Call ``entry`` of the library on ``anchor``'s device and current stream (the stream handle
+    is every entry point's last argument); raise on a non-zero status.  Tensor arguments on
+    another device than ``anchor`` are refused before anything is launched."""
+    with on_device(anchor):
+        status = getattr(_lib.lib(), entry)(*args, _lib.stream_handle(anchor.device))
+    _lib.check(status, entry.removeprefix("iflb200_"))
+
+
+def same_device(anchor: torch.Tensor, **tensors) -> None:
+    for name, t in tensors.items():
+        if t is not None and t.device != anchor.device:
+            raise ValueError(f"{name} is on {t.device}, expected {anchor.device}")

@@ -15,7 +15,7 @@ from __future__ import annotations
 import torch
 
 from .. import _lib
-from ._common import E4M3, ld, rows, stream, vec
+from ._common import E4M3, launch, ld, rows, same_device, vec
 
 GELU_TANH = 0
 SILU = 1
@@ -35,8 +35,8 @@ def gated_act_quant(gu, q, q_scale, *, row=None, col=None, act=GELU_TANH, num_wa
     if tuple(q.shape) != (M, F):
         raise ValueError(f"q must be [{M}, {F}], got {tuple(q.shape)}")
     vec(q_scale, "q_scale", M, gu.device)
-    st = _lib.lib().iflb200_gated_act_quant(
+    same_device(gu, q=q)
+    launch("iflb200_gated_act_quant", gu,
         gu.data_ptr(), _lib.dtype_code(gu.dtype), ld(gu), M, F,
         _lib.ptr(vec(row, "row", M, gu.device)), _lib.ptr(vec(col, "col", 2 * F, gu.device)), int(act),
-        q.data_ptr(), ld(q), q_scale.data_ptr(), stream(gu))
-    _lib.check(st, "gated_act_quant")
+        q.data_ptr(), ld(q), q_scale.data_ptr())

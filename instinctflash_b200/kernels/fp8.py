@@ -6,9 +6,10 @@ lines 19-27 there), ``quantize_weight`` packs with the same arithmetic (lines 30
 ``gemm`` writes ``bf16(sum_k a[m,k] * w[n,k])`` with unit scales (lines 50-53).  The GEMM is the
 tcgen05 kernel of ``csrc/gemm_fp8_sm100.cu`` instead of ``torch._scaled_mm``.
 
-``fp8_linear`` and ``fp8_linear_residual`` are additions: the same GEMM with the consumer
-(``dequant_rows`` / the residual part of ``residual_norm_quant``) applied in its epilogue, so the
-[M, N] raw accumulator never travels through memory.
+``fp8_linear``, ``fp8_linear_residual`` and ``fp8_linear_gated`` are additions: the same GEMM with
+the consumer (``dequant_rows`` / the residual part of ``residual_norm_quant`` / the activation part
+of ``gated_act_quant``) applied in its epilogue, so the [M, N] raw accumulator never travels
+through memory.
 """
 from __future__ import annotations
 
@@ -17,7 +18,7 @@ from dataclasses import dataclass
 import torch
 
 from .. import _lib
-from ._common import E4M3, ld, rows, stream, vec
+from ._common import E4M3, launch, ld, rows, same_device, vec
 
 FP8_MAX = 448.0
 
@@ -71,9 +72,8 @@ def gemm(a: torch.Tensor, w: Fp8Weight, out: torch.Tensor) -> torch.Tensor:
     rows(out, "out", (torch.bfloat16,))
     if tuple(out.shape) != (M, N):
         raise ValueError(f"out must be [{M}, {N}], got {tuple(out.shape)}")
-    st = _lib.lib().iflb200_gemm_fp8_raw(a.data_ptr(), ld(a), w.w.data_ptr(), ld(w.w), M, N, K,
-                                         out.data_ptr(), ld(out), stream(a))
-    _lib.check(st, "gemm")
+    same_device(a, out=out)
+    launch("iflb200_gemm_fp8_raw", a, a.data_ptr(), ld(a), w.w.data_ptr(), ld(w.w), M, N, K, out.data_ptr(), ld(out))
     return out
 
 
@@ -101,14 +101,14 @@ def fp8_linear(a: torch.Tensor, a_scale: torch.Tensor | None, w: Fp8Weight, out:
         raise ValueError(f"a_scale must have 1 or {M} elements")
     if cs is not None and cs.numel() not in (1, N):
         raise ValueError(f"w.scale must have 1 or {N} elements")
-    st = _lib.lib().iflb200_fp8_linear(
+    same_device(a, out=out, bias=b)
+    launch("iflb200_fp8_linear", a,
         a.data_ptr(), ld(a), w.w.data_ptr(), ld(w.w), M, N, K,
         _lib.ptr(rs), 0 if (rs is not None and rs.numel() == 1 and M != 1) else 1,
         _lib.ptr(cs), 0 if (cs is not None and cs.numel() == 1 and N != 1) else 1,
         _lib.ptr(b), _lib.dtype_code(b.dtype) if b is not None else _lib.F32,
         _lib.ROUND_EXACT if exact else _lib.ROUND_ENGINE,
-        out.data_ptr(), _lib.dtype_code(out.dtype), ld(out), stream(a))
-    _lib.check(st, "fp8_linear")
+        out.data_ptr(), _lib.dtype_code(out.dtype), ld(out))
     return out
 
 
@@ -130,9 +130,42 @@ def fp8_linear_residual(a: torch.Tensor, a_scale: torch.Tensor, w: Fp8Weight, re
     g = vec(gate, "gate", N, a.device)
     if gate_index is not None and (gate_index.dtype != torch.int32 or gate_index.numel() < M):
         raise ValueError("gate_index must be int32 with one entry per row")
-    st = _lib.lib().iflb200_fp8_linear_residual(
+    same_device(a, res=res, gate_index=gate_index)
+    launch("iflb200_fp8_linear_residual", a,
         a.data_ptr(), ld(a), w.w.data_ptr(), ld(w.w), M, N, K, _lib.ptr(rs), _lib.ptr(cs),
         _lib.ptr(b), _lib.ptr(g), _lib.ptr(gate_index), res.data_ptr(), _lib.dtype_code(res.dtype),
-        ld(res), stream(a))
-    _lib.check(st, "fp8_linear_residual")
+        ld(res))
     return res
+
+
+def fp8_linear_gated(a: torch.Tensor, a_scale: torch.Tensor, w: Fp8Weight, h: torch.Tensor, amax: torch.Tensor, *,
+                     act: int = 0) -> torch.Tensor:
+    """``gemm`` on a ``[gate | up]`` weight + the activation part of ``gated_act_quant`` in one kernel.
+
+    ``w.w`` is [2F, K]; ``h`` [M, F] float32 receives ``act(g) * u`` of the dequantised accumulators
+    (never rounded to 16 bits, like the reference's registers); ``amax`` [M] float32 must be zero on
+    entry and holds each row's maximum of ``|h|`` afterwards.  ``norm.row_quant_from_amax(h, amax,
+    q, q_scale)`` finishes the operator: together they write the codes and scales of
+    ``gemm`` + ``gated_act_quant`` bit for bit.  ``act``: 0 GELU-tanh, 1 SiLU.
+    """
+    rows(a, "a", (E4M3,))
+    rows(w.w, "w.w", (E4M3,))
+    rows(h, "h", (torch.float32,))
+    M, K = a.shape
+    N2, Kw = w.w.shape
+    if K != Kw or N2 % 2:
+        raise ValueError(f"a is [M, {K}] but the [gate | up] weight is [{N2}, {Kw}]")
+    F = N2 // 2
+    if K % 16 or F % 16:
+        raise ValueError("FP8 GEMM input/output dimensions must be multiples of 16")
+    if tuple(h.shape) != (M, F):
+        raise ValueError(f"h must be [{M}, {F}], got {tuple(h.shape)}")
+    if act not in (0, 1):
+        raise ValueError("act must be GELU_TANH (0) or SILU (1)")
+    rs = vec(a_scale, "a_scale", M, a.device)
+    cs = vec(w.scale, "w.scale", 2 * F, a.device)
+    vec(amax, "amax", M, a.device)
+    same_device(a, h=h, w=w.w)
+    launch("iflb200_fp8_linear_gated", a, a.data_ptr(), ld(a), w.w.data_ptr(), ld(w.w), M, F, K, _lib.ptr(rs),
+           _lib.ptr(cs), int(act), h.data_ptr(), ld(h), amax.data_ptr())
+    return h

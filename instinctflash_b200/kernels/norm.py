@@ -12,7 +12,7 @@ from __future__ import annotations
 import torch
 
 from .. import _lib
-from ._common import E4M3, ld, rows, stream, vec
+from ._common import E4M3, launch, ld, rows, same_device, vec
 
 FP8_MAX = 448.0
 _FLOATS = (torch.float32, torch.bfloat16, torch.float16)
@@ -26,12 +26,12 @@ def row_quant(x, q, q_scale, *, row=None, col=None, bias=None, gelu=False, num_w
     if tuple(q.shape) != (M, D):
         raise ValueError(f"q must be [{M}, {D}], got {tuple(q.shape)}")
     vec(q_scale, "q_scale", M, x.device)
-    st = _lib.lib().iflb200_row_quant(
+    same_device(x, q=q)
+    launch("iflb200_row_quant", x,
         x.data_ptr(), _lib.dtype_code(x.dtype), ld(x), M, D,
         _lib.ptr(vec(row, "row", M, x.device)), _lib.ptr(vec(col, "col", D, x.device)),
         _lib.ptr(vec(bias, "bias", D, x.device)), int(bool(gelu)),
-        q.data_ptr(), ld(q), q_scale.data_ptr(), stream(x))
-    _lib.check(st, "row_quant")
+        q.data_ptr(), ld(q), q_scale.data_ptr())
 
 
 def row_quant_sharded(x, q, q_scale, amax, phase, *, row=None, col=None, bias=None, gelu=False):
@@ -42,20 +42,27 @@ def row_quant_sharded(x, q, q_scale, amax, phase, *, row=None, col=None, bias=No
     rows(x, "x", _FLOATS)
     M, D = x.shape
     vec(amax, "amax", M, x.device)
-    if phase == 2:
+    if phase in (2, 3):
         rows(q, "q", (E4M3,))
         if tuple(q.shape) != (M, D):
             raise ValueError(f"q must be [{M}, {D}], got {tuple(q.shape)}")
         vec(q_scale, "q_scale", M, x.device)
     elif phase != 1:
-        raise ValueError("phase must be 1 (local maxima) or 2 (quantise with the reduced maxima)")
-    st = _lib.lib().iflb200_row_quant_sharded(
+        raise ValueError("phase must be 1 (local maxima), 2 (quantise with the reduced maxima) or 3 (2, then zero them)")
+    same_device(x, q=q if phase != 1 else None)
+    launch("iflb200_row_quant_sharded", x,
         x.data_ptr(), _lib.dtype_code(x.dtype), ld(x), M, D,
         _lib.ptr(vec(row, "row", M, x.device)), _lib.ptr(vec(col, "col", D, x.device)),
         _lib.ptr(vec(bias, "bias", D, x.device)), int(bool(gelu)), int(phase), amax.data_ptr(),
-        _lib.ptr(q) if phase == 2 else None, ld(q) if phase == 2 else 0,
-        _lib.ptr(q_scale) if phase == 2 else None, stream(x))
-    _lib.check(st, "row_quant_sharded")
+        _lib.ptr(q) if phase != 1 else None, ld(q) if phase != 1 else 0,
+        _lib.ptr(q_scale) if phase != 1 else None)
+
+
+def row_quant_from_amax(h, amax, q, q_scale):
+    """Second half of ``fp8.fp8_linear_gated``: quantise the rows of ``h`` [M, F] float32 with the
+    row maxima the GEMM epilogue left in ``amax`` [M] (scale = amax / 448, codes as ``row_quant``),
+    and leave ``amax`` at zero for the next call."""
+    row_quant_sharded(h, q, q_scale, amax, 3)
 
 
 def dequant_rows(x, y, *, row=None, col=None, bias=None, block=None, num_warps=4):
@@ -65,12 +72,12 @@ def dequant_rows(x, y, *, row=None, col=None, bias=None, block=None, num_warps=4
     M, D = x.shape
     if tuple(y.shape) != (M, D):
         raise ValueError(f"y must be [{M}, {D}], got {tuple(y.shape)}")
-    st = _lib.lib().iflb200_dequant_rows(
+    same_device(x, y=y)
+    launch("iflb200_dequant_rows", x,
         x.data_ptr(), _lib.dtype_code(x.dtype), ld(x), M, D,
         _lib.ptr(vec(row, "row", M, x.device)), _lib.ptr(vec(col, "col", D, x.device)),
         _lib.ptr(vec(bias, "bias", D, x.device)),
-        y.data_ptr(), _lib.dtype_code(y.dtype), ld(y), stream(x))
-    _lib.check(st, "dequant_rows")
+        y.data_ptr(), _lib.dtype_code(y.dtype), ld(y))
 
 
 def residual_norm_quant(res, *, delta=None, delta_row=None, delta_col=None, bias=None, gate=None,
@@ -110,7 +117,8 @@ def residual_norm_quant(res, *, delta=None, delta_row=None, delta_col=None, bias
         raise ValueError("mod_scale and mod_shift come together")
     if mod_index is not None and (mod_index.dtype != torch.int32 or mod_index.numel() < M):
         raise ValueError("mod_index must be int32 with one entry per row")
-    st = _lib.lib().iflb200_residual_norm_quant(
+    same_device(res, delta=delta, q=q, y=y, mod_index=mod_index)
+    launch("iflb200_residual_norm_quant", res,
         res.data_ptr(), _lib.dtype_code(res.dtype), ld(res), M, D,
         _lib.ptr(delta), ld(delta) if delta is not None else 0,
         _lib.ptr(vec(delta_row, "delta_row", M, dev)), _lib.ptr(vec(delta_col, "delta_col", D, dev)),
@@ -120,5 +128,4 @@ def residual_norm_quant(res, *, delta=None, delta_row=None, delta_col=None, bias
         _lib.ptr(mod_index), float(eps),
         _lib.ptr(q), ld(q) if q is not None else 0, _lib.ptr(q_scale),
         _lib.ptr(y), _lib.dtype_code(y.dtype) if y is not None else _lib.F32,
-        ld(y) if y is not None else 0, stream(res))
-    _lib.check(st, "residual_norm_quant")
+        ld(y) if y is not None else 0)

@@ -11,7 +11,7 @@ from __future__ import annotations
 import torch
 
 from .. import _lib
-from ._common import rows, stream, vec
+from ._common import launch, rows, vec
 
 _FLOATS = (torch.float32, torch.bfloat16, torch.float16)
 
@@ -81,7 +81,7 @@ def qkv_split(qkv, q_out, k_out, v_out, *, heads_q, heads_kv, head_dim, row=None
         if pos.shape[0] < T:
             raise ValueError("pos has fewer rows than qkv")
         ld_pos = pos.stride(0)
-    st = _lib.lib().iflb200_qkv_split(
+    launch("iflb200_qkv_split", qkv,
         qkv.data_ptr(), _lib.dtype_code(qkv.dtype), qkv.stride(0) if T > 1 else width, T, int(heads_q), int(heads_kv),
         int(head_dim), _lib.ptr(vec(row, "row", T, dev)), _lib.ptr(vec(col, "col", width, dev)),
         _lib.ptr(vec(bias, "bias", width, dev)), _lib.ptr(vec(q_norm, "q_norm", head_dim, dev)),
@@ -90,5 +90,4 @@ def qkv_split(qkv, q_out, k_out, v_out, *, heads_q, heads_kv, head_dim, row=None
         _lib.ptr(_index(sections, "sections", half, dev)), _lib.ptr(kv_base if dynamic else None),
         0 if dynamic else int(kv_base),
         q_out.data_ptr(), q_out.stride(0), q_out.stride(1), k_out.data_ptr(), k_out.stride(0), k_out.stride(1),
-        v_out.data_ptr(), v_out.stride(0), v_out.stride(1), _lib.dtype_code(q_out.dtype), stream(qkv))
-    _lib.check(st, "qkv_split")
+        v_out.data_ptr(), v_out.stride(0), v_out.stride(1), _lib.dtype_code(q_out.dtype))

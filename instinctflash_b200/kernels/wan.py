@@ -12,7 +12,7 @@ from __future__ import annotations
 import torch
 
 from .. import _lib
-from ._common import rows, stream, vec
+from ._common import launch, rows, vec
 from .rope import _FLOATS, _index
 
 
@@ -59,7 +59,7 @@ def wan_qkv(raw, q_out, *, heads, head_dim, tokens, k_pool=None, v_pool=None, sl
             raise ValueError("pos has fewer rows than tokens")
         ld_pos = pos.stride(0)
     kp, vp = k_pool, v_pool
-    st = _lib.lib().iflb200_wan_qkv(
+    launch("iflb200_wan_qkv", raw,
         raw.data_ptr(), _lib.dtype_code(raw.dtype), raw.stride(0) if n_rows > 1 else raw.shape[1], n_rows, int(tokens),
         int(heads), int(head_dim), _lib.ptr(vec(row, "row", n_rows, dev)), _lib.ptr(vec(col, "col", parts * D, dev)),
         _lib.ptr(vec(bias, "bias", parts * D, dev)), _lib.ptr(vec(q_norm, "q_norm", D, dev)),
@@ -69,5 +69,4 @@ def wan_qkv(raw, q_out, *, heads, head_dim, tokens, k_pool=None, v_pool=None, sl
         q_out.data_ptr(), q_out.stride(0) if n_rows > 1 else D,
         _lib.ptr(kp), kp.stride(0) if kp is not None else 0, kp.stride(1) if kp is not None else 0,
         _lib.ptr(vp), vp.stride(0) if vp is not None else 0, vp.stride(1) if vp is not None else 0,
-        _lib.dtype_code(q_out.dtype), stream(raw))
-    _lib.check(st, "wan_qkv")
+        _lib.dtype_code(q_out.dtype))

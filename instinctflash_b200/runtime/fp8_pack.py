@@ -12,6 +12,7 @@ from __future__ import annotations
 import torch
 
 from .. import _lib
+from ..kernels._common import launch
 
 
 def _check(x):
@@ -27,9 +28,7 @@ def pack_bf16_e4m3(x: torch.Tensor, scale: torch.Tensor) -> torch.Tensor:
         raise ValueError("FP8 packing requires one FP32 scale on the input device")
     out = torch.empty_like(x, dtype=torch.float8_e4m3fn)
     if x.numel():
-        st = _lib.lib().iflb200_pack_bf16_e4m3(x.data_ptr(), x.numel(), scale.data_ptr(), out.data_ptr(),
-                                               _lib.stream_handle(x.device))
-        _lib.check(st, "pack_bf16_e4m3")
+        launch("iflb200_pack_bf16_e4m3", x, x.data_ptr(), x.numel(), scale.data_ptr(), out.data_ptr())
     return out
 
 
@@ -43,7 +42,6 @@ def dynamic_pack_bf16_e4m3(x: torch.Tensor):
     workspace = torch.empty((nbytes + 3) // 4, device=x.device, dtype=torch.int32)
     scale = torch.empty((1,), device=x.device, dtype=torch.float32)
     out = torch.empty_like(x, dtype=torch.float8_e4m3fn)
-    st = lib.iflb200_dynamic_pack_bf16_e4m3(x.data_ptr(), n, out.data_ptr(), scale.data_ptr(),
-                                            workspace.data_ptr(), nbytes, _lib.stream_handle(x.device))
-    _lib.check(st, "dynamic_pack_bf16_e4m3")
+    launch("iflb200_dynamic_pack_bf16_e4m3", x, x.data_ptr(), n, out.data_ptr(), scale.data_ptr(),
+           workspace.data_ptr(), nbytes)
     return out, scale

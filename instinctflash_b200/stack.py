@@ -8,6 +8,11 @@ buffer is allocated once (the engines' arena pattern, instinctflash/engines/comm
 ``forward`` only enqueues kernels on the current stream, so it can be captured in a CUDA graph.
 The same driver runs any set of operators with the reference's signatures (``ops`` argument),
 so the reference's own kernels can be timed through it.
+
+With this package's operators the driver uses the fused forms by default (``fused=True``): the
+gated activation is evaluated in the gate_up GEMM's epilogue (``fp8_linear_gated`` +
+``row_quant_from_amax`` instead of ``gemm`` + ``gated_act_quant``), bit-identical to the unfused
+sequence; ``fused=False`` keeps the reference's three-launch structure per linear.
 """
 from __future__ import annotations
 
@@ -26,7 +31,9 @@ E4M3 = torch.float8_e4m3fn
 def native_ops() -> SimpleNamespace:
     return SimpleNamespace(gemm=_fp8.gemm, row_quant=_norm.row_quant, dequant_rows=_norm.dequant_rows,
                            residual_norm_quant=_norm.residual_norm_quant, gated_act_quant=_act.gated_act_quant,
-                           GELU_TANH=_act.GELU_TANH, Fp8Weight=_fp8.Fp8Weight)
+                           GELU_TANH=_act.GELU_TANH, Fp8Weight=_fp8.Fp8Weight,
+                           fp8_linear_gated=_fp8.fp8_linear_gated, row_quant_from_amax=_norm.row_quant_from_amax,
+                           fp8_linear_residual=_fp8.fp8_linear_residual)
 
 
 @dataclass(frozen=True)
@@ -146,9 +153,13 @@ def make_inputs(spec: StackSpec, device, *, cpu_seeded: bool = True):
 class LinearStack:
     """Static buffers + the per-layer call sequence.  ``ops`` supplies the operators."""
 
-    def __init__(self, spec: StackSpec, weights, device, ops=None):
+    def __init__(self, spec: StackSpec, weights, device, ops=None, *, fused: bool = True,
+                 fuse_residual: bool = False):
         self.spec, self.weights, self.dev = spec, weights, torch.device(device)
         self.ops = ops or native_ops()
+        # fused forms exist only in this package's operator set
+        self.fused = fused and hasattr(self.ops, "fp8_linear_gated")
+        self.fuse_residual = fuse_residual and hasattr(self.ops, "fp8_linear_residual")
         M, D, F = spec.M, spec.hidden, spec.ffn
         dev, bf16, f32 = self.dev, torch.bfloat16, torch.float32
         widest_in = max(k for _, _, k in spec.linears())
@@ -157,6 +168,9 @@ class LinearStack:
         self.raw = torch.zeros(M * widest_out, dtype=bf16, device=dev)
         self.scale = [torch.zeros(M, dtype=f32, device=dev) for _ in range(2)]
         self.res = torch.zeros(M, D, dtype=bf16 if spec.kind == "wan" else f32, device=dev)
+        if self.fused and spec.kind == "gemma":
+            self.h = torch.zeros(M, F, dtype=f32, device=dev)     # act(g) * u, never rounded to 16 bits
+            self.amax = torch.zeros(M, dtype=f32, device=dev)     # row maxima of |h|; zero between calls
         self.attn = None
         self.launches_per_forward = 0
 
@@ -184,15 +198,15 @@ class LinearStack:
                     o.gemm(self._q8(D), W["qkv"], self._raw(sp.qkv)); n += 1
                     if sp.o_in:
                         o.row_quant(self.attn, self._q8(sp.o_in), s[1]); n += 1
-                        o.gemm(self._q8(sp.o_in), W["o"], self._raw(D)); n += 1
-                        o.residual_norm_quant(self.res, delta=self._raw(D), delta_row=s[1], delta_col=W["o"].scale,
-                                              q=self._q8(D), q_scale=s[0]); n += 1
-                    o.gemm(self._q8(D), W["gate_up"], self._raw(2 * F)); n += 1
-                    o.gated_act_quant(self._raw(2 * F), self._q8(F), s[1], row=s[0], col=W["gate_up"].scale,
-                                      act=o.GELU_TANH); n += 1
-                    o.gemm(self._q8(F), W["down"], self._raw(D)); n += 1
-                    o.residual_norm_quant(self.res, delta=self._raw(D), delta_row=s[1], delta_col=W["down"].scale,
-                                          q=self._q8(D), q_scale=s[0]); n += 1
+                        n += self._residual_linear(self._q8(sp.o_in), s[1], W["o"])
+                    if self.fused:
+                        o.fp8_linear_gated(self._q8(D), s[0], W["gate_up"], self.h, self.amax, act=o.GELU_TANH); n += 1
+                        o.row_quant_from_amax(self.h, self.amax, self._q8(F), s[1]); n += 1
+                    else:
+                        o.gemm(self._q8(D), W["gate_up"], self._raw(2 * F)); n += 1
+                        o.gated_act_quant(self._raw(2 * F), self._q8(F), s[1], row=s[0], col=W["gate_up"].scale,
+                                          act=o.GELU_TANH); n += 1
+                    n += self._residual_linear(self._q8(F), s[1], W["down"])
                 else:
                     V = lw.vec
                     o.gemm(self._q8(D), W["qkv"], self._raw(sp.qkv)); n += 1
@@ -218,6 +232,19 @@ class LinearStack:
                                           q_scale=s[0]); n += 1
         self.launches_per_forward = n
         return self.res
+
+    def _residual_linear(self, a, a_scale, w) -> int:
+        """res += (a @ w^T) * a_scale * w.scale, then RMS norm + quantiser of the new residual
+        stream into q8 / scale[0] (Gemma layers).  Returns the number of launches."""
+        o, D = self.ops, self.spec.hidden
+        if self.fuse_residual:
+            o.fp8_linear_residual(a, a_scale, w, self.res)
+            o.residual_norm_quant(self.res, q=self._q8(D), q_scale=self.scale[0])
+        else:
+            o.gemm(a, w, self._raw(D))
+            o.residual_norm_quant(self.res, delta=self._raw(D), delta_row=a_scale, delta_col=w.scale,
+                                  q=self._q8(D), q_scale=self.scale[0])
+        return 2
 
     def capture(self):
         """Warm up on a side stream, then capture ``forward`` into a CUDA graph

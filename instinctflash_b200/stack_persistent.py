@@ -23,6 +23,7 @@ import torch
 
 from . import _lib
 from .kernels import norm as _norm
+from .kernels._common import launch
 from .stack import StackSpec
 
 E4M3 = torch.float8_e4m3fn
@@ -134,10 +135,8 @@ class PersistentExpertStack:
         _norm.residual_norm_quant(self.res, q=self.q8, q_scale=self.s0)
 
     def forward(self):
-        st = self.lib.iflb200_stack_run(self.d_ops.data_ptr(), self.num_ops, self.d_maps.data_ptr(),
-                                        self.d_bars.data_ptr(), self.num_bars, self.spec.M, self.status.data_ptr(),
-                                        _lib.stream_handle(self.dev))
-        _lib.check(st, "stack_run")
+        launch("iflb200_stack_run", self.res, self.d_ops.data_ptr(), self.num_ops, self.d_maps.data_ptr(),
+               self.d_bars.data_ptr(), self.num_bars, self.spec.M, self.status.data_ptr())
         return self.res
 
     def timeout_record(self) -> int:

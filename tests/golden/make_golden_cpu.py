@@ -20,7 +20,9 @@ import torch
 
 HERE = Path(__file__).resolve().parent
 sys.path.insert(0, str(HERE.parent))
-sys.path.insert(0, sys.argv[1] if len(sys.argv) > 1 else "/root/reference")
+if len(sys.argv) < 2:
+    raise SystemExit("usage: make_golden_cpu.py /path/to/InstinctFlash")
+sys.path.insert(0, sys.argv[1])
 
 import cases  # noqa: E402
 from instinctflash.kernels.fp8 import Fp8Weight, gemm, quantize_weight  # noqa: E402

@@ -8,7 +8,7 @@ capability gate and run on sm_100 as they are; the per-tensor packer does have o
 (instinctflash/runtime/fp8_pack.py:48-50), so ``torch.cuda.get_device_capability`` is patched
 to (9, 0) around it, the way the reference's own tests do (tests/test_sm89_fp8.py:52).
 
-    python tests/golden/make_golden_gpu.py --out gpurun_out/golden_b200.json
+    python tests/golden/make_golden_gpu.py --out /some/scratch/golden_b200.json
 
 The output is copied to ``tests/golden/golden_b200.json`` and committed.
 """
@@ -67,7 +67,7 @@ def quant_record(q, qs):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--out", default="gpurun_out/golden_b200.json")
+    ap.add_argument("--out", required=True)
     args = ap.parse_args()
 
     from instinctflash.kernels.activation import GELU_TANH, SILU, gated_act_quant

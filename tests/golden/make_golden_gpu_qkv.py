@@ -5,7 +5,7 @@ Runs the unmodified reference kernels ``qkv_split`` (instinctflash/kernels/rope.
 the seeded inputs of ``tests/cases.py`` and writes per output buffer its sha256, the first 64
 elements and every 97th element (as float32 bit patterns).
 
-    python tests/golden/make_golden_gpu_qkv.py --out gpurun_out/golden_b200_qkv.json
+    python tests/golden/make_golden_gpu_qkv.py --out /some/scratch/golden_b200_qkv.json
 
 The output is copied to ``tests/golden/golden_b200_qkv.json`` and committed.
 """
@@ -47,7 +47,7 @@ def dev(t):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--out", default="gpurun_out/golden_b200_qkv.json")
+    ap.add_argument("--out", required=True)
     args = ap.parse_args()
     from instinctflash.kernels.rope import qkv_split
     from instinctflash.kernels.wan import wan_qkv

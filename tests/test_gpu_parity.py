@@ -27,12 +27,24 @@ def ops():
     from instinctflash_b200.kernels import activation, fp8, norm
     from instinctflash_b200.runtime import fp8_pack, torch_fp8_linear
     lib = _lib.lib()   # raises if the CUDA library is missing: no fallback
-    # The bit-exact claims of this module (raw accumulator == the reference's cuBLASLt output,
-    # column shards == full matrix) hold for the unsplit K loop; cluster split-K, which the cost
-    # model picks for deep reductions with few tiles, is tested on its own below.
-    assert lib.iflb200_gemm_set_split_k(1) == 0
     yield dict(lib=lib, _lib=_lib, fp8=fp8, norm=norm, act=activation, pack=fp8_pack, lin=torch_fp8_linear)
-    lib.iflb200_gemm_set_split_k(0)
+
+
+@pytest.fixture
+def unsplit(ops):
+    """Tests whose claims hold for the unsplit K loop (raw accumulator == the reference's cuBLASLt
+    output, column shards == full matrix) switch cluster split-K off for their own duration; every
+    other test runs with all knobs at their defaults.  Note that the CTA-pair kernel is only taken
+    by the heuristic while this switch is at its default (see the pair tests below)."""
+    assert ops["lib"].iflb200_gemm_set_split_k(1) == 0
+    yield
+    assert ops["lib"].iflb200_gemm_set_split_k(0) == 0
+
+
+def last_launch(ops):
+    fam, bn, sk = ctypes.c_int(0), ctypes.c_int(0), ctypes.c_int(0)
+    assert ops["lib"].iflb200_gemm_last_launch(ctypes.byref(fam), ctypes.byref(bn), ctypes.byref(sk)) == 0
+    return fam.value, bn.value, sk.value
 
 
 @pytest.fixture(scope="module")
@@ -240,7 +252,7 @@ def test_residual_norm_quant_without_delta_and_write_res_false(ops, oracle):
 
 # ------------------------------------------------------------------------------------- GEMM
 @pytest.mark.parametrize("name", [n for n, _ in cases.gemm_cases()])
-def test_gemm_and_fused_linear(ops, oracle, B200, name):
+def test_gemm_and_fused_linear(ops, unsplit, oracle, B200, name):
     c = dict(cases.gemm_cases())[name]
     g = B200[f"gemm/{name}"]
     fp8, norm = ops["fp8"], ops["norm"]
@@ -285,7 +297,7 @@ def test_gemm_and_fused_linear(ops, oracle, B200, name):
 
 
 @pytest.mark.parametrize("tile_n", [64, 128, 192, 224, 256])
-def test_gemm_tile_shapes_agree(ops, tile_n):
+def test_gemm_tile_shapes_agree(ops, unsplit, tile_n):
     fp8 = ops["fp8"]
     g = torch.Generator().manual_seed(tile_n)
     a = dev((torch.randn(520, 3072, generator=g) * 60).clamp(-448, 448).to(E4M3))
@@ -305,7 +317,7 @@ def test_gemm_tile_shapes_agree(ops, tile_n):
 
 @pytest.mark.parametrize("tile_n", [192, 224])
 @pytest.mark.parametrize("out_dtype", [torch.bfloat16, torch.float16, torch.float32])
-def test_gemm_odd_tile_widths_all_epilogues(ops, tile_n, out_dtype):
+def test_gemm_odd_tile_widths_all_epilogues(ops, unsplit, tile_n, out_dtype):
     """Tiles of 192 and 224 columns: 128-byte pieces through TMA, the 32-column remainder of a
     224-wide tile straight from registers, clipped at a ragged N; identical to the default tiles."""
     fp8 = ops["fp8"]
@@ -338,7 +350,7 @@ def test_gemm_odd_tile_widths_all_epilogues(ops, tile_n, out_dtype):
 
 @pytest.mark.parametrize("M,N,K", [(816, 1040, 512), (300, 640, 256), (1000, 2048, 384), (512, 256, 128), (257, 144, 2048),
                                    (816, 8192, 256), (600, 20480, 128)])
-def test_gemm_swapped_form_is_bit_identical(ops, M, N, K):
+def test_gemm_swapped_form_is_bit_identical(ops, unsplit, M, N, K):
     """A few hundred tokens: tokens on the MMA's N side, tile stored transposed.  Same K loop, so
     the raw accumulator and the dequantised outputs equal the ordinary form bit for bit."""
     fp8, lib = ops["fp8"], ops["lib"]
@@ -375,6 +387,197 @@ def test_gemm_swapped_form_is_bit_identical(ops, M, N, K):
     no_timeout(ops)
 
 
+# CTA pairs (cta_group::2, 256 x 256 tiles): the kernel the heuristic takes for every GEMM of the
+# Wan-14B-shape stack (M = 16384).  Same K loop as the single-CTA kernel => identical bits.
+PAIR_SHAPES = [(600, 1040, 5120), (4200, 768, 13824), (257, 272, 128), (1024, 2048, 512)]
+
+
+@pytest.mark.parametrize("mode", [2, 3])
+@pytest.mark.parametrize("M,N,K", PAIR_SHAPES)
+def test_gemm_cta_pair_kernel_is_bit_identical(ops, M, N, K, mode):
+    """Forced CTA-pair kernel (one / two accumulators) against the single-CTA kernel: raw, dequant
+    into bf16 / f16 / f32 (engine and exact rounding), residual into f32 / bf16 with a gate table,
+    rows not a multiple of 256, columns not a multiple of 256, a strided output view."""
+    fp8, lib = ops["fp8"], ops["lib"]
+    g = torch.Generator().manual_seed(M * 7 + N + K + mode)
+    a = dev((torch.randn(M, K, generator=g) * 60).clamp(-448, 448).to(E4M3))
+    w = dev((torch.randn(N, K, generator=g) * 60).clamp(-448, 448).to(E4M3))
+    s = dev(cases.vector(M, 921, lo=0.001, hi=0.02))
+    W = fp8.Fp8Weight(w, dev(cases.vector(N, 922, lo=0.0001, hi=0.001)), dev(cases.vector(N, 923, sigma=0.05)))
+    gate = dev(cases.vector(3 * N, 924, sigma=0.5)).view(3, N)
+    gidx = (torch.arange(M, dtype=torch.int32) % 3).to(DEV)
+    res0 = dev(cases.activations(M, N, 925, dtype=torch.float32))
+    families = []
+
+    def run():
+        out = []
+        raw = torch.full((M, N), float("nan"), device=DEV, dtype=torch.bfloat16)
+        fp8.gemm(a, W, raw)
+        families.append(last_launch(ops)[0])
+        out.append(raw)
+        for odt in (torch.bfloat16, torch.float16, torch.float32):
+            y = torch.full((M, N), float("nan"), device=DEV, dtype=odt)
+            fp8.fp8_linear(a, s, W, y)
+            out.append(y)
+        ye = torch.full((M, N), float("nan"), device=DEV, dtype=torch.bfloat16)
+        fp8.fp8_linear(a, s, W, ye, exact=True)
+        out.append(ye)
+        for rdt in (torch.float32, torch.bfloat16):
+            r = res0.to(rdt)
+            fp8.fp8_linear_residual(a, s, W, r, bias=W.bias, gate=gate, gate_index=gidx)
+            families.append(last_launch(ops)[0])
+            out.append(r)
+        view = torch.full((M, N + 48), float("nan"), device=DEV, dtype=torch.bfloat16)
+        fp8.gemm(a, W, view[:, 16:16 + N])
+        out.append(view)
+        return out
+    try:
+        assert lib.iflb200_gemm_set_split_k(1) == 0 and lib.iflb200_gemm_set_mode(1) == 0
+        want = run()
+        assert set(families) == {1}
+        families.clear()
+        assert lib.iflb200_gemm_set_split_k(0) == 0 and lib.iflb200_gemm_set_mode(mode) == 0
+        got = run()
+        assert set(families) == {mode}, "the CTA-pair kernel did not run"
+    finally:
+        lib.iflb200_gemm_set_mode(0)
+        lib.iflb200_gemm_set_split_k(0)
+    names = ("raw", "dequant bf16", "dequant f16", "dequant f32", "dequant exact", "residual f32", "residual bf16")
+    for g_, w_, what in zip(got[:-1], want[:-1], names):
+        assert not torch.isnan(g_.float()).any(), what
+        assert torch.equal(g_, w_), what
+    assert torch.equal(got[-1][:, 16:16 + N], want[-1][:, 16:16 + N])
+    assert torch.isnan(got[-1][:, :16]).all() and torch.isnan(got[-1][:, 16 + N:]).all()   # nothing outside the view
+    no_timeout(ops)
+
+
+@pytest.mark.parametrize("name", ["c5_ff1_slice", "c4_qkv_slice", "c2_gate_up_slice", "c2_qkv"])
+@pytest.mark.parametrize("mode", [2, 3])
+def test_gemm_cta_pair_kernel_matches_reference_recording(ops, B200, name, mode):
+    """The forced CTA-pair kernel against the reference's recorded cuBLASLt output on a B200."""
+    c = dict(cases.gemm_cases())[name]
+    g = B200[f"gemm/{name}"]
+    fp8, lib = ops["fp8"], ops["lib"]
+    a, s = quantise(ops, dev(c["x"]))
+    W = fp8.Fp8Weight(dev(c["wq"]), dev(c["wscale"]), dev(c["bias"]))
+    M, N = a.shape[0], W.w.shape[0]
+    try:
+        assert lib.iflb200_gemm_set_mode(mode) == 0
+        raw = torch.full((M, N), float("nan"), device=DEV, dtype=torch.bfloat16)
+        fp8.gemm(a, W, raw)
+        assert last_launch(ops)[0] == mode
+        y = torch.full((M, N), float("nan"), device=DEV, dtype=torch.bfloat16)
+        fp8.fp8_linear(a, s, W, y)
+    finally:
+        lib.iflb200_gemm_set_mode(0)
+    assert sha(raw) == g["raw_sha"], "raw accumulator differs from the reference's gemm on a B200"
+    assert sha(y) == g["y_sha"], "fused linear differs from the reference's gemm + dequant_rows on a B200"
+    no_timeout(ops)
+
+
+HEURISTIC_PAIR = [("c5_o_rows", 4352, 5120, 5120), ("c5_ff2_rows", 4352, 5120, 13824), ("c5_qkv_rows", 4608, 15360, 5120)]
+
+
+@pytest.mark.parametrize("name,M,N,K", HEURISTIC_PAIR)
+def test_gemm_default_knobs_take_the_pair_kernel_for_large_m(ops, oracle, name, M, N, K):
+    """All knobs at their defaults, M >= 4096 and the Wan-14B-shape widths: the heuristic must
+    launch the CTA-pair kernel, and its output must equal the single-CTA kernel's bit for bit and
+    the exact oracle accumulator (after bf16 rounding) on a sample."""
+    fp8, lib = ops["fp8"], ops["lib"]
+    g = torch.Generator().manual_seed(M + N + K)
+    x = cases.activations(M, K, 3000 + K % 97, outlier_frac=0.005, outlier_scale=30.0)
+    a, s = quantise(ops, dev(x))
+    wq = (torch.randn(N, K, generator=g) * 120).clamp(-448, 448).to(E4M3)
+    W = fp8.Fp8Weight(dev(wq), dev(cases.vector(N, 931, lo=0.0001, hi=0.001)), dev(cases.vector(N, 932, sigma=0.05)))
+    raw = torch.full((M, N), float("nan"), device=DEV, dtype=torch.bfloat16)
+    fp8.gemm(a, W, raw)
+    assert last_launch(ops)[0] == 3, "the heuristic did not take the CTA-pair kernel"
+    y = torch.full((M, N), float("nan"), device=DEV, dtype=torch.float16)
+    fp8.fp8_linear(a, s, W, y)
+    assert last_launch(ops)[0] == 3
+    res0 = dev(cases.activations(M, N, 933, dtype=torch.float32)).to(torch.bfloat16)
+    r = res0.clone()
+    fp8.fp8_linear_residual(a, s, W, r, bias=W.bias)
+    assert last_launch(ops)[0] == 3
+    try:
+        assert lib.iflb200_gemm_set_split_k(1) == 0 and lib.iflb200_gemm_set_mode(1) == 0
+        raw1 = torch.empty_like(raw)
+        fp8.gemm(a, W, raw1)
+        assert last_launch(ops)[0] == 1
+        y1 = torch.empty_like(y)
+        fp8.fp8_linear(a, s, W, y1)
+        r1 = res0.clone()
+        fp8.fp8_linear_residual(a, s, W, r1, bias=W.bias)
+    finally:
+        lib.iflb200_gemm_set_mode(0)
+        lib.iflb200_gemm_set_split_k(0)
+    assert torch.equal(raw, raw1) and torch.equal(y, y1) and torch.equal(r, r1)
+    rows_idx = torch.randperm(M, generator=g)[:24]
+    cols_idx = torch.randperm(N, generator=g)[:384]
+    exact = oracle.gemm_acc(a.cpu()[rows_idx].contiguous(), wq[cols_idx].contiguous()).to(torch.bfloat16)
+    got = raw.cpu()[rows_idx][:, cols_idx]
+    assert (got != exact).float().mean().item() < 2e-3
+    assert rel_frobenius(got.float(), exact.float()) < 1e-4
+    no_timeout(ops)
+
+
+GATED_GEMM = [(816, 1024, 2048), (50, 4096, 1024), (96, 16384, 256), (130, 272, 256), (7, 48, 64), (300, 640, 512)]
+
+
+@pytest.mark.parametrize("act", [0, 1])
+@pytest.mark.parametrize("M,F,K", GATED_GEMM)
+def test_gated_epilogue_equals_gemm_plus_gated_act_quant(ops, unsplit, M, F, K, act):
+    """The gated activation evaluated in the GEMM epilogue (gate and up columns of a hidden unit
+    paired in one tile, h out in fp32, row maxima by atomicMax) followed by the quantiser pass must
+    write exactly the codes and scales of gemm + gated_act_quant -- the pair the recorded reference
+    vectors pin -- for every tile width, on consecutive calls (the maxima are left at zero), with
+    ragged widths and heights."""
+    fp8, norm, act_mod, lib = ops["fp8"], ops["norm"], ops["act"], ops["lib"]
+    g = torch.Generator().manual_seed(M + F + K + act)
+    x = cases.activations(M, K, 4000 + F % 89, outlier_frac=0.01, outlier_scale=20.0)
+    a, s = quantise(ops, dev(x))
+    wq, wscale = cases.pack_weight_cpu(cases.weights(2 * F, K, 4100 + F % 83))
+    W = fp8.Fp8Weight(dev(wq), dev(wscale), None)
+    raw = torch.empty(M, 2 * F, device=DEV, dtype=torch.bfloat16)
+    fp8.gemm(a, W, raw)
+    q_ref = torch.empty(M, F, device=DEV, dtype=E4M3)
+    s_ref = torch.empty(M, device=DEV)
+    act_mod.gated_act_quant(raw, q_ref, s_ref, row=s, col=W.scale, act=act)
+    amax = torch.zeros(M, device=DEV)
+    try:
+        for tile_n in (0, 64, 128, 256):
+            assert lib.iflb200_gemm_set_config(tile_n, 0, 0) == 0
+            for _ in range(2):
+                h = torch.full((M, F + 32), float("nan"), device=DEV)[:, :F]      # a strided view
+                fp8.fp8_linear_gated(a, s, W, h, amax, act=act)
+                fam, bn, _ = last_launch(ops)
+                assert fam == 9 and (tile_n == 0 or bn == tile_n)
+                assert torch.equal(amax, h.abs().amax(1))
+                q = torch.full((M, F), 0x7F, device=DEV, dtype=torch.uint8).view(E4M3)
+                qs = torch.full((M,), float("nan"), device=DEV)
+                norm.row_quant_from_amax(h, amax, q, qs)
+                assert torch.equal(i32(qs), i32(s_ref)), f"tile {tile_n}: scales differ"
+                assert torch.equal(u8(q), u8(q_ref)), f"tile {tile_n}: codes differ"
+                assert bool((amax == 0).all()), "the row maxima were not left at zero"
+    finally:
+        lib.iflb200_gemm_set_config(0, 0, 0)
+    no_timeout(ops)
+
+
+def test_gated_epilogue_rejects_bad_arguments(ops):
+    fp8 = ops["fp8"]
+    a = torch.zeros(4, 32, device=DEV, dtype=torch.uint8).view(E4M3)
+    W = fp8.Fp8Weight(torch.zeros(48, 32, device=DEV, dtype=torch.uint8).view(E4M3), torch.ones(48, device=DEV), None)
+    with pytest.raises(ValueError, match="multiples of 16"):                     # F = 24
+        fp8.fp8_linear_gated(a, torch.ones(4, device=DEV), W, torch.empty(4, 24, device=DEV), torch.zeros(4, device=DEV))
+    W = fp8.Fp8Weight(torch.zeros(64, 32, device=DEV, dtype=torch.uint8).view(E4M3), torch.ones(64, device=DEV), None)
+    with pytest.raises(ValueError):
+        fp8.fp8_linear_gated(a, torch.ones(4, device=DEV), W, torch.empty(4, 32, device=DEV, dtype=torch.bfloat16),
+                             torch.zeros(4, device=DEV))
+    with pytest.raises(ValueError, match="act"):
+        fp8.fp8_linear_gated(a, torch.ones(4, device=DEV), W, torch.empty(4, 32, device=DEV), torch.zeros(4, device=DEV), act=3)
+
+
 def test_gemm_reference_test_shape(ops):
     """instinctflash tests/test_gi_kernels.py:130-143: M=50, K=1024, N=2560 against x@w.T+b, < 0.05."""
     fp8, norm = ops["fp8"], ops["norm"]
@@ -391,7 +594,7 @@ def test_gemm_reference_test_shape(ops):
     assert ((y - ref).abs().max() / ref.abs().max()) < 0.05
 
 
-def test_gemm_strided_operands_and_output_views(ops):
+def test_gemm_strided_operands_and_output_views(ops, unsplit):
     fp8 = ops["fp8"]
     g = torch.Generator().manual_seed(11)
     arena_a = dev((torch.randn(70, 2048, generator=g) * 50).clamp(-448, 448).to(E4M3))
@@ -435,8 +638,9 @@ def test_gemm_cluster_split_k(ops, oracle, name, forced):
     W = fp8.Fp8Weight(dev(c["wq"]), dev(c["wscale"]), dev(c["bias"]))
     M, N = a.shape[0], W.w.shape[0]
     unsplit = torch.empty(M, N, device=DEV, dtype=torch.bfloat16)
-    fp8.gemm(a, W, unsplit)
     try:
+        assert lib.iflb200_gemm_set_split_k(1) == 0
+        fp8.gemm(a, W, unsplit)
         assert lib.iflb200_gemm_set_split_k(forced) == 0
         raw = torch.full((M, N), float("nan"), device=DEV, dtype=torch.bfloat16)
         fp8.gemm(a, W, raw)
@@ -461,7 +665,7 @@ def test_gemm_cluster_split_k(ops, oracle, name, forced):
         assert torch.equal(r1, r2)
         no_timeout(ops)
     finally:
-        lib.iflb200_gemm_set_split_k(1)
+        lib.iflb200_gemm_set_split_k(0)
 
 
 FULL_SIZE = [("c2_gate_up", 816, 32768, 2048, 1), ("c2_down", 816, 2048, 16384, 1), ("c4_qkv", 4680, 9216, 3072, 3),
@@ -469,7 +673,7 @@ FULL_SIZE = [("c2_gate_up", 816, 32768, 2048, 1), ("c2_down", 816, 2048, 16384, 
 
 
 @pytest.mark.parametrize("name,M,N,K,seed", FULL_SIZE)
-def test_gemm_properties_at_full_size(ops, oracle, name, M, N, K, seed):
+def test_gemm_properties_at_full_size(ops, unsplit, oracle, name, M, N, K, seed):
     """At the benchmark sizes: (a) column shards of the weight give bit-identical columns
     (N-partition invariance: the K loop order depends on K alone), (b) row shards of the
     activations give bit-identical rows, (c) a sampled set of rows/columns matches the exact
@@ -515,7 +719,7 @@ def test_gemm_properties_at_full_size(ops, oracle, name, M, N, K, seed):
     no_timeout(ops)
 
 
-def test_gemm_is_deterministic_and_graph_replayable(ops):
+def test_gemm_is_deterministic_and_graph_replayable(ops, unsplit):
     fp8, norm = ops["fp8"], ops["norm"]
     x = dev(cases.activations(816, 2048, 31))
     W = fp8.Fp8Weight(dev((torch.randn(2560, 2048) * 100).clamp(-448, 448).to(E4M3)), torch.rand(2560, device=DEV) * 1e-3,
@@ -590,7 +794,7 @@ def test_dynamic_pack_nan_and_graph_replay(ops):
     assert torch.isnan(scale).all()
 
 
-def test_sm100_fp8_linear_matches_reference_module_output(ops, B200):
+def test_sm100_fp8_linear_matches_reference_module_output(ops, unsplit, B200):
     c = cases.thor_linear_case()
     g = B200["thor_fp8_linear/40x1024x2048"]
     lin = torch.nn.Linear(2048, 1024, bias=True, dtype=torch.bfloat16)

@@ -39,6 +39,83 @@ def test_stack_matches_cpu_oracle_stack(kind, M):
     assert rel < 2e-2, rel
 
 
+@pytest.mark.parametrize("M,hidden,ffn", [(50, 1024, 4096), (816, 512, 2048), (130, 256, 272)])
+def test_fused_epilogues_give_the_bits_of_the_three_launch_structure(M, hidden, ffn):
+    """The driver's default (gated activation in the gate_up GEMM's epilogue) and the optional fused
+    residual epilogue against the reference's structure (gemm, then the consumer kernel): the same
+    residual stream, codes and scales, bit for bit, eagerly and from a captured graph."""
+    from instinctflash_b200 import _lib
+    lib = _lib.lib()
+    spec = StackSpec("t", "gemma", 3, M, hidden, ffn, 768, o_in=hidden, outlier_frac=0.02, outlier_scale=10.0, seed=21)
+    weights = make_weights(spec, DEV)
+    x, attn = make_inputs(spec, DEV)
+    assert lib.iflb200_gemm_set_split_k(1) == 0      # same K loop in every arm
+    try:
+        plain = LinearStack(spec, weights, DEV, fused=False)
+        plain.load(x, attn)
+        want = plain.forward().clone()
+        want_q, want_s = plain._q8(hidden).view(torch.uint8).clone(), plain.scale[0].clone()
+        for fuse_residual in (False, True):
+            st = LinearStack(spec, weights, DEV, fused=True, fuse_residual=fuse_residual)
+            assert st.fused and st.fuse_residual == fuse_residual
+            st.load(x, attn)
+            got = st.forward()
+            assert torch.equal(got, want), f"fuse_residual={fuse_residual}"
+            assert torch.equal(st._q8(hidden).view(torch.uint8), want_q) and torch.equal(st.scale[0], want_s)
+            g = st.capture()
+            st.load(x, attn)
+            g.replay()
+            torch.cuda.synchronize()
+            assert torch.equal(st.res, want) and bool((st.amax == 0).all())
+    finally:
+        lib.iflb200_gemm_set_split_k(0)
+
+
+@pytest.mark.parametrize("cfg", ["c2", "c3", "c4", "c5"])
+def test_benchmark_geometry_with_default_knobs(cfg):
+    """Two layers of each benchmark configuration at its full widths and its full row count, every
+    tuning knob at its default (so the kernels the heuristics pick for that configuration are the
+    ones that run: CTA pairs for M = 16384, cluster split-K for the deep, few-tile down projections).
+    Checked against (a) the same stack forced onto the single-CTA unsplit kernel, which the per-
+    operator tests pin to the reference's recorded bits: identical where no split-K is chosen,
+    within 5e-3 otherwise; (b) the CPU oracle stack on a sample of rows (rows are independent:
+    per-token scales, per-row norms), within the distance the oracle's IEEE divisions allow."""
+    from instinctflash_b200 import _lib
+    from instinctflash_b200.stack import SPECS
+    lib = _lib.lib()
+    full = SPECS[cfg]
+    spec = StackSpec(**{**full.__dict__, "layers": 2, "steps": 1, "name": cfg + "_two_layers"})
+    weights = make_weights(spec, DEV)
+    x, attn = make_inputs(spec, DEV)
+    st = LinearStack(spec, weights, DEV)
+    st.load(x, attn)
+    got = st.forward().clone()
+    torch.cuda.synchronize()
+    assert torch.isfinite(got.float()).all()
+    try:
+        assert lib.iflb200_gemm_set_mode(1) == 0 and lib.iflb200_gemm_set_split_k(1) == 0
+        st.load(x, attn)
+        plain = st.forward().clone()
+        torch.cuda.synchronize()
+    finally:
+        lib.iflb200_gemm_set_mode(0)
+        lib.iflb200_gemm_set_split_k(0)
+    if cfg in ("c4", "c5"):       # no split-K at these sizes: same K loop, same bits
+        assert torch.equal(got, plain)
+    else:
+        rel = float((got.float() - plain.float()).norm() / plain.float().norm())
+        assert rel < 5e-3, rel
+    rows = torch.randperm(spec.M, generator=torch.Generator().manual_seed(7))[:16].sort().values
+    sub = StackSpec(**{**spec.__dict__, "M": 16})
+    cpu = LinearStack(sub, to_cpu_weights(weights), "cpu", ops=oracle_ops.ops())
+    cpu.load(x.cpu()[rows], attn.cpu()[rows])
+    want = cpu.forward().float()
+    rel = float((got.float().cpu()[rows] - want).norm() / want.norm())
+    assert rel < 2e-2, rel
+    rec = __import__("ctypes").c_uint32(0)
+    assert lib.iflb200_gemm_take_timeout_record(__import__("ctypes").byref(rec), None) == 0 and rec.value == 0
+
+
 @pytest.mark.parametrize("M,split", [(50, 1), (7, 1), (100, 1), (50, 8), (64, 3)])
 def test_persistent_stack_against_per_operator_stack(M, split):
     from instinctflash_b200 import _lib
@@ -136,3 +213,48 @@ def test_dependent_launch_modes_give_identical_results(kind, M):
     assert lib.iflb200_set_dependent_launch(3) != 0
     for res, codes in results[1:]:
         assert torch.equal(res, results[0][0]) and torch.equal(codes, results[0][1])
+
+
+def test_a_wait_that_nothing_satisfies_runs_out_and_leaves_the_context_usable():
+    """Two operators; the second waits on a dependency counter that no operator arrives on.  With
+    the wait budget set to a few milliseconds the launch returns, status2[0] names the wait that
+    gave up (epilogue role 3, grid dependency 5, operator 1), and the next ordinary launch on the
+    same context passes.  Nothing waits without a bound."""
+    import numpy as np
+    from instinctflash_b200 import _lib
+    from instinctflash_b200.stack_persistent import GATED, GEMM, OP_DTYPE, PersistentExpertStack
+    lib = _lib.lib()
+    spec = StackSpec("expert", "gemma", 1, 50, 1024, 4096, 1536, steps=1, seed=9)
+    weights = make_weights(spec, DEV)
+    x, _ = make_inputs(spec, DEV)
+    ps = PersistentExpertStack(spec, weights, DEV, down_split_k=1)
+    ps.load(x)
+    ps.forward()
+    torch.cuda.synchronize()
+    assert ps.timeout_record() == 0
+    want = ps.res.clone()
+    program = np.frombuffer(ps.d_ops.cpu().numpy().tobytes(), dtype=OP_DTYPE).copy()
+    assert program["type"][0] == GEMM and program["type"][2] == GATED
+    two = program[[0, 2]].copy()
+    two["wait_bar"][0], two["arrive_bar"][0] = -1, -1      # the GEMM depends on nothing and signals nothing
+    two["wait_bar"][1], two["arrive_bar"][1] = 0, -1       # counter 0: nobody arrives on it
+    d_two = torch.from_numpy(two.view(np.uint8).copy()).to(DEV)
+    bars = torch.zeros(1, dtype=torch.int32, device=DEV)
+    status = torch.zeros(2, dtype=torch.int32, device=DEV)
+    try:
+        assert lib.iflb200_set_wait_budget_us(4000) == 0
+        st = lib.iflb200_stack_run(d_two.data_ptr(), 2, ps.d_maps.data_ptr(), bars.data_ptr(), 1, spec.M,
+                                   status.data_ptr(), torch.cuda.current_stream().cuda_stream)
+        assert st == 0
+        torch.cuda.synchronize()                            # returns: the wait is bounded
+    finally:
+        assert lib.iflb200_set_wait_budget_us(0) == 0
+    code = int(status[0].item()) & 0xFFFFFFFF
+    assert code == (3 << 24) | (5 << 16) | 1, hex(code)
+    assert int(status[1].item()) == 1                       # the abort word every spinning CTA watches
+    # the context is intact: the ordinary program runs and reproduces its earlier result
+    ps.load(x)
+    ps.forward()
+    torch.cuda.synchronize()
+    assert ps.timeout_record() == 0
+    assert torch.equal(ps.res, want)

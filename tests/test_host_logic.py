@@ -99,6 +99,43 @@ def test_install_rebinds_engine_and_kernel_modules():
     assert sorted(report["instinctflash.engines.pi05.engine"]) == ["gated_act_quant", "gemm", "residual_norm_quant", "row_quant"]
 
 
+def test_calls_run_with_the_tensor_device_current(monkeypatch):
+    """The library keys its per-device state and the launch itself on the current device, so every
+    call must be made with the operand's device current (and the previous one restored).  Checked on
+    the host with a stand-in library that records the device at call time: nothing is launched."""
+    from instinctflash_b200 import _lib
+    from instinctflash_b200.kernels import _common
+
+    state = {"current": 0, "seen": [], "sets": []}
+
+    class FakeLib:
+        def iflb200_probe(self, *args):
+            state["seen"].append((state["current"], args))
+            return 0
+
+        def iflb200_status_string(self, status):
+            return b"bad"
+
+    def set_device(i):
+        state["sets"].append(i)
+        state["current"] = i
+
+    monkeypatch.setattr(torch.cuda, "current_device", lambda: state["current"])
+    monkeypatch.setattr(torch.cuda, "set_device", set_device)
+    monkeypatch.setattr(_lib, "lib", lambda: FakeLib())
+    monkeypatch.setattr(_lib, "stream_handle", lambda device=None: 1000 + device.index)
+    on_gpu1 = types.SimpleNamespace(device=torch.device("cuda", 1))   # only .device is looked at
+    _common.launch("iflb200_probe", on_gpu1, 7, 8)
+    assert state["seen"] == [(1, (7, 8, 1001))]            # called with cuda:1 current, on cuda:1's stream
+    assert state["sets"] == [1, 0] and state["current"] == 0  # and cuda:0 current again afterwards
+    state["current"], state["sets"] = 1, []
+    _common.launch("iflb200_probe", on_gpu1, 9)
+    assert state["sets"] == []                              # already current: no switch
+    other = types.SimpleNamespace(device=torch.device("cuda", 0))
+    with pytest.raises(ValueError, match="expected"):
+        _common.same_device(on_gpu1, q=other)                # operands on different devices are refused
+
+
 def test_install_default_patches_only_imported_modules():
     assert isinstance(inst.install(), dict)
 
