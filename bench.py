@@ -1,13 +1,25 @@
 #!/usr/bin/env python
 """Benchmark of the FP8 linear hot path on B200.
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload c2|c3|c3ref|c4|c5] [--impl reference]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload c2|c3|c3ref|c4|c5]
+                    [--impl reference] [--parallel dp|tp|tokens] [--no-configs] [--no-sharded]
 
-A step is one pass of a layer stack (per-token e4m3 quantisers, FP8 GEMMs and their consumers
-in the reference engines' call order) over one batch of synthetic activations.  The default
-workload is the pi05 PaliGemma prefix stack (18 layers, M = 816).  With N > 1 every rank runs
-its own independent stack (independent robot episodes: data parallel, no collective) and the
-reported value is the aggregate.  Prints ONE JSON line on rank 0.
+A step is one pass of a layer stack (per-token e4m3 quantisers, FP8 GEMMs and their consumers in
+the reference engines' call order) over one batch of synthetic activations.  The default workload
+is the pi05 PaliGemma prefix stack (18 layers, M = 816).  With N > 1 every rank runs its own
+independent stack (independent robot episodes: data parallel, no collective) and the reported
+value is the aggregate.  Prints ONE JSON line on rank 0.
+
+Beside the headline the line carries
+  * ``gpu_reference``: the reference's own GPU kernels (its Triton row kernels and
+    ``torch._scaled_mm``, imported unmodified from ``baseline/_ref``) run through the same stack
+    driver and CUDA graph, timed interleaved with this build (A-B-B-A);
+  * ``configs``: short runs of the other benchmark configurations in the same process, each with
+    its roofline fraction and its ratio against the reference's GPU kernels;
+  * ``sharded``: the splits of the configurations that shard -- 64 independent action-expert
+    episodes divided over the ranks (no collective), the Wan-shape stack split over tokens (no
+    collective) and tensor parallel (NCCL) -- measured at this N (strong scaling);
+  * ``roofline``, ``cpu_baseline``, ``e2e``, ``clocks`` as the contract asks.
 
 ``--impl reference`` times the reference's CPU form of the path (torch per-token quantiser +
 dequantise-and-matmul, restated in ``oracle/``) on the host cores over a bounded sample.
@@ -15,6 +27,7 @@ dequantise-and-matmul, restated in ``oracle/``) on the host cores over a bounded
 from __future__ import annotations
 
 import argparse
+import ctypes
 import json
 import os
 import statistics
@@ -23,6 +36,7 @@ import sys
 import threading
 import time
 from pathlib import Path
+from types import SimpleNamespace
 
 import torch
 
@@ -33,6 +47,8 @@ METRIC = "fp8_linear_stack_tflops"
 UNIT = "TFLOP/s"
 NOMINAL_FP8_TFLOPS = 4500.0
 NOMINAL_HBM_GBS = 8000.0
+EPISODES = 64           # independent action-expert episodes of the sharded c3 configuration
+EPISODE_BRANCHES = 8    # episodes in flight on one GPU (parallel branches of one CUDA graph)
 
 
 def measured_peaks():
@@ -105,6 +121,9 @@ class ClockSampler:
         return {"sm_mhz": statistics.median(sm), "sm_max_mhz": max(smax), "reasons": sorted(reasons), "samples": len(sm)}
 
 
+# ------------------------------------------------------------------------------------------------
+# CPU arm: the reference's CPU form of the path
+# ------------------------------------------------------------------------------------------------
 def cpu_reference_step(spec, layers, sample_layers, threads):
     """One bounded sample of the reference's CPU form of the path: per linear the torch per-token
     quantiser and dequantise-and-matmul (instinctflash benchmarks/native/fp8_probe.py:32-36),
@@ -177,18 +196,310 @@ def workload_name(spec):
     return names.get(spec.name, spec.name)
 
 
-def run_tensor_parallel(args, spec, dev, dist, rank, world):
-    """Strong scaling of one Wan-shape stack over `world` GPUs (total work fixed)."""
-    from instinctflash_b200.stack import make_inputs, make_weights
-    from instinctflash_b200.tp import Comm, WanTPStack
+# ------------------------------------------------------------------------------------------------
+# GPU helpers
+# ------------------------------------------------------------------------------------------------
+def reference_gpu_ops():
+    """The reference's own GPU operators (unmodified, from ``baseline/_ref``) with the signatures the
+    stack driver calls, or (None, reason)."""
+    ref = ROOT / "baseline" / "_ref"
+    if not (ref / "instinctflash").is_dir():
+        return None, "the reference is not installed under baseline/_ref"
+    if str(ref) not in sys.path:
+        sys.path.insert(0, str(ref))
+    try:
+        from instinctflash.kernels import activation as RA
+        from instinctflash.kernels import fp8 as RF
+        from instinctflash.kernels import norm as RN
+    except Exception as exc:   # noqa: BLE001
+        return None, f"the reference's kernel modules do not import: {exc}"
+    return SimpleNamespace(gemm=RF.gemm, row_quant=RN.row_quant, dequant_rows=RN.dequant_rows,
+                           residual_norm_quant=RN.residual_norm_quant, gated_act_quant=RA.gated_act_quant,
+                           GELU_TANH=RA.GELU_TANH, Fp8Weight=RF.Fp8Weight), None
+
+
+def replay_ms(graph, n, stream, dev):
+    """Device time of n back-to-back replays, CUDA events on the launching stream."""
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    torch.cuda.synchronize(dev)
+    e0.record(stream)
+    for _ in range(n):
+        graph.replay()
+    e1.record(stream)
+    torch.cuda.synchronize(dev)
+    return e0.elapsed_time(e1)
+
+
+def abba(native, reference, n, stream, dev):
+    """native, reference, reference, native: n replays each; (native ms, reference ms) per replay."""
+    a1 = replay_ms(native, n, stream, dev)
+    b1 = replay_ms(reference, n, stream, dev)
+    b2 = replay_ms(reference, n, stream, dev)
+    a2 = replay_ms(native, n, stream, dev)
+    return (a1 + a2) / (2 * n), (b1 + b2) / (2 * n)
+
+
+def check_no_timeout(dev):
+    """Every wait inside the tcgen05 kernels is bounded; a wait that ran out left a record and an
+    incomplete output.  A benchmark number from such a run is worthless: fail."""
+    from instinctflash_b200 import _lib
+    rec = ctypes.c_uint32(0)
+    st = _lib.lib().iflb200_gemm_take_timeout_record(ctypes.byref(rec), torch.cuda.current_stream(dev).cuda_stream)
+    if st != 0 or rec.value != 0:
+        raise SystemExit(f"a wait inside a GEMM kernel timed out during the benchmark (status {st}, record {rec.value:#x})")
+
+
+def measure_fp8_peak(dev, seconds=2.0):
+    """torch._scaled_mm (cuBLASLt) e4m3 8192^3 with unit scales: best of 10 single launches (burst)
+    and back to back for `seconds` (sustained).  The measured FP8 tensor peak of this GPU, this run."""
+    n = 8192
+    a = (torch.randn(n, n, device=dev) * 0.5).to(torch.float8_e4m3fn)
+    b = (torch.randn(n, n, device=dev) * 0.5).to(torch.float8_e4m3fn)
+    one = torch.ones((), device=dev)
+    out = torch.empty(n, n, device=dev, dtype=torch.bfloat16)
+    stream = torch.cuda.current_stream(dev)
+
+    def mm():
+        torch._scaled_mm(a, b.t(), scale_a=one, scale_b=one, out_dtype=torch.bfloat16, out=out)
+    for _ in range(3):
+        mm()
+    best = None
+    for _ in range(10):
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(stream)
+        mm()
+        e1.record(stream)
+        torch.cuda.synchronize(dev)
+        t = e0.elapsed_time(e1)
+        best = t if best is None else min(best, t)
+    flops = 2.0 * n ** 3
+    reps = max(10, int(seconds * 1e3 / best))
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record(stream)
+    for _ in range(reps):
+        mm()
+    e1.record(stream)
+    torch.cuda.synchronize(dev)
+    sustained = e0.elapsed_time(e1) / reps
+    return {"burst_tflops": flops / (best * 1e-3) / 1e12, "sustained_tflops": flops / (sustained * 1e-3) / 1e12,
+            "how": f"torch._scaled_mm e4m3 {n}^3, unit scales, bf16 out: best of 10 / {reps} back to back"}
+
+
+def stack_bytes(spec):
+    """Algorithmic bytes of one pass: per linear N*K + 4N + M*K + 4M + 2*M*N, plus the quantisers'
+    3*M*K + 4M, over all layers and flow steps."""
+    per_layer = 0.0
+    for _, n, k in spec.linears():
+        per_layer += n * k + 4.0 * n + spec.M * k + 4.0 * spec.M + 2.0 * spec.M * n
+        per_layer += 3.0 * spec.M * k + 4.0 * spec.M
+    return per_layer * spec.layers * spec.steps
+
+
+def time_config(spec, dev, ref_ops, steps, warmup, *, persistent=False):
+    """Short run of one configuration: this build and, when available, the reference's GPU kernels,
+    through the same driver and CUDA graph, interleaved.  Returns a dict for the JSON line."""
+    from instinctflash_b200.stack import LinearStack, make_inputs, make_weights
+    stream = torch.cuda.current_stream(dev)
+    weights = make_weights(spec, dev)
+    x, attn = make_inputs(spec, dev)
+    st = LinearStack(spec, weights, dev)
+    st.load(x, attn)
+    g = st.capture()
+    for _ in range(warmup):
+        g.replay()
+    out = {"workload": workload_name(spec), "launches_per_step": st.launches_per_forward}
+    g_ref = None
+    if ref_ops is not None:
+        try:
+            st_ref = LinearStack(spec, weights, dev, ops=ref_ops)
+            st_ref.load(x, attn)
+            g_ref = st_ref.capture()
+            for _ in range(warmup):
+                g_ref.replay()
+        except Exception as exc:   # noqa: BLE001
+            out["gpu_reference"] = {"unavailable": f"{type(exc).__name__}: {exc}"[:200]}
+            g_ref = None
+    if g_ref is not None:
+        ms, ms_ref = abba(g, g_ref, steps, stream, dev)
+        out["gpu_reference"] = {"ms_per_step": ms_ref, "ratio": ms_ref / ms}
+    else:
+        ms = replay_ms(g, 2 * steps, stream, dev) / (2 * steps)
+    out["ms_per_step"] = ms
+    out["tflops"] = spec.flops() / (ms * 1e-3) / 1e12
+    peaks = measured_peaks()
+    if spec.M > 400:
+        peak = 2.0 * peaks["bf16_tflops_sustained"]
+        out["roofline"] = {"bound": "tensor", "frac": out["tflops"] / peak, "peak": peak, "unit": UNIT,
+                           "peak_source": "2 x bf16_tflops_sustained (a whole stack is a long step)",
+                           "frac_of_nominal_4500": out["tflops"] / NOMINAL_FP8_TFLOPS}
+    else:
+        gbs = stack_bytes(spec) / (ms * 1e-3) / 1e9
+        out["roofline"] = {"bound": "hbm", "frac": gbs / peaks["hbm_gbs"], "achieved": gbs, "peak": peaks["hbm_gbs"],
+                           "unit": "GB/s", "frac_of_nominal_8000": gbs / NOMINAL_HBM_GBS}
+    if persistent:
+        from instinctflash_b200.stack_persistent import PersistentExpertStack
+        ps = PersistentExpertStack(spec, weights, dev)
+        ps.load(x)
+        ps.forward()
+        torch.cuda.synchronize(dev)
+        gp = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(gp):
+            ps.forward()
+        for _ in range(warmup):
+            gp.replay()
+        out["persistent_kernel_ms_per_step"] = replay_ms(gp, 2 * steps, stream, dev) / (2 * steps)
+        if ps.timeout_record() != 0:
+            raise SystemExit(f"a wait inside the persistent kernel timed out: {ps.timeout_record():#x}")
+        del ps, gp
+    del st, g, g_ref, weights
+    torch.cuda.empty_cache()
+    return out
+
+
+def time_single_linear(dev, ref_ops, steps, warmup):
+    """Configuration 1: one FP8 linear, x bf16 [64, 1024] -> per-token quantiser -> [4096, 1024]
+    weight + bias -> bf16.  Thirty-two weight copies are rotated so the 4 MB weight is not served
+    from L2 (134 MB per pass)."""
+    from instinctflash_b200.kernels import fp8, norm
+    E4M3 = torch.float8_e4m3fn
+    M, K, N, copies = 64, 1024, 4096, 32
+    g = torch.Generator(device=dev).manual_seed(0)
+    x = torch.randn(M, K, device=dev, generator=g).to(torch.bfloat16)
+    ws = []
+    for _ in range(copies):
+        w = torch.randn(N, K, device=dev, generator=g) * 0.02
+        ws.append(fp8.quantize_weight(w, torch.randn(N, device=dev, generator=g) * 0.01))
+    q = torch.empty(M, K, device=dev, dtype=E4M3)
+    s = torch.empty(M, device=dev)
+    raw = torch.empty(M, N, device=dev, dtype=torch.bfloat16)
+    y = torch.empty(M, N, device=dev, dtype=torch.bfloat16)
+    stream = torch.cuda.current_stream(dev)
+
+    def native():
+        for w in ws:
+            norm.row_quant(x, q, s)
+            fp8.fp8_linear(q, s, w, y)
+
+    def reference():
+        for w in ws:
+            ref_ops.row_quant(x, q, s)
+            ref_ops.gemm(q, ref_ops.Fp8Weight(w.w, w.scale, w.bias), raw)
+            ref_ops.dequant_rows(raw, y, row=s, col=w.scale, bias=w.bias)
+
+    def capture(fn):
+        side = torch.cuda.Stream(dev)
+        side.wait_stream(stream)
+        with torch.cuda.stream(side):
+            fn()
+            fn()
+        stream.wait_stream(side)
+        gr = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(gr):
+            fn()
+        return gr
+    gn = capture(native)
+    for _ in range(warmup):
+        gn.replay()
+    out = {"workload": "single FP8 linear 64 x 4096 x 1024 with bias, quantiser + fused GEMM epilogue, 32 rotated weights",
+           "launches_per_step": 2 * copies}
+    if ref_ops is not None:
+        gr = capture(reference)
+        for _ in range(warmup):
+            gr.replay()
+        ms, ms_ref = abba(gn, gr, steps, stream, dev)
+        out["gpu_reference"] = {"us_per_linear": ms_ref / copies * 1e3, "ratio": ms_ref / ms}
+    else:
+        ms = replay_ms(gn, 2 * steps, stream, dev) / (2 * steps)
+    us = ms / copies * 1e3
+    nbytes = N * K + 8.0 * N + 3.0 * M * K + 8.0 * M + 2.0 * M * N
+    peaks = measured_peaks()
+    gbs = nbytes / (us * 1e-6) / 1e9
+    out.update({"us_per_linear": us, "tflops": 2.0 * M * N * K / (us * 1e-6) / 1e12,
+                "roofline": {"bound": "hbm", "frac": gbs / peaks["hbm_gbs"], "achieved": gbs, "peak": peaks["hbm_gbs"],
+                             "unit": "GB/s", "frac_of_nominal_8000": gbs / NOMINAL_HBM_GBS}})
+    return out
+
+
+# ------------------------------------------------------------------------------------------------
+# Sharded configurations (strong scaling over the ranks of this run)
+# ------------------------------------------------------------------------------------------------
+def max_over_ranks(ms, dist, dev):
     if dist is None:
-        import torch.distributed as dist
-        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
-        os.environ.setdefault("MASTER_PORT", "29555")
-        dist.init_process_group("nccl", rank=0, world_size=1, device_id=dev)
+        return ms
+    t = torch.tensor([ms], device=dev, dtype=torch.float64)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    return float(t[0])
+
+
+def sharded_c3_episodes(dev, dist, rank, world, steps, warmup):
+    """64 independent action-expert episodes (M = 50 each, 18 layers x 10 flow steps), 64 / p per
+    GPU, no collective.  On each GPU up to 8 episodes are in flight as parallel branches of one CUDA
+    graph (every GEMM still has M = 50 rows; branches that reach the same layer together find its
+    weights in L2)."""
+    from instinctflash_b200.stack import SPECS, EpisodeBatch, make_inputs, make_weights
+    spec = SPECS["c3"]
+    mine = EPISODES // world + (1 if rank < EPISODES % world else 0)
+    branches = min(EPISODE_BRANCHES, max(1, mine))
+    rounds = -(-mine // branches)
+    weights = make_weights(spec, dev)
+    x, attn = make_inputs(spec, dev)
+    batch = EpisodeBatch(spec, weights, dev, branches)
+    batch.load(x, attn)
+    g = batch.capture()
+    stream = torch.cuda.current_stream(dev)
+    for _ in range(warmup):
+        g.replay()
+    if dist is not None:
+        dist.barrier()
+    ms = replay_ms(g, rounds * steps, stream, dev) / steps      # all of this rank's episodes, once
+    ms = max_over_ranks(ms, dist, dev)
+    per_episode_bytes = stack_bytes(spec)
+    peaks = measured_peaks()
+    out = {"episodes": EPISODES, "episodes_per_rank": mine, "branches_per_gpu": branches, "ms_all_episodes": ms,
+           "episodes_per_s": EPISODES / (ms * 1e-3), "ms_per_episode_per_gpu": ms / max(1, mine),
+           "algorithmic_gbs_per_gpu": per_episode_bytes * mine / (ms * 1e-3) / 1e9,
+           "frac_of_hbm_peak": per_episode_bytes * mine / (ms * 1e-3) / 1e9 / peaks["hbm_gbs"],
+           "note": "algorithmic bytes count every weight once per episode and flow step; branches that share a layer's "
+                   "weights through L2 read less from DRAM than that", "collective": "none"}
+    del batch, g, weights
+    torch.cuda.empty_cache()
+    return out
+
+
+def sharded_c4_tokens(dev, dist, rank, world, steps, warmup):
+    """The Wan2.2-5B-shape stack with its M = 4680 rows split over the ranks: every operator of the
+    path is row-independent and the weights fit every GPU, so there is no collective."""
+    from instinctflash_b200.stack import SPECS, LinearStack, StackSpec, make_inputs, make_weights
+    full = SPECS["c4"]
+    spec = StackSpec(**{**full.__dict__, "M": -(-full.M // world)})
+    weights = make_weights(spec, dev)
+    x, attn = make_inputs(spec, dev)
+    st = LinearStack(spec, weights, dev)
+    st.load(x, attn)
+    g = st.capture()
+    stream = torch.cuda.current_stream(dev)
+    for _ in range(warmup):
+        g.replay()
+    if dist is not None:
+        dist.barrier()
+    ms = max_over_ranks(replay_ms(g, steps, stream, dev) / steps, dist, dev)
+    out = {"rows_per_rank": spec.M, "ms_per_step": ms, "tflops": full.flops() / (ms * 1e-3) / 1e12, "collective": "none"}
+    del st, g, weights
+    torch.cuda.empty_cache()
+    return out
+
+
+def sharded_c4_tp(dev, dist, rank, world, steps, warmup):
+    """The Wan2.2-5B-shape stack tensor parallel: column-split qkv / cross-q / ff1, row-split
+    o / cross-o / ff2 with NCCL over NVLink."""
+    from instinctflash_b200.stack import SPECS, make_inputs, make_weights
+    from instinctflash_b200.tp import Comm, WanTPStack
+    spec = SPECS["c4"]
+    if spec.M % world:
+        return {"unavailable": f"M={spec.M} is not divisible by {world}"}
     torch.manual_seed(1234)   # identical full weights on every rank, sharded afterwards
     weights = make_weights(spec, dev)
-    stack = WanTPStack(spec, weights, dev, Comm())
+    stack = WanTPStack(spec, weights, dev, Comm() if dist is not None else Comm.single())
     del weights
     torch.cuda.empty_cache()
     x, attn = make_inputs(spec, dev)
@@ -205,52 +516,77 @@ def run_tensor_parallel(args, spec, dev, dist, rank, world):
         graph = torch.cuda.CUDAGraph()
         with torch.cuda.graph(graph):
             stack.forward()
-    except Exception:
+    except Exception:   # noqa: BLE001
         graph = None
+    runner = graph if graph is not None else SimpleNamespace(replay=stack.forward)
+    for _ in range(warmup):
+        runner.replay()
+    if dist is not None:
+        dist.barrier()
+    ms = max_over_ranks(replay_ms(runner, steps, stream, dev) / steps, dist, dev)
+    return {"ms_per_step": ms, "tflops": spec.flops() / (ms * 1e-3) / 1e12, "cuda_graph": graph is not None,
+            "nvlink_bytes_per_rank_per_step": stack.comm_bytes_per_step(), "collective": stack.collectives,
+            "_keep": (stack, graph)}
 
-    def step():
-        if graph is not None:
-            graph.replay()
-        else:
+
+# ------------------------------------------------------------------------------------------------
+def run_tensor_parallel(args, spec, dev, dist, rank, world):
+    """--parallel tp: strong scaling of one Wan-shape stack over `world` GPUs as the headline."""
+    from instinctflash_b200.stack import make_inputs, make_weights
+    from instinctflash_b200.tp import Comm, WanTPStack
+    torch.manual_seed(1234)
+    weights = make_weights(spec, dev)
+    stack = WanTPStack(spec, weights, dev, Comm() if dist is not None else Comm.single())
+    del weights
+    torch.cuda.empty_cache()
+    x, attn = make_inputs(spec, dev)
+    stack.load(x, attn)
+    stream = torch.cuda.current_stream(dev)
+    graph = None
+    try:
+        side = torch.cuda.Stream(dev)
+        side.wait_stream(stream)
+        with torch.cuda.stream(side):
             stack.forward()
-
+        stream.wait_stream(side)
+        torch.cuda.synchronize(dev)
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            stack.forward()
+    except Exception:   # noqa: BLE001
+        graph = None
+    runner = graph if graph is not None else SimpleNamespace(replay=stack.forward)
     for _ in range(args.warmup):
-        step()
-    dist.barrier()
-    torch.cuda.synchronize(dev)
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        runner.replay()
+    if dist is not None:
+        dist.barrier()
     with ClockSampler(dev.index) as clocks:
         clocks.begin()
-        e0.record(stream)
-        for _ in range(args.steps):
-            step()
-        e1.record(stream)
-        dist.barrier()
-        torch.cuda.synchronize(dev)
+        ms = replay_ms(runner, args.steps, stream, dev)
         clocks.end()
-    t = torch.tensor([e0.elapsed_time(e1)], device=dev, dtype=torch.float64)
-    dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    ms = float(t[0])
+    ms = max_over_ranks(ms, dist, dev)
+    check_no_timeout(dev)
     if rank == 0:
-        p = world
-        D, M = spec.hidden, spec.M
-        n_row = 3 if spec.cross else 2
-        comm_bytes = spec.layers * n_row * ((4 * M * D) + (M * D + 4 * M) + 4 * M) * (p - 1) / p
         line = {"metric": METRIC, "value": spec.flops() * args.steps / (ms * 1e-3) / 1e12, "unit": UNIT, "n_gpus": world,
                 "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms / args.steps, "higher_is_better": True,
                 "scaling": "strong", "vs_baseline": None, "dtype": "e4m3 x e4m3 -> f32", "data": "synthetic",
-                "config": {"workload": workload_name(spec), "parallelism": f"tp{world} (column-split qkv/cross-q/ff1, "
-                           "row-split o/cross-o/ff2, NCCL all-reduce-max + fp32 reduce-scatter + all-gather)",
+                "config": {"workload": workload_name(spec), "parallelism": f"tp{world}: " + stack.collectives,
                            "cuda_graph": graph is not None,
-                           "nvlink_bytes_per_rank_per_step": comm_bytes},
+                           "nvlink_bytes_per_rank_per_step": stack.comm_bytes_per_step()},
                 "clocks": clocks.summary(), "gpu_launches": None}
         print(json.dumps(line), flush=True)
-    # A captured graph holds NCCL work, and tearing the process group down under it has hung
-    # (watchdog stuck in event destruction): finish all work, then leave without the teardown.
+    leave(dev, dist)
+
+
+def leave(dev, dist):
+    """A captured graph may hold NCCL work, and tearing the process group down under it has hung
+    (watchdog stuck in event destruction): finish all work, then leave without the teardown."""
     torch.cuda.synchronize(dev)
-    dist.barrier()
-    torch.cuda.synchronize(dev)
+    if dist is not None:
+        dist.barrier()
+        torch.cuda.synchronize(dev)
     sys.stdout.flush()
+    sys.stderr.flush()
     os._exit(0)
 
 
@@ -262,13 +598,17 @@ def main():
     ap.add_argument("--workload", default="c2")
     ap.add_argument("--impl", default="native", choices=["native", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-configs", action="store_true", help="skip the short runs of the other configurations")
+    ap.add_argument("--no-sharded", action="store_true", help="skip the sharded configurations (c3 episodes, c4 tokens / tp)")
+    ap.add_argument("--no-gpu-reference", action="store_true", help="do not time the reference's GPU kernels")
+    ap.add_argument("--unfused", action="store_true", help="the reference's three-launch structure per linear")
+    ap.add_argument("--fuse-residual", action="store_true", help="residual update in the GEMM epilogue as well")
     ap.add_argument("--episodes", type=int, default=1,
                     help="c3 only: independent episodes stacked along M on each GPU (rows are independent: "
                          "per-token scales and per-row norms, so this is arithmetically the same as separate runs)")
     ap.add_argument("--persistent", action="store_true",
                     help="c3: the whole stack as one cooperative launch (stack_persistent_kernel) instead of one "
-                         "launch per operator (the default: with dependent launches it is the faster of the two)")
-    ap.add_argument("--per-op", action="store_true", help="accepted for compatibility: one launch per operator is the default")
+                         "launch per operator")
     ap.add_argument("--parallel", default="dp", choices=["dp", "tp", "tokens"],
                     help="dp: every rank runs its own stack (default, weak scaling); tp: the Wan-shape stacks "
                          "(c4, c5) are column/row split over the ranks with NCCL all-gather / reduce-scatter; "
@@ -281,15 +621,13 @@ def main():
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
 
-    from instinctflash_b200.stack import SPECS, LinearStack, make_inputs, make_weights
+    from instinctflash_b200.stack import SPECS, LinearStack, StackSpec, make_inputs, make_weights
     spec = SPECS[args.workload]
     if args.episodes > 1:
-        from instinctflash_b200.stack import StackSpec
         spec = StackSpec(**{**spec.__dict__, "M": spec.M * args.episodes})
     total_flops_all_ranks = None
     if args.parallel == "tokens":
         # strong scaling over tokens: rank r owns rows [r*M/p, (r+1)*M/p) (ceil), full weights everywhere
-        from instinctflash_b200.stack import StackSpec
         total_flops_all_ranks = spec.flops()
         spec = StackSpec(**{**spec.__dict__, "M": -(-spec.M // world)})
 
@@ -306,19 +644,23 @@ def main():
     dist = None
     if world > 1:
         import torch.distributed as dist
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
         dist.init_process_group("nccl", device_id=dev)
 
     if args.parallel == "tp":
         run_tensor_parallel(args, spec, dev, dist, rank, world)
         return
 
+    ref_ops, ref_reason = (None, "switched off") if args.no_gpu_reference else reference_gpu_ops()
     weights = make_weights(spec, dev)
-    persistent = (spec.kind == "gemma" and not spec.o_in and spec.M <= 128 and args.persistent and not args.per_op)
+    persistent = (spec.kind == "gemma" and not spec.o_in and spec.M <= 128 and args.persistent)
     if persistent:
         # skinny expert loop: the whole stack is one cooperative launch
         from instinctflash_b200.stack_persistent import PersistentExpertStack
 
         class _Persistent(PersistentExpertStack):
+            fused = False
+
             def load(self, x, attn=None):
                 super().load(x)
 
@@ -338,7 +680,7 @@ def main():
 
         stack = _Persistent(spec, weights, dev)
     else:
-        stack = LinearStack(spec, weights, dev)
+        stack = LinearStack(spec, weights, dev, fused=not args.unfused, fuse_residual=args.fuse_residual)
     x_dev, attn = make_inputs(spec, dev)
     x_host = x_dev.cpu().pin_memory()
     out_host = torch.empty(spec.M, spec.hidden, dtype=stack.res.dtype).pin_memory()
@@ -388,64 +730,137 @@ def main():
     f1.record(stream)
     barrier()
     ms_e2e = f0.elapsed_time(f1)
+    check_no_timeout(dev)
+
+    # ---- the reference's GPU kernels through the same driver, interleaved with this build -------
+    gpu_reference = {"unavailable": ref_reason}
+    if ref_ops is not None and not persistent:
+        try:
+            st_ref = LinearStack(spec, weights, dev, ops=ref_ops)
+            st_ref.load(x_dev, attn)
+            g_ref = st_ref.capture()
+            for _ in range(args.warmup):
+                g_ref.replay()
+            n = max(3, min(args.steps, 10))
+            ms_nat, ms_ref = abba(graph, g_ref, n, stream, dev)
+            rel = float((stack.res.float() - st_ref.res.float()).norm() / st_ref.res.float().norm())
+            gpu_reference = {"ms_per_step": ms_ref, "native_ms_per_step": ms_nat, "value": flops / (ms_ref * 1e-3) / 1e12,
+                             "ratio": ms_ref / ms_nat, "replays_per_segment": n, "order": "native, reference, reference, native",
+                             "what": "the reference's Triton row kernels + torch._scaled_mm (cuBLASLt), unmodified, through "
+                                     "the same stack driver and CUDA graph, same weights",
+                             "residual_stream_rel_diff_after_all_replays": rel}
+            del st_ref, g_ref
+        except Exception as exc:   # noqa: BLE001
+            gpu_reference = {"unavailable": f"{type(exc).__name__}: {exc}"[:300]}
 
     # ---- dominant kernel: the widest FP8 GEMM of the stack, timed alone over rotating layers ----
     from instinctflash_b200.kernels import fp8 as K
     dom = max(spec.linears(), key=lambda t: t[1] * t[2])
     name, n_dom, k_dom = dom
     a_dom = stack._q8(k_dom)
-    out_dom = stack._raw(n_dom)
+    gated_dom = bool(getattr(stack, "fused", False)) and name == "gate_up"
+    if gated_dom:
+        def dom_call(w):
+            K.fp8_linear_gated(a_dom, stack.scale[0], w, stack.h, stack.amax, act=0)
+        kernel_name = f"gemm_fp8_tc5_kernel (gated epilogue) {spec.M}x{n_dom}x{k_dom} ({name})"
+        out_bytes = 4.0 * spec.M * (n_dom // 2)
+    else:
+        out_dom = stack._raw(n_dom)
+
+        def dom_call(w):
+            K.gemm(a_dom, w, out_dom)
+        kernel_name = f"gemm_fp8_tc5_kernel {spec.M}x{n_dom}x{k_dom} ({name})"
+        out_bytes = 2.0 * spec.M * n_dom
     reps = max(args.steps, 10)
     for lw in weights[:3]:
-        K.gemm(a_dom, lw.w[name], out_dom)
+        dom_call(lw.w[name])
     torch.cuda.synchronize(dev)
     g0, g1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     g0.record(stream)
     for i in range(reps):
-        K.gemm(a_dom, weights[i % len(weights)].w[name], out_dom)
+        dom_call(weights[i % len(weights)].w[name])
     g1.record(stream)
     torch.cuda.synchronize(dev)
+    if gated_dom:
+        stack.amax.zero_()
     dom_ms = g0.elapsed_time(g1) / reps
     dom_flops = 2.0 * spec.M * n_dom * k_dom
-    dom_bytes = n_dom * k_dom + spec.M * k_dom + 2.0 * spec.M * n_dom
+    dom_bytes = n_dom * k_dom + spec.M * k_dom + out_bytes
     peaks = measured_peaks()
-    tensor_bound = spec.M > 400
-    if tensor_bound:
+    fp8_peak = measure_fp8_peak(dev) if (rank == 0 and spec.M > 400) else None
+    if spec.M > 400:
         peak = 2.0 * peaks["bf16_tflops"]   # dense FP8 runs at twice the bf16 rate on the same tensor pipe
         achieved = dom_flops / (dom_ms * 1e-3) / 1e12
         roofline = {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak,
-                    "traffic": None, "kernel": f"gemm_fp8_tc5_kernel {spec.M}x{n_dom}x{k_dom} ({name})",
-                    "peak_source": f"2 x bf16_tflops of MEASURED_PEAKS.json ({peaks['source']})",
+                    "traffic": None, "kernel": kernel_name,
+                    "peak_source": f"2 x bf16_tflops of MEASURED_PEAKS.json ({peaks['source']}; the file has no FP8 entry)",
                     "frac_of_nominal_4500": achieved / NOMINAL_FP8_TFLOPS, "ms_per_launch": dom_ms}
+        if fp8_peak is not None:
+            roofline["measured_fp8_peak"] = fp8_peak
+            roofline["frac_of_measured_fp8_burst"] = achieved / fp8_peak["burst_tflops"]
     else:
         peak = peaks["hbm_gbs"]
         achieved = dom_bytes / (dom_ms * 1e-3) / 1e9
         roofline = {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-                    "traffic": None, "kernel": f"gemm_fp8_tc5_kernel {spec.M}x{n_dom}x{k_dom} ({name})",
+                    "traffic": None, "kernel": kernel_name,
                     "peak_source": f"hbm_gbs of MEASURED_PEAKS.json ({peaks['source']})",
                     "frac_of_nominal_8000": achieved / NOMINAL_HBM_GBS, "ms_per_launch": dom_ms}
     if persistent:
-        # the step is one launch of the persistent kernel: its algorithmic bytes are every weight
-        # matrix once per layer and flow step plus the activations each operator reads and writes
-        lin = spec.linears()
-        act = sum(spec.M * k + 2.0 * spec.M * n for _, n, k in lin) + spec.M * spec.ffn * 5.0 + spec.M * spec.hidden * 11.0
-        step_bytes = (spec.weight_bytes() + act * spec.layers) * spec.steps
+        step_bytes = stack_bytes(spec)
         achieved = step_bytes / (ms / args.steps * 1e-3) / 1e9
         roofline = {"bound": "hbm", "achieved": achieved, "peak": peaks["hbm_gbs"], "unit": "GB/s",
                     "frac": achieved / peaks["hbm_gbs"], "traffic": None,
                     "kernel": f"stack_persistent_kernel ({spec.layers} layers x {spec.steps} steps, M={spec.M})",
                     "peak_source": f"hbm_gbs of MEASURED_PEAKS.json ({peaks['source']})",
                     "frac_of_nominal_8000": achieved / NOMINAL_HBM_GBS, "ms_per_launch": ms / args.steps,
-                    "note": "bound by the chain of grid-wide dependencies (4 per layer and step), not by bandwidth"}
+                    "note": "bound by the chain of grid-wide dependencies, not by bandwidth"}
+        if stack.timeout_record() != 0:
+            raise SystemExit(f"a wait inside the persistent kernel timed out: {stack.timeout_record():#x}")
     traffic_file = ROOT / "profiles" / "traffic.json"
     if traffic_file.exists():
-        roofline["traffic"] = json.loads(traffic_file.read_text()).get(f"{spec.name}:{name}")
+        entry = json.loads(traffic_file.read_text()).get(f"{spec.name}:{name}:{'gated' if gated_dom else 'raw'}")
+        if entry is not None:
+            roofline["traffic"] = entry["bytes_per_launch"]
+            roofline["traffic_source"] = entry["source"]
 
     # ---- max over ranks -------------------------------------------------------------------------
     if dist is not None:
         t = torch.tensor([ms, ms_e2e], device=dev, dtype=torch.float64)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         ms, ms_e2e = float(t[0]), float(t[1])
+
+    # ---- the other configurations, short runs in the same process (rank 0 of a 1-GPU run) --------
+    configs = None
+    if world == 1 and not args.no_configs:
+        del stack, graph
+        torch.cuda.empty_cache()
+        configs = {}
+        short = {"c2": (10, 3), "c3": (10, 3), "c4": (5, 3), "c5": (3, 2)}
+        try:
+            configs["c1"] = time_single_linear(dev, ref_ops, 10, 3)
+            for cfg, (k, w) in short.items():
+                if cfg == args.workload:
+                    continue
+                configs[cfg] = time_config(SPECS[cfg], dev, ref_ops, k, w, persistent=cfg == "c3")
+        except Exception as exc:   # noqa: BLE001
+            configs["error"] = f"{type(exc).__name__}: {exc}"[:300]
+        check_no_timeout(dev)
+
+    # ---- sharded configurations at this N ----------------------------------------------------------
+    sharded = None
+    keep = []
+    if not args.no_sharded:
+        del weights
+        torch.cuda.empty_cache()
+        sharded = {"ranks": world, "scaling": "strong"}
+        for key, fn in (("c3_dp", sharded_c3_episodes), ("c4_tokens", sharded_c4_tokens), ("c4_tp", sharded_c4_tp)):
+            try:
+                r = fn(dev, dist, rank, world, 3, 2)
+                keep.append(r.pop("_keep", None))
+                sharded[key] = r
+            except Exception as exc:   # noqa: BLE001
+                sharded[key] = {"error": f"{type(exc).__name__}: {exc}"[:300]}
+        check_no_timeout(dev)
 
     # ---- CPU baseline (rank 0, N = 1): bounded sample of the same workload ----------------------
     cpu = None
@@ -469,12 +884,16 @@ def main():
         job_flops = total_flops_all_ranks if tokens else world * flops   # rows actually asked for, padding not counted
         value = job_flops * args.steps / (ms * 1e-3) / 1e12
         e2e_value = job_flops * args.steps / (ms_e2e * 1e-3) / 1e12
+        execution = ("persistent whole-stack kernel (one cooperative launch per step)" if persistent else
+                     "one launch per operator, CUDA graph; " +
+                     ("reference's three-launch structure per linear" if args.unfused else
+                      "gated activation in the gate_up GEMM's epilogue" + (", residual update in the GEMM epilogue" if args.fuse_residual else "")))
         line = {
             "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
             "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "strong" if tokens else "weak",
             "vs_baseline": None, "dtype": "e4m3 x e4m3 -> f32", "data": "synthetic",
             "config": {"workload": workload_name(spec) + (f", {args.episodes} episodes stacked along M (M={spec.M})" if args.episodes > 1 else ""),
-                       "execution": "persistent whole-stack kernel (one cooperative launch per step)" if persistent else "one launch per operator, CUDA graph",
+                       "execution": execution,
                        "parallelism": (f"tokens/{world}: rows of one stack split over the ranks ({spec.M} per rank), full "
                                        f"weights on every rank, no collective" if tokens
                                        else f"dp{world} (independent stacks, no collective)"),
@@ -485,11 +904,12 @@ def main():
                     "d2h_bytes_per_step": out_host.numel() * out_host.element_size(), "ms_per_step": ms_e2e / args.steps},
             "gpu_launches": launches_per_step * args.steps,
             "clocks": clock_summary,
-            "stack_ms": ms / args.steps,
+            "gpu_reference": gpu_reference,
+            "configs": configs,
+            "sharded": sharded,
         }
         print(json.dumps(line), flush=True)
-    if dist is not None:
-        dist.destroy_process_group()
+    leave(dev, dist)
 
 
 if __name__ == "__main__":

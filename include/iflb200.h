@@ -151,6 +151,26 @@ IFLB200_API int iflb200_wan_qkv(const void* raw, int raw_dtype, int64_t ld_raw, 
                     void* stream);
 
 /*
+ * Merge of split-KV attention partials and per-token e4m3 quantiser of the merged row (what feeds
+ * the O projection).  po [splits, batch, heads_kv, tokens*group, block_d] float32 (block_d =
+ * head_dim rounded up to a power of two), pm / pl [splits, batch, heads_kv, tokens*group] float32:
+ * unnormalised outputs, running maxima (base-2 exponent domain) and running sums of the splits;
+ * query row = token * group + head_in_group, group = heads_q / heads_kv.
+ *   out = (sum_sp 2^(pm_sp - m) * po_sp) / (sum_sp 2^(pm_sp - m) * pl_sp),  m = max_sp pm_sp
+ *   o[b, t, head, :] = o_dtype(out)                  (optional; strides in elements)
+ *   qs[t] = max(max_{head,d} |out|, 1e-8) / 448;  q[t, head*head_dim + d] = e4m3(out * (448 / amax))
+ * with the reference's instruction order (ex2.approx.ftz, fma chains in split order, div.full).
+ * The quantised row is indexed by token alone: batch must be 1 when q is given, as in the
+ * reference.  head_dim a multiple of 4, <= 512; heads_q*head_dim <= 8192.
+ * Replaces: instinctflash/kernels/attention.py:109-145 (_attn_combine) and its launch at
+ * :205-214.
+ */
+IFLB200_API int iflb200_attn_combine_quant(const float* po, const float* pm, const float* pl, int splits,
+                               int batch, int tokens, int heads_q, int heads_kv, int head_dim,
+                               void* o, int o_dtype, int64_t o_stride_b, int64_t o_stride_t,
+                               int64_t o_stride_h, void* q, int64_t ld_q, float* qs, void* stream);
+
+/*
  * Residual update + RMS/LayerNorm + affine + adaptive modulation + per-token quantiser,
  * one row per thread group (the MoE router tail of the reference kernel is not part of
  * this path).

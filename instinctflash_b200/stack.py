@@ -259,3 +259,47 @@ class LinearStack:
         with torch.cuda.graph(graph):
             self.forward()
         return graph
+
+
+class EpisodeBatch:
+    """``episodes`` independent inferences of one stack on one GPU: one ``LinearStack`` each (own
+    activations, residual stream and scales) over shared weights, captured as parallel branches
+    of ONE CUDA graph, so that the GPU always has several short dependent chains to pick kernels
+    from.  Every GEMM keeps the row count of a single episode.  Independent robot episodes are what
+    the skinny action-expert configuration shards over GPUs; this is the per-GPU part."""
+
+    def __init__(self, spec: StackSpec, weights, device, episodes: int, **stack_kw):
+        self.spec, self.dev = spec, torch.device(device)
+        self.stacks = [LinearStack(spec, weights, device, **stack_kw) for _ in range(episodes)]
+        self.streams = [torch.cuda.Stream(self.dev) for _ in range(episodes)]
+        self.launches_per_forward = 0
+
+    def load(self, x, attn):
+        xs = x if isinstance(x, (list, tuple)) else [x] * len(self.stacks)
+        for st, xi in zip(self.stacks, xs):
+            st.load(xi, attn)
+
+    def forward(self):
+        """Fork every episode onto its own stream, join on the current one."""
+        main = torch.cuda.current_stream(self.dev)
+        for st, side in zip(self.stacks, self.streams):
+            side.wait_stream(main)
+            with torch.cuda.stream(side):
+                st.forward()
+        for side in self.streams:
+            main.wait_stream(side)
+        self.launches_per_forward = sum(st.launches_per_forward for st in self.stacks)
+        return [st.res for st in self.stacks]
+
+    def capture(self):
+        warm = torch.cuda.Stream(self.dev)
+        warm.wait_stream(torch.cuda.current_stream(self.dev))
+        with torch.cuda.stream(warm):
+            for _ in range(2):
+                self.forward()
+        torch.cuda.current_stream(self.dev).wait_stream(warm)
+        torch.cuda.synchronize(self.dev)
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            self.forward()
+        return graph

@@ -36,7 +36,8 @@ def native_ops() -> SimpleNamespace:
         """fp32 accumulator of a @ w.w^T (no scales, no rounding): the partial sum of a K shard."""
         return _fp8.fp8_linear(a, None, _fp8.Fp8Weight(w.w, None, None), out, use_weight_bias=False, exact=True)
 
-    return SimpleNamespace(gemm=_fp8.gemm, gemm_acc=gemm_acc, row_quant_sharded=_norm.row_quant_sharded,
+    return SimpleNamespace(gemm=_fp8.gemm, gemm_acc=gemm_acc, row_quant=_norm.row_quant,
+                           row_quant_sharded=_norm.row_quant_sharded,
                            dequant_rows=_norm.dequant_rows, residual_norm_quant=_norm.residual_norm_quant,
                            Fp8Weight=_fp8.Fp8Weight)
 
@@ -48,6 +49,13 @@ class Comm:
         self.group = group
         self.rank = dist.get_rank(group)
         self.size = dist.get_world_size(group)
+
+    @classmethod
+    def single(cls):
+        """A group of one without a process group (every collective is a copy or nothing)."""
+        self = cls.__new__(cls)
+        self.group, self.rank, self.size = None, 0, 1
+        return self
 
     def all_reduce_max(self, t):
         if self.size > 1:
@@ -148,12 +156,32 @@ class WanTPStack:
         self.ops.residual_norm_quant(self.res, layernorm=True, q=self.q8_loc, q_scale=self.s0_loc)
         self._gather_input()
 
+    collectives = ("column-split qkv/cross-q/ff1, row-split o/cross-o/ff2; per row-split linear one all-reduce-max "
+                   "of the [M] row maxima, one fp32 reduce-scatter of the [M, D] partial and all-gathers of the "
+                   "codes and row scales (NCCL)")
+
+    def comm_bytes_per_step(self) -> float:
+        """Bytes each rank sends per pass: per row-split linear 4*M*D*(p-1)/p (reduce-scatter) +
+        (M*D + 4*M)*(p-1)/p (all-gathers) + 4*M*(p-1)/p (all-reduce-max, ring)."""
+        sp, p = self.spec, self.comm.size
+        n_row = 3 if sp.cross else 2
+        M, D = sp.M, sp.hidden
+        return sp.layers * n_row * ((4.0 * M * D) + (M * D + 4.0 * M) + 4.0 * M) * (p - 1) / p
+
     def _row_linear(self, x_shard, W, prologue, res_kw):
         """Quantise the local column shard with global row scales, K-split GEMM, fp32
-        reduce-scatter, bf16 rounding, residual + norm + quantiser on the local rows, all-gather."""
+        reduce-scatter, bf16 rounding, residual + norm + quantiser on the local rows, all-gather.
+        A group of one has nothing to exchange: one quantiser pass, the raw bf16 accumulator straight
+        from the GEMM, the residual kernel writing the replicated buffers (the single-GPU sequence)."""
         o, sp = self.ops, self.spec
         Kl = x_shard.shape[1]
         qk = self._qk(Kl)
+        if self.comm.size == 1 and hasattr(o, "row_quant"):
+            o.row_quant(x_shard, qk, self.s1, **prologue)
+            o.gemm(qk, W, self.delta)
+            o.residual_norm_quant(self.res, delta=self.delta, delta_row=self.s1, delta_col=W.scale, bias=W.bias,
+                                  layernorm=True, q=self.q8, q_scale=self.s0, **res_kw)
+            return
         o.row_quant_sharded(x_shard, qk, self.s1, self.amax, 1, **prologue)
         self.comm.all_reduce_max(self.amax)
         o.row_quant_sharded(x_shard, qk, self.s1, self.amax, 2, **prologue)

@@ -15,6 +15,7 @@
  *   oracle_e4m3_encode          instinctflash/runtime/fp8_pack.py:12-23 (integer RNE cast)
  *   oracle_qkv_split            instinctflash/kernels/rope.py:22-83
  *   oracle_wan_qkv              instinctflash/kernels/wan.py:20-82
+ *   oracle_attn_combine_quant   instinctflash/kernels/attention.py:109-145
  *
  * Known, documented differences from the GPU reference: the GPU uses the approximate PTX
  * instructions div.full.f32, ex2.approx.f32 and rsqrt.approx.ftz.f32; here they are IEEE
@@ -458,5 +459,41 @@ ORACLE_API void oracle_wan_qkv(const float* raw, int64_t ld, int rows, int token
       for (int d = 0; d < D; ++d) dst[d] = round_to(x[d], out_dtype);
     }
     free(x);
+  }
+}
+
+/* Merge of split-KV attention partials and the per-token quantiser of the merged row
+ * (instinctflash/kernels/attention.py:109-145).  po [splits, batch, hkv, n_rows, block_d],
+ * pm / pl [splits, batch, hkv, n_rows], n_rows = tokens * group, query row = t * group + h.
+ * out [batch, tokens, heads_q, head_dim] receives the merged values in fp32 (the caller rounds
+ * them to the output type); with q != NULL (batch 1) the token's full row is quantised with one
+ * scale.  exp2f stands for the GPU's ex2.approx.ftz and '/' for div.full. */
+ORACLE_API void oracle_attn_combine_quant(const float* po, const float* pm, const float* pl, int splits, int batch,
+                                          int tokens, int heads_q, int heads_kv, int head_dim, int block_d,
+                                          float* out, uint8_t* q, int64_t ld_q, float* qs) {
+  const int group = heads_q / heads_kv;
+  const int64_t n_rows = (int64_t)tokens * group;
+  for (int b = 0; b < batch; ++b) {
+    for (int t = 0; t < tokens; ++t) {
+      float* orow = out + ((int64_t)b * tokens + t) * heads_q * head_dim;
+      for (int head = 0; head < heads_q; ++head) {
+        const int kvh = head / group, h = head % group;
+        const int64_t row = (int64_t)t * group + h;
+        float m = -INFINITY;
+        for (int sp = 0; sp < splits; ++sp)
+          m = max_nn(m, pm[(((int64_t)sp * batch + b) * heads_kv + kvh) * n_rows + row]);
+        for (int d = 0; d < head_dim; ++d) {
+          float l = 0.0f, acc = 0.0f;
+          for (int sp = 0; sp < splits; ++sp) {
+            const int64_t base = (((int64_t)sp * batch + b) * heads_kv + kvh) * n_rows + row;
+            const float w = exp2f(pm[base] - m);
+            l = fmaf(w, pl[base], l);
+            acc = fmaf(w, po[base * block_d + d], acc);
+          }
+          orow[head * head_dim + d] = acc / l;
+        }
+      }
+      if (q) quant_tail(orow, heads_q * head_dim, q + (int64_t)t * ld_q, qs + t);
+    }
   }
 }

@@ -254,3 +254,20 @@ def dequantise_and_matmul(q, s_x, wq, s_w, bias=None, out_dtype=torch.bfloat16):
     if bias is not None:
         y = y + bias.to(torch.float32)
     return y.to(out_dtype)
+
+
+def attn_combine_quant(po, pm, pl, *, splits, batch, tokens, heads_q, heads_kv, head_dim, out_dtype=torch.float16,
+                       quant=True):
+    """Merge of split-KV attention partials + per-token quantiser of the merged row
+    (instinctflash/kernels/attention.py:109-145).  Returns (out [B, Tq, Hq, D] in ``out_dtype``,
+    codes [Tq, Hq*D] or None, scales [Tq] or None)."""
+    block_d = 1 << max(0, (int(head_dim) - 1).bit_length())
+    a_po, a_pm, a_pl = _f32(po), _f32(pm), _f32(pl)
+    out = np.zeros((batch, tokens, heads_q, head_dim), dtype=np.float32)
+    width = heads_q * head_dim
+    q = np.zeros((tokens, width), dtype=np.uint8) if quant else None
+    qs = np.zeros(tokens, dtype=np.float32) if quant else None
+    _lib().oracle_attn_combine_quant(_p(a_po), _p(a_pm), _p(a_pl), int(splits), int(batch), int(tokens), int(heads_q),
+                                     int(heads_kv), int(head_dim), block_d, _p(out), _p(q), ctypes.c_int64(width), _p(qs))
+    o = torch.from_numpy(out).to(out_dtype)
+    return o, (_as_e4m3(q) if quant else None), (torch.from_numpy(qs) if quant else None)

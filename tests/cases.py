@@ -216,6 +216,29 @@ def wan_qkv_cases():
             slots=torch.randperm(S, generator=g)[:T].to(torch.int32) if use_slots else None, pool_rows=S)
 
 
+def attn_combine_cases():
+    """Split-KV attention partials as the reference's attention kernel leaves them: unnormalised
+    output vectors, running maxima (base-2 exponent domain) and running sums per split.  Geometries
+    of the engines' call sites: pi05 / VLA grouped-query heads (8 q heads on 1 kv head, width 256),
+    LingBot-VLA (width 128, 2 kv heads), Wan (24 heads of 128, no grouping), SigLIP-like width 72."""
+    table = [  # name, tokens, hq, hkv, head_dim, splits, out dtype, write_o
+        ("pi05_expert", 50, 8, 1, 256, 4, torch.float16, True),
+        ("vla4", 51, 4, 2, 128, 3, torch.float16, False),
+        ("wan", 33, 24, 24, 128, 2, torch.bfloat16, True),
+        ("width72", 9, 16, 16, 72, 2, torch.float16, True),
+        ("one_split", 5, 8, 2, 64, 1, torch.float32, True),
+    ]
+    for j, (name, T, HQ, HKV, HD, SP, odt, write_o) in enumerate(table):
+        g = gen(950 + j)
+        rows = T * (HQ // HKV)
+        width = 1 << max(0, (HD - 1).bit_length())
+        pm = torch.randn(SP, 1, HKV, rows, generator=g) * 4.0
+        pl = torch.rand(SP, 1, HKV, rows, generator=g) * 30.0 + 1.0
+        po = torch.randn(SP, 1, HKV, rows, width, generator=g) * pl[..., None] * 0.3
+        yield name, dict(po=po.contiguous(), pm=pm.contiguous(), pl=pl.contiguous(), tokens=T, heads_q=HQ, heads_kv=HKV,
+                         head_dim=HD, splits=SP, out_dtype=odt, write_o=write_o)
+
+
 def pack_weight_cpu(wf: torch.Tensor):
     """Per-channel pack with CPU arithmetic (true division), the form every arm is fed."""
     amax = wf.abs().amax(dim=1).clamp_min(1e-12)

@@ -258,3 +258,29 @@ def test_a_wait_that_nothing_satisfies_runs_out_and_leaves_the_context_usable():
     torch.cuda.synchronize()
     assert ps.timeout_record() == 0
     assert torch.equal(ps.res, want)
+
+
+def test_episode_batch_branches_equal_separate_runs():
+    """Independent episodes in flight as parallel branches of one CUDA graph: every episode's
+    residual stream equals the one a lone stack computes from the same input."""
+    from instinctflash_b200.stack import EpisodeBatch
+    spec = StackSpec("expert", "gemma", 3, 50, 1024, 4096, 1536, steps=2, seed=4)
+    weights = make_weights(spec, DEV)
+    xs = []
+    for e in range(4):
+        x, attn = make_inputs(StackSpec(**{**spec.__dict__, "seed": 40 + e}), DEV)
+        xs.append(x)
+    want = []
+    for x in xs:
+        st = LinearStack(spec, weights, DEV)
+        st.load(x, attn)
+        want.append(st.forward().clone())
+    batch = EpisodeBatch(spec, weights, DEV, 4)
+    batch.load(xs, attn)
+    g = batch.capture()
+    batch.load(xs, attn)
+    g.replay()
+    torch.cuda.synchronize()
+    for st, w in zip(batch.stacks, want):
+        assert torch.equal(st.res, w)
+    assert batch.launches_per_forward == 4 * batch.stacks[0].launches_per_forward

@@ -293,3 +293,23 @@ def test_wan_qkv_oracle_closed_form():
     assert (vp[:, slots.long()] - x[:, 2 * D:].view(B, T, D)).abs().max() < 1e-4
     untouched = [s for s in range(10) if s not in slots.tolist()]
     assert kp[:, untouched].abs().max() == 0
+
+
+@pytest.mark.parametrize("name", [n for n, _ in cases.attn_combine_cases()])
+def test_attn_combine_oracle_against_the_plain_formula(name):
+    """The restated merge of split-KV partials (instinctflash/kernels/attention.py:109-145) against
+    softmax-merge algebra written with torch: out = sum_sp 2^(pm-m) po / sum_sp 2^(pm-m) pl."""
+    from oracle import oracle as O
+    c = dict(cases.attn_combine_cases())[name]
+    T, HQ, HKV, HD, SP = c["tokens"], c["heads_q"], c["heads_kv"], c["head_dim"], c["splits"]
+    o, q, s = O.attn_combine_quant(c["po"], c["pm"], c["pl"], splits=SP, batch=1, tokens=T, heads_q=HQ, heads_kv=HKV,
+                                   head_dim=HD, out_dtype=torch.float32)
+    G = HQ // HKV
+    pm, pl, po = c["pm"][:, 0], c["pl"][:, 0], c["po"][:, 0, :, :, :HD]
+    m = pm.amax(0)
+    w = torch.exp2(pm - m)
+    out = ((w[..., None] * po).sum(0) / (w * pl).sum(0)[..., None]).view(HKV, T, G, HD).permute(1, 0, 2, 3).reshape(T, HQ, HD)
+    assert (o[0] - out).abs().max().item() <= 4e-7 * out.abs().max().item() + 1e-7
+    full = o[0].reshape(T, -1)
+    assert torch.equal(s, full.abs().amax(1).clamp_min(1e-8) / 448.0)
+    assert ((q.float() * s[:, None] - full).abs().amax(1) <= full.abs().amax(1) * 2.0 ** -4 * 1.0001).all()

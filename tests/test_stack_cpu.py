@@ -57,6 +57,21 @@ def test_weight_sharding_keeps_full_matrix_scales():
         tp.shard_columns(w, 0, 3)
 
 
+def test_tensor_parallel_driver_with_one_rank_is_the_single_gpu_sequence():
+    """A group of one exchanges nothing: no fp32 partial, no extra rounding pass -- the same bits as
+    the plain stack driver (run on the CPU oracle operators, no process group)."""
+    spec = StackSpec("tiny_wan", "wan", layers=2, M=32, hidden=64, ffn=128, qkv=192, o_in=64, cross=True, seed=7)
+    weights = make_weights(spec, "cpu", cpu_seeded=True)
+    x, attn = make_inputs(spec, "cpu")
+    single = LinearStack(spec, weights, "cpu", ops=oracle_ops.ops())
+    single.load(x, attn)
+    want = single.forward().clone()
+    one = tp.WanTPStack(spec, weights, "cpu", tp.Comm.single(), ops=oracle_ops.ops())
+    one.load(x, attn)
+    assert torch.equal(one.forward(), want)
+    assert one.comm_bytes_per_step() == 0.0
+
+
 def test_tensor_parallel_driver_two_gloo_ranks_match_single_process():
     env = dict(os.environ, IFLB200_TP_BACKEND="gloo", MASTER_ADDR="127.0.0.1", MASTER_PORT="29533",
                OMP_NUM_THREADS="2")
