@@ -431,7 +431,7 @@ def max_over_ranks(ms, dist, dev):
     return float(t[0])
 
 
-def sharded_c3_episodes(dev, dist, rank, world, steps, warmup):
+def sharded_c3_episodes(dev, dist, rank, world, steps, warmup, max_branches=EPISODE_BRANCHES):
     """64 independent action-expert episodes (M = 50 each, 18 layers x 10 flow steps), 64 / p per
     GPU, no collective.  On each GPU up to 8 episodes are in flight as parallel branches of one CUDA
     graph (every GEMM still has M = 50 rows; branches that reach the same layer together find its
@@ -439,7 +439,7 @@ def sharded_c3_episodes(dev, dist, rank, world, steps, warmup):
     from instinctflash_b200.stack import SPECS, EpisodeBatch, make_inputs, make_weights
     spec = SPECS["c3"]
     mine = EPISODES // world + (1 if rank < EPISODES % world else 0)
-    branches = min(EPISODE_BRANCHES, max(1, mine))
+    branches = min(max_branches, max(1, mine))
     rounds = -(-mine // branches)
     weights = make_weights(spec, dev)
     x, attn = make_inputs(spec, dev)
@@ -603,6 +603,8 @@ def main():
     ap.add_argument("--no-gpu-reference", action="store_true", help="do not time the reference's GPU kernels")
     ap.add_argument("--unfused", action="store_true", help="the reference's three-launch structure per linear")
     ap.add_argument("--fuse-residual", action="store_true", help="residual update in the GEMM epilogue as well")
+    ap.add_argument("--gemm-mode", type=int, default=0, help="iflb200_gemm_set_mode value for the whole run (experiments)")
+    ap.add_argument("--branches", type=int, default=EPISODE_BRANCHES, help="c3 episodes in flight per GPU")
     ap.add_argument("--episodes", type=int, default=1,
                     help="c3 only: independent episodes stacked along M on each GPU (rows are independent: "
                          "per-token scales and per-row norms, so this is arithmetically the same as separate runs)")
@@ -639,6 +641,8 @@ def main():
         raise SystemExit("bench.py needs a CUDA device: the FP8 linear path has no CPU fallback")
     from instinctflash_b200 import _lib
     _lib.lib()  # fail loudly when the CUDA library is missing
+    if args.gemm_mode and _lib.lib().iflb200_gemm_set_mode(args.gemm_mode) != 0:
+        raise SystemExit(f"--gemm-mode {args.gemm_mode} is not a valid mode")
     torch.cuda.set_device(local_rank)
     dev = torch.device("cuda", local_rank)
     dist = None
@@ -680,7 +684,7 @@ def main():
 
         stack = _Persistent(spec, weights, dev)
     else:
-        stack = LinearStack(spec, weights, dev, fused=not args.unfused, fuse_residual=args.fuse_residual)
+        stack = LinearStack(spec, weights, dev, fused=False if args.unfused else "auto", fuse_residual=args.fuse_residual)
     x_dev, attn = make_inputs(spec, dev)
     x_host = x_dev.cpu().pin_memory()
     out_host = torch.empty(spec.M, spec.hidden, dtype=stack.res.dtype).pin_memory()
@@ -853,7 +857,8 @@ def main():
         del weights
         torch.cuda.empty_cache()
         sharded = {"ranks": world, "scaling": "strong"}
-        for key, fn in (("c3_dp", sharded_c3_episodes), ("c4_tokens", sharded_c4_tokens), ("c4_tp", sharded_c4_tp)):
+        c3 = lambda *a: sharded_c3_episodes(*a, max_branches=args.branches)   # noqa: E731
+        for key, fn in (("c3_dp", c3), ("c4_tokens", sharded_c4_tokens), ("c4_tp", sharded_c4_tp)):
             try:
                 r = fn(dev, dist, rank, world, 3, 2)
                 keep.append(r.pop("_keep", None))

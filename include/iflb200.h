@@ -205,7 +205,10 @@ IFLB200_API int iflb200_gemm_fp8_raw(const void* a, int64_t ld_a, const void* w,
  *   y[m,n] = out_dtype(fma(r*row_scale[m], col_scale[n], bias[n])),
  *   r = fp32(bf16_rn(acc)) in IFLB200_ROUND_ENGINE, r = acc in IFLB200_ROUND_EXACT.
  * row_scale_stride / col_scale_stride are 1 for per-token / per-channel vectors and 0
- * for a single per-tensor scale (the per-tensor recipe of torch_fp8_linear.py).
+ * for a single per-tensor scale (the per-tensor recipe of torch_fp8_linear.py).  With
+ * IFLB200_ROUND_EXACT and BOTH scales per-tensor the epilogue follows torch._scaled_mm's order,
+ * y = out_dtype((acc * (row_scale * col_scale)) + bias) with every operation rounded on its own,
+ * which reproduces that call's output bit for bit on B200.
  * Replaces: instinctflash/kernels/fp8.py:50-53 followed by
  * instinctflash/kernels/norm.py:162-185; with stride-0 scales and EXACT rounding also the
  * torch._scaled_mm call of instinctflash/runtime/torch_fp8_linear.py:74-78.
@@ -387,7 +390,8 @@ IFLB200_API int iflb200_set_dependent_launch(int enable);
  * straight from registers instead of through shared memory and TMA; add 256 to take the
  * swapped form (tokens on the MMA's N side, 257..1024 tokens, two-byte raw or dequantised output;
  * not chosen by the heuristic) wherever it exists, 128 to forbid it, 512 to keep the swapped form
- * off CTA pairs.  Any other bit is refused.  Every mode writes the same output bits.  For
+ * off CTA pairs; add 1024 / 2048 to run the gated form's 256-wide tiles with sixteen / eight
+ * epilogue warps.  Any other bit is refused.  Every mode writes the same output bits.  For
  * experiments and tests.  No reference counterpart. */
 IFLB200_API int iflb200_gemm_set_mode(int mode);
 

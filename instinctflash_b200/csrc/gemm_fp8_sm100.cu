@@ -43,7 +43,9 @@ struct GemmParams {
   int M, N, K;
   int num_m, num_n, num_k, num_tiles, group_m;
   int epilogue;
-  int exact;  // 1: scales applied to the fp32 accumulator without the bf16 rounding
+  int exact;  // 1: scales applied to the fp32 accumulator without the bf16 rounding; 2: the same with two
+              // per-tensor scales in the order torch._scaled_mm applies them: (acc * (s_a * s_b)) + bias,
+              // every operation rounded on its own (measured on B200: bit-identical to cuBLASLt's epilogue)
   const float* row;
   int row_stride;
   const float* col;
@@ -81,14 +83,14 @@ __device__ __forceinline__ float ld_dsmem_f32(uint32_t addr) {
   return v;
 }
 
-template <int BN, int STAGES>
+template <int BN, int STAGES, int EW = kEpilogueWarps>
 struct SmemLayout {
   static constexpr int kABytes = BM * BK;
   static constexpr int kBBytes = BN * BK;
   static constexpr int kStageBytes = kABytes + kBBytes;
-  // epilogue staging: per epilogue warp two 32-row x 128-byte buffers (TMA-store sources)
+  // epilogue staging: one 32-row x 128-byte buffer per epilogue warp (TMA-store source)
   static constexpr int kStagingOffset = STAGES * kStageBytes;
-  static constexpr int kBarOffset = kStagingOffset + kStagingBytes;
+  static constexpr int kBarOffset = kStagingOffset + EW * 32 * 128;
   // full[STAGES], empty[STAGES], tmem_full[2], tmem_empty[2], then the TMEM base word and the
   // abort flag.
   static constexpr int kNumBars = 2 * STAGES + 4;
@@ -195,6 +197,15 @@ __device__ __forceinline__ void epilogue_chunk(const GemmParams& p, const uint32
 #pragma unroll
     for (int i = 0; i < 8; ++i) {
       const int n = n0 + 8 * j + i;
+      if (p.exact == 2) {
+        float t = __fmul_rn(v[8 * j + i], __fmul_rn(rs, __ldg(p.col)));
+        if (p.bias)
+          t = __fadd_rn(t, (p.bias_dtype == IFLB200_F32)
+                               ? __ldg(reinterpret_cast<const float*>(p.bias) + n)
+                               : __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(p.bias)[n]));
+        y[i] = t;
+        continue;
+      }
       Chain ch(v[8 * j + i]);
       if (p.row) ch.mul(rs);
       if (p.col) ch.mul(__ldg(p.col + (int64_t)n * p.col_stride));
@@ -271,11 +282,20 @@ __device__ __forceinline__ void epilogue_values(const GemmParams& p, const uint3
         bs[i] = (p.bias_dtype == IFLB200_F32) ? __ldg(reinterpret_cast<const float*>(p.bias) + n)
                                                : __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(p.bias)[n]);
     }
-    Chain8 ch(v);
-    if (p.row) ch.mul(rs);
-    if (p.col) ch.mul(cs);
-    if (p.bias) ch.add(bs);
-    ch.done(v);
+    if (p.exact == 2) {
+      const float alpha = __fmul_rn(rs, __ldg(p.col));
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        v[i] = __fmul_rn(v[i], alpha);
+        if (p.bias) v[i] = __fadd_rn(v[i], bs[i]);
+      }
+    } else {
+      Chain8 ch(v);
+      if (p.row) ch.mul(rs);
+      if (p.col) ch.mul(cs);
+      if (p.bias) ch.add(bs);
+      ch.done(v);
+    }
 #pragma unroll
     for (int i = 0; i < 8; ++i) y[8 * j + i] = v[i];
   }
@@ -373,24 +393,30 @@ __device__ __forceinline__ void epilogue_tma_store(const GemmParams& p, const CU
 // p.amax with an integer atomicMax on the float's bits: a maximum does not depend on the order
 // it is taken in, so the row scale and the codes a later pass derives from it are exactly those of
 // the one-kernel-per-row form.
-template <int BN>
+// This is the one epilogue whose arithmetic (about 25 instructions per element) is comparable to
+// the main loop's duration, so the warps of a TMEM lane quadrant (PARTS of them) split the hidden
+// units of the tile, and the column scales come in as 128-bit loads with the ragged-width masking
+// confined to the last chunk of a row.
+template <int BN, int PARTS>
 __device__ __forceinline__ void epilogue_gated(const GemmParams& p, const CUtensorMap* tm_out, uint32_t t_row,
                                                uint32_t staging, uint8_t* staging_ptr, int row0, int n_base,
-                                               int half, int m, bool row_ok, float rs, int lane) {
+                                               int part, int m, bool row_ok, float rs, int lane) {
   constexpr int HW = BN / 2;        // hidden units per tile
-  constexpr int kChunks = HW / 32;  // 4, 2 or 1 chunks of 32 columns
-  constexpr int kPerHalf = kChunks >= 2 ? kChunks / 2 : 1;
-  if (kChunks == 1 && half == 1) return;  // a 32-wide tile is one store: the first warp of the quadrant takes it
-  const int c_begin = (kChunks >= 2 ? half * kPerHalf : 0) * 32;
+  constexpr int kChunks = HW / 32;  // chunks of 32 columns in a tile: 4, 2 or 1
+  constexpr int kPerPart = kChunks >= PARTS ? kChunks / PARTS : 1;
+  if (part * kPerPart >= kChunks) return;  // fewer chunks than warps in the quadrant: the first ones take them
+  const int c_begin = part * kPerPart * 32;
   uint8_t* mine = staging_ptr + lane * 128;
+  const bool vec_scales = p.col && ((reinterpret_cast<uintptr_t>(p.col) & 15) == 0);
   float row_max = 0.0f;
   bool any = false;
 #pragma unroll 1
-  for (int k = 0; k < kPerHalf; ++k) {
+  for (int k = 0; k < kPerPart; ++k) {
     const int c = c_begin + 32 * k;
     const int n0 = n_base + c;
     if (n0 >= p.N) break;  // uniform
     any = true;
+    const bool whole = n0 + 32 <= p.N;  // uniform: all 32 columns of the chunk are hidden units
     uint32_t rg[32], ru[32];
     tmem_ld_32x32b_x32(t_row + c, rg);
     tmem_ld_32x32b_x32(t_row + HW + c, ru);
@@ -399,7 +425,7 @@ __device__ __forceinline__ void epilogue_gated(const GemmParams& p, const CUtens
     __syncwarp();
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
-      float g[8], u[8], cg[8], cu[8];
+      float g[8], u[8];
 #pragma unroll
       for (int i = 0; i < 4; ++i) {  // the bf16 rounding point of the accumulators
         const uint32_t wg = pack_bf16x2(__uint_as_float(rg[8 * j + 2 * i]), __uint_as_float(rg[8 * j + 2 * i + 1]));
@@ -418,12 +444,22 @@ __device__ __forceinline__ void epilogue_gated(const GemmParams& p, const CUtens
         }
       }
       if (p.col) {
+        float cg[8], cu[8];
+        const int n = n0 + 8 * j;
+        if (whole && vec_scales) {  // hidden widths are multiples of 16 and n of 8: both vectors are 16-byte aligned
+          const float4 a0 = __ldg(reinterpret_cast<const float4*>(p.col + n));
+          const float4 a1 = __ldg(reinterpret_cast<const float4*>(p.col + n + 4));
+          const float4 b0 = __ldg(reinterpret_cast<const float4*>(p.col + p.N + n));
+          const float4 b1 = __ldg(reinterpret_cast<const float4*>(p.col + p.N + n + 4));
+          cg[0] = a0.x; cg[1] = a0.y; cg[2] = a0.z; cg[3] = a0.w; cg[4] = a1.x; cg[5] = a1.y; cg[6] = a1.z; cg[7] = a1.w;
+          cu[0] = b0.x; cu[1] = b0.y; cu[2] = b0.z; cu[3] = b0.w; cu[4] = b1.x; cu[5] = b1.y; cu[6] = b1.z; cu[7] = b1.w;
+        } else {
 #pragma unroll
-        for (int i = 0; i < 8; ++i) {
-          const int n = n0 + 8 * j + i;
-          const bool in = n < p.N;
-          cg[i] = in ? __ldg(p.col + n) : 0.0f;
-          cu[i] = in ? __ldg(p.col + p.N + n) : 0.0f;
+          for (int i = 0; i < 8; ++i) {
+            const bool in = n + i < p.N;
+            cg[i] = in ? __ldg(p.col + n + i) : 0.0f;
+            cu[i] = in ? __ldg(p.col + p.N + n + i) : 0.0f;
+          }
         }
 #pragma unroll
         for (int i = 0; i < 8; i += 2) {
@@ -442,11 +478,13 @@ __device__ __forceinline__ void epilogue_gated(const GemmParams& p, const CUtens
 #pragma unroll
         for (int i = 0; i < 8; ++i) h[i] = __fmul_rn(u[i], silu_ref(g[i]));
       }
+      if (!whole) {  // columns past the hidden width: not stored, not in the maximum
 #pragma unroll
-      for (int i = 0; i < 8; ++i) {
-        if (n0 + 8 * j + i >= p.N) h[i] = 0.0f;  // columns past the hidden width: not stored, not in the maximum
-        row_max = max_f32(row_max, fabsf(h[i]));
+        for (int i = 0; i < 8; ++i)
+          if (n0 + 8 * j + i >= p.N) h[i] = 0.0f;
       }
+#pragma unroll
+      for (int i = 0; i < 8; ++i) row_max = max_f32(row_max, fabsf(h[i]));
       *reinterpret_cast<float4*>(mine + (((2 * j) ^ (lane & 7)) * 16)) = make_float4(h[0], h[1], h[2], h[3]);
       *reinterpret_cast<float4*>(mine + (((2 * j + 1) ^ (lane & 7)) * 16)) = make_float4(h[4], h[5], h[6], h[7]);
     }
@@ -502,11 +540,16 @@ __device__ __forceinline__ void epilogue_swapped(const GemmParams& p, const CUte
       float v = __uint_as_float(r[j]);
       if (p.epilogue == EPI_DEQUANT) {
         if (!p.exact) v = __bfloat162float(__float2bfloat16_rn(v));
-        Chain ch(v);
-        if (p.row) ch.mul(__ldg(p.row + (int64_t)min(tok + j, p.N - 1) * p.row_stride));
-        if (p.col) ch.mul(cs);
-        if (p.bias) ch.add(bs);
-        v = ch.done();
+        if (p.exact == 2) {
+          v = __fmul_rn(v, __fmul_rn(__ldg(p.row), cs));
+          if (p.bias) v = __fadd_rn(v, bs);
+        } else {
+          Chain ch(v);
+          if (p.row) ch.mul(__ldg(p.row + (int64_t)min(tok + j, p.N - 1) * p.row_stride));
+          if (p.col) ch.mul(cs);
+          if (p.bias) ch.add(bs);
+          v = ch.done();
+        }
       }
       const uint16_t h = p.out_dtype == IFLB200_F16 ? (uint16_t)f32_to_f16_bits(v) : (uint16_t)f32_to_bf16_bits(v);
       *reinterpret_cast<uint16_t*>(blk + j * 64) = h;
@@ -529,11 +572,13 @@ __device__ __forceinline__ void epilogue_swapped(const GemmParams& p, const CUte
 // launch in instruction fetch (0.2 ms per pass of the M = 50 stack).
 // GATED: the gated form (see epilogue_gated): a tile pairs BN/2 gate columns with the BN/2 up
 // columns of the same hidden units; p.N counts hidden units.
-template <int BN, int STAGES, int SPLIT, bool SWAP = false, bool GATED = false>
-__global__ void __launch_bounds__(kGemmThreads, 1)
+// EW: epilogue warps (8, or 16 for the gated form: EW / 4 per TMEM lane quadrant).
+template <int BN, int STAGES, int SPLIT, bool SWAP = false, bool GATED = false, int EW = kEpilogueWarps>
+__global__ void __launch_bounds__(64 + 32 * EW, 1)
 gemm_fp8_tc5_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_w,
                     const __grid_constant__ CUtensorMap tm_out, const GemmParams p) {
-  using L = SmemLayout<BN, STAGES>;
+  using L = SmemLayout<BN, STAGES, EW>;
+  static_assert(EW == kEpilogueWarps || GATED, "only the gated epilogue is written for more than eight warps");
   // two accumulators, each at a power-of-two column offset; BN in {64, 128, 192, 224, 256}
   constexpr uint32_t kAccStride = BN <= 64 ? 64 : (BN <= 128 ? 128 : 256);
   constexpr uint32_t kTmemCols = 2 * kAccStride;
@@ -572,7 +617,7 @@ gemm_fp8_tc5_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
     }
     for (int a = 0; a < 2; ++a) {
       mbar_init(tfull_bar(a), 1);
-      mbar_init(tempty_bar(a), kEpilogueWarps);  // one arrival per epilogue warp
+      mbar_init(tempty_bar(a), EW);  // one arrival per epilogue warp
     }
     tmem_slot[1] = 0;
     fence_barrier_init();
@@ -741,8 +786,8 @@ gemm_fp8_tc5_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
       }
       const float rs = (row_ok && p.row) ? __ldg(p.row + (int64_t)m * p.row_stride) : 1.0f;
       if constexpr (GATED) {
-        epilogue_gated<BN>(p, &tm_out, t_row, staging, staging_ptr, m_blk * BM + quad * 32, n_blk * (BN / 2), half, m,
-                           row_ok, rs, lane);
+        epilogue_gated<BN, EW / 4>(p, &tm_out, t_row, staging, staging_ptr, m_blk * BM + quad * 32, n_blk * (BN / 2),
+                                   half, m, row_ok, rs, lane);
         tc_fence_before();
         __syncwarp();
         if (lane == 0) mbar_arrive(tempty_bar(acc));
@@ -1236,24 +1281,27 @@ static int g_cfg_split_k = 0;  // 0: cost model, 1: never split K, 2/4/8: forced
 static int g_cfg_direct_store = 0;  // 1: epilogue stores straight from registers (experiments)
 static int g_cfg_pair_swap = 1;  // the swapped form on CTA pairs where the shape allows
 static int g_cfg_swap = 0;  // 0: cost model, 1: never, 2: always where the form exists
+static int g_cfg_gated_warps = 0;  // gated form, 256-wide tiles: 0 heuristic, 8 or 16 epilogue warps
 static int g_cfg_mode = 0;  // 0 auto, 1 single-CTA tiles only, 2 CTA pairs with one accumulator, 3 CTA pairs with two
 
-template <int BN, int STAGES, int SPLIT, bool SWAP = false, bool GATED = false>
+template <int BN, int STAGES, int SPLIT, bool SWAP = false, bool GATED = false, int EW = kEpilogueWarps>
 static int launch_gemm_form(const CUtensorMap& ta, const CUtensorMap& tw, const CUtensorMap& to, const GemmParams& p,
                             int grid, cudaStream_t s) {
-  using L = SmemLayout<BN, STAGES>;
+  using L = SmemLayout<BN, STAGES, EW>;
+  static_assert(L::kDynamic <= 227 * 1024, "stage ring + staging exceed the shared memory of an SM");
   static bool attr_set[64] = {};
   int dev = 0;
   cudaGetDevice(&dev);
   if (dev < 0 || dev >= 64) return IFLB200_ERR_DEVICE;
   if (!attr_set[dev]) {
-    cudaError_t e = cudaFuncSetAttribute(gemm_fp8_tc5_kernel<BN, STAGES, SPLIT, SWAP, GATED>,
+    cudaError_t e = cudaFuncSetAttribute(gemm_fp8_tc5_kernel<BN, STAGES, SPLIT, SWAP, GATED, EW>,
                                          cudaFuncAttributeMaxDynamicSharedMemorySize, L::kDynamic);
     if (e != cudaSuccess) return (int)e;
     attr_set[dev] = true;
   }
-  const cudaError_t e = launch_dep(gemm_fp8_tc5_kernel<BN, STAGES, SPLIT, SWAP, GATED>, dim3(grid), dim3(kGemmThreads),
-                                   L::kDynamic, s, p.split_k, dependent_launch_for(SWAP ? p.N : p.M), ta, tw, to, p);
+  const cudaError_t e = launch_dep(gemm_fp8_tc5_kernel<BN, STAGES, SPLIT, SWAP, GATED, EW>, dim3(grid),
+                                   dim3(64 + 32 * EW), L::kDynamic, s, p.split_k,
+                                   dependent_launch_for(SWAP ? p.N : p.M), ta, tw, to, p);
   return e != cudaSuccess ? (int)e : (int)cudaGetLastError();
 }
 
@@ -1524,7 +1572,10 @@ static int run_gemm_gated(const void* a, int64_t ld_a, const void* w, int64_t ld
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
   g_last_launch[0] = 1 + 8; g_last_launch[1] = bn; g_last_launch[2] = 1; g_last_launch[3] = 0;
   switch (bn) {
-    case 256: return launch_gemm_form<256, 4, 0, false, true>(ta, tw, to, p, grid, s);
+    case 256:
+      // sixteen epilogue warps with a three-stage ring (64 KB of staging), or eight with four stages
+      if (g_cfg_gated_warps == 16) return launch_gemm_form<256, 3, 0, false, true, 16>(ta, tw, to, p, grid, s);
+      return launch_gemm_form<256, 4, 0, false, true>(ta, tw, to, p, grid, s);
     case 128: return launch_gemm_form<128, 6, 0, false, true>(ta, tw, to, p, grid, s);
     default: return launch_gemm_form<64, 8, 0, false, true>(ta, tw, to, p, grid, s);
   }
@@ -1559,7 +1610,10 @@ extern "C" int iflb200_set_dependent_launch(int enable) {
 extern "C" int iflb200_gemm_set_mode(int mode) {
   // bit 4 (value 16) selects the direct-store epilogue; the low bits the kernel family
   const int family = mode & 15;
-  if (mode < 0 || family > 3 || (mode & ~(15 | 16 | 128 | 256 | 512)) || (mode & 384) == 384) return IFLB200_ERR_ARG;
+  if (mode < 0 || family > 3 || (mode & ~(15 | 16 | 128 | 256 | 512 | 1024 | 2048)) || (mode & 384) == 384 ||
+      (mode & 3072) == 3072)
+    return IFLB200_ERR_ARG;
+  g_cfg_gated_warps = (mode & 1024) ? 16 : ((mode & 2048) ? 8 : 0);
   g_cfg_swap = (mode & 128) ? 1 : ((mode & 256) ? 2 : 0);  // 128: never the swapped form, 256: wherever it exists
   g_cfg_pair_swap = (mode & 512) ? 0 : 1;                  // 512: the swapped form on single CTAs only
   g_cfg_mode = family;
@@ -1622,6 +1676,7 @@ extern "C" int iflb200_fp8_linear(const void* a, int64_t ld_a, const void* w, in
   p.M = M; p.N = N; p.K = K;
   p.epilogue = EPI_DEQUANT;
   p.exact = rounding == IFLB200_ROUND_EXACT;
+  if (p.exact && row_scale && col_scale && row_scale_stride == 0 && col_scale_stride == 0) p.exact = 2;
   p.row = row_scale; p.row_stride = row_scale_stride;
   p.col = col_scale; p.col_stride = col_scale_stride;
   p.bias = bias; p.bias_dtype = bias_dtype;

@@ -17,6 +17,34 @@ from ..kernels.fp8 import Fp8Weight, fp8_linear
 from .fp8_pack import dynamic_pack_bf16_e4m3
 
 
+def _target_device(weight: torch.Tensor, device, storage_device, capabilities) -> torch.device:
+    """Where the packed projection will live; raises for everything the recipe does not cover
+    (same conditions and messages as the reference's constructor, minus its CPU-source branch)."""
+    target = weight.device if device is None else torch.device(device)
+    on_cuda = target.type == "cuda"
+    if not on_cuda or torch.cuda.get_device_capability(target) not in capabilities:
+        raise ValueError(f"FP8 projections require CUDA capability in {capabilities}")
+    if storage_device is not None and torch.device(storage_device) != target:
+        raise ValueError("Packed storage lives on the target device for this recipe")
+    if weight.device != target:
+        # "cuda" without an index and the current CUDA device are the same place
+        resolved = torch.device("cuda", torch.cuda.current_device() if target.index is None else target.index)
+        if weight.device != resolved:
+            raise ValueError("Pack FP8 weights on their target device")
+    return target
+
+
+def pack_per_tensor(weight: torch.Tensor):
+    """(codes [N, K] e4m3, scale [1] float32) with one scale for the whole matrix:
+    scale = max(|w|, 1e-12) / 448 -- on CUDA torch divides a tensor by a Python scalar by
+    multiplying with fp32(1/448), the arithmetic the reference pins
+    (instinctflash/runtime/torch_fp8_linear.py:39-48, tests/test_sm89_fp8.py:48-56)."""
+    wide = weight.float()
+    scale = wide.abs().amax().clamp_min(1e-12).reshape(1) / 448.0
+    codes = (wide / scale).clamp(-448, 448).to(torch.float8_e4m3fn).contiguous()
+    return codes, scale
+
+
 class SM100FP8Linear(nn.Module):
     recipe = "e4m3fn_weights_dynamic_per_tensor_activations_fp32_accum_bf16_output"
     supported_capabilities = ((10, 0), (10, 3))
@@ -25,31 +53,24 @@ class SM100FP8Linear(nn.Module):
         super().__init__()
         if type(linear) is not nn.Linear:
             raise TypeError("FP8 packing requires a plain nn.Linear with no custom forward")
-        w = linear.weight.detach()
-        target = torch.device(device) if device is not None else w.device
-        if target.type != "cuda" or torch.cuda.get_device_capability(target) not in self.supported_capabilities:
-            raise ValueError(f"FP8 projections require CUDA capability in {self.supported_capabilities}")
-        if storage_device is not None and torch.device(storage_device) != target:
-            raise ValueError("Packed storage lives on the target device for this recipe")
-        if w.device != target:
-            index = target.index if target.index is not None else torch.cuda.current_device()
-            if w.device != torch.device("cuda", index):
-                raise ValueError("Pack FP8 weights on their target device")
-        if w.dtype != torch.bfloat16:
-            raise ValueError("This FP8 recipe requires native BF16 projection weights")
-        if linear.in_features % 16 or linear.out_features % 16:
-            raise ValueError("FP8 projection input/output dimensions must be multiples of 16")
-        if not torch.isfinite(w).all():
-            raise ValueError("Cannot quantize non-finite projection weights")
+        weight = linear.weight.detach()
+        _target_device(weight, device, storage_device, self.supported_capabilities)
+        bias = None if linear.bias is None else linear.bias.detach().clone()
+        problems = (
+            (weight.dtype != torch.bfloat16, "This FP8 recipe requires native BF16 projection weights"),
+            (linear.in_features % 16 or linear.out_features % 16,
+             "FP8 projection input/output dimensions must be multiples of 16"),
+            (weight.dtype == torch.bfloat16 and not torch.isfinite(weight).all(), "Cannot quantize non-finite projection weights"),
+            (bias is not None and (bias.dtype != torch.bfloat16 or not torch.isfinite(bias).all()),
+             "This FP8 recipe requires finite BF16 bias"),
+        )
+        for bad, message in problems:
+            if bad:
+                raise ValueError(message)
         self.in_features, self.out_features = linear.in_features, linear.out_features
-        wf = w.float()
-        top = wf.abs().amax().clamp_min(1e-12).reshape(1)
-        scale = top / 448.0  # on CUDA: multiplication by fp32(1/448), the arithmetic the reference pins
-        self.register_buffer("weight_fp8", (wf / scale).clamp(-448, 448).to(torch.float8_e4m3fn).contiguous())
+        codes, scale = pack_per_tensor(weight)
+        self.register_buffer("weight_fp8", codes)
         self.register_buffer("weight_scale", scale)
-        bias = linear.bias.detach().clone() if linear.bias is not None else None
-        if bias is not None and (bias.dtype != torch.bfloat16 or not torch.isfinite(bias).all()):
-            raise ValueError("This FP8 recipe requires finite BF16 bias")
         self.register_buffer("bias", bias)
 
     @torch.no_grad()
@@ -62,7 +83,7 @@ class SM100FP8Linear(nn.Module):
             raise RuntimeError("FP8 packed buffers were cast after construction; pack after model.to()")
         shape = (*x.shape[:-1], self.out_features)
         if x.numel() == 0:
-            return x.new_empty(shape)
+            return x.new_empty(shape)     # a model may call a tower whose token partition is empty
         rows = x.reshape(-1, self.in_features).contiguous()
         packed, scale = dynamic_pack_bf16_e4m3(rows)
         out = torch.empty(rows.shape[0], self.out_features, device=x.device, dtype=torch.bfloat16)

@@ -9,8 +9,8 @@ buffer is allocated once (the engines' arena pattern, instinctflash/engines/comm
 The same driver runs any set of operators with the reference's signatures (``ops`` argument),
 so the reference's own kernels can be timed through it.
 
-With this package's operators the driver uses the fused forms by default (``fused=True``): the
-gated activation is evaluated in the gate_up GEMM's epilogue (``fp8_linear_gated`` +
+With this package's operators the driver uses the fused forms by default (``fused="auto"``: for
+more than 128 rows): the gated activation is evaluated in the gate_up GEMM's epilogue (``fp8_linear_gated`` +
 ``row_quant_from_amax`` instead of ``gemm`` + ``gated_act_quant``), bit-identical to the unfused
 sequence; ``fused=False`` keeps the reference's three-launch structure per linear.
 """
@@ -153,12 +153,15 @@ def make_inputs(spec: StackSpec, device, *, cpu_seeded: bool = True):
 class LinearStack:
     """Static buffers + the per-layer call sequence.  ``ops`` supplies the operators."""
 
-    def __init__(self, spec: StackSpec, weights, device, ops=None, *, fused: bool = True,
-                 fuse_residual: bool = False):
+    def __init__(self, spec: StackSpec, weights, device, ops=None, *, fused="auto", fuse_residual: bool = False):
         self.spec, self.weights, self.dev = spec, weights, torch.device(device)
         self.ops = ops or native_ops()
-        # fused forms exist only in this package's operator set
-        self.fused = fused and hasattr(self.ops, "fp8_linear_gated")
+        # fused forms exist only in this package's operator set; "auto" takes the gated epilogue where the
+        # GEMM is long enough to hide it (measured: with M = 50 the two-kernel gated form is slower
+        # than gemm + gated_act_quant, whose single row kernel costs one short launch)
+        if fused == "auto":
+            fused = spec.M > 128
+        self.fused = bool(fused) and hasattr(self.ops, "fp8_linear_gated")
         self.fuse_residual = fuse_residual and hasattr(self.ops, "fp8_linear_residual")
         M, D, F = spec.M, spec.hidden, spec.ffn
         dev, bf16, f32 = self.dev, torch.bfloat16, torch.float32

@@ -423,7 +423,7 @@ def test_gemm_cta_pair_kernel_is_bit_identical(ops, M, N, K, mode):
         fp8.fp8_linear(a, s, W, ye, exact=True)
         out.append(ye)
         for rdt in (torch.float32, torch.bfloat16):
-            r = res0.to(rdt)
+            r = res0.clone().to(rdt)      # a private copy: the update is in place
             fp8.fp8_linear_residual(a, s, W, r, bias=W.bias, gate=gate, gate_index=gidx)
             families.append(last_launch(ops)[0])
             out.append(r)
@@ -545,8 +545,8 @@ def test_gated_epilogue_equals_gemm_plus_gated_act_quant(ops, unsplit, M, F, K, 
     act_mod.gated_act_quant(raw, q_ref, s_ref, row=s, col=W.scale, act=act)
     amax = torch.zeros(M, device=DEV)
     try:
-        for tile_n in (0, 64, 128, 256):
-            assert lib.iflb200_gemm_set_config(tile_n, 0, 0) == 0
+        for tile_n, mode in ((0, 0), (64, 0), (128, 0), (256, 2048), (256, 1024)):   # 8 / 16 epilogue warps on the wide tile
+            assert lib.iflb200_gemm_set_config(tile_n, 0, 0) == 0 and lib.iflb200_gemm_set_mode(mode) == 0
             for _ in range(2):
                 h = torch.full((M, F + 32), float("nan"), device=DEV)[:, :F]      # a strided view
                 fp8.fp8_linear_gated(a, s, W, h, amax, act=act)
@@ -561,6 +561,7 @@ def test_gated_epilogue_equals_gemm_plus_gated_act_quant(ops, unsplit, M, F, K, 
                 assert bool((amax == 0).all()), "the row maxima were not left at zero"
     finally:
         lib.iflb200_gemm_set_config(0, 0, 0)
+        lib.iflb200_gemm_set_mode(0)
     no_timeout(ops)
 
 
@@ -795,6 +796,10 @@ def test_dynamic_pack_nan_and_graph_replay(ops):
 
 
 def test_sm100_fp8_linear_matches_reference_module_output(ops, unsplit, B200):
+    """The per-tensor projection against (a) the recording of the reference's ThorFP8Linear on a
+    B200 (weights, scale and the WHOLE output by hash) and (b) the recipe its qualification script
+    demands bit-equality with (scripts/qualify_sm89_fp8.py:83-143): torch._scaled_mm on the packed
+    operands, rank-3 and strided inputs, the empty token partition, changed-input graph replay."""
     c = cases.thor_linear_case()
     g = B200["thor_fp8_linear/40x1024x2048"]
     lin = torch.nn.Linear(2048, 1024, bias=True, dtype=torch.bfloat16)
@@ -803,12 +808,46 @@ def test_sm100_fp8_linear_matches_reference_module_output(ops, unsplit, B200):
         lin.bias.copy_(c["bias"])
     mod = ops["lin"].SM100FP8Linear(lin.to(DEV))
     assert sha(mod.weight_fp8) == g["weight_sha"] and i32(mod.weight_scale).tolist() == g["weight_scale_bits"]
-    y = mod(dev(c["x"]))
+    x = dev(c["x"])
+    y = mod(x)
     assert y.dtype == torch.bfloat16 and y.shape == (40, 1024)
-    ref_head = torch.tensor(g["y_head"], dtype=torch.int16).view(torch.bfloat16).float()
-    assert (y[0, :64].cpu().float() - ref_head).abs().max().item() <= ref_head.abs().max().item() * 2.0 ** -7
-    assert mod(dev(c["x"]).reshape(2, 20, 2048)).shape == (2, 20, 1024)
-    assert mod(torch.empty(0, 2048, device=DEV, dtype=torch.bfloat16)).shape == (0, 1024)
+    assert y[0, :64].cpu().view(torch.int16).tolist() == g["y_head"]
+    assert sha(y) == g["y_sha"], "projection output differs from the reference module's on a B200"
+    packed, scale = ops["pack"].dynamic_pack_bf16_e4m3(x)
+    expected = torch._scaled_mm(packed, mod.weight_fp8.t(), scale_a=scale, scale_b=mod.weight_scale, bias=mod.bias,
+                                out_dtype=torch.bfloat16, use_fast_accum=False)
+    assert torch.equal(y, expected), "projection recipe"
+    assert torch.equal(mod(x.reshape(2, 20, 2048)).reshape(40, 1024), y), "rank-three input"
+    assert torch.equal(mod(x.t().contiguous().t()), y), "strided input"
+    assert mod(x[:0]).shape == (0, 1024) and mod(x[:0]).dtype == torch.bfloat16
     with pytest.raises(ValueError):
-        mod(dev(c["x"]).float())
+        mod(x.float())
+    # no bias, and a larger ragged shape
+    for rows, width, outputs, bias in ((300, 5120, 5120, False), (64, 512, 13824, True), (7, 2048, 1024, True)):
+        gen_ = torch.Generator().manual_seed(rows + outputs)
+        lin2 = torch.nn.Linear(width, outputs, bias=bias, dtype=torch.bfloat16)
+        with torch.no_grad():
+            lin2.weight.copy_((torch.randn(outputs, width, generator=gen_) * 0.02).to(torch.bfloat16))
+            if bias:
+                lin2.bias.copy_((torch.randn(outputs, generator=gen_) * 0.1).to(torch.bfloat16))
+        m2 = ops["lin"].SM100FP8Linear(lin2.to(DEV))
+        x2 = dev(cases.activations(rows, width, 990 + rows))
+        p2, s2 = ops["pack"].dynamic_pack_bf16_e4m3(x2)
+        want = torch._scaled_mm(p2, m2.weight_fp8.t(), scale_a=s2, scale_b=m2.weight_scale, bias=m2.bias,
+                                out_dtype=torch.bfloat16, use_fast_accum=False)
+        assert torch.equal(m2(x2), want), (rows, width, outputs, bias)
+    # changed-input graph replay
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        for _ in range(3):
+            mod(x)
+    torch.cuda.current_stream().wait_stream(side)
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph, stream=side):
+        captured = mod(x)
+    for magnitude in (0, 1e-4, 20):
+        x.copy_(torch.randn_like(x) * magnitude)
+        graph.replay()
+        assert torch.equal(captured, mod(x)), "changed-input graph replay"
     no_timeout(ops)
