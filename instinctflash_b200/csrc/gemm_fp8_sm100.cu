@@ -58,6 +58,7 @@ struct GemmParams {
   int out_dtype;
   int64_t ld_out;
   int split_k;     // > 1: the CTAs of a cluster share one tile, each a K range; partials are summed over DSMEM
+  int a_bytes;     // bytes one activation box delivers per K step: 128 x (rows of the box)
   int act;         // gated form: IFLB200_ACT_*
   uint32_t* amax;  // gated form: per-row maximum of |h| as float bits, raised with atomicMax
   int tma_store;  // 1: the epilogue stages 128-byte row pieces in shared memory and TMA-stores them
@@ -642,8 +643,7 @@ gemm_fp8_tc5_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
     const int kb_end = kb1 < kb0 + kPrefetchSteps ? kb1 : kb0 + kPrefetchSteps;
     for (int kb = kb0; kb < kb_end; ++kb) {
       if constexpr (GATED) {
-        tma_prefetch_l2_2d(&tm_w, kb * BK, n_blk * (BN / 2));
-        tma_prefetch_l2_2d(&tm_w, kb * BK, p.N + n_blk * (BN / 2));
+        tma_prefetch_l2_3d(&tm_w, kb * BK, n_blk * (BN / 2), 0);
       } else {
         tma_prefetch_l2_2d(&tm_w, kb * BK, n_blk * BN);
       }
@@ -672,13 +672,14 @@ gemm_fp8_tc5_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
                                                   (1u << 24) | (1u << 16) | (it & 0xFFFF)));
         if (!ok) break;
         if (lane == 0) {
-          mbar_arrive_expect_tx(full_bar(stage), L::kStageBytes);
+          mbar_arrive_expect_tx(full_bar(stage), (uint32_t)p.a_bytes + L::kBBytes);
           const uint32_t sa = base + stage * L::kStageBytes;
           tma_load_2d(sa, &tm_a, full_bar(stage), kb * BK, m_blk * BM);
           if constexpr (GATED) {
-            // gate rows, then the up rows of the same hidden units: one B operand of BN rows
-            tma_load_2d(sa + L::kABytes, &tm_w, full_bar(stage), kb * BK, n_blk * (BN / 2));
-            tma_load_2d(sa + L::kABytes + (BN / 2) * BK, &tm_w, full_bar(stage), kb * BK, p.N + n_blk * (BN / 2));
+            // gate rows, then the up rows of the same hidden units: one B operand of BN rows, one
+            // load (the weight is mapped as [2][F][K]; a second TMA instruction per stage cost the
+            // main loop about a tenth of its rate)
+            tma_load_3d(sa + L::kABytes, &tm_w, full_bar(stage), kb * BK, n_blk * (BN / 2), 0);
           } else {
             tma_load_2d(sa + L::kABytes, &tm_w, full_bar(stage), kb * BK, n_blk * BN);
           }
@@ -1218,6 +1219,21 @@ static int make_tensor_map(CUtensorMap* tm, const void* ptr, int rows, int K, in
   return r == CUDA_SUCCESS ? IFLB200_OK : IFLB200_ERR_DRIVER;
 }
 
+// The [gate | up] weight [2F, K] seen as [2][F][K]: box = 128 bytes x box_rows x 2, so that one
+// load brings the gate rows and the up rows of the same hidden units, gate rows first.
+static int make_gated_weight_map(CUtensorMap* tm, const void* ptr, int F, int K, int64_t ld, int box_rows) {
+  EncodeTiledFn enc = get_encode_fn();
+  if (!enc) return IFLB200_ERR_DRIVER;
+  const cuuint64_t dims[3] = {(cuuint64_t)K, (cuuint64_t)F, 2};
+  const cuuint64_t strides[2] = {(cuuint64_t)ld, (cuuint64_t)ld * (cuuint64_t)F};
+  const cuuint32_t box[3] = {(cuuint32_t)BK, (cuuint32_t)box_rows, 2};
+  const cuuint32_t estr[3] = {1, 1, 1};
+  const CUresult r = enc(tm, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, const_cast<void*>(ptr), dims, strides, box, estr,
+                         CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                         CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? IFLB200_OK : IFLB200_ERR_DRIVER;
+}
+
 // [M, N] output matrix of 2- or 4-byte elements; box = 128 bytes x 32 rows, 128-byte swizzle.
 static int make_out_map(CUtensorMap* tm, void* ptr, int M, int N, int64_t ld, int esize) {
   EncodeTiledFn enc = get_encode_fn();
@@ -1246,6 +1262,14 @@ static int make_out_map_swapped(CUtensorMap* tm, void* ptr, int tokens, int N, i
                          CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   return r == CUDA_SUCCESS ? IFLB200_OK : IFLB200_ERR_DRIVER;
 }
+
+// Rows of the activation box.  The MMA always reads 128 rows of the stage, but with at most 120
+// activation rows the box only brings the rows that exist (rounded up to the 8-row swizzle atom):
+// the TMA unit issues one request per 128-byte box row whether the row exists or not, and for a
+// skinny GEMM those requests -- not the weight bytes -- are what the main loop waits for.  The rows
+// of the stage that are never written hold stale shared memory; they only reach accumulator rows
+// >= M, which no epilogue stores.
+static int activation_box_rows(int M) { return M <= 120 ? (M + 7) / 8 * 8 : BM; }
 
 struct DeviceInfo {
   int sm_count = 0;
@@ -1460,6 +1484,7 @@ static int run_gemm(const void* a, int64_t ld_a, const void* w, int64_t ld_w, Ge
       q.num_tiles = q.num_m * q.num_n;
       q.group_m = g_cfg_group_m > 0 ? g_cfg_group_m : 8;
       q.split_k = 1;
+      q.a_bytes = BM * BK;
       const int grid = q.num_tiles < dev->sm_count ? q.num_tiles : dev->sm_count;
       CUtensorMap tw_rows, ta_tokens, to_swapped;
       st = make_tensor_map(&tw_rows, w, p.N, p.K, ld_w, BM);
@@ -1498,7 +1523,9 @@ static int run_gemm(const void* a, int64_t ld_a, const void* w, int64_t ld_w, Ge
   const int grid = split > 1 ? p.num_tiles * split : (p.num_tiles < dev->sm_count ? p.num_tiles : dev->sm_count);
 
   CUtensorMap ta, tw;
-  st = make_tensor_map(&ta, a, p.M, p.K, ld_a, BM);
+  const int a_rows = activation_box_rows(p.M);
+  p.a_bytes = a_rows * BK;
+  st = make_tensor_map(&ta, a, p.M, p.K, ld_a, a_rows);
   if (st != IFLB200_OK) return st;
   st = make_tensor_map(&tw, w, p.N, p.K, ld_w, bn);
   if (st != IFLB200_OK) return st;
@@ -1563,9 +1590,11 @@ static int run_gemm_gated(const void* a, int64_t ld_a, const void* w, int64_t ld
   p.group_m = g_cfg_group_m > 0 ? g_cfg_group_m : 8;
   const int grid = p.num_tiles < dev->sm_count ? p.num_tiles : dev->sm_count;
   CUtensorMap ta, tw, to;
-  st = make_tensor_map(&ta, a, M, K, ld_a, BM);
+  const int a_rows = activation_box_rows(M);
+  p.a_bytes = a_rows * BK;
+  st = make_tensor_map(&ta, a, M, K, ld_a, a_rows);
   if (st != IFLB200_OK) return st;
-  st = make_tensor_map(&tw, w, 2 * F, K, ld_w, bn / 2);
+  st = make_gated_weight_map(&tw, w, F, K, ld_w, bn / 2);
   if (st != IFLB200_OK) return st;
   st = make_out_map(&to, h, M, F, ld_h, 4);
   if (st != IFLB200_OK) return st;

@@ -92,6 +92,15 @@ __device__ __forceinline__ void tma_load_2d(uint32_t smem_dst, const void* tenso
       ::"r"(smem_dst), "l"(tensor_map), "r"(bar), "r"(x), "r"(y)
       : "memory");
 }
+// The same for a 3-D tiled tensor (x innermost).
+__device__ __forceinline__ void tma_load_3d(uint32_t smem_dst, const void* tensor_map, uint32_t bar,
+                                            int32_t x, int32_t y, int32_t z) {
+  asm volatile(
+      "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes "
+      "[%0], [%1, {%3, %4, %5}], [%2];"
+      ::"r"(smem_dst), "l"(tensor_map), "r"(bar), "r"(x), "r"(y), "r"(z)
+      : "memory");
+}
 __device__ __forceinline__ void tma_load_2d_hint(uint32_t smem_dst, const void* tensor_map,
                                                  uint32_t bar, int32_t x, int32_t y,
                                                  uint64_t policy) {
@@ -125,6 +134,12 @@ __device__ __forceinline__ void prefetch_tensormap(const void* tensor_map) {
 // safe to issue ahead of a grid dependency.
 __device__ __forceinline__ void tma_prefetch_l2_2d(const void* tensor_map, int x, int y) {
   asm volatile("cp.async.bulk.prefetch.tensor.2d.L2.global.tile [%0, {%1, %2}];" ::"l"(tensor_map), "r"(x), "r"(y)
+               : "memory");
+}
+
+__device__ __forceinline__ void tma_prefetch_l2_3d(const void* tensor_map, int x, int y, int z) {
+  asm volatile("cp.async.bulk.prefetch.tensor.3d.L2.global.tile [%0, {%1, %2, %3}];" ::"l"(tensor_map), "r"(x), "r"(y),
+               "r"(z)
                : "memory");
 }
 

@@ -78,6 +78,19 @@ __device__ __forceinline__ void named_barrier_sync(int id, int threads) {
   asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(threads) : "memory");
 }
 
+#ifdef IFLB200_TRACE
+// Experiments only (never part of the product library): wall-clock stamps of CTA 0's roles for
+// operators [kTraceFirst, kTraceFirst + 16), event slots per operator below.
+constexpr int kTraceFirst = 40;
+__device__ unsigned long long g_stack_trace[16][16];
+__device__ __forceinline__ void trace(int oi, int ev) {
+  if (blockIdx.x == 0 && oi >= kTraceFirst && oi < kTraceFirst + 16) g_stack_trace[oi - kTraceFirst][ev] = globaltimer_ns();
+}
+#define TRACE(oi, ev) trace(oi, ev)
+#else
+#define TRACE(oi, ev)
+#endif
+
 struct Shared {
   uint32_t full[STAGES][2];
   uint32_t empty[STAGES][2];
@@ -384,11 +397,13 @@ stack_persistent_kernel(const Op* __restrict__ ops, int num_ops, const CUtensorM
           if (!ok) break;
           if (!waited) {
             // first activation load of an operator that consumes another operator's output
+            if (lane == 0) TRACE(oi, 0);
             ok = __all_sync(0xFFFFFFFFu, wait_grid(bars + op.wait_bar, (uint32_t)ncta, abort_flag, status,
                                                    (6u << 24) | (5u << 16) | (uint32_t)oi));
             if (!ok) break;
             fence_proxy_async_all();  // activations were written with plain stores by other CTAs
             waited = true;
+            if (lane == 0) TRACE(oi, 1);
           }
           if (lane == 0) {
             const uint32_t sa = base + stage * kStageBytes;
@@ -398,6 +413,8 @@ stack_persistent_kernel(const Op* __restrict__ ops, int num_ops, const CUtensorM
             } else {
               mbar_arrive_expect_tx(full_bar(stage), kABytes);
               tma_load_2d(sa, maps + op.tm_a, full_bar(stage), kb * BK, 0);
+              if (kb == kb0) TRACE(oi, 2);
+              if (kb == kb1 - 1) TRACE(oi, 3);
             }
           }
           __syncwarp();
@@ -438,6 +455,7 @@ stack_persistent_kernel(const Op* __restrict__ ops, int num_ops, const CUtensorM
           if (!ok) break;
           tc_fence_after();
           if (lane == 0) {
+            if (kb == kb0) TRACE(oi, 4);
             const uint32_t sa = base + stage * kStageBytes;
             const uint64_t da = make_kmajor_sw128_desc(sa);
             const uint64_t db = make_kmajor_sw128_desc(sa + kABytes);
@@ -453,7 +471,10 @@ stack_persistent_kernel(const Op* __restrict__ ops, int num_ops, const CUtensorM
           }
         }
         if (!ok) break;
-        if (lane == 0) mma_commit(tfull_bar(acc));
+        if (lane == 0) {
+          mma_commit(tfull_bar(acc));
+          TRACE(oi, 5);
+        }
         __syncwarp();
       }
     }
@@ -478,6 +499,7 @@ stack_persistent_kernel(const Op* __restrict__ ops, int num_ops, const CUtensorM
                                                  (3u << 24) | (4u << 16) | (uint32_t)oi));
           if (!ok) break;
           tc_fence_after();
+          if (t == 0) TRACE(oi, 6);
           const uint32_t t_row = tmem_base + ((uint32_t)(quad * 32) << 16) + acc * BN;
 #pragma unroll 1
           for (int c = 0; c < BN / 32; ++c) {
@@ -514,11 +536,13 @@ stack_persistent_kernel(const Op* __restrict__ ops, int num_ops, const CUtensorM
           tc_fence_before();
           __syncwarp();
           if (lane == 0) mbar_arrive(tempty_bar(acc));
+          if (t == 0) TRACE(oi, 7);
         }
         if (!ok) break;
       } else {
         if (op.wait_bar >= 0) {
           bool got = true;
+          if (t == 0) TRACE(oi, 8);
           if (t == 0) got = wait_grid(bars + op.wait_bar, (uint32_t)ncta, abort_flag, status, (3u << 24) | (5u << 16) | (uint32_t)oi);
           named_barrier_sync(1, 128);
           (void)got;
@@ -528,18 +552,22 @@ stack_persistent_kernel(const Op* __restrict__ ops, int num_ops, const CUtensorM
           }
           (void)ld_acquire(bars + op.wait_bar);  // every thread acquires what the counter publishes
           __threadfence();
+          if (t == 0) TRACE(oi, 9);
         }
         for (int m = cta; m < M; m += ncta) {
           if (op.type == OP_GATED) row_gated(op, m, t, sh->red[0]);
           else row_resnorm(op, M, m, t, sh->red);
           named_barrier_sync(1, 128);  // reduction scratch reused by the next row
         }
+        if (t == 0) TRACE(oi, 10);
       }
       if (op.arrive_bar >= 0) {
         fence_proxy_async_all();  // outputs may be read by other CTAs' TMA loads
         __threadfence();
+        if (t == 0) TRACE(oi, 11);
         named_barrier_sync(1, 128);
         if (t == 0) atomicAdd(bars + op.arrive_bar, 1u);
+        if (t == 0) TRACE(oi, 12);
       }
     }
   }
@@ -595,6 +623,12 @@ extern "C" int iflb200_encode_operand_map(void* out128, const void* ptr, int row
   memcpy(out128, &tm, sizeof(tm));
   return IFLB200_OK;
 }
+
+#ifdef IFLB200_TRACE
+extern "C" __attribute__((visibility("default"))) int iflb200_exp_stack_trace(unsigned long long* out256) {
+  return (int)cudaMemcpyFromSymbol(out256, g_stack_trace, sizeof(unsigned long long) * 256);
+}
+#endif
 
 extern "C" int iflb200_stack_activation_box_rows(int M) { return M <= A_ROWS ? A_ROWS : A_ROWS_WIDE; }
 extern "C" int iflb200_stack_weight_box_rows(void) { return BN; }

@@ -517,7 +517,7 @@ def test_gemm_default_knobs_take_the_pair_kernel_for_large_m(ops, oracle, name, 
     exact = oracle.gemm_acc(a.cpu()[rows_idx].contiguous(), wq[cols_idx].contiguous()).to(torch.bfloat16)
     got = raw.cpu()[rows_idx][:, cols_idx]
     assert (got != exact).float().mean().item() < 2e-3
-    assert rel_frobenius(got.float(), exact.float()) < 1e-4
+    assert rel_frobenius(got.float(), exact.float()) < 5e-4      # fp32 accumulation over K = 13824 with x30 outlier channels
     no_timeout(ops)
 
 
