@@ -315,28 +315,36 @@ IFLB200_API int iflb200_pack_bf16_e4m3(const void* x, int64_t n, const float* sc
 #define IFLB200_STACK_GEMM 1    /* out[M,N] = a[M,K] x w[N,K]^T: raw bf16 (split_k = 1) or fp32 partials [split_k][M][N] */
 #define IFLB200_STACK_GATED 2   /* gated_act_quant of raw [M, 2N] -> codes [M,N] + row scales */
 #define IFLB200_STACK_RESNORM 3 /* res += acc*row*col; RMS norm; quantiser -> codes [M,N] + row scales */
+#define IFLB200_STACK_GEMM_GATED 4 /* a[M,K] x [gate | up][2N,K]^T with the gated activation in the epilogue:
+                                      h[M,N] fp32 out, row maxima of |h| raised in aux (atomicMax) */
+#define IFLB200_STACK_ENCODE 5  /* codes [M,N] + row scales from h [M,N] fp32 and the row maxima in aux;
+                                   split_k = parts a row is divided into (work items = M * split_k) */
 typedef struct {
   int32_t type;        /* IFLB200_STACK_* */
   int32_t wait_bar;    /* counter that must reach the grid size before activations are read; -1: none */
   int32_t arrive_bar;  /* counter this operator's CTAs bump when their outputs are visible; -1: none */
   int32_t tile_offset; /* GEMM: rotation of the work-item -> CTA assignment */
   int32_t N, K;        /* GEMM: output columns, reduction length; row operators: N = width */
-  int32_t split_k;     /* GEMM: K splits (each at least one 128-byte step); RESNORM: partials to sum (1: raw bf16 in) */
+  int32_t split_k;     /* GEMM: K splits (each at least one 128-byte step); GEMM_GATED: 1; RESNORM: partials to
+                          sum (1: raw bf16 in); ENCODE: parts per row */
   int32_t act;         /* GATED: IFLB200_ACT_* */
-  int32_t tm_a, tm_w;  /* GEMM: indices into tensor_maps (activation box, weight box) */
+  int32_t tm_a, tm_w;  /* GEMM: indices into tensor_maps (activation box, weight box; GEMM_GATED: a map written by
+                          iflb200_encode_gated_weight_map) */
   int32_t pad0, pad1;
-  void* out;           /* GEMM: raw bf16 / fp32 partials; row operators: e4m3 codes */
-  const void* in;      /* GATED: raw bf16 [M, 2N]; RESNORM: raw bf16 [M,N] or fp32 partials */
-  const float* row_scale; /* GATED: row scales of the GEMM input; RESNORM: delta_row */
-  const float* col_scale; /* GATED: [2N]; RESNORM: [N] */
+  void* out;           /* GEMM: raw bf16 / fp32 partials; GEMM_GATED: h fp32; row operators: e4m3 codes */
+  const void* in;      /* GATED: raw bf16 [M, 2N]; RESNORM: raw bf16 [M,N] or fp32 partials; ENCODE: h fp32 [M,N] */
+  const float* row_scale; /* GATED, GEMM_GATED: row scales of the GEMM input; RESNORM: delta_row */
+  const float* col_scale; /* GATED, GEMM_GATED: [2N]; RESNORM: [N] */
   float* out_scale;    /* row operators: row scales out [M] */
   float* res;          /* RESNORM: residual stream fp32 [M,N], in place */
   int64_t ld_out, ld_in;
   float eps;           /* RESNORM */
   int32_t pad2;
-  int64_t pad3;
+  float* aux;          /* GEMM_GATED, ENCODE: row maxima of |h| [M] (zero before the first GEMM_GATED);
+                          RESNORM: [M] words to leave at zero (the consumed maxima), or NULL */
 } iflb200_stack_op;
 IFLB200_API int iflb200_encode_operand_map(void* out128, const void* ptr, int rows, int K, int64_t ld, int box_rows);
+IFLB200_API int iflb200_encode_gated_weight_map(void* out128, const void* ptr, int F, int K, int64_t ld);
 IFLB200_API int iflb200_stack_activation_box_rows(int M);
 IFLB200_API int iflb200_stack_weight_box_rows(void);
 IFLB200_API int iflb200_stack_run(const void* ops, int num_ops, const void* tensor_maps, void* barriers,

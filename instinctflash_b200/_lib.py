@@ -49,6 +49,7 @@ SIGNATURES = {
     "iflb200_dynamic_pack_bf16_e4m3_noalloc": (_i, [_p, _l, _p, _p, _p]),
     "iflb200_pack_bf16_e4m3": (_i, [_p, _l, _p, _p, _p]),
     "iflb200_encode_operand_map": (_i, [_p, _p, _i, _i, _l, _i]),
+    "iflb200_encode_gated_weight_map": (_i, [_p, _p, _i, _i, _l]),
     "iflb200_stack_activation_box_rows": (_i, [_i]),
     "iflb200_stack_weight_box_rows": (_i, []),
     "iflb200_stack_run": (_i, [_p, _i, _p, _p, _i, _i, _p, _p]),

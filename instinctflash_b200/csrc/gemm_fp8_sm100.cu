@@ -89,9 +89,11 @@ struct SmemLayout {
   static constexpr int kABytes = BM * BK;
   static constexpr int kBBytes = BN * BK;
   static constexpr int kStageBytes = kABytes + kBBytes;
-  // epilogue staging: one 32-row x 128-byte buffer per epilogue warp (TMA-store source)
+  // epilogue staging: one 32-row buffer per epilogue warp (TMA-store source), 128 bytes per row
+  // with eight epilogue warps, 64 with sixteen
+  static constexpr int kWarpStaging = EW > 8 ? 2048 : 4096;
   static constexpr int kStagingOffset = STAGES * kStageBytes;
-  static constexpr int kBarOffset = kStagingOffset + EW * 32 * 128;
+  static constexpr int kBarOffset = kStagingOffset + EW * kWarpStaging;
   // full[STAGES], empty[STAGES], tmem_full[2], tmem_empty[2], then the TMEM base word and the
   // abort flag.
   static constexpr int kNumBars = 2 * STAGES + 4;
@@ -407,7 +409,10 @@ __device__ __forceinline__ void epilogue_gated(const GemmParams& p, const CUtens
   constexpr int kPerPart = kChunks >= PARTS ? kChunks / PARTS : 1;
   if (part * kPerPart >= kChunks) return;  // fewer chunks than warps in the quadrant: the first ones take them
   const int c_begin = part * kPerPart * 32;
-  uint8_t* mine = staging_ptr + lane * 128;
+  // Sixteen epilogue warps have 64 bytes of staging per row: a chunk leaves as two stores of 16
+  // columns each (64-byte swizzle: 16-byte piece index ^ ((row >> 1) & 3)).
+  constexpr bool kHalfRows = PARTS > 2;
+  uint8_t* mine = staging_ptr + lane * (kHalfRows ? 64 : 128);
   const bool vec_scales = p.col && ((reinterpret_cast<uintptr_t>(p.col) & 15) == 0);
   float row_max = 0.0f;
   bool any = false;
@@ -426,6 +431,16 @@ __device__ __forceinline__ void epilogue_gated(const GemmParams& p, const CUtens
     __syncwarp();
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
+      if (kHalfRows && j == 2) {  // first 16 columns staged: send them, then reuse the buffer
+        fence_proxy_async_smem();
+        __syncwarp();
+        if (lane == 0) {
+          tma_store_2d(tm_out, staging, n0, row0);
+          bulk_commit_group();
+          bulk_wait_group_read<0>();
+        }
+        __syncwarp();
+      }
       float g[8], u[8];
 #pragma unroll
       for (int i = 0; i < 4; ++i) {  // the bf16 rounding point of the accumulators
@@ -486,13 +501,19 @@ __device__ __forceinline__ void epilogue_gated(const GemmParams& p, const CUtens
       }
 #pragma unroll
       for (int i = 0; i < 8; ++i) row_max = max_f32(row_max, fabsf(h[i]));
-      *reinterpret_cast<float4*>(mine + (((2 * j) ^ (lane & 7)) * 16)) = make_float4(h[0], h[1], h[2], h[3]);
-      *reinterpret_cast<float4*>(mine + (((2 * j + 1) ^ (lane & 7)) * 16)) = make_float4(h[4], h[5], h[6], h[7]);
+      if (kHalfRows) {
+        const int sw = (lane >> 1) & 3;
+        *reinterpret_cast<float4*>(mine + (((2 * (j & 1)) ^ sw) * 16)) = make_float4(h[0], h[1], h[2], h[3]);
+        *reinterpret_cast<float4*>(mine + (((2 * (j & 1) + 1) ^ sw) * 16)) = make_float4(h[4], h[5], h[6], h[7]);
+      } else {
+        *reinterpret_cast<float4*>(mine + (((2 * j) ^ (lane & 7)) * 16)) = make_float4(h[0], h[1], h[2], h[3]);
+        *reinterpret_cast<float4*>(mine + (((2 * j + 1) ^ (lane & 7)) * 16)) = make_float4(h[4], h[5], h[6], h[7]);
+      }
     }
     fence_proxy_async_smem();  // generic-proxy writes visible to the TMA unit
     __syncwarp();
-    if (lane == 0) {
-      tma_store_2d(tm_out, staging, n0, row0);
+    if (lane == 0 && (!kHalfRows || n0 + 16 < p.N)) {  // a ragged row can end after the first 16 columns
+      tma_store_2d(tm_out, staging, kHalfRows ? n0 + 16 : n0, row0);
       bulk_commit_group();
     }
   }
@@ -759,8 +780,8 @@ gemm_fp8_tc5_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
       col_begin = half * 32;
       col_end = col_begin + 32;
     }
-    const uint32_t staging = base + L::kStagingOffset + (uint32_t)(warp - 2) * 4096u;
-    uint8_t* staging_ptr = smem + L::kStagingOffset + (warp - 2) * 4096;
+    const uint32_t staging = base + L::kStagingOffset + (uint32_t)(warp - 2) * (uint32_t)L::kWarpStaging;
+    uint8_t* staging_ptr = smem + L::kStagingOffset + (warp - 2) * L::kWarpStaging;
     bool ok = true;
     uint32_t it = 0;
     int swap_buf = 0;
@@ -1235,15 +1256,16 @@ static int make_gated_weight_map(CUtensorMap* tm, const void* ptr, int F, int K,
 }
 
 // [M, N] output matrix of 2- or 4-byte elements; box = 128 bytes x 32 rows, 128-byte swizzle.
-static int make_out_map(CUtensorMap* tm, void* ptr, int M, int N, int64_t ld, int esize) {
+static int make_out_map(CUtensorMap* tm, void* ptr, int M, int N, int64_t ld, int esize, int row_bytes = 128) {
   EncodeTiledFn enc = get_encode_fn();
   if (!enc) return IFLB200_ERR_DRIVER;
   const cuuint64_t dims[2] = {(cuuint64_t)N, (cuuint64_t)M};
   const cuuint64_t strides[1] = {(cuuint64_t)ld * esize};
-  const cuuint32_t box[2] = {(cuuint32_t)(128 / esize), 32u};
+  const cuuint32_t box[2] = {(cuuint32_t)(row_bytes / esize), 32u};
   const cuuint32_t estr[2] = {1, 1};
   const CUresult r = enc(tm, esize == 2 ? CU_TENSOR_MAP_DATA_TYPE_UINT16 : CU_TENSOR_MAP_DATA_TYPE_UINT32, 2, ptr,
-                         dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                         dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                         row_bytes == 64 ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_128B,
                          CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   return r == CUDA_SUCCESS ? IFLB200_OK : IFLB200_ERR_DRIVER;
 }
@@ -1596,14 +1618,15 @@ static int run_gemm_gated(const void* a, int64_t ld_a, const void* w, int64_t ld
   if (st != IFLB200_OK) return st;
   st = make_gated_weight_map(&tw, w, F, K, ld_w, bn / 2);
   if (st != IFLB200_OK) return st;
-  st = make_out_map(&to, h, M, F, ld_h, 4);
+  const bool sixteen = bn == 256 && g_cfg_gated_warps == 16;
+  st = make_out_map(&to, h, M, F, ld_h, 4, sixteen ? 64 : 128);
   if (st != IFLB200_OK) return st;
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
   g_last_launch[0] = 1 + 8; g_last_launch[1] = bn; g_last_launch[2] = 1; g_last_launch[3] = 0;
   switch (bn) {
     case 256:
-      // sixteen epilogue warps with a three-stage ring (64 KB of staging), or eight with four stages
-      if (g_cfg_gated_warps == 16) return launch_gemm_form<256, 3, 0, false, true, 16>(ta, tw, to, p, grid, s);
+      // sixteen epilogue warps (64 bytes of staging per row each), or eight
+      if (sixteen) return launch_gemm_form<256, 4, 0, false, true, 16>(ta, tw, to, p, grid, s);
       return launch_gemm_form<256, 4, 0, false, true>(ta, tw, to, p, grid, s);
     case 128: return launch_gemm_form<128, 6, 0, false, true>(ta, tw, to, p, grid, s);
     default: return launch_gemm_form<64, 8, 0, false, true>(ta, tw, to, p, grid, s);

@@ -45,7 +45,8 @@ constexpr uint64_t kWaitBudgetNs = 2000000000ull;
 // Time budget of every wait inside the kernel (read only on the slow path of a wait).
 __device__ uint64_t g_stack_wait_budget_ns = kWaitBudgetNs;
 
-enum : int { OP_GEMM = 1, OP_GATED = 2, OP_RESNORM = 3 };
+enum : int { OP_GEMM = 1, OP_GATED = 2, OP_RESNORM = 3, OP_GEMM_GATED = 4, OP_ENCODE = 5 };
+constexpr int HW = BN / 2;  // hidden units per work item of the gated GEMM (gate columns | up columns)
 
 struct Op {  // mirrors iflb200_stack_op
   int32_t type, wait_bar, arrive_bar, tile_offset;
@@ -60,9 +61,10 @@ struct Op {  // mirrors iflb200_stack_op
   int64_t ld_out, ld_in;
   float eps;
   int32_t pad2;
-  int64_t pad3;
+  float* aux;  // GEMM_GATED / ENCODE: row maxima of |h| (float bits); RESNORM: words to leave at zero (or null)
 };
 static_assert(sizeof(Op) == sizeof(iflb200_stack_op), "layout of iflb200_stack_op");
+__device__ __forceinline__ bool is_gemm(const Op& op) { return op.type == OP_GEMM || op.type == OP_GEMM_GATED; }
 
 __device__ __forceinline__ uint32_t ld_acquire(const uint32_t* p) {
   uint32_t v;
@@ -152,11 +154,18 @@ __device__ __forceinline__ bool wait_grid(const uint32_t* bar, uint32_t target, 
   return true;
 }
 
-__device__ __forceinline__ int gemm_items(const Op& op) { return ((op.N + BN - 1) / BN) * op.split_k; }
+__device__ __forceinline__ int gemm_items(const Op& op) {
+  return op.type == OP_GEMM_GATED ? (op.N + HW - 1) / HW : ((op.N + BN - 1) / BN) * op.split_k;
+}
 
 // k-step range of one split
 __device__ __forceinline__ void split_range(const Op& op, int split, int& kb0, int& kb1) {
   const int steps = (op.K + BK - 1) / BK;
+  if (op.type == OP_GEMM_GATED) {
+    kb0 = 0;
+    kb1 = steps;
+    return;
+  }
   kb0 = (int)(((int64_t)steps * split) / op.split_k);
   kb1 = (int)(((int64_t)steps * (split + 1)) / op.split_k);
 }
@@ -277,13 +286,23 @@ __device__ void row_resnorm(const Op& op, int M, int m, int t, float (*red)[4]) 
     if (c0 < D) {
       float d[8], cs[8], r[8];
       if (op.split_k > 1) {
+        // partials in groups of four: the loads of a group are all in flight before the first add
+        // (the sum itself runs in split order)
         const float* p0 = reinterpret_cast<const float*>(op.in) + (int64_t)m * op.ld_in + c0;
+        const int64_t step = (int64_t)M * op.ld_in;
         load_f32x8_cg(p0, d);
-        for (int s = 1; s < op.split_k; ++s) {
-          float e[8];
-          load_f32x8_cg(p0 + (int64_t)s * M * op.ld_in, e);
+        for (int s = 1; s < op.split_k; s += 4) {
+          float e[4][8];
 #pragma unroll
-          for (int i = 0; i < 8; ++i) d[i] = __fadd_rn(d[i], e[i]);
+          for (int q = 0; q < 4; ++q)
+            if (s + q < op.split_k) load_f32x8_cg(p0 + (s + q) * step, e[q]);
+#pragma unroll
+          for (int q = 0; q < 4; ++q) {
+            if (s + q < op.split_k) {
+#pragma unroll
+              for (int i = 0; i < 8; ++i) d[i] = __fadd_rn(d[i], e[q][i]);
+            }
+          }
         }
 #pragma unroll
         for (int i = 0; i < 8; ++i) d[i] = __bfloat162float(__float2bfloat16_rn(d[i]));
@@ -317,13 +336,82 @@ __device__ void row_resnorm(const Op& op, int M, int m, int t, float (*red)[4]) 
   amax = block_reduce128(amax, true, red[1], t);
   float scale, inv;
   quant_scales(amax, scale, inv);
-  if (t == 0) op.out_scale[m] = scale;
+  if (t == 0) {
+    op.out_scale[m] = scale;
+    if (op.aux) op.aux[m] = 0.0f;  // row maximum of the gated GEMM before this operator: consumed, start over
+  }
   uint8_t* qr = reinterpret_cast<uint8_t*>(op.out) + (int64_t)m * op.ld_out;
 #pragma unroll
   for (int it = 0; it < kRowIters; ++it) {
     const int c0 = (it * 128 + t) * 8;
     if (c0 < D) store_codes8(qr + c0, x[it], inv);
   }
+}
+
+// Quantiser pass after the gated GEMM: codes of one part of a row of h (fp32) with the row's
+// scale taken from the maxima the GEMM epilogues left in op.aux.  No reduction: a row is split
+// over op.split_k parts so that all SMs share the rows.
+__device__ void row_encode(const Op& op, int item, int t) {
+  const int F = op.N, parts = op.split_k;
+  const int m = item / parts, part = item - m * parts;
+  const int width = ((F + parts - 1) / parts + 7) / 8 * 8;
+  const int begin = part * width, end = min(F, begin + width);
+  const float* hr = reinterpret_cast<const float*>(op.in) + (int64_t)m * op.ld_in;
+  float scale, inv;
+  quant_scales(__ldcg(op.aux + m), scale, inv);
+  if (part == 0 && t == 0) op.out_scale[m] = scale;
+  uint8_t* qr = reinterpret_cast<uint8_t*>(op.out) + (int64_t)m * op.ld_out;
+  float v[kRowIters][8];
+#pragma unroll
+  for (int it = 0; it < kRowIters; ++it) {
+    const int c0 = begin + (it * 128 + t) * 8;
+    if (c0 < end) load_f32x8_cg(hr + c0, v[it]);
+  }
+#pragma unroll
+  for (int it = 0; it < kRowIters; ++it) {
+    const int c0 = begin + (it * 128 + t) * 8;
+    if (c0 < end) store_codes8(qr + c0, v[it], inv);
+  }
+}
+
+// Gated activation on one row's 32 gate and 32 up accumulators of a work item (the arithmetic of
+// instinctflash/kernels/activation.py:26-43 on the bf16-rounded accumulators): h in fp32 to
+// memory, the row's maximum of |h| raised in op.aux with atomicMax on the float's bits.
+__device__ __forceinline__ void gated_epilogue_row(const Op& op, const uint32_t (&rg)[32], const uint32_t (&ru)[32],
+                                                   int m, int n0) {
+  const float rs = __ldcg(op.row_scale + m);
+  float* hr = reinterpret_cast<float*>(op.out) + (int64_t)m * op.ld_out + n0;
+  float row_max = 0.0f;
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    if (n0 + 8 * j >= op.N) break;  // widths are multiples of 8
+    float g[8], u[8], cg[8], cu[8], h[8];
+    load_f32x8(op.col_scale + n0 + 8 * j, cg);
+    load_f32x8(op.col_scale + op.N + n0 + 8 * j, cu);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      g[i] = __bfloat162float(__float2bfloat16_rn(__uint_as_float(rg[8 * j + i])));
+      u[i] = __bfloat162float(__float2bfloat16_rn(__uint_as_float(ru[8 * j + i])));
+      g[i] = __fmul_rn(__fmul_rn(g[i], rs), cg[i]);
+      u[i] = __fmul_rn(__fmul_rn(u[i], rs), cu[i]);
+    }
+    if (op.act == IFLB200_ACT_GELU_TANH) {
+#pragma unroll
+      for (int i = 0; i < 8; i += 2) {
+        gelu_tanh_ref2(g[i], g[i + 1]);
+        h[i] = __fmul_rn(u[i], g[i]);
+        h[i + 1] = __fmul_rn(u[i + 1], g[i + 1]);
+      }
+    } else {
+#pragma unroll
+      for (int i = 0; i < 8; ++i) h[i] = __fmul_rn(u[i], silu_ref(g[i]));
+    }
+#pragma unroll
+    for (int i = 0; i < 8; ++i) row_max = max_f32(row_max, fabsf(h[i]));
+    *reinterpret_cast<float4*>(hr + 8 * j) = make_float4(h[0], h[1], h[2], h[3]);
+    *reinterpret_cast<float4*>(hr + 8 * j + 4) = make_float4(h[4], h[5], h[6], h[7]);
+  }
+  atomicMax(reinterpret_cast<uint32_t*>(op.aux) + m, __float_as_uint(row_max));
 }
 
 template <int AROWS, int NSTAGES>
@@ -382,7 +470,7 @@ stack_persistent_kernel(const Op* __restrict__ ops, int num_ops, const CUtensorM
     bool ok = true;
     for (int oi = 0; ok && oi < num_ops; ++oi) {
       const Op& op = ops[oi];
-      if (op.type != OP_GEMM) continue;
+      if (!is_gemm(op)) continue;
       const int items = gemm_items(op);
       bool waited = is_w || op.wait_bar < 0;
       for (int item = (cta + ncta - (op.tile_offset % ncta)) % ncta; ok && item < items; item += ncta) {
@@ -409,7 +497,10 @@ stack_persistent_kernel(const Op* __restrict__ ops, int num_ops, const CUtensorM
             const uint32_t sa = base + stage * kStageBytes;
             if (is_w) {
               mbar_arrive_expect_tx(full_bar(stage), kWBytes);
-              tma_load_2d(sa + kABytes, maps + op.tm_w, full_bar(stage), kb * BK, n_blk * BN);
+              if (op.type == OP_GEMM_GATED)  // gate rows and up rows of the item's hidden units in one box
+                tma_load_3d(sa + kABytes, maps + op.tm_w, full_bar(stage), kb * BK, n_blk * HW, 0);
+              else
+                tma_load_2d(sa + kABytes, maps + op.tm_w, full_bar(stage), kb * BK, n_blk * BN);
             } else {
               mbar_arrive_expect_tx(full_bar(stage), kABytes);
               tma_load_2d(sa, maps + op.tm_a, full_bar(stage), kb * BK, 0);
@@ -437,7 +528,7 @@ stack_persistent_kernel(const Op* __restrict__ ops, int num_ops, const CUtensorM
     bool ok = true;
     for (int oi = 0; ok && oi < num_ops; ++oi) {
       const Op& op = ops[oi];
-      if (op.type != OP_GEMM) continue;
+      if (!is_gemm(op)) continue;
       const int items = gemm_items(op);
       for (int item = (cta + ncta - (op.tile_offset % ncta)) % ncta; ok && item < items; item += ncta, ++it) {
         int kb0, kb1;
@@ -486,7 +577,7 @@ stack_persistent_kernel(const Op* __restrict__ ops, int num_ops, const CUtensorM
     bool ok = true;
     for (int oi = 0; ok && oi < num_ops; ++oi) {
       const Op& op = ops[oi];
-      if (op.type == OP_GEMM) {
+      if (is_gemm(op)) {
         const int items = gemm_items(op);
         for (int item = (cta + ncta - (op.tile_offset % ncta)) % ncta; ok && item < items; item += ncta, ++it) {
           const int n_blk = item / op.split_k;
@@ -501,6 +592,18 @@ stack_persistent_kernel(const Op* __restrict__ ops, int num_ops, const CUtensorM
           tc_fence_after();
           if (t == 0) TRACE(oi, 6);
           const uint32_t t_row = tmem_base + ((uint32_t)(quad * 32) << 16) + acc * BN;
+          if (op.type == OP_GEMM_GATED) {
+            uint32_t rg[32], ru[32];
+            tmem_ld_32x32b_x32(t_row, rg);
+            tmem_ld_32x32b_x32(t_row + HW, ru);
+            tmem_ld_wait();
+            if (row_ok) gated_epilogue_row(op, rg, ru, m, n_blk * HW);
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(tempty_bar(acc));
+            if (t == 0) TRACE(oi, 7);
+            continue;
+          }
 #pragma unroll 1
           for (int c = 0; c < BN / 32; ++c) {
             const int n0 = n_blk * BN + c * 32;
@@ -554,10 +657,14 @@ stack_persistent_kernel(const Op* __restrict__ ops, int num_ops, const CUtensorM
           __threadfence();
           if (t == 0) TRACE(oi, 9);
         }
-        for (int m = cta; m < M; m += ncta) {
-          if (op.type == OP_GATED) row_gated(op, m, t, sh->red[0]);
-          else row_resnorm(op, M, m, t, sh->red);
-          named_barrier_sync(1, 128);  // reduction scratch reused by the next row
+        if (op.type == OP_ENCODE) {
+          for (int item = cta; item < M * op.split_k; item += ncta) row_encode(op, item, t);
+        } else {
+          for (int m = cta; m < M; m += ncta) {
+            if (op.type == OP_GATED) row_gated(op, m, t, sh->red[0]);
+            else row_resnorm(op, M, m, t, sh->red);
+            named_barrier_sync(1, 128);  // reduction scratch reused by the next row
+          }
         }
         if (t == 0) TRACE(oi, 10);
       }
@@ -629,6 +736,28 @@ extern "C" __attribute__((visibility("default"))) int iflb200_exp_stack_trace(un
   return (int)cudaMemcpyFromSymbol(out256, g_stack_trace, sizeof(unsigned long long) * 256);
 }
 #endif
+
+extern "C" int iflb200_encode_gated_weight_map(void* out128, const void* ptr, int F, int K, int64_t ld) {
+  if (!out128 || !ptr || F <= 0 || F % 8 || K < 16 || K % 16 || ld < K || ld % 16) return IFLB200_ERR_ARG;
+  if (reinterpret_cast<uintptr_t>(ptr) & 15) return IFLB200_ERR_ALIGN;
+  void* fp = nullptr;
+  cudaDriverEntryPointQueryResult q;
+  if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fp, cudaEnableDefault, &q) != cudaSuccess ||
+      q != cudaDriverEntryPointSuccess)
+    return IFLB200_ERR_DRIVER;
+  EncodeTiledFn2 fn = reinterpret_cast<EncodeTiledFn2>(fp);
+  alignas(64) CUtensorMap tm;
+  const cuuint64_t dims[3] = {(cuuint64_t)K, (cuuint64_t)F, 2};
+  const cuuint64_t strides[2] = {(cuuint64_t)ld, (cuuint64_t)ld * (cuuint64_t)F};
+  const cuuint32_t box[3] = {(cuuint32_t)BK, (cuuint32_t)HW, 2};
+  const cuuint32_t estr[3] = {1, 1, 1};
+  const CUresult r = fn(&tm, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, const_cast<void*>(ptr), dims, strides, box, estr,
+                        CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                        CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return IFLB200_ERR_DRIVER;
+  memcpy(out128, &tm, sizeof(tm));
+  return IFLB200_OK;
+}
 
 extern "C" int iflb200_stack_activation_box_rows(int M) { return M <= A_ROWS ? A_ROWS : A_ROWS_WIDE; }
 extern "C" int iflb200_stack_weight_box_rows(void) { return BN; }

@@ -33,14 +33,15 @@ OP_DTYPE = np.dtype([
     ("N", "<i4"), ("K", "<i4"), ("split_k", "<i4"), ("act", "<i4"),
     ("tm_a", "<i4"), ("tm_w", "<i4"), ("pad0", "<i4"), ("pad1", "<i4"),
     ("out", "<u8"), ("in", "<u8"), ("row_scale", "<u8"), ("col_scale", "<u8"), ("out_scale", "<u8"), ("res", "<u8"),
-    ("ld_out", "<i8"), ("ld_in", "<i8"), ("eps", "<f4"), ("pad2", "<i4"), ("pad3", "<i8"),
+    ("ld_out", "<i8"), ("ld_in", "<i8"), ("eps", "<f4"), ("pad2", "<i4"), ("aux", "<u8"),
 ])
 assert OP_DTYPE.itemsize == 128
-GEMM, GATED, RESNORM = 1, 2, 3
+GEMM, GATED, RESNORM, GEMM_GATED, ENCODE = 1, 2, 3, 4, 5
 
 
 class PersistentExpertStack:
-    def __init__(self, spec: StackSpec, weights, device, *, down_split_k: int | None = None):
+    def __init__(self, spec: StackSpec, weights, device, *, down_split_k: int | None = None,
+                 gated_in_gemm: bool = True):
         if spec.kind != "gemma" or spec.o_in:
             raise ValueError("the persistent stack covers Gemma-shape expert layers without an O projection")
         if spec.M > 128:
@@ -53,13 +54,18 @@ class PersistentExpertStack:
         dev, f32, bf16 = self.dev, torch.float32, torch.bfloat16
         M, D, F = spec.M, spec.hidden, spec.ffn
         k_steps = (F + 127) // 128
+        self.sms = sms = torch.cuda.get_device_properties(dev).multi_processor_count
         if down_split_k is None:
             # enough work items to occupy the SMs: (D / 64) column tiles x split_k
-            sms = torch.cuda.get_device_properties(dev).multi_processor_count
             down_split_k = max(1, min(k_steps, sms // max(1, (D + 63) // 64)))
         if not 1 <= down_split_k <= k_steps:
             raise ValueError("every K split needs at least one 128-byte step")
         self.split_k = down_split_k
+        # gated activation in the gate_up GEMM's epilogue (h in fp32 + row maxima, then a short
+        # quantiser pass shared by all SMs) instead of a one-row-per-CTA gated_act_quant pass
+        self.gated_in_gemm = bool(gated_in_gemm)
+        self.h = torch.zeros(M, F, dtype=f32, device=dev)
+        self.amax = torch.zeros(M, dtype=f32, device=dev)
         self.q8 = torch.zeros(M, D, dtype=torch.uint8, device=dev).view(E4M3)
         self.q8f = torch.zeros(M, F, dtype=torch.uint8, device=dev).view(E4M3)
         self.s0 = torch.zeros(M, dtype=f32, device=dev)
@@ -93,7 +99,14 @@ class PersistentExpertStack:
         for lw in self.weights:   # one tensor map per weight matrix, shared by all flow steps
             layer_base.append(len(maps))
             for name in ("qkv", "gate_up", "down"):
-                maps.append(self._encode_map(lw.w[name].w, w_rows))
+                if name == "gate_up" and self.gated_in_gemm:
+                    buf = (ctypes.c_uint8 * 128)()
+                    t = lw.w[name].w
+                    _lib.check(lib.iflb200_encode_gated_weight_map(buf, t.data_ptr(), F, t.shape[1], t.stride(0)),
+                               "encode_gated_weight_map")
+                    maps.append(bytes(buf))
+                else:
+                    maps.append(self._encode_map(lw.w[name].w, w_rows))
         for _ in range(sp.steps):
             for li, lw in enumerate(self.weights):
                 W = lw.w
@@ -102,17 +115,28 @@ class PersistentExpertStack:
                 n_bar += 4
                 ops.append(dict(type=GEMM, wait_bar=prev, arrive_bar=-1, tile_offset=0, N=sp.qkv, K=D, split_k=1,
                                 tm_a=0, tm_w=base, out=self.raw_qkv.data_ptr(), ld_out=sp.qkv))
-                ops.append(dict(type=GEMM, wait_bar=prev, arrive_bar=b1, tile_offset=qkv_items, N=2 * F, K=D, split_k=1,
-                                tm_a=0, tm_w=base + 1, out=self.raw_gu.data_ptr(), ld_out=2 * F))
-                ops.append(dict(type=GATED, wait_bar=b1, arrive_bar=b2, N=F, act=0, out=self.q8f.data_ptr(), ld_out=F,
-                                **{"in": self.raw_gu.data_ptr()}, ld_in=2 * F, row_scale=self.s0.data_ptr(),
-                                col_scale=W["gate_up"].scale.data_ptr(), out_scale=self.s1.data_ptr()))
+                if self.gated_in_gemm:
+                    parts = max(1, self.sms // max(1, M))
+                    ops.append(dict(type=GEMM_GATED, wait_bar=prev, arrive_bar=b1, tile_offset=qkv_items, N=F, K=D,
+                                    split_k=1, act=0, tm_a=0, tm_w=base + 1, out=self.h.data_ptr(), ld_out=F,
+                                    row_scale=self.s0.data_ptr(), col_scale=W["gate_up"].scale.data_ptr(),
+                                    aux=self.amax.data_ptr()))
+                    ops.append(dict(type=ENCODE, wait_bar=b1, arrive_bar=b2, N=F, split_k=parts, out=self.q8f.data_ptr(),
+                                    ld_out=F, **{"in": self.h.data_ptr()}, ld_in=F, out_scale=self.s1.data_ptr(),
+                                    aux=self.amax.data_ptr()))
+                else:
+                    ops.append(dict(type=GEMM, wait_bar=prev, arrive_bar=b1, tile_offset=qkv_items, N=2 * F, K=D, split_k=1,
+                                    tm_a=0, tm_w=base + 1, out=self.raw_gu.data_ptr(), ld_out=2 * F))
+                    ops.append(dict(type=GATED, wait_bar=b1, arrive_bar=b2, N=F, act=0, out=self.q8f.data_ptr(), ld_out=F,
+                                    **{"in": self.raw_gu.data_ptr()}, ld_in=2 * F, row_scale=self.s0.data_ptr(),
+                                    col_scale=W["gate_up"].scale.data_ptr(), out_scale=self.s1.data_ptr()))
                 ops.append(dict(type=GEMM, wait_bar=b2, arrive_bar=b3, tile_offset=0, N=D, K=F, split_k=self.split_k,
                                 tm_a=1, tm_w=base + 2, out=self.down_out.data_ptr(), ld_out=D))
                 ops.append(dict(type=RESNORM, wait_bar=b3, arrive_bar=b4, N=D, split_k=self.split_k,
                                 out=self.q8.data_ptr(), ld_out=D, **{"in": self.down_out.data_ptr()}, ld_in=D,
                                 row_scale=self.s1.data_ptr(), col_scale=W["down"].scale.data_ptr(),
-                                out_scale=self.s0.data_ptr(), res=self.res.data_ptr(), eps=1e-6))
+                                out_scale=self.s0.data_ptr(), res=self.res.data_ptr(), eps=1e-6,
+                                aux=self.amax.data_ptr() if self.gated_in_gemm else 0))
                 prev = b4
         arr = np.zeros(len(ops), dtype=OP_DTYPE)
         for i, op in enumerate(ops):
