@@ -305,7 +305,8 @@ IFLB200_API int iflb200_pack_bf16_e4m3(const void* x, int64_t n, const float* sc
  * iflb200_encode_operand_map), `barriers` (num_barriers uint32) and `status2` (2 uint32) are
  * device buffers owned by the caller; barriers and status2[1] are zeroed by the call itself.
  * The program lives in device memory and is NOT validated by the call.  The caller guarantees:
- * N a multiple of 8 and row strides / base pointers of every operand 16-byte aligned; row
+ * K a multiple of 128 for every GEMM (the encoders below refuse other widths: operands are mapped
+ * as [K / 128][rows][128 bytes] so that one TMA instruction brings four K slabs); N a multiple of 8 and row strides / base pointers of every operand 16-byte aligned; row
  * operators at most 8192 columns wide; every K split of a GEMM at least one 128-byte step
  * (split_k <= ceil(K / 128)); wait_bar / arrive_bar below num_barriers; every counter that an
  * operator waits on is the arrive_bar of an earlier operator (a counter nobody arrives on makes
@@ -399,7 +400,8 @@ IFLB200_API int iflb200_set_dependent_launch(int enable);
  * swapped form (tokens on the MMA's N side, 257..1024 tokens, two-byte raw or dequantised output;
  * not chosen by the heuristic) wherever it exists, 128 to forbid it, 512 to keep the swapped form
  * off CTA pairs; add 1024 / 2048 to run the gated form's 256-wide tiles with sixteen / eight
- * epilogue warps.  Any other bit is refused.  Every mode writes the same output bits.  For
+ * epilogue warps; add 4096 to keep the skinny-regime kernel on one K slab per TMA instruction.
+ * Any other bit is refused.  Every mode writes the same output bits.  For
  * experiments and tests.  No reference counterpart. */
 IFLB200_API int iflb200_gemm_set_mode(int mode);
 

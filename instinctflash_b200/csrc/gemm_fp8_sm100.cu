@@ -84,10 +84,13 @@ __device__ __forceinline__ float ld_dsmem_f32(uint32_t addr) {
   return v;
 }
 
-template <int BN, int STAGES, int EW = kEpilogueWarps>
+// SL: 128-byte K slabs per stage.  With SL > 1 one TMA instruction per operand brings SL slabs (the
+// operands are mapped as [K / 128][rows][128 bytes]): a skinny GEMM's main loop is bound by the
+// rate at which one SM can issue TMA instructions (about 0.2 us each, measured), not by bytes.
+template <int BN, int STAGES, int EW = kEpilogueWarps, int SL = 1>
 struct SmemLayout {
-  static constexpr int kABytes = BM * BK;
-  static constexpr int kBBytes = BN * BK;
+  static constexpr int kABytes = BM * BK * SL;
+  static constexpr int kBBytes = BN * BK * SL;
   static constexpr int kStageBytes = kABytes + kBBytes;
   // epilogue staging: one 32-row buffer per epilogue warp (TMA-store source), 128 bytes per row
   // with eight epilogue warps, 64 with sixteen
@@ -595,12 +598,13 @@ __device__ __forceinline__ void epilogue_swapped(const GemmParams& p, const CUte
 // GATED: the gated form (see epilogue_gated): a tile pairs BN/2 gate columns with the BN/2 up
 // columns of the same hidden units; p.N counts hidden units.
 // EW: epilogue warps (8, or 16 for the gated form: EW / 4 per TMEM lane quadrant).
-template <int BN, int STAGES, int SPLIT, bool SWAP = false, bool GATED = false, int EW = kEpilogueWarps>
+template <int BN, int STAGES, int SPLIT, bool SWAP = false, bool GATED = false, int EW = kEpilogueWarps, int SL = 1>
 __global__ void __launch_bounds__(64 + 32 * EW, 1)
 gemm_fp8_tc5_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_w,
                     const __grid_constant__ CUtensorMap tm_out, const GemmParams p) {
-  using L = SmemLayout<BN, STAGES, EW>;
+  using L = SmemLayout<BN, STAGES, EW, SL>;
   static_assert(EW == kEpilogueWarps || GATED, "only the gated epilogue is written for more than eight warps");
+  static_assert(SL == 1 || (!GATED && !SWAP), "several slabs per load: ordinary form only");
   // two accumulators, each at a power-of-two column offset; BN in {64, 128, 192, 224, 256}
   constexpr uint32_t kAccStride = BN <= 64 ? 64 : (BN <= 128 ? 128 : 256);
   constexpr uint32_t kTmemCols = 2 * kAccStride;
@@ -627,8 +631,10 @@ gemm_fp8_tc5_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
   const int split_rank = split ? (int)cluster_ctarank() : 0;
   const int tile_first = split ? (int)blockIdx.x / p.split_k : (int)blockIdx.x;
   const int tile_stride = split ? p.num_tiles : (int)gridDim.x;
-  const int kb0 = split ? (int)(((int64_t)p.num_k * split_rank) / p.split_k) : 0;
-  const int kb1 = split ? (int)(((int64_t)p.num_k * (split_rank + 1)) / p.split_k) : p.num_k;
+  // K ranges in whole stages (SL slabs each)
+  const int k_stages = (p.num_k + SL - 1) / SL;
+  const int kb0 = split ? (int)(((int64_t)k_stages * split_rank) / p.split_k) * SL : 0;
+  const int kb1 = split ? min(p.num_k, (int)(((int64_t)k_stages * (split_rank + 1)) / p.split_k) * SL) : p.num_k;
 
   if (threadIdx.x == 0) {
     prefetch_tensormap(&tm_a);
@@ -662,9 +668,11 @@ gemm_fp8_tc5_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
     int m_blk, n_blk;
     tile_coords(p, tile_first, m_blk, n_blk);
     const int kb_end = kb1 < kb0 + kPrefetchSteps ? kb1 : kb0 + kPrefetchSteps;
-    for (int kb = kb0; kb < kb_end; ++kb) {
+    for (int kb = kb0; kb < kb_end; kb += SL) {
       if constexpr (GATED) {
         tma_prefetch_l2_3d(&tm_w, kb * BK, n_blk * (BN / 2), 0);
+      } else if constexpr (SL > 1) {
+        tma_prefetch_l2_3d(&tm_w, 0, n_blk * BN, kb);
       } else {
         tma_prefetch_l2_2d(&tm_w, kb * BK, n_blk * BN);
       }
@@ -688,13 +696,18 @@ gemm_fp8_tc5_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
     for (int tile = tile_first; ok && tile < p.num_tiles; tile += tile_stride, ++it) {
       int m_blk, n_blk;
       tile_coords(p, tile, m_blk, n_blk);
-      for (int kb = kb0; kb < kb1; ++kb) {
+      for (int kb = kb0; kb < kb1; kb += SL) {
         ok = __all_sync(0xFFFFFFFFu, wait_bounded(empty_bar(stage), phase ^ 1, abort_flag,
                                                   (1u << 24) | (1u << 16) | (it & 0xFFFF)));
         if (!ok) break;
         if (lane == 0) {
-          mbar_arrive_expect_tx(full_bar(stage), (uint32_t)p.a_bytes + L::kBBytes);
+          mbar_arrive_expect_tx(full_bar(stage), (uint32_t)(SL * p.a_bytes) + L::kBBytes);
           const uint32_t sa = base + stage * L::kStageBytes;
+          if constexpr (SL > 1) {
+            // SL slabs of each operand per instruction; slabs past the end of K read as zeros
+            tma_load_3d(sa, &tm_a, full_bar(stage), 0, m_blk * BM, kb);
+            tma_load_3d(sa + L::kABytes, &tm_w, full_bar(stage), 0, n_blk * BN, kb);
+          } else {
           tma_load_2d(sa, &tm_a, full_bar(stage), kb * BK, m_blk * BM);
           if constexpr (GATED) {
             // gate rows, then the up rows of the same hidden units: one B operand of BN rows, one
@@ -703,6 +716,7 @@ gemm_fp8_tc5_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
             tma_load_3d(sa + L::kABytes, &tm_w, full_bar(stage), kb * BK, n_blk * (BN / 2), 0);
           } else {
             tma_load_2d(sa + L::kABytes, &tm_w, full_bar(stage), kb * BK, n_blk * BN);
+          }
           }
         }
         armed |= 1u << stage;
@@ -742,19 +756,24 @@ gemm_fp8_tc5_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
       if (!ok) break;
       tc_fence_after();
       const uint32_t d_tmem = tmem_base + acc * kAccStride;
-      for (int kb = kb0; kb < kb1; ++kb) {
+      for (int kb = kb0; kb < kb1; kb += SL) {
         ok = __all_sync(0xFFFFFFFFu, wait_bounded(full_bar(stage), phase, abort_flag,
                                                   (2u << 24) | (3u << 16) | (it & 0xFFFF)));
         if (!ok) break;
         tc_fence_after();
         if (lane == 0) {
           const uint32_t sa = base + stage * L::kStageBytes;
-          const uint64_t da = make_kmajor_sw128_desc(sa);
-          const uint64_t db = make_kmajor_sw128_desc(sa + L::kABytes);
 #pragma unroll
-          for (int j = 0; j < BK / 32; ++j) {
-            // 32 bytes further along K inside the swizzled 128-byte row: +2 in 16-byte units.
-            mma_f8f6f4(d_tmem, da + 2 * j, db + 2 * j, kIdesc, (kb > kb0 || j > 0) ? 1u : 0u);
+          for (int sl = 0; sl < SL; ++sl) {
+            if (kb + sl >= kb1) break;  // slabs past the end of K (zeros) need no instruction
+            // the activation slabs follow each other at the size of the box that brought them
+            const uint64_t da = make_kmajor_sw128_desc(sa + sl * (SL > 1 ? p.a_bytes : 0));
+            const uint64_t db = make_kmajor_sw128_desc(sa + L::kABytes + sl * BN * BK);
+#pragma unroll
+            for (int j = 0; j < BK / 32; ++j) {
+              // 32 bytes further along K inside the swizzled 128-byte row: +2 in 16-byte units.
+              mma_f8f6f4(d_tmem, da + 2 * j, db + 2 * j, kIdesc, (kb + sl > kb0 || j > 0) ? 1u : 0u);
+            }
           }
           mma_commit(empty_bar(stage));  // stage reusable once these MMAs have read it
         }
@@ -1240,6 +1259,22 @@ static int make_tensor_map(CUtensorMap* tm, const void* ptr, int rows, int K, in
   return r == CUDA_SUCCESS ? IFLB200_OK : IFLB200_ERR_DRIVER;
 }
 
+// [rows, K] e4m3 matrix, K a multiple of 128, seen as [K / 128][rows][128 bytes]: box = 128 bytes x
+// box_rows x `slabs`, so that one load brings `slabs` consecutive 128-byte K slabs of the tile, each
+// laid out in shared memory like the box of make_tensor_map.
+static int make_slab_map(CUtensorMap* tm, const void* ptr, int rows, int K, int64_t ld, int box_rows, int slabs) {
+  EncodeTiledFn enc = get_encode_fn();
+  if (!enc) return IFLB200_ERR_DRIVER;
+  const cuuint64_t dims[3] = {(cuuint64_t)BK, (cuuint64_t)rows, (cuuint64_t)(K / BK)};
+  const cuuint64_t strides[2] = {(cuuint64_t)ld, (cuuint64_t)BK};
+  const cuuint32_t box[3] = {(cuuint32_t)BK, (cuuint32_t)box_rows, (cuuint32_t)slabs};
+  const cuuint32_t estr[3] = {1, 1, 1};
+  const CUresult r = enc(tm, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, const_cast<void*>(ptr), dims, strides, box, estr,
+                         CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                         CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? IFLB200_OK : IFLB200_ERR_DRIVER;
+}
+
 // The [gate | up] weight [2F, K] seen as [2][F][K]: box = 128 bytes x box_rows x 2, so that one
 // load brings the gate rows and the up rows of the same hidden units, gate rows first.
 static int make_gated_weight_map(CUtensorMap* tm, const void* ptr, int F, int K, int64_t ld, int box_rows) {
@@ -1327,25 +1362,26 @@ static int g_cfg_split_k = 0;  // 0: cost model, 1: never split K, 2/4/8: forced
 static int g_cfg_direct_store = 0;  // 1: epilogue stores straight from registers (experiments)
 static int g_cfg_pair_swap = 1;  // the swapped form on CTA pairs where the shape allows
 static int g_cfg_swap = 0;  // 0: cost model, 1: never, 2: always where the form exists
+static int g_cfg_slabs = 0;  // 1: one K slab per TMA instruction everywhere (experiments)
 static int g_cfg_gated_warps = 0;  // gated form, 256-wide tiles: 0 heuristic, 8 or 16 epilogue warps
 static int g_cfg_mode = 0;  // 0 auto, 1 single-CTA tiles only, 2 CTA pairs with one accumulator, 3 CTA pairs with two
 
-template <int BN, int STAGES, int SPLIT, bool SWAP = false, bool GATED = false, int EW = kEpilogueWarps>
+template <int BN, int STAGES, int SPLIT, bool SWAP = false, bool GATED = false, int EW = kEpilogueWarps, int SL = 1>
 static int launch_gemm_form(const CUtensorMap& ta, const CUtensorMap& tw, const CUtensorMap& to, const GemmParams& p,
                             int grid, cudaStream_t s) {
-  using L = SmemLayout<BN, STAGES, EW>;
+  using L = SmemLayout<BN, STAGES, EW, SL>;
   static_assert(L::kDynamic <= 227 * 1024, "stage ring + staging exceed the shared memory of an SM");
   static bool attr_set[64] = {};
   int dev = 0;
   cudaGetDevice(&dev);
   if (dev < 0 || dev >= 64) return IFLB200_ERR_DEVICE;
   if (!attr_set[dev]) {
-    cudaError_t e = cudaFuncSetAttribute(gemm_fp8_tc5_kernel<BN, STAGES, SPLIT, SWAP, GATED, EW>,
+    cudaError_t e = cudaFuncSetAttribute(gemm_fp8_tc5_kernel<BN, STAGES, SPLIT, SWAP, GATED, EW, SL>,
                                          cudaFuncAttributeMaxDynamicSharedMemorySize, L::kDynamic);
     if (e != cudaSuccess) return (int)e;
     attr_set[dev] = true;
   }
-  const cudaError_t e = launch_dep(gemm_fp8_tc5_kernel<BN, STAGES, SPLIT, SWAP, GATED, EW>, dim3(grid),
+  const cudaError_t e = launch_dep(gemm_fp8_tc5_kernel<BN, STAGES, SPLIT, SWAP, GATED, EW, SL>, dim3(grid),
                                    dim3(64 + 32 * EW), L::kDynamic, s, p.split_k,
                                    dependent_launch_for(SWAP ? p.N : p.M), ta, tw, to, p);
   return e != cudaSuccess ? (int)e : (int)cudaGetLastError();
@@ -1553,6 +1589,16 @@ static int run_gemm(const void* a, int64_t ld_a, const void* w, int64_t ld_w, Ge
   if (st != IFLB200_OK) return st;
   const int stages = g_cfg_stages;
   g_last_launch[0] = 1; g_last_launch[1] = bn; g_last_launch[2] = split; g_last_launch[3] = stages;
+  // Skinny regime (64-wide tiles): four K slabs per TMA instruction where the layout allows it
+  // (K a multiple of 128, at least one full stage per CTA); the K order is unchanged, so are the bits.
+  if (bn == 64 && g_cfg_slabs != 1 && p.K % BK == 0 && p.num_k / split >= 4 && stages == 0) {
+    CUtensorMap sa_map, sw_map;
+    if (make_slab_map(&sa_map, a, p.M, p.K, ld_a, a_rows, 4) == IFLB200_OK &&
+        make_slab_map(&sw_map, w, p.N, p.K, ld_w, bn, 4) == IFLB200_OK) {
+      g_last_launch[3] = 104;
+      return launch_gemm_form<64, 2, 2, false, false, kEpilogueWarps, 4>(sa_map, sw_map, to, p, grid, s);
+    }
+  }
   switch (bn) {
     case 256: return (stages == 3) ? launch_gemm<256, 3>(ta, tw, to, p, grid, s) : launch_gemm<256, 4>(ta, tw, to, p, grid, s);
     case 224: return launch_gemm<224, 4>(ta, tw, to, p, grid, s);
@@ -1618,7 +1664,9 @@ static int run_gemm_gated(const void* a, int64_t ld_a, const void* w, int64_t ld
   if (st != IFLB200_OK) return st;
   st = make_gated_weight_map(&tw, w, F, K, ld_w, bn / 2);
   if (st != IFLB200_OK) return st;
-  const bool sixteen = bn == 256 && g_cfg_gated_warps == 16;
+  // sixteen epilogue warps unless eight are asked for: the activation's arithmetic per element is
+  // heavy enough that the epilogue of a CTA's last tile, which nothing overlaps, is worth halving
+  const bool sixteen = bn == 256 && g_cfg_gated_warps != 8;
   st = make_out_map(&to, h, M, F, ld_h, 4, sixteen ? 64 : 128);
   if (st != IFLB200_OK) return st;
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
@@ -1662,10 +1710,11 @@ extern "C" int iflb200_set_dependent_launch(int enable) {
 extern "C" int iflb200_gemm_set_mode(int mode) {
   // bit 4 (value 16) selects the direct-store epilogue; the low bits the kernel family
   const int family = mode & 15;
-  if (mode < 0 || family > 3 || (mode & ~(15 | 16 | 128 | 256 | 512 | 1024 | 2048)) || (mode & 384) == 384 ||
+  if (mode < 0 || family > 3 || (mode & ~(15 | 16 | 128 | 256 | 512 | 1024 | 2048 | 4096)) || (mode & 384) == 384 ||
       (mode & 3072) == 3072)
     return IFLB200_ERR_ARG;
   g_cfg_gated_warps = (mode & 1024) ? 16 : ((mode & 2048) ? 8 : 0);
+  g_cfg_slabs = (mode & 4096) ? 1 : 0;
   g_cfg_swap = (mode & 128) ? 1 : ((mode & 256) ? 2 : 0);  // 128: never the swapped form, 256: wherever it exists
   g_cfg_pair_swap = (mode & 512) ? 0 : 1;                  // 512: the swapped form on single CTAs only
   g_cfg_mode = family;

@@ -101,6 +101,14 @@ __device__ __forceinline__ void tma_load_3d(uint32_t smem_dst, const void* tenso
       ::"r"(smem_dst), "l"(tensor_map), "r"(bar), "r"(x), "r"(y), "r"(z)
       : "memory");
 }
+__device__ __forceinline__ void tma_load_4d(uint32_t smem_dst, const void* tensor_map, uint32_t bar,
+                                            int32_t x, int32_t y, int32_t z, int32_t w) {
+  asm volatile(
+      "cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes "
+      "[%0], [%1, {%3, %4, %5, %6}], [%2];"
+      ::"r"(smem_dst), "l"(tensor_map), "r"(bar), "r"(x), "r"(y), "r"(z), "r"(w)
+      : "memory");
+}
 __device__ __forceinline__ void tma_load_2d_hint(uint32_t smem_dst, const void* tensor_map,
                                                  uint32_t bar, int32_t x, int32_t y,
                                                  uint64_t policy) {

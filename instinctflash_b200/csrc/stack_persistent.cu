@@ -7,10 +7,12 @@
 // 0.3-1.3 us of HBM time: launch latency, not bandwidth, bounds the per-operator path.
 //
 // Design (one CTA per SM, 224 threads):
-//   warp 0     W producer: streams 64-row weight tiles through a 12-stage shared-memory ring by
-//              TMA.  Weights do not depend on activations, so it runs ahead across operator
-//              boundaries: while the grid waits at a dependency, up to 96 KB of the next
-//              operator's weights per SM are already in flight (14 MB over the GPU, a whole layer).
+//   warp 0     W producer: streams 64-row weight tiles through a shared-memory ring by TMA, four
+//              128-byte K slabs per instruction and stage (the operands are mapped as
+//              [K / 128][rows][128 bytes]).  Weights do not depend on activations, so it runs
+//              ahead across operator boundaries: while the grid waits at a dependency, up to
+//              96 KB of the next operator's weights per SM are already in flight (14 MB over the
+//              GPU, a whole layer).
 //   warp 6     A producer: loads the activation tile of each K step into the same stage; it is
 //              the one that waits for grid-wide dependencies.
 //   warp 1     MMA issuer: tcgen05.mma 128 x 64 x 32 (rows >= M are padding, never stored),
@@ -37,7 +39,10 @@ namespace stackk {
 constexpr int BM = 128;       // UMMA M (rows >= M are padding)
 constexpr int BN = 64;        // weight rows (output columns) per tile
 constexpr int BK = 128;       // bytes per K step
-constexpr int STAGES = 12;
+constexpr int kSlabs = 4;     // 128-byte K slabs per stage and per TMA instruction: a CTA can issue a TMA
+                              // instruction about every 0.2 us, so a K step per instruction made the
+                              // activation loads of an operator (eight of them) its longest part
+constexpr int STAGES = 3;     // stages of kSlabs slabs (M <= 64); two for the 128-row activation box
 constexpr int A_ROWS = 64;    // rows of the activation box actually loaded (M <= 64) ...
 constexpr int A_ROWS_WIDE = 128;  // ... or 128 (64 < M <= 128), with 8 stages
 constexpr int kThreads = 224;
@@ -418,8 +423,10 @@ template <int AROWS, int NSTAGES>
 __global__ void __launch_bounds__(kThreads, 1)
 stack_persistent_kernel(const Op* __restrict__ ops, int num_ops, const CUtensorMap* __restrict__ maps,
                         uint32_t* __restrict__ bars, int M, uint32_t* __restrict__ status) {
-  constexpr int kABytes = AROWS * BK;
-  constexpr int kWBytes = BN * BK;
+  constexpr int kASlab = AROWS * BK;  // one K slab of the activation box
+  constexpr int kWSlab = BN * BK;
+  constexpr int kABytes = kSlabs * kASlab;
+  constexpr int kWBytes = kSlabs * kWSlab;
   constexpr int kStageBytes = kABytes + kWBytes;
   constexpr uint32_t kIdesc = make_idesc_e4m3_f32(BM, BN);
   constexpr uint32_t kTmemCols = 2 * BN;
@@ -477,7 +484,7 @@ stack_persistent_kernel(const Op* __restrict__ ops, int num_ops, const CUtensorM
         const int n_blk = item / op.split_k;
         int kb0, kb1;
         split_range(op, item % op.split_k, kb0, kb1);
-        for (int kb = kb0; kb < kb1; ++kb) {
+        for (int kb = kb0; kb < kb1; kb += kSlabs) {
           // the A producer reaches a stage after the W producer has freed and re-armed it or
           // before; either way both wait for the stage to be empty themselves
           ok = __all_sync(0xFFFFFFFFu, wait_mbar(empty_bar(stage), phase ^ 1, abort_flag, status,
@@ -497,15 +504,17 @@ stack_persistent_kernel(const Op* __restrict__ ops, int num_ops, const CUtensorM
             const uint32_t sa = base + stage * kStageBytes;
             if (is_w) {
               mbar_arrive_expect_tx(full_bar(stage), kWBytes);
+              // kSlabs slabs from slab kb on (slabs past the end of K read as zeros; slabs past
+              // the end of this item's K range are loaded and not used)
               if (op.type == OP_GEMM_GATED)  // gate rows and up rows of the item's hidden units in one box
-                tma_load_3d(sa + kABytes, maps + op.tm_w, full_bar(stage), kb * BK, n_blk * HW, 0);
+                tma_load_4d(sa + kABytes, maps + op.tm_w, full_bar(stage), 0, n_blk * HW, 0, kb);
               else
-                tma_load_2d(sa + kABytes, maps + op.tm_w, full_bar(stage), kb * BK, n_blk * BN);
+                tma_load_3d(sa + kABytes, maps + op.tm_w, full_bar(stage), 0, n_blk * BN, kb);
             } else {
               mbar_arrive_expect_tx(full_bar(stage), kABytes);
-              tma_load_2d(sa, maps + op.tm_a, full_bar(stage), kb * BK, 0);
+              tma_load_3d(sa, maps + op.tm_a, full_bar(stage), 0, 0, kb);
               if (kb == kb0) TRACE(oi, 2);
-              if (kb == kb1 - 1) TRACE(oi, 3);
+              if (kb + kSlabs >= kb1) TRACE(oi, 3);
             }
           }
           __syncwarp();
@@ -540,7 +549,7 @@ stack_persistent_kernel(const Op* __restrict__ ops, int num_ops, const CUtensorM
         if (!ok) break;
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + acc * BN;
-        for (int kb = kb0; kb < kb1; ++kb) {
+        for (int kb = kb0; kb < kb1; kb += kSlabs) {
           ok = __all_sync(0xFFFFFFFFu, wait_mbar(full_bar(stage), phase, abort_flag, status,
                                                  (2u << 24) | (3u << 16) | (uint32_t)oi));
           if (!ok) break;
@@ -548,11 +557,15 @@ stack_persistent_kernel(const Op* __restrict__ ops, int num_ops, const CUtensorM
           if (lane == 0) {
             if (kb == kb0) TRACE(oi, 4);
             const uint32_t sa = base + stage * kStageBytes;
-            const uint64_t da = make_kmajor_sw128_desc(sa);
-            const uint64_t db = make_kmajor_sw128_desc(sa + kABytes);
 #pragma unroll
-            for (int j = 0; j < BK / 32; ++j)
-              mma_f8f6f4(d_tmem, da + 2 * j, db + 2 * j, kIdesc, (kb > kb0 || j > 0) ? 1u : 0u);
+            for (int sl = 0; sl < kSlabs; ++sl) {
+              if (kb + sl >= kb1) break;
+              const uint64_t da = make_kmajor_sw128_desc(sa + sl * kASlab);
+              const uint64_t db = make_kmajor_sw128_desc(sa + kABytes + sl * kWSlab);
+#pragma unroll
+              for (int j = 0; j < BK / 32; ++j)
+                mma_f8f6f4(d_tmem, da + 2 * j, db + 2 * j, kIdesc, (kb + sl > kb0 || j > 0) ? 1u : 0u);
+            }
             mma_commit(empty_bar(stage));
           }
           __syncwarp();
@@ -718,12 +731,13 @@ extern "C" int iflb200_encode_operand_map(void* out128, const void* ptr, int row
       return IFLB200_ERR_DRIVER;
     fn = reinterpret_cast<EncodeTiledFn2>(p);
   }
+  if (K % BK) return IFLB200_ERR_SHAPE;  // operands are mapped as [K / 128][rows][128 bytes]
   alignas(64) CUtensorMap tm;
-  const cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)rows};
-  const cuuint64_t strides[1] = {(cuuint64_t)ld};
-  const cuuint32_t box[2] = {(cuuint32_t)BK, (cuuint32_t)box_rows};
-  const cuuint32_t estr[2] = {1, 1};
-  const CUresult r = fn(&tm, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(ptr), dims, strides, box, estr,
+  const cuuint64_t dims[3] = {(cuuint64_t)BK, (cuuint64_t)rows, (cuuint64_t)(K / BK)};
+  const cuuint64_t strides[2] = {(cuuint64_t)ld, (cuuint64_t)BK};
+  const cuuint32_t box[3] = {(cuuint32_t)BK, (cuuint32_t)box_rows, (cuuint32_t)kSlabs};
+  const cuuint32_t estr[3] = {1, 1, 1};
+  const CUresult r = fn(&tm, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, const_cast<void*>(ptr), dims, strides, box, estr,
                         CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                         CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS) return IFLB200_ERR_DRIVER;
@@ -739,6 +753,7 @@ extern "C" __attribute__((visibility("default"))) int iflb200_exp_stack_trace(un
 
 extern "C" int iflb200_encode_gated_weight_map(void* out128, const void* ptr, int F, int K, int64_t ld) {
   if (!out128 || !ptr || F <= 0 || F % 8 || K < 16 || K % 16 || ld < K || ld % 16) return IFLB200_ERR_ARG;
+  if (K % BK) return IFLB200_ERR_SHAPE;
   if (reinterpret_cast<uintptr_t>(ptr) & 15) return IFLB200_ERR_ALIGN;
   void* fp = nullptr;
   cudaDriverEntryPointQueryResult q;
@@ -747,11 +762,11 @@ extern "C" int iflb200_encode_gated_weight_map(void* out128, const void* ptr, in
     return IFLB200_ERR_DRIVER;
   EncodeTiledFn2 fn = reinterpret_cast<EncodeTiledFn2>(fp);
   alignas(64) CUtensorMap tm;
-  const cuuint64_t dims[3] = {(cuuint64_t)K, (cuuint64_t)F, 2};
-  const cuuint64_t strides[2] = {(cuuint64_t)ld, (cuuint64_t)ld * (cuuint64_t)F};
-  const cuuint32_t box[3] = {(cuuint32_t)BK, (cuuint32_t)HW, 2};
-  const cuuint32_t estr[3] = {1, 1, 1};
-  const CUresult r = fn(&tm, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, const_cast<void*>(ptr), dims, strides, box, estr,
+  const cuuint64_t dims[4] = {(cuuint64_t)BK, (cuuint64_t)F, 2, (cuuint64_t)(K / BK)};
+  const cuuint64_t strides[3] = {(cuuint64_t)ld, (cuuint64_t)ld * (cuuint64_t)F, (cuuint64_t)BK};
+  const cuuint32_t box[4] = {(cuuint32_t)BK, (cuuint32_t)HW, 2, (cuuint32_t)kSlabs};
+  const cuuint32_t estr[4] = {1, 1, 1, 1};
+  const CUresult r = fn(&tm, CU_TENSOR_MAP_DATA_TYPE_UINT8, 4, const_cast<void*>(ptr), dims, strides, box, estr,
                         CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                         CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS) return IFLB200_ERR_DRIVER;
@@ -787,11 +802,11 @@ extern "C" int iflb200_stack_run(const void* ops, int num_ops, const void* tenso
   uint32_t* dstatus = reinterpret_cast<uint32_t*>(status2);
   void* args[] = {(void*)&dops, (void*)&num_ops, (void*)&dmaps, (void*)&dbars, (void*)&M, (void*)&dstatus};
   const bool narrow = M <= A_ROWS;
-  const size_t smem = (narrow ? (size_t)STAGES * (A_ROWS * BK + BN * BK) + (BM - A_ROWS) * BK
-                              : (size_t)8 * (A_ROWS_WIDE * BK + BN * BK)) +
+  const size_t smem = (narrow ? (size_t)STAGES * kSlabs * (A_ROWS * BK + BN * BK) + (BM - A_ROWS) * BK
+                              : (size_t)2 * kSlabs * (A_ROWS_WIDE * BK + BN * BK)) +
                       sizeof(Shared) + 1024;
   const void* fn = narrow ? (const void*)stack_persistent_kernel<A_ROWS, STAGES>
-                          : (const void*)stack_persistent_kernel<A_ROWS_WIDE, 8>;
+                          : (const void*)stack_persistent_kernel<A_ROWS_WIDE, 2>;
   static bool attr_set[2][64] = {};
   if (dev < 64 && !attr_set[narrow][dev]) {
     e = cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);

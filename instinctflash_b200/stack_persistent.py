@@ -46,6 +46,8 @@ class PersistentExpertStack:
             raise ValueError("the persistent stack covers Gemma-shape expert layers without an O projection")
         if spec.M > 128:
             raise ValueError("the persistent stack is for skinny activations (M <= 128)")
+        if spec.hidden % 128 or spec.ffn % 128:
+            raise ValueError("the persistent stack maps its operands in 128-byte K slabs: hidden and ffn must be multiples of 128")
         if spec.ffn > 8192 or spec.hidden > 8192:
             raise ValueError("row operators of the persistent stack hold at most 8192 columns")
         lib = _lib.lib()

@@ -85,9 +85,9 @@ def test_tuning_switches_validate_their_arguments():
     defaults are restored afterwards (no device is touched)."""
     lib = _lib.lib()
     try:
-        for ok in (0, 1, 2, 3, 16, 128, 256, 256 + 512, 3 + 16, 1024, 2048):
+        for ok in (0, 1, 2, 3, 16, 128, 256, 256 + 512, 3 + 16, 1024, 2048, 4096):
             assert lib.iflb200_gemm_set_mode(ok) == 0, ok
-        for bad in (-1, 4, 32, 64, 3 + 16 + 64, 128 + 256, 1024 + 2048, 4096):
+        for bad in (-1, 4, 32, 64, 3 + 16 + 64, 128 + 256, 1024 + 2048, 8192):
             assert lib.iflb200_gemm_set_mode(bad) != 0, bad
         for ok in (0, 1, 2, 4):
             assert lib.iflb200_gemm_set_split_k(ok) == 0
