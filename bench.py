@@ -578,6 +578,39 @@ def run_tensor_parallel(args, spec, dev, dist, rank, world):
     leave(dev, dist)
 
 
+def profile_operator(args, spec, dev):
+    """One layer of the workload and `--steps` launches of one operator, nothing timed: the small,
+    self-ending program a profiler capture wants."""
+    from instinctflash_b200.kernels import fp8 as K
+    from instinctflash_b200.stack import LinearStack, StackSpec, make_inputs, make_weights
+    one = StackSpec(**{**spec.__dict__, "layers": 1, "steps": 1})
+    weights = make_weights(one, dev)
+    x, attn = make_inputs(one, dev)
+    st = LinearStack(one, weights, dev, fused=False if args.unfused else "auto")
+    st.load(x, attn)
+    st.forward()            # every buffer holds plausible values
+    torch.cuda.synchronize(dev)
+    if args.profile_op == "layer":
+        for _ in range(args.steps):
+            st.forward()
+    else:
+        lin = {n: (nn, kk) for n, nn, kk in one.linears()}
+        if args.profile_op not in lin:
+            raise SystemExit(f"--profile-op: {args.profile_op} is not one of {sorted(lin)} or 'layer'")
+        n, k = lin[args.profile_op]
+        w = weights[0].w[args.profile_op]
+        a = st._q8(k)
+        gated = st.fused and args.profile_op == "gate_up"
+        for _ in range(args.steps):
+            if gated:
+                K.fp8_linear_gated(a, st.scale[0], w, st.h, st.amax, act=0)
+            else:
+                K.gemm(a, w, st._raw(n))
+    torch.cuda.synchronize(dev)
+    check_no_timeout(dev)
+    print(json.dumps({"profiled": args.profile_op, "workload": workload_name(spec), "launches": args.steps}), flush=True)
+
+
 def leave(dev, dist):
     """A captured graph may hold NCCL work, and tearing the process group down under it has hung
     (watchdog stuck in event destruction): finish all work, then leave without the teardown."""
@@ -603,6 +636,10 @@ def main():
     ap.add_argument("--no-gpu-reference", action="store_true", help="do not time the reference's GPU kernels")
     ap.add_argument("--unfused", action="store_true", help="the reference's three-launch structure per linear")
     ap.add_argument("--fuse-residual", action="store_true", help="residual update in the GEMM epilogue as well")
+    ap.add_argument("--profile-op", default=None,
+                    help="for profilers: build ONE layer of the workload, launch only the named operator of the path "
+                         "`--steps` times (a linear of the stack: qkv, o, gate_up, down, ff1, ff2 ...; or 'layer' for "
+                         "one eager pass of the whole layer) and exit without timing anything")
     ap.add_argument("--gemm-mode", type=int, default=0, help="iflb200_gemm_set_mode value for the whole run (experiments)")
     ap.add_argument("--branches", type=int, default=EPISODE_BRANCHES, help="c3 episodes in flight per GPU")
     ap.add_argument("--episodes", type=int, default=1,
@@ -653,6 +690,10 @@ def main():
 
     if args.parallel == "tp":
         run_tensor_parallel(args, spec, dev, dist, rank, world)
+        return
+
+    if args.profile_op:
+        profile_operator(args, spec, dev)
         return
 
     ref_ops, ref_reason = (None, "switched off") if args.no_gpu_reference else reference_gpu_ops()

@@ -193,12 +193,45 @@ IFLB200_API int iflb200_residual_norm_quant(void* res, int res_dtype, int64_t ld
                                 void* y, int y_dtype, int64_t ld_y, void* stream);
 
 /*
+ * residual_norm_quant whose delta arrives as the fp32 partial sums of a K-split GEMM
+ * (iflb200_gemm_fp8_partials): delta_partials [splits][M][ld_delta] float32, 1 <= splits <= 8.  The
+ * planes are added in split order and the sum is rounded to bf16 -- the rounding point of the raw
+ * accumulator -- before the chain of iflb200_residual_norm_quant runs on it.  D <= 4096, 16-byte
+ * aligned rows.  Only the summation order of the accumulator differs from the unsplit sequence.
+ * Extends instinctflash/kernels/norm.py:26-124 for split-K producers; no reference counterpart
+ * for the split itself.
+ */
+IFLB200_API int iflb200_residual_norm_quant_partials(void* res, int res_dtype, int64_t ld_res, int M, int D,
+                                const float* delta_partials, int splits, int64_t ld_delta,
+                                const float* delta_row, const float* delta_col,
+                                const float* bias, const float* gate, int write_res,
+                                int layernorm, const float* weight, const float* beta,
+                                const float* mod_scale, const float* mod_shift,
+                                const int32_t* mod_index, float eps,
+                                void* q, int64_t ld_q, float* qs,
+                                void* y, int y_dtype, int64_t ld_y, void* stream);
+
+/*
  * Raw-accumulator FP8 GEMM: out[M,N] (bf16) = bf16_rn(sum_k a[m,k] * w[n,k]), fp32
  * accumulation on the tcgen05 tensor cores, unit scales.  K, N multiples of 16.
  * Replaces: instinctflash/kernels/fp8.py:50-53 (gemm -> torch._scaled_mm).
  */
 IFLB200_API int iflb200_gemm_fp8_raw(const void* a, int64_t ld_a, const void* w, int64_t ld_w,
                          int M, int N, int K, void* out, int64_t ld_out, void* stream);
+
+/*
+ * Split-K for skinny activations (M <= 128): K is divided into `splits` ranges, each range of each
+ * 64-column tile goes to its own CTA (tiles x splits CTAs, so that a deep reduction with few
+ * output columns still uses the whole GPU), and every CTA writes its fp32 partial sums:
+ *   out[s][m][n] = sum over the s-th K range of a[m,k] * w[n,k]       (no scales, no rounding)
+ * The consumer (iflb200_residual_norm_quant_partials) adds the planes in split order, so the
+ * result does not depend on timing.  K a multiple of 128; splits <= ceil(K / 512); `out` is
+ * scratch owned by the caller, splits * M * ld_out floats.
+ * Replaces: instinctflash/kernels/fp8.py:50-53 for the deep, narrow projections of the action
+ * expert (instinctflash/engines/pi05/engine.py:244-250); the split has no reference counterpart.
+ */
+IFLB200_API int iflb200_gemm_fp8_partials(const void* a, int64_t ld_a, const void* w, int64_t ld_w,
+                              int M, int N, int K, int splits, float* out, int64_t ld_out, void* stream);
 
 /*
  * Fused linear: GEMM + the dequant_rows consumer in the epilogue.

@@ -35,12 +35,15 @@ SIGNATURES = {
     "iflb200_gated_act_quant": (_i, [_p, _i, _l, _i, _i, _p, _p, _i, _p, _l, _p, _p]),
     "iflb200_residual_norm_quant": (_i, [_p, _i, _l, _i, _i, _p, _l, _p, _p, _p, _p, _i, _i, _p, _p,
                                          _p, _p, _p, _f, _p, _l, _p, _p, _i, _l, _p]),
+    "iflb200_residual_norm_quant_partials": (_i, [_p, _i, _l, _i, _i, _p, _i, _l, _p, _p, _p, _p, _i, _i, _p, _p,
+                                                  _p, _p, _p, _f, _p, _l, _p, _p, _i, _l, _p]),
     "iflb200_qkv_split": (_i, [_p, _i, _l, _i, _i, _i, _i, _p, _p, _p, _p, _p, _f, _p, _p, _l, _p, _p, _i,
                                _p, _l, _l, _p, _l, _l, _p, _l, _l, _i, _p]),
     "iflb200_wan_qkv": (_i, [_p, _i, _l, _i, _i, _i, _i, _p, _p, _p, _p, _p, _f, _p, _p, _l, _p, _p,
                              _p, _l, _p, _l, _l, _p, _l, _l, _i, _p]),
     "iflb200_attn_combine_quant": (_i, [_p, _p, _p, _i, _i, _i, _i, _i, _i, _p, _i, _l, _l, _l, _p, _l, _p, _p]),
     "iflb200_gemm_fp8_raw": (_i, [_p, _l, _p, _l, _i, _i, _i, _p, _l, _p]),
+    "iflb200_gemm_fp8_partials": (_i, [_p, _l, _p, _l, _i, _i, _i, _i, _p, _l, _p]),
     "iflb200_fp8_linear": (_i, [_p, _l, _p, _l, _i, _i, _i, _p, _i, _p, _i, _p, _i, _i, _p, _i, _l, _p]),
     "iflb200_fp8_linear_residual": (_i, [_p, _l, _p, _l, _i, _i, _i, _p, _p, _p, _p, _p, _p, _i, _l, _p]),
     "iflb200_fp8_linear_gated": (_i, [_p, _l, _p, _l, _i, _i, _i, _p, _p, _i, _p, _l, _p, _p]),

@@ -59,6 +59,8 @@ struct GemmParams {
   int64_t ld_out;
   int split_k;     // > 1: the CTAs of a cluster share one tile, each a K range; partials are summed over DSMEM
   int a_bytes;     // bytes one activation box delivers per K step: 128 x (rows of the box)
+  int partials;    // > 1: K is split over that many independent CTAs per tile; each writes its fp32 partial
+                   // accumulator to out[split][M][ld_out] (summed in split order by the consumer)
   int act;         // gated form: IFLB200_ACT_*
   uint32_t* amax;  // gated form: per-row maximum of |h| as float bits, raised with atomicMax
   int tma_store;  // 1: the epilogue stages 128-byte row pieces in shared memory and TMA-stores them
@@ -363,7 +365,7 @@ __device__ __forceinline__ void stage_columns(const GemmParams& p, const uint32_
 template <int BN>
 __device__ __forceinline__ void epilogue_tma_store(const GemmParams& p, const CUtensorMap* tm_out, uint32_t t_row,
                                                    uint32_t staging, uint8_t* staging_ptr, int row0, int n_base,
-                                                   int col_begin, int col_end, float rs, int lane) {
+                                                   int col_begin, int col_end, float rs, int lane, int z = -1) {
   const int es = (p.out_dtype == IFLB200_F32) ? 4 : 2;
   const int cols_per_store = 128 / es;  // 64 or 32
   uint8_t* mine = staging_ptr + lane * 128;
@@ -383,7 +385,8 @@ __device__ __forceinline__ void epilogue_tma_store(const GemmParams& p, const CU
     fence_proxy_async_smem();  // generic-proxy writes visible to the TMA unit
     __syncwarp();
     if (lane == 0) {
-      tma_store_2d(tm_out, staging, n0, row0);
+      if (z >= 0) tma_store_3d(tm_out, staging, n0, row0, z);  // partial sums: plane z of [splits][M][N]
+      else tma_store_2d(tm_out, staging, n0, row0);
       bulk_commit_group();
     }
   }
@@ -627,14 +630,17 @@ gemm_fp8_tc5_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
   const int lane = threadIdx.x & 31;
   // Split-K: the S CTAs of a cluster work on the same tile, CTA r on K steps [kb0, kb1); one
   // tile per CTA (the host launches tiles x S CTAs, at most one wave).
-  const bool split = SPLIT == 1 || (SPLIT == 2 && p.split_k > 1);
-  const int split_rank = split ? (int)cluster_ctarank() : 0;
-  const int tile_first = split ? (int)blockIdx.x / p.split_k : (int)blockIdx.x;
-  const int tile_stride = split ? p.num_tiles : (int)gridDim.x;
+  // Partials: K split over independent CTAs (no cluster), each writing its fp32 partial sums.
+  const bool partials = SPLIT == 2 && p.partials > 1;
+  const bool split = !partials && (SPLIT == 1 || (SPLIT == 2 && p.split_k > 1));
+  const int k_parts = partials ? p.partials : (split ? p.split_k : 1);
+  const int split_rank = partials ? (int)blockIdx.x % k_parts : (split ? (int)cluster_ctarank() : 0);
+  const int tile_first = k_parts > 1 ? (int)blockIdx.x / k_parts : (int)blockIdx.x;
+  const int tile_stride = k_parts > 1 ? p.num_tiles : (int)gridDim.x;
   // K ranges in whole stages (SL slabs each)
   const int k_stages = (p.num_k + SL - 1) / SL;
-  const int kb0 = split ? (int)(((int64_t)k_stages * split_rank) / p.split_k) * SL : 0;
-  const int kb1 = split ? min(p.num_k, (int)(((int64_t)k_stages * (split_rank + 1)) / p.split_k) * SL) : p.num_k;
+  const int kb0 = k_parts > 1 ? (int)(((int64_t)k_stages * split_rank) / k_parts) * SL : 0;
+  const int kb1 = k_parts > 1 ? min(p.num_k, (int)(((int64_t)k_stages * (split_rank + 1)) / k_parts) * SL) : p.num_k;
 
   if (threadIdx.x == 0) {
     prefetch_tensormap(&tm_a);
@@ -844,7 +850,7 @@ gemm_fp8_tc5_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
         const int per_store = (p.out_dtype == IFLB200_F32) ? 32 : 64;
         const int col_tma_end = col_begin + (col_end - col_begin) / per_store * per_store;
         epilogue_tma_store<BN>(p, &tm_out, t_row, staging, staging_ptr, m_blk * BM + quad * 32, n_blk * BN,
-                               col_begin, col_tma_end, rs, lane);
+                               col_begin, col_tma_end, rs, lane, partials ? split_rank : -1);
         if (BN % 64 != 0 && col_tma_end < col_end) {
           const int n0 = n_blk * BN + col_tma_end;
           if (n0 < p.N) {
@@ -1609,6 +1615,65 @@ static int run_gemm(const void* a, int64_t ld_a, const void* w, int64_t ld_w, Ge
   }
 }
 
+// [splits][M][N] fp32 partial sums; box = 32 columns (128 bytes) x 32 rows x 1 plane.
+static int make_partials_map(CUtensorMap* tm, void* ptr, int M, int N, int64_t ld, int splits) {
+  EncodeTiledFn enc = get_encode_fn();
+  if (!enc) return IFLB200_ERR_DRIVER;
+  const cuuint64_t dims[3] = {(cuuint64_t)N, (cuuint64_t)M, (cuuint64_t)splits};
+  const cuuint64_t strides[2] = {(cuuint64_t)ld * 4, (cuuint64_t)ld * 4 * (cuuint64_t)M};
+  const cuuint32_t box[3] = {32u, 32u, 1u};
+  const cuuint32_t estr[3] = {1, 1, 1};
+  const CUresult r = enc(tm, CU_TENSOR_MAP_DATA_TYPE_UINT32, 3, ptr, dims, strides, box, estr,
+                         CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_NONE,
+                         CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? IFLB200_OK : IFLB200_ERR_DRIVER;
+}
+
+// Split-K over independent CTAs for skinny activations: out[s][m][n] = sum over the s-th K range of
+// a[m,k] * w[n,k], fp32, no scales, no rounding; the consumer sums the planes in order (and rounds
+// the sum to bf16, the raw accumulator's rounding point).  K a multiple of 128, M <= 128.
+static int run_gemm_partials(const void* a, int64_t ld_a, const void* w, int64_t ld_w, int M, int N, int K, int splits,
+                             float* out, int64_t ld_out, void* stream) {
+  if (M < 0 || N < 0 || K < 0 || splits < 1) return IFLB200_ERR_ARG;
+  if (M == 0 || N == 0) return IFLB200_OK;
+  if (!a || !w || !out) return IFLB200_ERR_ARG;
+  if (K < BK || K % BK || N % 16 || M > BM) return IFLB200_ERR_SHAPE;
+  const int num_k = K / BK;
+  if (splits > (num_k + 3) / 4) return IFLB200_ERR_SHAPE;  // every split owns at least one stage of four slabs
+  if (ld_a < K || ld_w < K || ld_out < N) return IFLB200_ERR_ARG;
+  if ((reinterpret_cast<uintptr_t>(a) & 15) || (reinterpret_cast<uintptr_t>(w) & 15) || ld_a % 16 || ld_w % 16 ||
+      (reinterpret_cast<uintptr_t>(out) & 15) || (ld_out * 4) % 16)
+    return IFLB200_ERR_ALIGN;
+  DeviceInfo* dev = nullptr;
+  int st = device_info(&dev);
+  if (st != IFLB200_OK) return st;
+  GemmParams p = {};
+  p.M = M; p.N = N; p.K = K;
+  p.epilogue = EPI_DEQUANT;
+  p.exact = 1;
+  p.out = out; p.out_dtype = IFLB200_F32; p.ld_out = ld_out;
+  p.split_k = 1;
+  p.partials = splits;
+  p.tma_store = 1;
+  p.num_m = 1;
+  p.num_n = (N + 63) / 64;
+  p.num_k = num_k;
+  p.num_tiles = p.num_n;
+  p.group_m = 1;
+  const int a_rows = activation_box_rows(M);
+  p.a_bytes = a_rows * BK;
+  CUtensorMap ta, tw, to;
+  st = make_slab_map(&ta, a, M, K, ld_a, a_rows, 4);
+  if (st != IFLB200_OK) return st;
+  st = make_slab_map(&tw, w, N, K, ld_w, 64, 4);
+  if (st != IFLB200_OK) return st;
+  st = make_partials_map(&to, out, M, N, ld_out, splits);
+  if (st != IFLB200_OK) return st;
+  cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+  g_last_launch[0] = 1 + 16; g_last_launch[1] = 64; g_last_launch[2] = splits; g_last_launch[3] = 104;
+  return launch_gemm_form<64, 2, 2, false, false, kEpilogueWarps, 4>(ta, tw, to, p, p.num_tiles * splits, s);
+}
+
 // The gated form: W is [2F, K] = [gate rows | up rows]; h [M, F] fp32; amax [M] float bits.
 static int run_gemm_gated(const void* a, int64_t ld_a, const void* w, int64_t ld_w, int M, int F, int K,
                           const float* row, const float* col, int act, float* h, int64_t ld_h, uint32_t* amax,
@@ -1799,6 +1864,11 @@ extern "C" int iflb200_fp8_linear_residual(const void* a, int64_t ld_a, const vo
   p.gate = gate; p.gate_index = gate ? gate_index : nullptr;
   p.out = res; p.out_dtype = res_dtype; p.ld_out = ld_res;
   return run_gemm(a, ld_a, w, ld_w, p, stream);
+}
+
+extern "C" int iflb200_gemm_fp8_partials(const void* a, int64_t ld_a, const void* w, int64_t ld_w, int M, int N,
+                                         int K, int splits, float* out, int64_t ld_out, void* stream) {
+  return run_gemm_partials(a, ld_a, w, ld_w, M, N, K, splits, out, ld_out, stream);
 }
 
 extern "C" int iflb200_fp8_linear_gated(const void* a, int64_t ld_a, const void* w, int64_t ld_w, int M, int F,

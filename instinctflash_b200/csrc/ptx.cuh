@@ -125,6 +125,11 @@ __device__ __forceinline__ void tma_store_2d(const void* tensor_map, uint32_t sm
                ::"l"(tensor_map), "r"(smem_src), "r"(x), "r"(y)
                : "memory");
 }
+__device__ __forceinline__ void tma_store_3d(const void* tensor_map, uint32_t smem_src, int32_t x, int32_t y, int32_t z) {
+  asm volatile("cp.async.bulk.tensor.3d.global.shared::cta.bulk_group [%0, {%2, %3, %4}], [%1];"
+               ::"l"(tensor_map), "r"(smem_src), "r"(x), "r"(y), "r"(z)
+               : "memory");
+}
 __device__ __forceinline__ void bulk_commit_group() {
   asm volatile("cp.async.bulk.commit_group;" ::: "memory");
 }

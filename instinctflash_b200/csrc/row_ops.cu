@@ -498,6 +498,10 @@ struct ResNormArgs {
   int M, D, iters;
   const __nv_bfloat16* delta;
   int64_t ld_delta;
+  // the delta as fp32 partial sums of a K-split GEMM, [dsplits][M][ld_delta] (delta is null then): summed in
+  // split order and rounded to bf16, the raw accumulator's rounding point
+  const float* dpart;
+  int dsplits;
   const float* drow;
   const float* dcol;
   const float* bias;
@@ -527,7 +531,9 @@ __device__ __forceinline__ float round_through<__nv_bfloat16>(float x) {
   return __bfloat162float(__float2bfloat16_rn(x));
 }
 
-template <typename RT, int TPR, int IT, bool FAST>
+// PART: the delta arrives as fp32 partial sums of a K-split GEMM (a.dpart) instead of a raw bf16
+// accumulator; a separate instantiation so that the ordinary one keeps its registers.
+template <typename RT, int TPR, int IT, bool FAST, bool PART = false>
 __global__ void __launch_bounds__(kRowThreads, resnorm_min_blocks<IT>())
 residual_norm_quant_kernel(const ResNormArgs a) {
   row_dependency_wait();  // inputs may come from the kernel before this one in the stream
@@ -538,6 +544,8 @@ residual_norm_quant_kernel(const ResNormArgs a) {
   const bool live = m < a.M;
   RT* rr = reinterpret_cast<RT*>(a.res) + (live ? (int64_t)m * a.ld_res : 0);
   const __nv_bfloat16* dr = a.delta ? a.delta + (live ? (int64_t)m * a.ld_delta : 0) : nullptr;
+  const float* dp = PART ? a.dpart + (live ? (int64_t)m * a.ld_delta : 0) : nullptr;
+  const int64_t dp_plane = (int64_t)a.M * a.ld_delta;
   const int64_t mofs = (live && a.mod_index) ? (int64_t)a.mod_index[m] * a.D : 0;
   const float drs = (live && a.drow) ? a.drow[m] : 1.0f;
   const float fD = (float)a.D;
@@ -549,7 +557,7 @@ residual_norm_quant_kernel(const ResNormArgs a) {
     const int c0 = (it * TPR + t) * 8;
     const bool on = it < a.iters && live && c0 < a.D;
     rres[it] = fetch<FAST, RT>(rr, c0, a.D, on);
-    rdel[it] = fetch<FAST, __nv_bfloat16>(dr, c0, a.D, on && dr != nullptr);
+    rdel[it] = fetch<FAST, __nv_bfloat16>(dr, c0, a.D, on && dr != nullptr && !PART);
   }
   float x[IT][8];
   float sum = 0.0f, sumsq = 0.0f;
@@ -558,9 +566,31 @@ residual_norm_quant_kernel(const ResNormArgs a) {
     const int c0 = (it * TPR + t) * 8;
     unpack(rres[it], x[it]);
     if (it < a.iters && live && c0 < a.D) {
-      if (dr) {
+      if (dr || PART) {
         float d[8], cs[8], bs[8], gs[8];
-        unpack(rdel[it], d);
+        if constexpr (PART) {
+          // four planes in flight together, added in split order
+#pragma unroll
+          for (int i = 0; i < 8; ++i) d[i] = 0.0f;
+#pragma unroll 1
+          for (int s0 = 0; s0 < a.dsplits; s0 += 4) {
+            float e[4][8];
+#pragma unroll
+            for (int sp = 0; sp < 4; ++sp)
+              if (s0 + sp < a.dsplits) load_f32<FAST>(dp + (s0 + sp) * dp_plane, c0, a.D, e[sp]);
+#pragma unroll
+            for (int sp = 0; sp < 4; ++sp) {
+              if (s0 + sp < a.dsplits) {
+#pragma unroll
+                for (int i = 0; i < 8; ++i) d[i] = (s0 + sp == 0) ? e[sp][i] : __fadd_rn(d[i], e[sp][i]);
+              }
+            }
+          }
+#pragma unroll
+          for (int i = 0; i < 8; ++i) d[i] = __bfloat162float(__float2bfloat16_rn(d[i]));
+        } else {
+          unpack(rdel[it], d);
+        }
         if (a.dcol) load_f32<FAST>(a.dcol, c0, a.D, cs);
         if (a.bias) load_f32<FAST>(a.bias, c0, a.D, bs);
         if (a.gate) load_f32<FAST>(a.gate + mofs, c0, a.D, gs);
@@ -866,6 +896,26 @@ static void launch_gated(GatedArgs a, bool fast, cudaStream_t s) {
     launch_dep(gated_act_quant_kernel<XT, TPR, IT, true>, dim3(grid), dim3(kRowThreads), 0, s, 1, dependent_launch_for(a.M), a);
   });
 }
+// The partial-sum form: rows of at most 4096 columns on the aligned path (skinny activations).
+template <typename RT>
+static int launch_resnorm_partials(ResNormArgs a, bool fast, cudaStream_t s) {
+  if (!fast || a.D > 4096) return IFLB200_ERR_SHAPE;
+  if (a.D <= 1024) {
+    a.iters = 1;
+    launch_dep(residual_norm_quant_kernel<RT, 128, 1, true, true>, dim3((a.M + 1) / 2), dim3(kRowThreads), 0, s, 1,
+               dependent_launch_for(a.M), a);
+  } else if (a.D <= 2048) {
+    a.iters = 1;
+    launch_dep(residual_norm_quant_kernel<RT, kRowThreads, 1, true, true>, dim3(a.M), dim3(kRowThreads), 0, s, 1,
+               dependent_launch_for(a.M), a);
+  } else {
+    a.iters = 2;
+    launch_dep(residual_norm_quant_kernel<RT, kRowThreads, 2, true, true>, dim3(a.M), dim3(kRowThreads), 0, s, 1,
+               dependent_launch_for(a.M), a);
+  }
+  return IFLB200_OK;
+}
+
 template <typename RT>
 static void launch_resnorm(ResNormArgs a, bool fast, cudaStream_t s) {
   if (!fast) {
@@ -1017,15 +1067,11 @@ extern "C" int iflb200_dequant_rows(const void* x, int x_dtype, int64_t ld_x, in
 #endif
 
 #if IFLB200_ROW_PART == 2 || IFLB200_ROW_PART == -1
-extern "C" int iflb200_residual_norm_quant(void* res, int res_dtype, int64_t ld_res, int M, int D,
-                                           const void* delta, int64_t ld_delta,
-                                           const float* delta_row, const float* delta_col,
-                                           const float* bias, const float* gate, int write_res,
-                                           int layernorm, const float* weight, const float* beta,
-                                           const float* mod_scale, const float* mod_shift,
-                                           const int32_t* mod_index, float eps,
-                                           void* q, int64_t ld_q, float* qs,
-                                           void* y, int y_dtype, int64_t ld_y, void* stream) {
+static int resnorm_impl(void* res, int res_dtype, int64_t ld_res, int M, int D, const void* delta, int delta_splits,
+                        int64_t ld_delta, const float* delta_row, const float* delta_col, const float* bias,
+                        const float* gate, int write_res, int layernorm, const float* weight, const float* beta,
+                        const float* mod_scale, const float* mod_shift, const int32_t* mod_index, float eps, void* q,
+                        int64_t ld_q, float* qs, void* y, int y_dtype, int64_t ld_y, void* stream) {
   if (M < 0 || D < 0) return IFLB200_ERR_ARG;
   if (M == 0 || D == 0) return IFLB200_OK;
   if (!res) return IFLB200_ERR_ARG;
@@ -1037,7 +1083,10 @@ extern "C" int iflb200_residual_norm_quant(void* res, int res_dtype, int64_t ld_
   if (ld_res < D || (delta && ld_delta < D) || (q && ld_q < D) || (y && ld_y < D)) return IFLB200_ERR_ARG;
   ResNormArgs a;
   a.res = res; a.ld_res = ld_res; a.M = M; a.D = D;
-  a.delta = reinterpret_cast<const __nv_bfloat16*>(delta); a.ld_delta = ld_delta;
+  a.delta = delta_splits ? nullptr : reinterpret_cast<const __nv_bfloat16*>(delta);
+  a.dpart = delta_splits ? reinterpret_cast<const float*>(delta) : nullptr;
+  a.dsplits = delta_splits;
+  a.ld_delta = ld_delta;
   a.drow = delta ? delta_row : nullptr; a.dcol = delta ? delta_col : nullptr;
   a.bias = delta ? bias : nullptr; a.gate = delta ? gate : nullptr;
   a.write_res = (write_res && delta) ? 1 : 0;
@@ -1050,13 +1099,47 @@ extern "C" int iflb200_residual_norm_quant(void* res, int res_dtype, int64_t ld_
                          (!beta || aligned16(beta)) && (!mod_scale || aligned16(mod_scale)) &&
                          (!mod_shift || aligned16(mod_shift));
   const bool fast = D % 8 == 0 && aligned16(res) && (ld_res * esize(res_dtype)) % 16 == 0 &&
-                    (!delta || (aligned16(delta) && (ld_delta * 2) % 16 == 0)) &&
+                    (!delta || (aligned16(delta) && (ld_delta * (delta_splits ? 4 : 2)) % 16 == 0)) &&
                     (!q || (aligned8(q) && ld_q % 8 == 0)) &&
                     (!y || (aligned16(y) && (ld_y * esize(y_dtype)) % 16 == 0)) && tables_ok;
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+  if (delta_splits) {
+    const int st = res_dtype == IFLB200_F32 ? launch_resnorm_partials<float>(a, fast, s)
+                                            : launch_resnorm_partials<__nv_bfloat16>(a, fast, s);
+    if (st != IFLB200_OK) return st;
+    return (int)cudaGetLastError();
+  }
   if (res_dtype == IFLB200_F32) launch_resnorm<float>(a, fast, s);
   else launch_resnorm<__nv_bfloat16>(a, fast, s);
   return (int)cudaGetLastError();
+}
+
+extern "C" int iflb200_residual_norm_quant(void* res, int res_dtype, int64_t ld_res, int M, int D,
+                                           const void* delta, int64_t ld_delta,
+                                           const float* delta_row, const float* delta_col,
+                                           const float* bias, const float* gate, int write_res,
+                                           int layernorm, const float* weight, const float* beta,
+                                           const float* mod_scale, const float* mod_shift,
+                                           const int32_t* mod_index, float eps,
+                                           void* q, int64_t ld_q, float* qs,
+                                           void* y, int y_dtype, int64_t ld_y, void* stream) {
+  return resnorm_impl(res, res_dtype, ld_res, M, D, delta, 0, ld_delta, delta_row, delta_col, bias, gate, write_res,
+                      layernorm, weight, beta, mod_scale, mod_shift, mod_index, eps, q, ld_q, qs, y, y_dtype, ld_y, stream);
+}
+
+extern "C" int iflb200_residual_norm_quant_partials(void* res, int res_dtype, int64_t ld_res, int M, int D,
+                                                    const float* delta_partials, int splits, int64_t ld_delta,
+                                                    const float* delta_row, const float* delta_col,
+                                                    const float* bias, const float* gate, int write_res,
+                                                    int layernorm, const float* weight, const float* beta,
+                                                    const float* mod_scale, const float* mod_shift,
+                                                    const int32_t* mod_index, float eps,
+                                                    void* q, int64_t ld_q, float* qs,
+                                                    void* y, int y_dtype, int64_t ld_y, void* stream) {
+  if (!delta_partials || splits < 1 || splits > 8) return IFLB200_ERR_ARG;
+  return resnorm_impl(res, res_dtype, ld_res, M, D, delta_partials, splits, ld_delta, delta_row, delta_col, bias, gate,
+                      write_res, layernorm, weight, beta, mod_scale, mod_shift, mod_index, eps, q, ld_q, qs, y, y_dtype,
+                      ld_y, stream);
 }
 
 #endif

@@ -291,18 +291,18 @@ __device__ void row_resnorm(const Op& op, int M, int m, int t, float (*red)[4]) 
     if (c0 < D) {
       float d[8], cs[8], r[8];
       if (op.split_k > 1) {
-        // partials in groups of four: the loads of a group are all in flight before the first add
+        // partials in groups of eight: the loads of a group are all in flight before the first add
         // (the sum itself runs in split order)
         const float* p0 = reinterpret_cast<const float*>(op.in) + (int64_t)m * op.ld_in + c0;
         const int64_t step = (int64_t)M * op.ld_in;
         load_f32x8_cg(p0, d);
-        for (int s = 1; s < op.split_k; s += 4) {
-          float e[4][8];
+        for (int s = 1; s < op.split_k; s += 8) {
+          float e[8][8];
 #pragma unroll
-          for (int q = 0; q < 4; ++q)
+          for (int q = 0; q < 8; ++q)
             if (s + q < op.split_k) load_f32x8_cg(p0 + (s + q) * step, e[q]);
 #pragma unroll
-          for (int q = 0; q < 4; ++q) {
+          for (int q = 0; q < 8; ++q) {
             if (s + q < op.split_k) {
 #pragma unroll
               for (int i = 0; i < 8; ++i) d[i] = __fadd_rn(d[i], e[q][i]);

@@ -169,3 +169,27 @@ def fp8_linear_gated(a: torch.Tensor, a_scale: torch.Tensor, w: Fp8Weight, h: to
     launch("iflb200_fp8_linear_gated", a, a.data_ptr(), ld(a), w.w.data_ptr(), ld(w.w), M, F, K, _lib.ptr(rs),
            _lib.ptr(cs), int(act), h.data_ptr(), ld(h), amax.data_ptr())
     return h
+
+
+def partial_splits(M: int, N: int, K: int, sm_count: int = 148) -> int:
+    """How many K ranges ``gemm_partials`` should use for a skinny projection: enough (tile, range)
+    pairs to occupy the GPU, every range at least four 128-byte K slabs, at most eight planes."""
+    if M > 128 or K % 128:
+        return 1
+    tiles = (N + 63) // 64
+    return max(1, min(8, sm_count // max(1, tiles), (K // 128) // 4))
+
+
+def gemm_partials(a: torch.Tensor, w: Fp8Weight, out: torch.Tensor) -> torch.Tensor:
+    """Split-K ``gemm`` for skinny activations: ``out`` [S, M, N] float32 receives the partial sums of
+    S K ranges (no scales, no rounding); ``norm.residual_norm_quant(..., delta=out)`` adds the planes
+    in order, rounds the sum to bf16 (the raw accumulator's rounding point) and goes on as usual."""
+    M, N, K = _operands(a, w)
+    if out.dtype != torch.float32 or out.ndim != 3 or tuple(out.shape[1:]) != (M, N) or not out.is_contiguous():
+        raise ValueError(f"out must be a contiguous float32 [S, {M}, {N}] tensor")
+    if M > 128 or K % 128:
+        raise ValueError("gemm_partials is for at most 128 rows and K a multiple of 128")
+    same_device(a, out=out)
+    launch("iflb200_gemm_fp8_partials", a, a.data_ptr(), ld(a), w.w.data_ptr(), ld(w.w), M, N, K, int(out.shape[0]),
+           out.data_ptr(), N)
+    return out

@@ -98,7 +98,14 @@ def residual_norm_quant(res, *, delta=None, delta_row=None, delta_col=None, bias
     rows(res, "res", (torch.float32, torch.bfloat16))
     M, D = res.shape
     dev = res.device
-    if delta is not None:
+    partials = delta is not None and delta.ndim == 3
+    if partials:
+        # fp32 partial sums of a K-split GEMM (fp8.gemm_partials): [S, M, D], added in split order
+        if delta.dtype != torch.float32 or tuple(delta.shape[1:]) != (M, D) or not delta.is_contiguous() or not 1 <= delta.shape[0] <= 8:
+            raise ValueError(f"split-K partial sums must be a contiguous float32 [S <= 8, {M}, {D}] tensor")
+        if delta.device.type != "cuda":
+            raise ValueError("delta must live on a CUDA device; this path has no CPU implementation")
+    elif delta is not None:
         rows(delta, "delta", (torch.bfloat16,))
         if tuple(delta.shape) != (M, D):
             raise ValueError(f"delta must be [{M}, {D}], got {tuple(delta.shape)}")
@@ -118,9 +125,10 @@ def residual_norm_quant(res, *, delta=None, delta_row=None, delta_col=None, bias
     if mod_index is not None and (mod_index.dtype != torch.int32 or mod_index.numel() < M):
         raise ValueError("mod_index must be int32 with one entry per row")
     same_device(res, delta=delta, q=q, y=y, mod_index=mod_index)
-    launch("iflb200_residual_norm_quant", res,
+    launch("iflb200_residual_norm_quant_partials" if partials else "iflb200_residual_norm_quant", res,
         res.data_ptr(), _lib.dtype_code(res.dtype), ld(res), M, D,
-        _lib.ptr(delta), ld(delta) if delta is not None else 0,
+        *((delta.data_ptr(), int(delta.shape[0]), D) if partials else
+          (_lib.ptr(delta), ld(delta) if delta is not None else 0)),
         _lib.ptr(vec(delta_row, "delta_row", M, dev)), _lib.ptr(vec(delta_col, "delta_col", D, dev)),
         _lib.ptr(vec(bias, "bias", D, dev)), _lib.ptr(vec(gate, "gate", D, dev)), int(bool(write_res)),
         int(bool(layernorm)), _lib.ptr(vec(weight, "weight", D, dev)), _lib.ptr(vec(beta, "beta", D, dev)),

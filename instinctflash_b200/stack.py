@@ -33,7 +33,8 @@ def native_ops() -> SimpleNamespace:
                            residual_norm_quant=_norm.residual_norm_quant, gated_act_quant=_act.gated_act_quant,
                            GELU_TANH=_act.GELU_TANH, Fp8Weight=_fp8.Fp8Weight,
                            fp8_linear_gated=_fp8.fp8_linear_gated, row_quant_from_amax=_norm.row_quant_from_amax,
-                           fp8_linear_residual=_fp8.fp8_linear_residual)
+                           fp8_linear_residual=_fp8.fp8_linear_residual, gemm_partials=_fp8.gemm_partials,
+                           partial_splits=_fp8.partial_splits)
 
 
 @dataclass(frozen=True)
@@ -153,7 +154,8 @@ def make_inputs(spec: StackSpec, device, *, cpu_seeded: bool = True):
 class LinearStack:
     """Static buffers + the per-layer call sequence.  ``ops`` supplies the operators."""
 
-    def __init__(self, spec: StackSpec, weights, device, ops=None, *, fused="auto", fuse_residual: bool = False):
+    def __init__(self, spec: StackSpec, weights, device, ops=None, *, fused="auto", fuse_residual: bool = False,
+                 split_partials: bool = True):
         self.spec, self.weights, self.dev = spec, weights, torch.device(device)
         self.ops = ops or native_ops()
         # fused forms exist only in this package's operator set; "auto" takes the gated epilogue where the
@@ -163,6 +165,10 @@ class LinearStack:
             fused = spec.M > 128
         self.fused = bool(fused) and hasattr(self.ops, "fp8_linear_gated")
         self.fuse_residual = fuse_residual and hasattr(self.ops, "fp8_linear_residual")
+        # skinny activations: deep, narrow projections (down, o) run split-K over independent CTAs, the
+        # residual kernel adds the fp32 partial sums (this package's operators only)
+        self.split_partials = (split_partials and spec.kind == "gemma" and spec.M <= 128 and
+                               hasattr(self.ops, "gemm_partials"))
         M, D, F = spec.M, spec.hidden, spec.ffn
         dev, bf16, f32 = self.dev, torch.bfloat16, torch.float32
         widest_in = max(k for _, _, k in spec.linears())
@@ -174,6 +180,11 @@ class LinearStack:
         if self.fused and spec.kind == "gemma":
             self.h = torch.zeros(M, F, dtype=f32, device=dev)     # act(g) * u, never rounded to 16 bits
             self.amax = torch.zeros(M, dtype=f32, device=dev)     # row maxima of |h|; zero between calls
+        if self.split_partials:
+            sms = torch.cuda.get_device_properties(dev).multi_processor_count
+            ks = [k for name, n, k in spec.linears() if n == D and name in ("o", "down")]
+            self.splits = {k: self.ops.partial_splits(M, D, k, sms) for k in ks}
+            self.part = torch.zeros(max(self.splits.values(), default=1) * M * D, dtype=f32, device=dev)
         self.attn = None
         self.launches_per_forward = 0
 
@@ -240,7 +251,13 @@ class LinearStack:
         """res += (a @ w^T) * a_scale * w.scale, then RMS norm + quantiser of the new residual
         stream into q8 / scale[0] (Gemma layers).  Returns the number of launches."""
         o, D = self.ops, self.spec.hidden
-        if self.fuse_residual:
+        S = self.splits.get(a.shape[1], 1) if self.split_partials else 1
+        if S > 1:
+            part = self.part[: S * self.spec.M * D].view(S, self.spec.M, D)
+            o.gemm_partials(a, w, part)
+            o.residual_norm_quant(self.res, delta=part, delta_row=a_scale, delta_col=w.scale,
+                                  q=self._q8(D), q_scale=self.scale[0])
+        elif self.fuse_residual:
             o.fp8_linear_residual(a, a_scale, w, self.res)
             o.residual_norm_quant(self.res, q=self._q8(D), q_scale=self.scale[0])
         else:

@@ -59,7 +59,7 @@ class PersistentExpertStack:
         self.sms = sms = torch.cuda.get_device_properties(dev).multi_processor_count
         if down_split_k is None:
             # enough work items to occupy the SMs: (D / 64) column tiles x split_k
-            down_split_k = max(1, min(k_steps, sms // max(1, (D + 63) // 64)))
+            down_split_k = max(1, min(k_steps, 9, sms // max(1, (D + 63) // 64)))
         if not 1 <= down_split_k <= k_steps:
             raise ValueError("every K split needs at least one 128-byte step")
         self.split_k = down_split_k

@@ -51,12 +51,12 @@ def test_fused_epilogues_give_the_bits_of_the_three_launch_structure(M, hidden, 
     x, attn = make_inputs(spec, DEV)
     assert lib.iflb200_gemm_set_split_k(1) == 0      # same K loop in every arm
     try:
-        plain = LinearStack(spec, weights, DEV, fused=False)
+        plain = LinearStack(spec, weights, DEV, fused=False, split_partials=False)
         plain.load(x, attn)
         want = plain.forward().clone()
         want_q, want_s = plain._q8(hidden).view(torch.uint8).clone(), plain.scale[0].clone()
         for fuse_residual in (False, True):
-            st = LinearStack(spec, weights, DEV, fused=True, fuse_residual=fuse_residual)
+            st = LinearStack(spec, weights, DEV, fused=True, fuse_residual=fuse_residual, split_partials=False)
             assert st.fused and st.fuse_residual == fuse_residual
             st.load(x, attn)
             got = st.forward()
@@ -124,7 +124,7 @@ def test_persistent_stack_against_per_operator_stack(M, split, gated_in_gemm):
     spec = StackSpec("expert", "gemma", 3, M, 1024, 4096, 1536, steps=2, seed=2)
     weights = make_weights(spec, DEV)
     x, attn = make_inputs(spec, DEV)
-    ref = LinearStack(spec, weights, DEV)
+    ref = LinearStack(spec, weights, DEV, split_partials=False)
     ref.load(x, attn)
     _lib.lib().iflb200_gemm_set_split_k(1)   # the per-operator arm with the unsplit K loop
     try:
@@ -324,3 +324,50 @@ def test_results_do_not_depend_on_what_ran_before():
             got = cases_[n]()
             torch.cuda.synchronize()
             assert torch.equal(got, recorded[n]), f"{n} changed after {order}"
+
+
+@pytest.mark.parametrize("M,N,K", [(50, 1024, 4096), (7, 1024, 2048), (128, 2048, 4096), (50, 1024, 1024), (33, 272, 512)])
+def test_split_k_partials_feed_the_residual_kernel(M, N, K):
+    """Skinny split-K: (tile, K range) pairs on independent CTAs write fp32 partial sums, the residual
+    kernel adds the planes in split order and rounds the sum to bf16.  One plane reproduces
+    gemm + residual_norm_quant bit for bit; several planes differ only in the summation order of the
+    accumulator (GEMM bar) and are deterministic."""
+    import cases
+    from util import assert_gemm_parity
+    from instinctflash_b200.kernels import fp8, norm
+    E4M3 = torch.float8_e4m3fn
+    x = cases.activations(M, K, 5000 + M, outlier_frac=0.01, outlier_scale=20.0).to(DEV)
+    a = torch.empty(M, K, device=DEV, dtype=E4M3)
+    s = torch.empty(M, device=DEV)
+    norm.row_quant(x, a, s)
+    wq, wscale = cases.pack_weight_cpu(cases.weights(N, K, 5100 + N))
+    W = fp8.Fp8Weight(wq.to(DEV), wscale.to(DEV), None)
+    res0 = cases.activations(M, N, 5200, dtype=torch.float32).to(DEV)
+    raw = torch.empty(M, N, device=DEV, dtype=torch.bfloat16)
+    fp8.gemm(a, W, raw)
+    want = res0.clone()
+    q0 = torch.empty(M, N, device=DEV, dtype=E4M3)
+    s0 = torch.empty(M, device=DEV)
+    norm.residual_norm_quant(want, delta=raw, delta_row=s, delta_col=W.scale, q=q0, q_scale=s0)
+    limit = max(1, min(8, (K // 128 + 3) // 4))
+    suggested = fp8.partial_splits(M, N, K)
+    assert 1 <= suggested <= limit
+    for S in sorted({1, suggested, limit}):
+        part = torch.full((S, M, N), float("nan"), device=DEV)
+        fp8.gemm_partials(a, W, part)
+        assert not torch.isnan(part).any()
+        got = res0.clone()
+        q1 = torch.empty(M, N, device=DEV, dtype=E4M3)
+        s1 = torch.empty(M, device=DEV)
+        norm.residual_norm_quant(got, delta=part, delta_row=s, delta_col=W.scale, q=q1, q_scale=s1)
+        if S == 1:
+            assert torch.equal(got, want) and torch.equal(q1.view(torch.uint8), q0.view(torch.uint8)) and torch.equal(s1, s0)
+        else:
+            assert_gemm_parity(got - res0, want - res0, f"{S} planes")
+            again = res0.clone()
+            part2 = torch.empty_like(part)
+            fp8.gemm_partials(a, W, part2)
+            norm.residual_norm_quant(again, delta=part2, delta_row=s, delta_col=W.scale, q=q1, q_scale=s1)
+            assert torch.equal(part, part2) and torch.equal(again, got)
+    with pytest.raises(RuntimeError, match="unsupported shape"):
+        fp8.gemm_partials(a, W, torch.empty(limit + 1, M, N, device=DEV))
