@@ -850,7 +850,8 @@ gemm_fp8_tc5_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
         const int per_store = (p.out_dtype == IFLB200_F32) ? 32 : 64;
         const int col_tma_end = col_begin + (col_end - col_begin) / per_store * per_store;
         epilogue_tma_store<BN>(p, &tm_out, t_row, staging, staging_ptr, m_blk * BM + quad * 32, n_blk * BN,
-                               col_begin, col_tma_end, rs, lane, partials ? split_rank : -1);
+                               col_begin, col_tma_end, rs, lane,
+                               (SPLIT == 2 && p.partials >= 1) ? split_rank : -1);  // a plane map takes a 3-D store
         if (BN % 64 != 0 && col_tma_end < col_end) {
           const int n0 = n_blk * BN + col_tma_end;
           if (n0 < p.N) {
