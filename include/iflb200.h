@@ -393,6 +393,23 @@ IFLB200_API int iflb200_stack_run(const void* ops, int num_ops, const void* tens
 IFLB200_API int iflb200_gemm_take_timeout_record(uint32_t* record, void* stream);
 
 /*
+ * Barrier between the GPUs of a tensor-parallel group over peer memory.  Every rank owns `p` flag
+ * words that its peers can write (peer-mapped memory, zero at start); peer_flag_ptrs is a device
+ * array of `p` pointers, entry r = the address of rank r's flag words as seen from this GPU
+ * (entry `rank` is unused).  The call stores this rank's next arrival number into word `rank` of
+ * every peer's flags (release, system scope) and waits until every word of my_flags has reached
+ * it; `arrival` (one device word, zero at start) is advanced by the kernel, so the call can be
+ * replayed from a CUDA graph.  Work enqueued before the call on this stream -- kernels and copies
+ * that wrote into peers' memory -- is complete before the arrival is published; work enqueued after
+ * it runs after every peer has arrived.  The wait is bounded (iflb200_set_wait_budget_us): when it
+ * runs out, `status[0]` receives 0x50000000 | peer << 16 | arrival and the kernel returns.  Plain
+ * peer loads and stores; no multicast.  One process per GPU; never call it for two ranks that
+ * share a GPU.  No reference counterpart (the reference is single-GPU).
+ */
+IFLB200_API int iflb200_peer_barrier(const void* peer_flag_ptrs, void* my_flags, void* arrival, int rank, int p,
+                         void* status, void* stream);
+
+/*
  * Time budget of the waits inside the tcgen05 GEMM and the persistent stack kernel, in
  * microseconds (0 restores the default of 2 s).  A wait that outlives it makes the kernel record
  * where it gave up (iflb200_gemm_take_timeout_record / status2[0] of iflb200_stack_run), drain and

@@ -57,6 +57,7 @@ SIGNATURES = {
     "iflb200_stack_weight_box_rows": (_i, []),
     "iflb200_stack_run": (_i, [_p, _i, _p, _p, _i, _i, _p, _p]),
     "iflb200_gemm_take_timeout_record": (_i, [ctypes.POINTER(ctypes.c_uint32), _p]),
+    "iflb200_peer_barrier": (_i, [_p, _p, _p, _i, _i, _p, _p]),
     "iflb200_set_wait_budget_us": (_i, [_l]),
     "iflb200_gemm_last_launch": (_i, [ctypes.POINTER(_i), ctypes.POINTER(_i), ctypes.POINTER(_i)]),
     "iflb200_gemm_set_config": (_i, [_i, _i, _i]),

@@ -22,6 +22,7 @@ SOURCES = (("gemm_fp8_sm100.cu", (), "gemm_fp8_sm100"),
            ("stack_persistent.cu", (), "stack_persistent"),
            ("qkv_ops.cu", (), "qkv_ops"),
            ("attn_ops.cu", (), "attn_ops"),
+           ("xgpu_ops.cu", (), "xgpu_ops"),
            ("row_ops.cu", ("-DIFLB200_ROW_PART=0",), "row_ops_quant"),
            ("row_ops.cu", ("-DIFLB200_ROW_PART=1",), "row_ops_gated_pack"),
            ("row_ops.cu", ("-DIFLB200_ROW_PART=2",), "row_ops_resnorm"))

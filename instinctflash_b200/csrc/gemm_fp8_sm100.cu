@@ -71,6 +71,7 @@ __device__ uint32_t g_timeout_record[4];
 // Time budget of every wait inside the GEMM kernels (read only on the slow path of a wait).
 __device__ uint64_t g_gemm_wait_budget_ns = kWaitBudgetNs;
 int set_stack_wait_budget_ns(uint64_t ns);  // stack_persistent.cu
+int set_peer_wait_budget_ns(uint64_t ns);   // xgpu_ops.cu
 
 __device__ __forceinline__ uint32_t map_to_cta(uint32_t smem_addr, uint32_t rank) {
   uint32_t r;
@@ -1793,7 +1794,8 @@ extern "C" int iflb200_set_wait_budget_us(int64_t microseconds) {
   const uint64_t ns = microseconds ? (uint64_t)microseconds * 1000ull : kWaitBudgetNs;
   const cudaError_t e = cudaMemcpyToSymbol(g_gemm_wait_budget_ns, &ns, sizeof(ns));
   if (e != cudaSuccess) return (int)e;
-  return set_stack_wait_budget_ns(ns);
+  const int st = set_stack_wait_budget_ns(ns);
+  return st != 0 ? st : set_peer_wait_budget_ns(ns);
 }
 
 extern "C" int iflb200_gemm_last_launch(int* family, int* tile_n, int* split_k) {

@@ -376,3 +376,58 @@ def test_split_k_partials_feed_the_residual_kernel(M, N, K):
             assert torch.equal(part, part2) and torch.equal(again, got)
     with pytest.raises(RuntimeError, match="unsupported shape"):
         fp8.gemm_partials(a, W, torch.empty(limit + 1, M, N, device=DEV))
+
+
+def test_install_on_the_reference_engine_module_and_run_its_call_sequence_both_ways():
+    """The reference's pi05 engine module (unmodified, from baseline/_ref) before and after
+    install(): the names its _forward resolves (gemm, row_quant, gated_act_quant,
+    residual_norm_quant) drive the layer sequence of instinctflash/engines/pi05/engine.py:199-216
+    through the same driver.  After install() they are this package's operators (bit-identical to
+    calling the package directly); against the reference's own kernels the residual stream agrees
+    to quantisation noise and the first quantiser's codes are bit-identical."""
+    import importlib
+    import sys
+    from pathlib import Path
+    from types import SimpleNamespace
+    ref = Path(__file__).resolve().parents[1] / "baseline" / "_ref"
+    if not (ref / "instinctflash").is_dir():
+        pytest.skip("the reference is not installed under baseline/_ref")
+    sys.path.insert(0, str(ref))
+    try:
+        eng = importlib.import_module("instinctflash.engines.pi05.engine")
+        fp8_mod = importlib.import_module("instinctflash.kernels.fp8")
+    except Exception as exc:   # noqa: BLE001
+        pytest.skip(f"the reference's engine module does not import here: {exc}")
+    finally:
+        sys.path.remove(str(ref))
+    from instinctflash_b200 import install as inst
+
+    def resolved():
+        g = eng.Pi05Engine._forward.__globals__ if hasattr(eng, "Pi05Engine") else vars(eng)
+        return SimpleNamespace(gemm=g["gemm"], row_quant=g["row_quant"], residual_norm_quant=g["residual_norm_quant"],
+                               gated_act_quant=g["gated_act_quant"], dequant_rows=vars(importlib.import_module(
+                                   "instinctflash.kernels.norm"))["dequant_rows"], GELU_TANH=0, Fp8Weight=fp8_mod.Fp8Weight)
+
+    spec = StackSpec("t", "gemma", 2, 200, 512, 1024, 768, o_in=512, outlier_frac=0.02, outlier_scale=10.0, seed=41)
+    weights = make_weights(spec, DEV)
+    x, attn = make_inputs(spec, DEV)
+    saved = {n: getattr(eng, n) for n in inst.REPLACEMENTS if hasattr(eng, n)}
+    before = LinearStack(spec, weights, DEV, ops=resolved())
+    before.load(x, attn)
+    first_codes = before._q8(spec.hidden).view(torch.uint8).clone()
+    ref_res = before.forward().clone()
+    try:
+        report = inst.install([eng])
+        assert {"gemm", "row_quant", "gated_act_quant", "residual_norm_quant"} <= set(report[eng.__name__])
+        after = LinearStack(spec, weights, DEV, ops=resolved())
+        after.load(x, attn)
+        assert torch.equal(after._q8(spec.hidden).view(torch.uint8), first_codes)     # same norm + quantiser bits up to its tail
+        got = after.forward().clone()
+    finally:
+        for n, fn in saved.items():
+            setattr(eng, n, fn)
+    native = LinearStack(spec, weights, DEV, fused=False, split_partials=False)
+    native.load(x, attn)
+    assert torch.equal(native.forward(), got)                       # the installed names ARE this package's operators
+    rel = float((got - ref_res).norm() / ref_res.norm())
+    assert rel < 2e-2, rel
