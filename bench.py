@@ -489,21 +489,8 @@ def sharded_c4_tokens(dev, dist, rank, world, steps, warmup):
     return out
 
 
-def sharded_c4_tp(dev, dist, rank, world, steps, warmup):
-    """The Wan2.2-5B-shape stack tensor parallel: column-split qkv / cross-q / ff1, row-split
-    o / cross-o / ff2 with NCCL over NVLink."""
-    from instinctflash_b200.stack import SPECS, make_inputs, make_weights
-    from instinctflash_b200.tp import Comm, WanTPStack
-    spec = SPECS["c4"]
-    if spec.M % world:
-        return {"unavailable": f"M={spec.M} is not divisible by {world}"}
-    torch.manual_seed(1234)   # identical full weights on every rank, sharded afterwards
-    weights = make_weights(spec, dev)
-    stack = WanTPStack(spec, weights, dev, Comm() if dist is not None else Comm.single())
-    del weights
-    torch.cuda.empty_cache()
-    x, attn = make_inputs(spec, dev)
-    stack.load(x, attn)
+def _time_tp_stack(stack, dev, dist, steps, warmup):
+    """ms per pass of a tensor-parallel stack (graph replay when capture works), max over ranks."""
     stream = torch.cuda.current_stream(dev)
     graph = None
     try:
@@ -524,9 +511,52 @@ def sharded_c4_tp(dev, dist, rank, world, steps, warmup):
     if dist is not None:
         dist.barrier()
     ms = max_over_ranks(replay_ms(runner, steps, stream, dev) / steps, dist, dev)
-    return {"ms_per_step": ms, "tflops": spec.flops() / (ms * 1e-3) / 1e12, "cuda_graph": graph is not None,
-            "nvlink_bytes_per_rank_per_step": stack.comm_bytes_per_step(), "collective": stack.collectives,
-            "_keep": (stack, graph)}
+    if stack.link is not None:
+        stack.link.check()
+    return ms, graph
+
+
+def sharded_c4_tp(dev, dist, rank, world, steps, warmup):
+    """The Wan2.2-5B-shape stack tensor parallel: column-split qkv / cross-q / ff1, row-split
+    o / cross-o / ff2; the exchange steps over peer memory (the GEMM's stores into the row owner's
+    planes, single-CTA barrier kernels), with the NCCL transport timed beside it."""
+    from instinctflash_b200.stack import SPECS, make_inputs, make_weights
+    from instinctflash_b200.tp import Comm, PeerLink, WanTPStack
+    spec = SPECS["c4"]
+    if spec.M % world:
+        return {"unavailable": f"M={spec.M} is not divisible by {world}"}
+    torch.manual_seed(1234)   # identical full weights on every rank, sharded afterwards
+    weights = make_weights(spec, dev)
+    comm = Comm() if dist is not None else Comm.single()
+    x, attn = make_inputs(spec, dev)
+    out, keep = {}, []
+    link, why = None, None
+    if world > 1:
+        try:
+            link = PeerLink(WanTPStack.peer_layout(spec, world), dev)
+        except Exception as exc:   # noqa: BLE001
+            why = f"{type(exc).__name__}: {exc}"[:200]
+        ok = torch.tensor([1.0 if link is not None else 0.0], device=dev)
+        dist.all_reduce(ok, op=dist.ReduceOp.MIN)
+        if ok.item() == 0.0:
+            link = None
+    stacks = [("nccl", None)] + ([("peer", link)] if link is not None else [])
+    for name, lk in stacks:
+        stack = WanTPStack(spec, weights, dev, comm, link=lk)
+        stack.load(x, attn)
+        ms, graph = _time_tp_stack(stack, dev, dist, steps, warmup)
+        out[name] = {"ms_per_step": ms, "tflops": spec.flops() / (ms * 1e-3) / 1e12, "cuda_graph": graph is not None,
+                     "nvlink_bytes_per_rank_per_step": stack.comm_bytes_per_step(), "collective": stack.collectives}
+        keep.append((stack, graph))
+    del weights
+    best = min(out, key=lambda k: out[k]["ms_per_step"])
+    res = dict(out[best], transport=best if world > 1 else "none")
+    if world > 1:
+        res["transports"] = {k: {"ms_per_step": v["ms_per_step"]} for k, v in out.items()}
+        if why:
+            res["peer_unavailable"] = why
+    res["_keep"] = keep
+    return res
 
 
 # ------------------------------------------------------------------------------------------------

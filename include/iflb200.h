@@ -94,6 +94,16 @@ IFLB200_API int iflb200_row_quant_sharded(const void* x, int x_dtype, int64_t ld
                               void* stream);
 
 /*
+ * Phase 1 of iflb200_row_quant_sharded that also writes the row maxima into up to 7 further
+ * buffers: amax_mirrors is a HOST array of `mirrors` device pointers (the slots this rank owns in
+ * the other GPUs' peer-mapped buffers), so the maxima need no separate transfer before the barrier
+ * and the max over the ranks (iflb200_peer_exchange).  No reference counterpart.
+ */
+IFLB200_API int iflb200_row_max_sharded(const void* x, int x_dtype, int64_t ld_x, int M, int K,
+                            const float* row, const float* col, const float* bias, int gelu,
+                            float* amax, float* const* amax_mirrors, int mirrors, void* stream);
+
+/*
  * Consumer of a raw accumulator: y[m,n] = out_dtype(x[m,n] (*row[m]) (*col[n]) (+bias[n])),
  * the last multiply fused with the bias add (fma.rn) exactly as the reference compiles.
  * Replaces: instinctflash/kernels/norm.py:162-185 (_dequant_rows_kernel, dequant_rows).
@@ -196,7 +206,7 @@ IFLB200_API int iflb200_residual_norm_quant(void* res, int res_dtype, int64_t ld
  * residual_norm_quant whose delta arrives as the fp32 partial sums of a K-split GEMM
  * (iflb200_gemm_fp8_partials): delta_partials [splits][M][ld_delta] float32, 1 <= splits <= 8.  The
  * planes are added in split order and the sum is rounded to bf16 -- the rounding point of the raw
- * accumulator -- before the chain of iflb200_residual_norm_quant runs on it.  D <= 4096, 16-byte
+ * accumulator -- before the chain of iflb200_residual_norm_quant runs on it.  D <= 8192, 16-byte
  * aligned rows.  Only the summation order of the accumulator differs from the unsplit sequence.
  * Extends instinctflash/kernels/norm.py:26-124 for split-K producers; no reference counterpart
  * for the split itself.
@@ -210,6 +220,27 @@ IFLB200_API int iflb200_residual_norm_quant_partials(void* res, int res_dtype, i
                                 const int32_t* mod_index, float eps,
                                 void* q, int64_t ld_q, float* qs,
                                 void* y, int y_dtype, int64_t ld_y, void* stream);
+
+/*
+ * iflb200_residual_norm_quant_partials for the row owner of a tensor-parallel group: the planes are
+ * the ranks' partial sums of this rank's rows (plane r written by rank r's
+ * iflb200_gemm_fp8_rowblocks, summed in rank order: the reduce-scatter's sum at the same place
+ * before the bf16 rounding), and the codes and row scales are also written into up to 7 further
+ * buffers -- q_mirrors / qs_mirrors are HOST arrays of `mirrors` device pointers, the same rows of
+ * the other GPUs' replicas of the next block's input (peer-mapped; row stride ld_q) -- from the
+ * registers that hold them: the all-gather rides inside the kernel.  No `y` output.
+ * No reference counterpart (the reference is single-GPU).
+ */
+IFLB200_API int iflb200_residual_norm_quant_peers(void* res, int res_dtype, int64_t ld_res, int M, int D,
+                                const float* delta_partials, int splits, int64_t ld_delta,
+                                const float* delta_row, const float* delta_col,
+                                const float* bias, const float* gate, int write_res,
+                                int layernorm, const float* weight, const float* beta,
+                                const float* mod_scale, const float* mod_shift,
+                                const int32_t* mod_index, float eps,
+                                void* q, int64_t ld_q, float* qs,
+                                void* const* q_mirrors, float* const* qs_mirrors, int mirrors,
+                                void* stream);
 
 /*
  * Raw-accumulator FP8 GEMM: out[M,N] (bf16) = bf16_rn(sum_k a[m,k] * w[n,k]), fp32
@@ -393,6 +424,23 @@ IFLB200_API int iflb200_stack_run(const void* ops, int num_ops, const void* tens
 IFLB200_API int iflb200_gemm_take_timeout_record(uint32_t* record, void* stream);
 
 /*
+ * K-split linear of a tensor-parallel group as ONE launch whose stores go to several GPUs: `a` holds
+ * `groups` blocks of `group_rows` activation rows ([groups * group_rows, K] e4m3); block g's fp32
+ * accumulators a_g @ w^T (no scales, no rounding: the partial sums of this GPU's K range) are written
+ * through d_out_maps[g], an array of `groups` 128-byte tensor maps in DEVICE memory (64-byte
+ * aligned), each encoded by iflb200_encode_rowblock_map for a [group_rows, N] fp32 buffer that may
+ * live on this GPU or be a peer-mapped buffer of another one (TMA stores over NVLink; loads never
+ * touch peer memory).  The tiles of the blocks alternate in the launch order, so the stores towards
+ * a peer are spread over the whole launch and drain under the main loops of the other tiles: the
+ * transfer of a reduce-scatter rides inside the GEMM.  The K loop order is that of
+ * iflb200_fp8_linear: the bits of block g equal those of a separate call on its rows.
+ * No reference counterpart (the reference is single-GPU).
+ */
+IFLB200_API int iflb200_encode_rowblock_map(void* out, int rows, int N, int64_t ld_out, void* map128);
+IFLB200_API int iflb200_gemm_fp8_rowblocks(const void* a, int64_t ld_a, const void* w, int64_t ld_w, int groups,
+                               int group_rows, int N, int K, const void* d_out_maps, void* stream);
+
+/*
  * Barrier between the GPUs of a tensor-parallel group over peer memory.  Every rank owns `p` flag
  * words that its peers can write (peer-mapped memory, zero at start); peer_flag_ptrs is a device
  * array of `p` pointers, entry r = the address of rank r's flag words as seen from this GPU
@@ -402,12 +450,30 @@ IFLB200_API int iflb200_gemm_take_timeout_record(uint32_t* record, void* stream)
  * replayed from a CUDA graph.  Work enqueued before the call on this stream -- kernels and copies
  * that wrote into peers' memory -- is complete before the arrival is published; work enqueued after
  * it runs after every peer has arrived.  The wait is bounded (iflb200_set_wait_budget_us): when it
- * runs out, `status[0]` receives 0x50000000 | peer << 16 | arrival and the kernel returns.  Plain
+ * runs out, `status[0]` receives 0x50000000 | peer << 16 | arrival and the kernel returns; while
+ * status[0] is non-zero later calls signal and return without waiting (the host reads and clears
+ * the word).  Plain
  * peer loads and stores; no multicast.  One process per GPU; never call it for two ranks that
  * share a GPU.  No reference counterpart (the reference is single-GPU).
  */
 IFLB200_API int iflb200_peer_barrier(const void* peer_flag_ptrs, void* my_flags, void* arrival, int rank, int p,
                          void* status, void* stream);
+
+/*
+ * The barrier with a small payload in front and a reduction behind, one single-CTA kernel:
+ *   before signalling, copy `bytes` bytes (a multiple of 16; src and destinations 16-byte aligned)
+ *   from src into the buffer of every peer r != rank at peer_dst_ptrs[r] (a device array of `p`
+ *   pointers, as seen from this GPU);
+ *   after every peer has arrived, max_out[i] = max over r < p of max_in[r * max_n + i], i < max_n
+ *   (max_in: this rank's [p][max_n] slots, slot r written by rank r's payload copy, the own slot
+ *   by an earlier kernel of this stream): the all-reduce-max of the row maxima between the two
+ *   phases of iflb200_row_quant_sharded.
+ * bytes == 0 and max_n == 0 skip the respective part.  Payloads of a few tens of kilobytes; larger
+ * transfers belong to the copy engines or to the producing kernel's own stores.
+ */
+IFLB200_API int iflb200_peer_exchange(const void* peer_flag_ptrs, void* my_flags, void* arrival, int rank, int p,
+                          void* status, const void* src, const void* peer_dst_ptrs, int64_t bytes,
+                          const float* max_in, float* max_out, int max_n, void* stream);
 
 /*
  * Time budget of the waits inside the tcgen05 GEMM and the persistent stack kernel, in
@@ -421,7 +487,8 @@ IFLB200_API int iflb200_set_wait_budget_us(int64_t microseconds);
 /*
  * Which kernel the last GEMM call of this process launched (host-side record, no device access):
  * family 1 = single-CTA tiles, 2 / 3 = CTA pairs with one / two accumulators, +4 = the swapped
- * form, +8 = the gated form (paired gate / up columns); the tile width in columns (tokens for the
+ * form, +8 = the gated form (paired gate / up columns), +16 = split-K partial planes, +32 = row blocks
+ * to several destinations; the tile width in columns (tokens for the
  * swapped form); the cluster split-K factor.  Any pointer may be NULL.  For tests that must know
  * that a given kernel really ran.  No reference counterpart.
  */

@@ -17,6 +17,7 @@ LIBRARY_NAME = "libiflb200.so"
 ABI_VERSION = 1
 
 F32, BF16, F16 = 0, 1, 2
+ERR_ARG, ERR_SHAPE, ERR_ALIGN, ERR_DTYPE = -1, -2, -3, -4   # IFLB200_ERR_* of include/iflb200.h
 ROUND_ENGINE, ROUND_EXACT = 0, 1
 
 _p = ctypes.c_void_p
@@ -31,12 +32,15 @@ SIGNATURES = {
     "iflb200_status_string": (ctypes.c_char_p, [_i]),
     "iflb200_row_quant": (_i, [_p, _i, _l, _i, _i, _p, _p, _p, _i, _p, _l, _p, _p]),
     "iflb200_row_quant_sharded": (_i, [_p, _i, _l, _i, _i, _p, _p, _p, _i, _i, _p, _p, _l, _p, _p]),
+    "iflb200_row_max_sharded": (_i, [_p, _i, _l, _i, _i, _p, _p, _p, _i, _p, _p, _i, _p]),
     "iflb200_dequant_rows": (_i, [_p, _i, _l, _i, _i, _p, _p, _p, _p, _i, _l, _p]),
     "iflb200_gated_act_quant": (_i, [_p, _i, _l, _i, _i, _p, _p, _i, _p, _l, _p, _p]),
     "iflb200_residual_norm_quant": (_i, [_p, _i, _l, _i, _i, _p, _l, _p, _p, _p, _p, _i, _i, _p, _p,
                                          _p, _p, _p, _f, _p, _l, _p, _p, _i, _l, _p]),
     "iflb200_residual_norm_quant_partials": (_i, [_p, _i, _l, _i, _i, _p, _i, _l, _p, _p, _p, _p, _i, _i, _p, _p,
                                                   _p, _p, _p, _f, _p, _l, _p, _p, _i, _l, _p]),
+    "iflb200_residual_norm_quant_peers": (_i, [_p, _i, _l, _i, _i, _p, _i, _l, _p, _p, _p, _p, _i, _i, _p, _p,
+                                               _p, _p, _p, _f, _p, _l, _p, _p, _p, _i, _p]),
     "iflb200_qkv_split": (_i, [_p, _i, _l, _i, _i, _i, _i, _p, _p, _p, _p, _p, _f, _p, _p, _l, _p, _p, _i,
                                _p, _l, _l, _p, _l, _l, _p, _l, _l, _i, _p]),
     "iflb200_wan_qkv": (_i, [_p, _i, _l, _i, _i, _i, _i, _p, _p, _p, _p, _p, _f, _p, _p, _l, _p, _p,
@@ -57,7 +61,10 @@ SIGNATURES = {
     "iflb200_stack_weight_box_rows": (_i, []),
     "iflb200_stack_run": (_i, [_p, _i, _p, _p, _i, _i, _p, _p]),
     "iflb200_gemm_take_timeout_record": (_i, [ctypes.POINTER(ctypes.c_uint32), _p]),
+    "iflb200_encode_rowblock_map": (_i, [_p, _i, _i, _l, _p]),
+    "iflb200_gemm_fp8_rowblocks": (_i, [_p, _l, _p, _l, _i, _i, _i, _i, _p, _p]),
     "iflb200_peer_barrier": (_i, [_p, _p, _p, _i, _i, _p, _p]),
+    "iflb200_peer_exchange": (_i, [_p, _p, _p, _i, _i, _p, _p, _p, _l, _p, _p, _i, _p]),
     "iflb200_set_wait_budget_us": (_i, [_l]),
     "iflb200_gemm_last_launch": (_i, [ctypes.POINTER(_i), ctypes.POINTER(_i), ctypes.POINTER(_i)]),
     "iflb200_gemm_set_config": (_i, [_i, _i, _i]),

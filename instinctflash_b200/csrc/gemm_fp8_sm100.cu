@@ -64,6 +64,14 @@ struct GemmParams {
   int act;         // gated form: IFLB200_ACT_*
   uint32_t* amax;  // gated form: per-row maximum of |h| as float bits, raised with atomicMax
   int tma_store;  // 1: the epilogue stages 128-byte row pieces in shared memory and TMA-stores them
+  // Row blocks to several destinations (tensor parallel, row-split linears): the activation holds
+  // `groups` blocks of `group_rows` rows (M = group_rows); block g's tiles are stored through
+  // out_maps[g] (tensor maps in global memory, e.g. one per GPU's buffer).  Tiles of the blocks
+  // alternate, so stores to a slow destination (a peer over NVLink) are spread over the whole launch
+  // and drain under the main loops of the other blocks' tiles.
+  int groups;
+  int group_rows;
+  const CUtensorMap* out_maps;
 };
 
 // role << 24 | barrier kind << 16 | low 16 bits of the tile counter; 0 = no timeout.
@@ -117,6 +125,16 @@ __device__ __forceinline__ void tile_coords(const GemmParams& p, int tile, int& 
   const int r = tile - g * band;
   m_blk = first_m + r % size;
   n_blk = r / size;
+}
+
+// The same with the destination block of the row-blocks form (block 0 otherwise).
+__device__ __forceinline__ void tile_place(const GemmParams& p, int tile, int& m_blk, int& n_blk, int& grp) {
+  grp = 0;
+  if (p.groups > 1) {
+    grp = tile % p.groups;
+    tile /= p.groups;
+  }
+  tile_coords(p, tile, m_blk, n_blk);
 }
 
 // Bounded wait on an mbarrier phase.  Returns false when the CTA is aborting.
@@ -672,8 +690,8 @@ gemm_fp8_tc5_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
   // stale data into the kernel: the loads proper are issued after the dependency wait and L2 is
   // the coherence point), then wait for that kernel's results.
   if (warp == 0 && lane == 0 && tile_first < p.num_tiles) {
-    int m_blk, n_blk;
-    tile_coords(p, tile_first, m_blk, n_blk);
+    int m_blk, n_blk, grp;
+    tile_place(p, tile_first, m_blk, n_blk, grp);
     const int kb_end = kb1 < kb0 + kPrefetchSteps ? kb1 : kb0 + kPrefetchSteps;
     for (int kb = kb0; kb < kb_end; kb += SL) {
       if constexpr (GATED) {
@@ -701,8 +719,9 @@ gemm_fp8_tc5_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
     bool ok = true;
     uint32_t it = 0;
     for (int tile = tile_first; ok && tile < p.num_tiles; tile += tile_stride, ++it) {
-      int m_blk, n_blk;
-      tile_coords(p, tile, m_blk, n_blk);
+      int m_blk, n_blk, grp;
+      tile_place(p, tile, m_blk, n_blk, grp);
+      const int a_row = grp * p.group_rows + m_blk * BM;  // rows past a block's end belong to the next block: loaded, never stored
       for (int kb = kb0; kb < kb1; kb += SL) {
         ok = __all_sync(0xFFFFFFFFu, wait_bounded(empty_bar(stage), phase ^ 1, abort_flag,
                                                   (1u << 24) | (1u << 16) | (it & 0xFFFF)));
@@ -712,10 +731,10 @@ gemm_fp8_tc5_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
           const uint32_t sa = base + stage * L::kStageBytes;
           if constexpr (SL > 1) {
             // SL slabs of each operand per instruction; slabs past the end of K read as zeros
-            tma_load_3d(sa, &tm_a, full_bar(stage), 0, m_blk * BM, kb);
+            tma_load_3d(sa, &tm_a, full_bar(stage), 0, a_row, kb);
             tma_load_3d(sa + L::kABytes, &tm_w, full_bar(stage), 0, n_blk * BN, kb);
           } else {
-          tma_load_2d(sa, &tm_a, full_bar(stage), kb * BK, m_blk * BM);
+          tma_load_2d(sa, &tm_a, full_bar(stage), kb * BK, a_row);
           if constexpr (GATED) {
             // gate rows, then the up rows of the same hidden units: one B operand of BN rows, one
             // load (the weight is mapped as [2][F][K]; a second TMA instruction per stage cost the
@@ -812,8 +831,9 @@ gemm_fp8_tc5_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
     uint32_t it = 0;
     int swap_buf = 0;
     for (int tile = tile_first; ok && tile < p.num_tiles; tile += tile_stride, ++it) {
-      int m_blk, n_blk;
-      tile_coords(p, tile, m_blk, n_blk);
+      int m_blk, n_blk, grp;
+      tile_place(p, tile, m_blk, n_blk, grp);
+      const CUtensorMap* tm_dst = p.groups > 1 ? p.out_maps + grp : &tm_out;
       const uint32_t acc = it & 1u;
       const uint32_t acc_phase = (it >> 1) & 1u;
       ok = __all_sync(0xFFFFFFFFu, wait_bounded(tfull_bar(acc), acc_phase, abort_flag,
@@ -850,7 +870,7 @@ gemm_fp8_tc5_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
         // 224-wide tile (two-byte outputs) straight from registers
         const int per_store = (p.out_dtype == IFLB200_F32) ? 32 : 64;
         const int col_tma_end = col_begin + (col_end - col_begin) / per_store * per_store;
-        epilogue_tma_store<BN>(p, &tm_out, t_row, staging, staging_ptr, m_blk * BM + quad * 32, n_blk * BN,
+        epilogue_tma_store<BN>(p, tm_dst, t_row, staging, staging_ptr, m_blk * BM + quad * 32, n_blk * BN,
                                col_begin, col_tma_end, rs, lane,
                                (SPLIT == 2 && p.partials >= 1) ? split_rank : -1);  // a plane map takes a 3-D store
         if (BN % 64 != 0 && col_tma_end < col_end) {
@@ -1676,6 +1696,54 @@ static int run_gemm_partials(const void* a, int64_t ld_a, const void* w, int64_t
   return launch_gemm_form<64, 2, 2, false, false, kEpilogueWarps, 4>(ta, tw, to, p, p.num_tiles * splits, s);
 }
 
+// Row blocks to several destinations: a holds `groups` blocks of `group_rows` rows; block g's
+// fp32 accumulators (no scales, no rounding) go through d_out_maps[g], tensor maps in DEVICE memory
+// encoded by iflb200_encode_rowblock_map for [group_rows][N] fp32 buffers (on this GPU or a peer).
+static int run_gemm_rowblocks(const void* a, int64_t ld_a, const void* w, int64_t ld_w, int groups, int group_rows,
+                              int N, int K, const void* d_out_maps, void* stream) {
+  if (groups < 1 || groups > 64 || group_rows < 0 || N < 0 || K < 0) return IFLB200_ERR_ARG;
+  if (group_rows == 0 || N == 0) return IFLB200_OK;
+  if (!a || !w || !d_out_maps) return IFLB200_ERR_ARG;
+  if (K < 16 || K % 16 || N % 16) return IFLB200_ERR_SHAPE;
+  if (ld_a < K || ld_w < K) return IFLB200_ERR_ARG;
+  if ((reinterpret_cast<uintptr_t>(a) & 15) || (reinterpret_cast<uintptr_t>(w) & 15) || ld_a % 16 || ld_w % 16 ||
+      (reinterpret_cast<uintptr_t>(d_out_maps) & 63))
+    return IFLB200_ERR_ALIGN;
+  DeviceInfo* dev = nullptr;
+  int st = device_info(&dev);
+  if (st != IFLB200_OK) return st;
+  GemmParams p = {};
+  p.M = group_rows; p.N = N; p.K = K;
+  p.epilogue = EPI_DEQUANT;
+  p.exact = 1;
+  p.out = nullptr; p.out_dtype = IFLB200_F32; p.ld_out = N;
+  p.split_k = 1;
+  p.tma_store = 1;
+  p.groups = groups; p.group_rows = group_rows;
+  p.out_maps = reinterpret_cast<const CUtensorMap*>(d_out_maps);
+  const int bn = N >= 256 ? 256 : (N >= 128 ? 128 : 64);
+  p.num_m = (group_rows + BM - 1) / BM;
+  p.num_n = (N + bn - 1) / bn;
+  p.num_k = (K + BK - 1) / BK;
+  p.num_tiles = groups * p.num_m * p.num_n;
+  p.group_m = g_cfg_group_m > 0 ? g_cfg_group_m : 8;
+  p.a_bytes = BM * BK;
+  const int grid = p.num_tiles < dev->sm_count ? p.num_tiles : dev->sm_count;
+  CUtensorMap ta, tw, to;
+  memset(&to, 0, sizeof(to));
+  st = make_tensor_map(&ta, a, groups * group_rows, K, ld_a, BM);
+  if (st != IFLB200_OK) return st;
+  st = make_tensor_map(&tw, w, N, K, ld_w, bn);
+  if (st != IFLB200_OK) return st;
+  cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+  g_last_launch[0] = 1 + 32; g_last_launch[1] = bn; g_last_launch[2] = 1; g_last_launch[3] = 0;
+  switch (bn) {
+    case 256: return launch_gemm<256, 4>(ta, tw, to, p, grid, s);
+    case 128: return launch_gemm<128, 6>(ta, tw, to, p, grid, s);
+    default: return launch_gemm<64, 8>(ta, tw, to, p, grid, s);
+  }
+}
+
 // The gated form: W is [2F, K] = [gate rows | up rows]; h [M, F] fp32; amax [M] float bits.
 static int run_gemm_gated(const void* a, int64_t ld_a, const void* w, int64_t ld_w, int M, int F, int K,
                           const float* row, const float* col, int act, float* h, int64_t ld_h, uint32_t* amax,
@@ -1872,6 +1940,21 @@ extern "C" int iflb200_fp8_linear_residual(const void* a, int64_t ld_a, const vo
 extern "C" int iflb200_gemm_fp8_partials(const void* a, int64_t ld_a, const void* w, int64_t ld_w, int M, int N,
                                          int K, int splits, float* out, int64_t ld_out, void* stream) {
   return run_gemm_partials(a, ld_a, w, ld_w, M, N, K, splits, out, ld_out, stream);
+}
+
+extern "C" int iflb200_encode_rowblock_map(void* out, int rows, int N, int64_t ld_out, void* map128) {
+  if (!out || !map128 || rows < 1 || N < 1 || ld_out < N) return IFLB200_ERR_ARG;
+  if ((reinterpret_cast<uintptr_t>(out) & 15) || (ld_out * 4) % 16) return IFLB200_ERR_ALIGN;
+  CUtensorMap tm;
+  const int st = make_out_map(&tm, out, rows, N, ld_out, 4);
+  if (st != IFLB200_OK) return st;
+  memcpy(map128, &tm, sizeof(tm));
+  return IFLB200_OK;
+}
+
+extern "C" int iflb200_gemm_fp8_rowblocks(const void* a, int64_t ld_a, const void* w, int64_t ld_w, int groups,
+                                          int group_rows, int N, int K, const void* d_out_maps, void* stream) {
+  return run_gemm_rowblocks(a, ld_a, w, ld_w, groups, group_rows, N, K, d_out_maps, stream);
 }
 
 extern "C" int iflb200_fp8_linear_gated(const void* a, int64_t ld_a, const void* w, int64_t ld_w, int M, int F,

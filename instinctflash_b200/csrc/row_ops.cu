@@ -238,6 +238,8 @@ __host__ __device__ constexpr int resnorm_min_blocks() {
 // --------------------------------------------------------------------------------------------
 // row_quant: 2K (bf16 in) + K (codes out) + 4 bytes per row.
 // --------------------------------------------------------------------------------------------
+constexpr int kMaxMirrors = 7;  // copies of a result in the buffers of the other GPUs of a group of up to eight
+
 struct RowQuantArgs {
   const void* x;
   int64_t ld_x;
@@ -256,7 +258,17 @@ struct RowQuantArgs {
   // which needs the words to start at zero the next time).
   int phase;
   float* amax;
+  // phase 1 only: further copies of the row maxima (the other GPUs' slots for this rank, peer-mapped)
+  float* amax_mirror[kMaxMirrors];
+  int mirrors;
 };
+
+__device__ __forceinline__ void write_row_max(const RowQuantArgs& a, int m, float amax) {
+  a.amax[m] = amax;
+#pragma unroll
+  for (int k = 0; k < kMaxMirrors; ++k)
+    if (k < a.mirrors) a.amax_mirror[k][m] = amax;
+}
 
 // PLAIN: no prologue.  The row then stays in registers as loaded (4 registers per 8 elements)
 // and is widened twice, once for the maximum and once for the cast, which keeps enough CTAs
@@ -290,7 +302,7 @@ row_quant_kernel(const RowQuantArgs a) {
     }
     amax = row_reduce<TPR, true>(amax, red);
     if (a.phase == 1) {
-      if (live && t == 0) a.amax[m] = amax;
+      if (live && t == 0) write_row_max(a, m, amax);
       return;
     }
     if (a.phase >= 2 && live) amax = a.amax[m];
@@ -339,7 +351,7 @@ row_quant_kernel(const RowQuantArgs a) {
   }
   amax = row_reduce<TPR, true>(amax, red);
   if (a.phase == 1) {
-    if (live && t == 0) a.amax[m] = amax;
+    if (live && t == 0) write_row_max(a, m, amax);
     return;
   }
   if (a.phase >= 2 && live) amax = a.amax[m];
@@ -520,6 +532,11 @@ struct ResNormArgs {
   void* y;
   int y_dtype;
   int64_t ld_y;
+  // partial-sum form only: further copies of the codes and row scales (same row stride as q), the
+  // other GPUs' replicas of the next block's input, written from the same registers
+  uint8_t* q_mirror[kMaxMirrors];
+  float* qs_mirror[kMaxMirrors];
+  int mirrors;
 };
 
 template <typename RT>
@@ -534,7 +551,7 @@ __device__ __forceinline__ float round_through<__nv_bfloat16>(float x) {
 // PART: the delta arrives as fp32 partial sums of a K-split GEMM (a.dpart) instead of a raw bf16
 // accumulator; a separate instantiation so that the ordinary one keeps its registers.
 template <typename RT, int TPR, int IT, bool FAST, bool PART = false>
-__global__ void __launch_bounds__(kRowThreads, resnorm_min_blocks<IT>())
+__global__ void __launch_bounds__(kRowThreads, (PART && IT > 1) ? 2 : resnorm_min_blocks<IT>())
 residual_norm_quant_kernel(const ResNormArgs a) {
   row_dependency_wait();  // inputs may come from the kernel before this one in the stream
   row_trigger();
@@ -680,6 +697,20 @@ residual_norm_quant_kernel(const ResNormArgs a) {
   for (int it = 0; it < IT; ++it) {
     const int c0 = (it * TPR + t) * 8;
     if (it < a.iters && c0 < a.D) store_codes<FAST>(qr, c0, a.D, x[it], inv);
+  }
+  if constexpr (PART) {
+#pragma unroll
+    for (int k = 0; k < kMaxMirrors; ++k) {
+      if (k < a.mirrors) {
+        if (t == 0) a.qs_mirror[k][m] = scale;
+        uint8_t* qm = a.q_mirror[k] + (int64_t)m * a.ld_q;
+#pragma unroll
+        for (int it = 0; it < IT; ++it) {
+          const int c0 = (it * TPR + t) * 8;
+          if (it < a.iters && c0 < a.D) store_codes<FAST>(qm, c0, a.D, x[it], inv);
+        }
+      }
+    }
   }
 }
 
@@ -896,10 +927,10 @@ static void launch_gated(GatedArgs a, bool fast, cudaStream_t s) {
     launch_dep(gated_act_quant_kernel<XT, TPR, IT, true>, dim3(grid), dim3(kRowThreads), 0, s, 1, dependent_launch_for(a.M), a);
   });
 }
-// The partial-sum form: rows of at most 4096 columns on the aligned path (skinny activations).
+// The partial-sum form: rows of at most 8192 columns on the aligned path.
 template <typename RT>
 static int launch_resnorm_partials(ResNormArgs a, bool fast, cudaStream_t s) {
-  if (!fast || a.D > 4096) return IFLB200_ERR_SHAPE;
+  if (!fast || a.D > 8192) return IFLB200_ERR_SHAPE;
   if (a.D <= 1024) {
     a.iters = 1;
     launch_dep(residual_norm_quant_kernel<RT, 128, 1, true, true>, dim3((a.M + 1) / 2), dim3(kRowThreads), 0, s, 1,
@@ -908,9 +939,21 @@ static int launch_resnorm_partials(ResNormArgs a, bool fast, cudaStream_t s) {
     a.iters = 1;
     launch_dep(residual_norm_quant_kernel<RT, kRowThreads, 1, true, true>, dim3(a.M), dim3(kRowThreads), 0, s, 1,
                dependent_launch_for(a.M), a);
-  } else {
+  } else if (a.D <= 3072) {  // 128 threads x 3 chunks use every chunk slot; two rows per CTA
+    a.iters = 3;
+    launch_dep(residual_norm_quant_kernel<RT, 128, 3, true, true>, dim3((a.M + 1) / 2), dim3(kRowThreads), 0, s, 1,
+               dependent_launch_for(a.M), a);
+  } else if (a.D <= 4096) {
     a.iters = 2;
     launch_dep(residual_norm_quant_kernel<RT, kRowThreads, 2, true, true>, dim3(a.M), dim3(kRowThreads), 0, s, 1,
+               dependent_launch_for(a.M), a);
+  } else if (a.D <= 6144) {
+    a.iters = 3;
+    launch_dep(residual_norm_quant_kernel<RT, kRowThreads, 3, true, true>, dim3(a.M), dim3(kRowThreads), 0, s, 1,
+               dependent_launch_for(a.M), a);
+  } else {
+    a.iters = 4;
+    launch_dep(residual_norm_quant_kernel<RT, kRowThreads, 4, true, true>, dim3(a.M), dim3(kRowThreads), 0, s, 1,
                dependent_launch_for(a.M), a);
   }
   return IFLB200_OK;
@@ -959,8 +1002,10 @@ extern "C" int iflb200_row_set_group(int threads_per_row) {
 
 static int row_quant_impl(const void* x, int x_dtype, int64_t ld_x, int M, int K, const float* row,
                           const float* col, const float* bias, int gelu, void* q, int64_t ld_q, float* qs,
-                          int phase, float* amax, void* stream) {
+                          int phase, float* amax, void* stream, float* const* amax_mirrors = nullptr,
+                          int mirrors = 0) {
   if (M < 0 || K < 0) return IFLB200_ERR_ARG;
+  if (mirrors < 0 || mirrors > kMaxMirrors || (mirrors > 0 && (!amax_mirrors || phase != 1))) return IFLB200_ERR_ARG;
   if (M == 0 || K == 0) return IFLB200_OK;
   if (!x) return IFLB200_ERR_ARG;
   if (phase != 1 && (!q || !qs)) return IFLB200_ERR_ARG;
@@ -973,6 +1018,11 @@ static int row_quant_impl(const void* x, int x_dtype, int64_t ld_x, int M, int K
   a.row = row; a.col = col; a.bias = bias; a.gelu = gelu;
   a.q = reinterpret_cast<uint8_t*>(q); a.ld_q = ld_q; a.qs = qs;
   a.phase = phase; a.amax = amax;
+  a.mirrors = mirrors;
+  for (int k = 0; k < kMaxMirrors; ++k) {
+    a.amax_mirror[k] = k < mirrors ? amax_mirrors[k] : nullptr;
+    if (k < mirrors && !a.amax_mirror[k]) return IFLB200_ERR_ARG;
+  }
   const bool fast = K % 8 == 0 && aligned16(x) && (ld_x * esize(x_dtype)) % 16 == 0 &&
                     (phase == 1 || (aligned8(q) && ld_q % 8 == 0)) && (!col || aligned16(col)) &&
                     (!bias || aligned16(bias));
@@ -995,6 +1045,13 @@ extern "C" int iflb200_row_quant_sharded(const void* x, int x_dtype, int64_t ld_
                                          void* stream) {
   if (phase != 1 && phase != 2 && phase != 3) return IFLB200_ERR_ARG;
   return row_quant_impl(x, x_dtype, ld_x, M, K, row, col, bias, gelu, q, ld_q, qs, phase, amax, stream);
+}
+
+extern "C" int iflb200_row_max_sharded(const void* x, int x_dtype, int64_t ld_x, int M, int K, const float* row,
+                                       const float* col, const float* bias, int gelu, float* amax,
+                                       float* const* amax_mirrors, int mirrors, void* stream) {
+  return row_quant_impl(x, x_dtype, ld_x, M, K, row, col, bias, gelu, nullptr, 0, nullptr, 1, amax, stream,
+                        amax_mirrors, mirrors);
 }
 
 #endif
@@ -1071,8 +1128,11 @@ static int resnorm_impl(void* res, int res_dtype, int64_t ld_res, int M, int D, 
                         int64_t ld_delta, const float* delta_row, const float* delta_col, const float* bias,
                         const float* gate, int write_res, int layernorm, const float* weight, const float* beta,
                         const float* mod_scale, const float* mod_shift, const int32_t* mod_index, float eps, void* q,
-                        int64_t ld_q, float* qs, void* y, int y_dtype, int64_t ld_y, void* stream) {
+                        int64_t ld_q, float* qs, void* y, int y_dtype, int64_t ld_y, void* stream,
+                        void* const* q_mirrors = nullptr, float* const* qs_mirrors = nullptr, int mirrors = 0) {
   if (M < 0 || D < 0) return IFLB200_ERR_ARG;
+  if (mirrors < 0 || mirrors > kMaxMirrors || (mirrors > 0 && (!q_mirrors || !qs_mirrors || !q || !delta_splits)))
+    return IFLB200_ERR_ARG;
   if (M == 0 || D == 0) return IFLB200_OK;
   if (!res) return IFLB200_ERR_ARG;
   if (res_dtype != IFLB200_F32 && res_dtype != IFLB200_BF16) return IFLB200_ERR_DTYPE;
@@ -1094,6 +1154,15 @@ static int resnorm_impl(void* res, int res_dtype, int64_t ld_res, int M, int D, 
   a.mod_scale = mod_scale; a.mod_shift = mod_shift; a.mod_index = mod_index; a.eps = eps;
   a.q = reinterpret_cast<uint8_t*>(q); a.ld_q = ld_q; a.qs = qs;
   a.y = y; a.y_dtype = y_dtype; a.ld_y = ld_y;
+  a.mirrors = mirrors;
+  bool mirrors_ok = true;
+  for (int k = 0; k < kMaxMirrors; ++k) {
+    a.q_mirror[k] = k < mirrors ? reinterpret_cast<uint8_t*>(q_mirrors[k]) : nullptr;
+    a.qs_mirror[k] = k < mirrors ? qs_mirrors[k] : nullptr;
+    if (k < mirrors && (!a.q_mirror[k] || !a.qs_mirror[k])) return IFLB200_ERR_ARG;
+    if (k < mirrors && !aligned8(a.q_mirror[k])) mirrors_ok = false;
+  }
+  if (!mirrors_ok) return IFLB200_ERR_ALIGN;
   const bool tables_ok = (!a.dcol || aligned16(a.dcol)) && (!a.bias || aligned16(a.bias)) &&
                          (!a.gate || aligned16(a.gate)) && (!weight || aligned16(weight)) &&
                          (!beta || aligned16(beta)) && (!mod_scale || aligned16(mod_scale)) &&
@@ -1140,6 +1209,20 @@ extern "C" int iflb200_residual_norm_quant_partials(void* res, int res_dtype, in
   return resnorm_impl(res, res_dtype, ld_res, M, D, delta_partials, splits, ld_delta, delta_row, delta_col, bias, gate,
                       write_res, layernorm, weight, beta, mod_scale, mod_shift, mod_index, eps, q, ld_q, qs, y, y_dtype,
                       ld_y, stream);
+}
+
+extern "C" int iflb200_residual_norm_quant_peers(void* res, int res_dtype, int64_t ld_res, int M, int D,
+                                                 const float* delta_partials, int splits, int64_t ld_delta,
+                                                 const float* delta_row, const float* delta_col, const float* bias,
+                                                 const float* gate, int write_res, int layernorm, const float* weight,
+                                                 const float* beta, const float* mod_scale, const float* mod_shift,
+                                                 const int32_t* mod_index, float eps, void* q, int64_t ld_q, float* qs,
+                                                 void* const* q_mirrors, float* const* qs_mirrors, int mirrors,
+                                                 void* stream) {
+  if (!delta_partials || splits < 1 || splits > 8) return IFLB200_ERR_ARG;
+  return resnorm_impl(res, res_dtype, ld_res, M, D, delta_partials, splits, ld_delta, delta_row, delta_col, bias, gate,
+                      write_res, layernorm, weight, beta, mod_scale, mod_shift, mod_index, eps, q, ld_q, qs, nullptr, 0,
+                      0, stream, q_mirrors, qs_mirrors, mirrors);
 }
 
 #endif

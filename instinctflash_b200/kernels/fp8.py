@@ -193,3 +193,34 @@ def gemm_partials(a: torch.Tensor, w: Fp8Weight, out: torch.Tensor) -> torch.Ten
     launch("iflb200_gemm_fp8_partials", a, a.data_ptr(), ld(a), w.w.data_ptr(), ld(w.w), M, N, K, int(out.shape[0]),
            out.data_ptr(), N)
     return out
+
+
+def encode_rowblock_maps(buffers) -> torch.Tensor:
+    """Device array of tensor maps, one per destination of ``gemm_rowblocks``: ``buffers`` are
+    float32 [rows, N] tensors of equal shape with contiguous rows, on this GPU or peer-mapped.  The
+    maps hold the buffers' addresses: keep the buffers alive and in place."""
+    first = buffers[0]
+    host = torch.zeros(len(buffers), 128, dtype=torch.uint8)
+    for i, b in enumerate(buffers):
+        if b.dtype != torch.float32 or b.ndim != 2 or b.shape != first.shape or b.stride(1) != 1:
+            raise ValueError("destinations must be float32 [rows, N] tensors of one shape")
+        _lib.check(_lib.lib().iflb200_encode_rowblock_map(b.data_ptr(), int(b.shape[0]), int(b.shape[1]), ld(b),
+                                                          host[i].data_ptr()), "encode_rowblock_map")
+    return host.to(first.device)
+
+
+def gemm_rowblocks(a: torch.Tensor, w: Fp8Weight, group_rows: int, maps: torch.Tensor) -> None:
+    """K-split linear whose row blocks go to different destinations in one launch: ``a`` [G * group_rows,
+    K] e4m3, block g's float32 accumulators (no scales, no rounding) stored through ``maps[g]``
+    (``encode_rowblock_maps``).  Tiles of the blocks alternate, so stores towards a peer GPU drain
+    under the other tiles' main loops."""
+    M, N, K = _operands(a, w)
+    G = int(maps.shape[0])
+    if maps.dtype != torch.uint8 or maps.ndim != 2 or maps.shape[1] != 128 or not maps.is_contiguous() or maps.data_ptr() % 64:
+        raise ValueError("maps must be the device tensor encode_rowblock_maps returned")
+    if group_rows * G != M:
+        raise ValueError(f"a has {M} rows, expected {G} blocks of {group_rows}")
+    same_device(a, maps=maps)
+    launch("iflb200_gemm_fp8_rowblocks", a, a.data_ptr(), ld(a), w.w.data_ptr(), ld(w.w), G, int(group_rows), N, K,
+           maps.data_ptr())
+

@@ -9,6 +9,8 @@ quantiser are bit-identical to the reference's on the same inputs.
 """
 from __future__ import annotations
 
+import ctypes
+
 import torch
 
 from .. import _lib
@@ -58,6 +60,23 @@ def row_quant_sharded(x, q, q_scale, amax, phase, *, row=None, col=None, bias=No
         _lib.ptr(q_scale) if phase != 1 else None)
 
 
+def row_max_sharded(x, amax, mirrors=(), *, row=None, col=None, bias=None, gelu=False):
+    """Phase 1 of ``row_quant_sharded`` that also writes the row maxima into ``mirrors`` (up to 7
+    float32 [M] buffers: this rank's slots in the other GPUs' peer-mapped buffers)."""
+    rows(x, "x", _FLOATS)
+    M, D = x.shape
+    vec(amax, "amax", M, x.device)
+    if len(mirrors) > 7:
+        raise ValueError("at most 7 mirrors")
+    for t in mirrors:
+        vec(t, "amax mirror", M, x.device)
+    n = len(mirrors)
+    launch("iflb200_row_max_sharded", x, x.data_ptr(), _lib.dtype_code(x.dtype), ld(x), M, D,
+           _lib.ptr(vec(row, "row", M, x.device)), _lib.ptr(vec(col, "col", D, x.device)),
+           _lib.ptr(vec(bias, "bias", D, x.device)), int(bool(gelu)), amax.data_ptr(),
+           (ctypes.c_void_p * n)(*[t.data_ptr() for t in mirrors]) if n else None, n)
+
+
 def row_quant_from_amax(h, amax, q, q_scale):
     """Second half of ``fp8.fp8_linear_gated``: quantise the rows of ``h`` [M, F] float32 with the
     row maxima the GEMM epilogue left in ``amax`` [M] (scale = amax / 448, codes as ``row_quant``),
@@ -93,6 +112,24 @@ def residual_norm_quant(res, *, delta=None, delta_row=None, delta_col=None, bias
     ``res`` is float32 (bf16 for the Wan residual stream) and updated in place; ``gate``,
     ``mod_scale`` and ``mod_shift`` are [D] or, with ``mod_index`` (int32 [M]), tables [n, D].
     """
+    return _residual_norm_quant(res, delta, delta_row, delta_col, bias, gate, write_res, layernorm, weight, beta,
+                                mod_scale, mod_shift, q, q_scale, y, eps, router, mod_index, None, None)
+
+
+def residual_norm_quant_peers(res, *, delta, q, q_scale, q_mirrors, q_scale_mirrors, delta_row=None, delta_col=None,
+                              bias=None, gate=None, write_res=True, layernorm=False, weight=None, beta=None,
+                              mod_scale=None, mod_shift=None, eps=1e-6, mod_index=None):
+    """``residual_norm_quant`` for the row owner of a tensor-parallel group: ``delta`` [p, M, D]
+    float32 holds the ranks' partial sums of these rows (added in rank order, then rounded to bf16);
+    the codes and row scales also go into ``q_mirrors`` / ``q_scale_mirrors`` (up to 7 each): the
+    same rows of the other GPUs' replicas of the next block's input, peer-mapped."""
+    return _residual_norm_quant(res, delta, delta_row, delta_col, bias, gate, write_res, layernorm, weight, beta,
+                                mod_scale, mod_shift, q, q_scale, None, eps, None, mod_index, list(q_mirrors),
+                                list(q_scale_mirrors))
+
+
+def _residual_norm_quant(res, delta, delta_row, delta_col, bias, gate, write_res, layernorm, weight, beta, mod_scale,
+                         mod_shift, q, q_scale, y, eps, router, mod_index, q_mirrors, q_scale_mirrors):
     if router is not None:
         raise NotImplementedError("the MoE router tail of residual_norm_quant is outside the FP8 linear path")
     rows(res, "res", (torch.float32, torch.bfloat16))
@@ -125,6 +162,26 @@ def residual_norm_quant(res, *, delta=None, delta_row=None, delta_col=None, bias
     if mod_index is not None and (mod_index.dtype != torch.int32 or mod_index.numel() < M):
         raise ValueError("mod_index must be int32 with one entry per row")
     same_device(res, delta=delta, q=q, y=y, mod_index=mod_index)
+    if q_mirrors:
+        if not partials or q is None or y is not None or len(q_mirrors) != len(q_scale_mirrors or ()) or len(q_mirrors) > 7:
+            raise ValueError("mirrors go with the partial-sum form: q without y, as many scale mirrors as code mirrors, at most 7")
+        for t in q_mirrors:
+            rows(t, "q mirror", (E4M3,))
+            if tuple(t.shape) != (M, D) or ld(t) != ld(q):
+                raise ValueError("a q mirror must have q's shape and row stride")
+        for t in q_scale_mirrors:
+            vec(t, "q_scale mirror", M, dev)
+        n = len(q_mirrors)
+        launch("iflb200_residual_norm_quant_peers", res,
+            res.data_ptr(), _lib.dtype_code(res.dtype), ld(res), M, D, delta.data_ptr(), int(delta.shape[0]), D,
+            _lib.ptr(vec(delta_row, "delta_row", M, dev)), _lib.ptr(vec(delta_col, "delta_col", D, dev)),
+            _lib.ptr(vec(bias, "bias", D, dev)), _lib.ptr(vec(gate, "gate", D, dev)), int(bool(write_res)),
+            int(bool(layernorm)), _lib.ptr(vec(weight, "weight", D, dev)), _lib.ptr(vec(beta, "beta", D, dev)),
+            _lib.ptr(vec(mod_scale, "mod_scale", D, dev)), _lib.ptr(vec(mod_shift, "mod_shift", D, dev)),
+            _lib.ptr(mod_index), float(eps), _lib.ptr(q), ld(q), _lib.ptr(q_scale),
+            (ctypes.c_void_p * n)(*[t.data_ptr() for t in q_mirrors]),
+            (ctypes.c_void_p * n)(*[t.data_ptr() for t in q_scale_mirrors]), n)
+        return
     launch("iflb200_residual_norm_quant_partials" if partials else "iflb200_residual_norm_quant", res,
         res.data_ptr(), _lib.dtype_code(res.dtype), ld(res), M, D,
         *((delta.data_ptr(), int(delta.shape[0]), D) if partials else

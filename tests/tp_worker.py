@@ -24,7 +24,7 @@ SMALL = StackSpec("small_wan", "wan", layers=2, M=256, hidden=1024, ffn=2048, qk
                   outlier_frac=0.01, outlier_scale=20.0, seed=8)
 
 
-def run(spec, device, ops_single, ops_tp, comm):
+def run(spec, device, ops_single, ops_tp, comm, link=None):
     """Returns a dict of checks (all ranks compute it; rank 0 reports)."""
     weights = make_weights(spec, device, cpu_seeded=True)
     x, attn = make_inputs(spec, device)
@@ -33,7 +33,7 @@ def run(spec, device, ops_single, ops_tp, comm):
     first_codes = single._q8(spec.hidden).clone()
     first_scales = single.scale[0].clone()
     single.forward()
-    tp = WanTPStack(spec, weights, device, comm, ops=ops_tp)
+    tp = WanTPStack(spec, weights, device, comm, ops=ops_tp, link=link)
     tp.load(x, attn)
     out = {}
     # replicated input after load: per-row norm + quantiser on row shards, all-gathered
@@ -44,6 +44,11 @@ def run(spec, device, ops_single, ops_tp, comm):
     ref = single.res.float()
     out["residual_rel_frobenius"] = float((full - ref).norm() / ref.norm())
     out["residual_row_max_fraction"] = float(((full - ref).abs().amax(1) / ref.abs().amax(1)).max())
+    out["full"] = full
+    if link is not None:
+        if device.type == "cuda":
+            torch.cuda.synchronize(device)
+        link.check()
     return out
 
 
@@ -96,6 +101,20 @@ def main():
     ok_q = sharded_quantiser_exact(device, ops_single, ops_tp, comm)
     res = run(spec, device, ops_single, ops_tp, comm)
     res["sharded_quantiser_exact"] = ok_q
+    # the same stack over the peer-memory transport: plane sums in rank order are the
+    # reduce-scatter's sums (bit for bit between two ranks, where fp32 addition commutes)
+    layout = WanTPStack.peer_layout(spec, comm.size)
+    if backend == "nccl":
+        from instinctflash_b200.tp import PeerLink
+        link = PeerLink(layout, device)
+    else:
+        from fake_link import GlooLink
+        link = GlooLink(layout)
+    peer = run(spec, device, ops_single, ops_tp, comm, link=link)
+    peer_ok = bool(peer["input_codes_equal"] and peer["input_scales_equal"] and peer["residual_rel_frobenius"] <= 2e-2)
+    if comm.size == 2:
+        peer_ok = peer_ok and bool(torch.equal(peer["full"], res["full"]))
+    ok_q = ok_q and peer_ok
     flags = torch.tensor([float(ok_q), float(res["input_codes_equal"]), float(res["input_scales_equal"]),
                           res["residual_rel_frobenius"], res["residual_row_max_fraction"]], device=device)
     dist.all_reduce(flags, op=dist.ReduceOp.MAX)
@@ -103,7 +122,8 @@ def main():
     dist.all_reduce(ok_all, op=dist.ReduceOp.MIN)
     if rank == 0:
         print("TP_RESULT", dict(world=comm.size, exact_ok=bool(ok_all.item()), rel_frobenius=float(flags[3]),
-                                row_max_fraction=float(flags[4])), flush=True)
+                                row_max_fraction=float(flags[4]), peer_transport_ok=peer_ok,
+                                peer_rel_frobenius=peer["residual_rel_frobenius"]), flush=True)
     dist.barrier()
     dist.destroy_process_group()
     # the K-split sums differ from the single-device accumulator only by summation order; two
