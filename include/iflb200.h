@@ -460,20 +460,14 @@ IFLB200_API int iflb200_peer_barrier(const void* peer_flag_ptrs, void* my_flags,
                          void* status, void* stream);
 
 /*
- * The barrier with a small payload in front and a reduction behind, one single-CTA kernel:
- *   before signalling, copy `bytes` bytes (a multiple of 16; src and destinations 16-byte aligned)
- *   from src into the buffer of every peer r != rank at peer_dst_ptrs[r] (a device array of `p`
- *   pointers, as seen from this GPU);
- *   after every peer has arrived, max_out[i] = max over r < p of max_in[r * max_n + i], i < max_n
- *   (max_in: this rank's [p][max_n] slots, slot r written by rank r's payload copy, the own slot
- *   by an earlier kernel of this stream): the all-reduce-max of the row maxima between the two
- *   phases of iflb200_row_quant_sharded.
- * bytes == 0 and max_n == 0 skip the respective part.  Payloads of a few tens of kilobytes; larger
- * transfers belong to the copy engines or to the producing kernel's own stores.
+ * The barrier with a reduction behind it, one single-CTA kernel: after every peer has arrived,
+ *   max_out[i] = max over r < p of max_in[r * max_n + i], i < max_n
+ * (max_in: this rank's [p][max_n] slots, slot r written by rank r -- iflb200_row_max_sharded's
+ * mirrors -- the own slot by an earlier kernel of this stream): the all-reduce-max of the row
+ * maxima between the two phases of iflb200_row_quant_sharded.  max_n == 0: the plain barrier.
  */
 IFLB200_API int iflb200_peer_exchange(const void* peer_flag_ptrs, void* my_flags, void* arrival, int rank, int p,
-                          void* status, const void* src, const void* peer_dst_ptrs, int64_t bytes,
-                          const float* max_in, float* max_out, int max_n, void* stream);
+                          void* status, const float* max_in, float* max_out, int max_n, void* stream);
 
 /*
  * Time budget of the waits inside the tcgen05 GEMM and the persistent stack kernel, in

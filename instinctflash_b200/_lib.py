@@ -64,7 +64,7 @@ SIGNATURES = {
     "iflb200_encode_rowblock_map": (_i, [_p, _i, _i, _l, _p]),
     "iflb200_gemm_fp8_rowblocks": (_i, [_p, _l, _p, _l, _i, _i, _i, _i, _p, _p]),
     "iflb200_peer_barrier": (_i, [_p, _p, _p, _i, _i, _p, _p]),
-    "iflb200_peer_exchange": (_i, [_p, _p, _p, _i, _i, _p, _p, _p, _l, _p, _p, _i, _p]),
+    "iflb200_peer_exchange": (_i, [_p, _p, _p, _i, _i, _p, _p, _p, _i, _p]),
     "iflb200_set_wait_budget_us": (_i, [_l]),
     "iflb200_gemm_last_launch": (_i, [ctypes.POINTER(_i), ctypes.POINTER(_i), ctypes.POINTER(_i)]),
     "iflb200_gemm_set_config": (_i, [_i, _i, _i]),

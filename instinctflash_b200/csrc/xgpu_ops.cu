@@ -1,10 +1,10 @@
 // Barrier between the GPUs of a tensor-parallel group over peer memory (NVLink), for the exchange
 // steps of the row-split FP8 linears: every rank writes its partial sums / codes / row maxima
-// straight into its peers' buffers (the GEMM's TMA stores and plain device copies through
+// straight into its peers' buffers (the GEMM's TMA stores, the row kernels' stores through
 // peer-mapped pointers) and then meets the others here before anyone reads.  The reference has
 // nothing distributed; this replaces the latency of a library collective (15-20 us for an 18 KB
-// all-reduce) by one single-CTA kernel, which can also carry a small payload to the peers before it
-// signals and reduce the row maxima of all ranks after it has waited.
+// all-reduce) by one single-CTA kernel, which can also reduce the row maxima of all ranks after it
+// has waited.
 //
 // Each rank owns an array of `p` flag words in memory its peers can write.  Arrival number e of
 // rank r is the store of e into word r of every peer's array (release, system scope: everything
@@ -32,36 +32,26 @@ __device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* p) {
   return v;
 }
 
-// One CTA.  (1) every thread copies its 16-byte pieces of `src` into each peer's destination;
-// (2) thread r < p publishes arrival e to peer r and waits for peer r's arrival e; (3) the CTA
-// reduces `max_in` [p][max_n] (slot r written by rank r, the local slot by an earlier kernel of this
-// stream) to max_out[i] = max_r max_in[r][i].  Steps 1 and 3 are optional.
+// One CTA.  Thread r < p publishes arrival e to peer r and waits for peer r's arrival e; then the
+// CTA reduces `max_in` [p][max_n] (slot r written by rank r before its arrival, the local slot by an
+// earlier kernel of this stream) to max_out[i] = max_r max_in[r][i] (optional).
 __global__ void __launch_bounds__(1024) peer_exchange_kernel(uint32_t* const* __restrict__ peer_flags,
                                                             uint32_t* __restrict__ my_flags, uint32_t* __restrict__ arrival,
                                                             int rank, int p, uint32_t* __restrict__ status,
-                                                            const uint4* __restrict__ src, uint4* const* __restrict__ peer_dst,
-                                                            int64_t pieces, const float* __restrict__ max_in,
-                                                            float* __restrict__ max_out, int max_n) {
+                                                            const float* __restrict__ max_in, float* __restrict__ max_out,
+                                                            int max_n) {
   const uint32_t e = *arrival + 1;
-  if (pieces > 0) {
-    for (int64_t i = threadIdx.x; i < pieces; i += blockDim.x) {
-      const uint4 v = src[i];
-      for (int r = 0; r < p; ++r)
-        if (r != rank) peer_dst[r][i] = v;
-    }
-    __threadfence_system();
-  }
-  __syncthreads();  // every thread has read *arrival and issued its payload stores
+  __syncthreads();  // every thread has read *arrival
   const int r = threadIdx.x;
   if (r < p && r != rank) {
     __threadfence_system();
     st_release_sys(peer_flags[r] + rank, e);
     uint64_t t0 = 0;
     uint32_t spins = 0;
-    // arrival numbers only grow; the signed difference keeps the comparison right across wrap-around
     // a wait that ran out earlier stays on record until the host clears it: later barriers of the
     // same run signal and go on instead of spending the budget again
     const bool gave_up_before = *reinterpret_cast<volatile uint32_t*>(status) != 0;
+    // arrival numbers only grow; the signed difference keeps the comparison right across wrap-around
     while (!gave_up_before && (int32_t)(ld_acquire_sys(my_flags + r) - e) < 0) {
       if (++spins > 256) {
         if (t0 == 0) t0 = globaltimer_ns();
@@ -92,28 +82,20 @@ int set_peer_wait_budget_ns(uint64_t ns) {
 using namespace iflb200;
 
 extern "C" int iflb200_peer_exchange(const void* peer_flag_ptrs, void* my_flags, void* arrival, int rank, int p,
-                                     void* status, const void* src, const void* peer_dst_ptrs, int64_t bytes,
-                                     const float* max_in, float* max_out, int max_n, void* stream) {
+                                     void* status, const float* max_in, float* max_out, int max_n, void* stream) {
   if (!peer_flag_ptrs || !my_flags || !arrival || !status) return IFLB200_ERR_ARG;
   if (p < 1 || p > 32 || rank < 0 || rank >= p) return IFLB200_ERR_ARG;
-  if (bytes < 0 || max_n < 0 || (bytes > 0 && (!src || !peer_dst_ptrs)) || (max_n > 0 && (!max_in || !max_out)))
-    return IFLB200_ERR_ARG;
-  if ((reinterpret_cast<uintptr_t>(peer_flag_ptrs) & 7) || (reinterpret_cast<uintptr_t>(my_flags) & 3) ||
-      (reinterpret_cast<uintptr_t>(peer_dst_ptrs) & 7) || (reinterpret_cast<uintptr_t>(src) & 15) || (bytes & 15))
+  if (max_n < 0 || (max_n > 0 && (!max_in || !max_out))) return IFLB200_ERR_ARG;
+  if ((reinterpret_cast<uintptr_t>(peer_flag_ptrs) & 7) || (reinterpret_cast<uintptr_t>(my_flags) & 3))
     return IFLB200_ERR_ALIGN;
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
-  const int threads = (bytes > 0 || max_n > 0) ? 1024 : 32;
-  peer_exchange_kernel<<<1, threads, 0, s>>>(reinterpret_cast<uint32_t* const*>(peer_flag_ptrs),
-                                            reinterpret_cast<uint32_t*>(my_flags), reinterpret_cast<uint32_t*>(arrival),
-                                            rank, p, reinterpret_cast<uint32_t*>(status),
-                                            reinterpret_cast<const uint4*>(src),
-                                            reinterpret_cast<uint4* const*>(peer_dst_ptrs), bytes / 16, max_in, max_out,
-                                            max_n);
+  peer_exchange_kernel<<<1, max_n > 0 ? 1024 : 32, 0, s>>>(
+      reinterpret_cast<uint32_t* const*>(peer_flag_ptrs), reinterpret_cast<uint32_t*>(my_flags),
+      reinterpret_cast<uint32_t*>(arrival), rank, p, reinterpret_cast<uint32_t*>(status), max_in, max_out, max_n);
   return (int)cudaGetLastError();
 }
 
 extern "C" int iflb200_peer_barrier(const void* peer_flag_ptrs, void* my_flags, void* arrival, int rank, int p,
                                     void* status, void* stream) {
-  return iflb200_peer_exchange(peer_flag_ptrs, my_flags, arrival, rank, p, status, nullptr, nullptr, 0, nullptr, nullptr,
-                               0, stream);
+  return iflb200_peer_exchange(peer_flag_ptrs, my_flags, arrival, rank, p, status, nullptr, nullptr, 0, stream);
 }

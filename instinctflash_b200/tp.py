@@ -98,9 +98,8 @@ class PeerLink:
     allocation per GPU, mapped into every process of the group with plain peer mappings -- a
     multicast binding is refused, the data path uses ordinary loads and stores) and carves the
     ``layout`` ({name: (shape, dtype)}) out of it at identical offsets.  ``buffer(r, name)`` is rank
-    r's copy as a tensor on this device; ``exchange`` is ``iflb200_peer_exchange``: an optional small
-    payload to the peers, the barrier (bounded wait, status word), an optional max over the ranks'
-    slots.  One process per GPU."""
+    r's copy as a tensor on this device; ``exchange`` is ``iflb200_peer_exchange``: the barrier
+    (bounded wait, status word) and an optional max over the ranks' slots.  One process per GPU."""
 
     def __init__(self, layout: dict, device, group=None):
         os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")
@@ -130,7 +129,6 @@ class PeerLink:
         self.arrival = torch.zeros(1, dtype=torch.int32, device=self.dev)
         self.status = torch.zeros(1, dtype=torch.int32, device=self.dev)
         self._flag_ptrs = torch.tensor(self.base, dtype=torch.int64, device=self.dev)
-        self._dst_ptrs = {}
         self._views = {}
         torch.cuda.synchronize(self.dev)
         dist.barrier(self.group)      # nobody signals before every rank's flag words are zero
@@ -160,22 +158,9 @@ class PeerLink:
             d = (self.rank + step) % self.size
             self.buffer(d, name)[index].copy_(src)
 
-    def exchange(self, send=None, maxima=None) -> None:
-        """``send=(name, index)``: the payload region (a few tens of KB at most), copied by the
-        barrier kernel itself.  ``maxima=(name, out)``: after the barrier, out[i] = max over r of
-        the local ``name`` buffer [p][n]."""
-        src_ptr, dst_ptrs, nbytes = None, None, 0
-        if send is not None:
-            name, index = send
-            region = self.local(name)[index]
-            if not region.is_contiguous():
-                raise ValueError("a payload region must be contiguous")
-            rel = region.data_ptr() - self.base[self.rank]
-            nbytes = region.numel() * region.element_size()
-            key = (name, rel)
-            if key not in self._dst_ptrs:
-                self._dst_ptrs[key] = torch.tensor([b + rel for b in self.base], dtype=torch.int64, device=self.dev)
-            src_ptr, dst_ptrs = region.data_ptr(), self._dst_ptrs[key].data_ptr()
+    def exchange(self, maxima=None) -> None:
+        """The barrier.  ``maxima=(name, out)``: afterwards out[i] = max over r of the local ``name``
+        buffer [p][n] (slot r written by rank r before it arrived)."""
         max_in = max_out = None
         max_n = 0
         if maxima is not None:
@@ -183,8 +168,7 @@ class PeerLink:
             slots = self.local(name)
             max_in, max_out, max_n = slots.data_ptr(), out.data_ptr(), int(slots.shape[1])
         _launch("iflb200_peer_exchange", self.arrival, self._flag_ptrs.data_ptr(), self.base[self.rank],
-                self.arrival.data_ptr(), self.rank, self.size, self.status.data_ptr(), src_ptr, dst_ptrs, nbytes,
-                max_in, max_out, max_n)
+                self.arrival.data_ptr(), self.rank, self.size, self.status.data_ptr(), max_in, max_out, max_n)
 
     def check(self) -> None:
         """Host read of the status word (after a synchronize): raises if a wait ran out."""
@@ -287,7 +271,8 @@ class WanTPStack:
         if self.link is not None:
             # the owner's rows are already in place locally: push them to the peers and meet
             self.link.put("q8", self.rows)
-            self.link.exchange(send=("s0", self.rows))
+            self.link.put("s0", self.rows)
+            self.link.exchange()
             return
         self.comm.all_gather(self.q8.view(torch.uint8), self.q8_loc.view(torch.uint8))
         self.comm.all_gather(self.s0, self.s0_loc)

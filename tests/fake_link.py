@@ -47,9 +47,7 @@ class GlooLink:
     def _bytes(t):
         return t.view(torch.uint8) if t.dtype == torch.float8_e4m3fn else t
 
-    def exchange(self, send=None, maxima=None):
-        if send is not None:
-            self.put(*send)
+    def exchange(self, maxima=None):
         self.exchanges += 1
         for name in self.layout:
             work, landing = [], []

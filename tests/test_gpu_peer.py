@@ -16,21 +16,18 @@ def _ptrs(*tensors):
     return torch.tensor([t.data_ptr() for t in tensors], dtype=torch.int64, device=DEV)
 
 
-def _exchange(lib, flag_ptrs, my_flags, arrival, rank, p, status, src=None, dst_ptrs=None, nbytes=0, max_in=None,
-              max_out=None, max_n=0):
+def _exchange(lib, flag_ptrs, my_flags, arrival, rank, p, status, max_in=None, max_out=None, max_n=0):
     st = lib.iflb200_peer_exchange(flag_ptrs.data_ptr(), my_flags.data_ptr(), arrival.data_ptr(), rank, p,
-                                   status.data_ptr(), None if src is None else src.data_ptr(),
-                                   None if dst_ptrs is None else dst_ptrs.data_ptr(), nbytes,
-                                   None if max_in is None else max_in.data_ptr(),
+                                   status.data_ptr(), None if max_in is None else max_in.data_ptr(),
                                    None if max_out is None else max_out.data_ptr(), max_n,
                                    torch.cuda.current_stream().cuda_stream)
     assert st == 0, st
 
 
-def test_exchange_copies_the_payload_signals_every_peer_and_reduces_the_maxima():
-    """Rank 1 of 3 with both peers already arrived (their words preset): the payload lands in both
-    peers' buffers, arrival number 1 is stored into word 1 of both peers' flags, the arrival counter
-    advances, and the slots are reduced with max -- twice, the second time with arrival 2."""
+def test_exchange_signals_every_peer_and_reduces_the_maxima():
+    """Rank 1 of 3 with both peers already arrived (their words preset): arrival number 1 is stored
+    into word 1 of both peers' flags, the arrival counter advances, and the slots are reduced with
+    max -- twice, the second time with arrival 2."""
     lib = _lib.lib()
     p, rank, n = 3, 1, 1000
     flags = [torch.zeros(p, dtype=torch.int32, device=DEV) for _ in range(p)]   # flags[r] = rank r's words
@@ -38,28 +35,23 @@ def test_exchange_copies_the_payload_signals_every_peer_and_reduces_the_maxima()
     status = torch.zeros(1, dtype=torch.int32, device=DEV)
     g = torch.Generator(device="cpu").manual_seed(5)
     slots = torch.rand(p, n, generator=g).to(DEV)                               # this rank's [p][n] maxima slots
-    peer_slots = [torch.zeros(p, n, device=DEV) for _ in range(p)]
     out = torch.zeros(n, device=DEV)
     flag_ptrs = _ptrs(*flags)
-    dst_ptrs = _ptrs(*[peer_slots[r][rank] for r in range(p)])
     for e in (1, 2):
         flags[rank][0] = e
         flags[rank][2] = e                                                      # "peers 0 and 2 have arrived"
-        _exchange(lib, flag_ptrs, flags[rank], arrival, rank, p, status, src=slots[rank], dst_ptrs=dst_ptrs,
-                  nbytes=n * 4, max_in=slots, max_out=out, max_n=n)
+        _exchange(lib, flag_ptrs, flags[rank], arrival, rank, p, status, max_in=slots, max_out=out, max_n=n)
         torch.cuda.synchronize()
         assert int(status.item()) == 0
         assert int(arrival.item()) == e
         for r in (0, 2):
             assert int(flags[r][rank].item()) == e
-            assert torch.equal(peer_slots[r][rank], slots[rank])
-            assert float(peer_slots[r][0].abs().max()) == 0.0                   # nothing else was written
-        assert torch.equal(peer_slots[rank], torch.zeros_like(peer_slots[rank]))  # no copy to itself
+            assert int(flags[r][0].item()) == 0 and int(flags[r][2].item()) == 0   # only this rank's word
         assert torch.equal(out, slots.amax(0))
         slots.mul_(0.5)
 
 
-def test_plain_barrier_is_the_exchange_without_payload():
+def test_plain_barrier_is_the_exchange_without_a_reduction():
     lib = _lib.lib()
     flags = [torch.zeros(2, dtype=torch.int32, device=DEV) for _ in range(2)]
     flags[0][1] = 1
@@ -102,10 +94,10 @@ def test_argument_checks():
     s = torch.cuda.current_stream().cuda_stream
     assert lib.iflb200_peer_barrier(None, f.data_ptr(), f.data_ptr(), 0, 2, f.data_ptr(), s) == _lib.ERR_ARG
     assert lib.iflb200_peer_barrier(ptrs.data_ptr(), f.data_ptr(), f.data_ptr(), 2, 2, f.data_ptr(), s) == _lib.ERR_ARG
-    assert lib.iflb200_peer_exchange(ptrs.data_ptr(), f.data_ptr(), f.data_ptr(), 0, 2, f.data_ptr(), f.data_ptr(),
-                                     ptrs.data_ptr(), 24, None, None, 0, s) == _lib.ERR_ALIGN
-    assert lib.iflb200_peer_exchange(ptrs.data_ptr(), f.data_ptr(), f.data_ptr(), 0, 2, f.data_ptr(), None, None, 0,
-                                     None, None, 8, s) == _lib.ERR_ARG
+    assert lib.iflb200_peer_exchange(ptrs.data_ptr(), f.data_ptr(), f.data_ptr(), 0, 2, f.data_ptr(), None, None, 8,
+                                     s) == _lib.ERR_ARG
+    assert lib.iflb200_peer_exchange(ptrs.data_ptr(), f.data_ptr() + 2, f.data_ptr(), 0, 2, f.data_ptr(), None, None, 0,
+                                     s) == _lib.ERR_ALIGN
 
 
 # ---- the fused kernels of the tensor-parallel row-split linear, with local stand-ins for the peers ----
