@@ -670,6 +670,7 @@ def main():
                     help="for profilers: build ONE layer of the workload, launch only the named operator of the path "
                          "`--steps` times (a linear of the stack: qkv, o, gate_up, down, ff1, ff2 ...; or 'layer' for "
                          "one eager pass of the whole layer) and exit without timing anything")
+    ap.add_argument("--gemm-group-m", type=int, default=0, help="band height of the GEMM's tile walk for the whole run (experiments)")
     ap.add_argument("--gemm-mode", type=int, default=0, help="iflb200_gemm_set_mode value for the whole run (experiments)")
     ap.add_argument("--branches", type=int, default=EPISODE_BRANCHES, help="c3 episodes in flight per GPU")
     ap.add_argument("--episodes", type=int, default=1,
@@ -710,6 +711,8 @@ def main():
     _lib.lib()  # fail loudly when the CUDA library is missing
     if args.gemm_mode and _lib.lib().iflb200_gemm_set_mode(args.gemm_mode) != 0:
         raise SystemExit(f"--gemm-mode {args.gemm_mode} is not a valid mode")
+    if args.gemm_group_m and _lib.lib().iflb200_gemm_set_config(0, 0, args.gemm_group_m) != 0:
+        raise SystemExit(f"--gemm-group-m {args.gemm_group_m} is not valid")
     torch.cuda.set_device(local_rank)
     dev = torch.device("cuda", local_rank)
     dist = None

@@ -1471,18 +1471,19 @@ static int run_gemm(const void* a, int64_t ld_a, const void* w, int64_t ld_w, Ge
   } else {
     memset(&to, 0, sizeof(to));
   }
-  // CTA pairs by choice of the heuristic: in the large-M regime both kernels sit at the tensor
-  // pipe's rate, but a pair moves 32 KB per SM and K step instead of 48 KB, and a layer stack that
-  // runs for milliseconds is power-capped: measured inside the M = 16384 stack the pair kernel is
-  // 3.3 % faster, inside the M = 4680 stack (19 pair row blocks for 18.3 needed, 10 waves for 9)
-  // 2-3 % slower.  It is taken when its wave count (of equal work) is not above the single-CTA one.
+  // CTA pairs by choice of the heuristic.  A pair moves 32 KB per SM and K step instead of 48 KB
+  // and its 256 x 256 tile takes about 0.87 of the time two SMs need for two 128 x 256 tiles
+  // (measured per shape at M = 4680: 9216 x 3072 98.7 us on pairs in 10 waves against 103.7 us on
+  // single CTAs in 9; 14336 x 3072 149.5 against 161.2; but 3072 x 14336 186 against 150 where the
+  // pairs need 4 waves for 3).  So the pair kernel is taken when its wave count, weighted by that
+  // factor, is below the single-CTA one.
   bool pair_by_heuristic = false;
-  if (g_cfg_mode == 0 && g_cfg_tile_n == 0 && g_cfg_split_k == 0 && p.M >= 4096 && p.N >= 256) {
+  if (g_cfg_mode == 0 && g_cfg_tile_n == 0 && g_cfg_split_k == 0 && p.M >= 2048 && p.N >= 256) {
     const int64_t single_tiles = (int64_t)((p.M + BM - 1) / BM) * ((p.N + 255) / 256);
     const int64_t pair_tiles = (int64_t)((p.M + 2 * BM - 1) / (2 * BM)) * ((p.N + 255) / 256);
     const int64_t single_waves = (single_tiles + dev->sm_count - 1) / dev->sm_count;
     const int64_t pair_waves = (pair_tiles + dev->sm_count / 2 - 1) / (dev->sm_count / 2);
-    pair_by_heuristic = pair_waves <= single_waves;
+    pair_by_heuristic = pair_waves * 87 < single_waves * 100;
   }
   if ((g_cfg_mode >= 2 || pair_by_heuristic) && p.N >= 256) {
     // CTA pairs: 256 x 256 tiles, each CTA loads 128 rows of A and 128 rows of W per K step.
@@ -1491,9 +1492,14 @@ static int run_gemm(const void* a, int64_t ld_a, const void* w, int64_t ld_w, Ge
     p.num_n = (p.N + PBN - 1) / PBN;
     p.num_k = (p.K + BK - 1) / BK;
     p.num_tiles = p.num_m * p.num_n;
-    // band height (row blocks that run side by side and share W tiles through L2): measured at
-    // M = 16384, deep reductions are fastest with 2 (888 vs 942 us at K = 13824), the others with 4
-    p.group_m = g_cfg_group_m > 0 ? g_cfg_group_m : (p.K >= 8192 ? 2 : 4);
+    // band height (pair row blocks that run side by side and share W tiles through L2).  W is read
+    // from DRAM once per band when it does not stay in L2 beside the output stream, so taller bands
+    // read less (16384 x 15360 x 5120 with bands of 4: 1317 MB read for 163 MB of operands); a band's
+    // own A rows must stay resident while the walk crosses the columns.  Measured inside the
+    // M = 16384 stack: bands of 16 are 4 % faster than bands of 4, bands of 32 lose half of that
+    // again; at M = 4680 (19 pair row blocks) one band of all rows is fastest (98.7 against 101.1 us
+    // on 9216 x 3072).  So: 16, or every row block when a second band would be a sliver.
+    p.group_m = g_cfg_group_m > 0 ? g_cfg_group_m : (p.num_m <= 24 ? p.num_m : 16);
     const int pairs = dev->sm_count / 2;
     const int grid = 2 * (p.num_tiles < pairs ? p.num_tiles : pairs);
     CUtensorMap ta, tw;
