@@ -356,6 +356,104 @@ def time_config(spec, dev, ref_ops, steps, warmup, *, persistent=False):
     return out
 
 
+def qkv_consumer_calls(dev, which, ref=False):
+    """The consumers of a fused QKV accumulator at benchmark sizes, as zero-argument callables over
+    rotated inputs larger than L2: ``qkv_split`` at the C2 prefix shape (816 tokens, 8 + 2x1 heads of
+    256: instinctflash/engines/pi05/engine.py:200-201) and ``wan_qkv`` at the C5 shape (2 x 8192
+    tokens, 40 heads of 128, q/k norm, three-axis rotary, pooled K/V:
+    instinctflash/engines/wan_va/engine.py:215-217).  ``ref``: the reference's Triton kernels."""
+    if ref:
+        ref_root = ROOT / "baseline" / "_ref"
+        if str(ref_root) not in sys.path:
+            sys.path.insert(0, str(ref_root))
+        from instinctflash.kernels.rope import qkv_split, rope_inv_freq
+        from instinctflash.kernels.wan import wan_qkv
+    else:
+        from instinctflash_b200.kernels.rope import qkv_split, rope_inv_freq
+        from instinctflash_b200.kernels.wan import wan_qkv
+    g = torch.Generator(device=dev).manual_seed(7)
+    if which == "qkv_split":
+        T, HQ, HKV, HD = 816, 8, 1, 256
+        W = (HQ + 2 * HKV) * HD
+        copies = 48                                            # 48 x 4.2 MB of accumulators: 200 MB
+        raws = [torch.randn(T, W, device=dev, generator=g).to(torch.bfloat16) for _ in range(copies)]
+        row = torch.rand(T, device=dev, generator=g) * 0.02
+        col = torch.rand(W, device=dev, generator=g)
+        inv = rope_inv_freq(HD, 10000.0, dev)
+        pos = torch.arange(T, device=dev).float()[:, None].contiguous()
+        q = torch.empty(T, HQ, HD, device=dev, dtype=torch.float16)
+        k = torch.empty(1024, HKV, HD, device=dev, dtype=torch.float16)
+        v = torch.empty_like(k)
+        kw = dict(heads_q=HQ, heads_kv=HKV, head_dim=HD, row=row, col=col, inv_freq=inv, pos=pos)
+        calls = [lambda r=r: qkv_split(r, q, k, v, **kw) for r in raws]
+        return calls, T * W * 4.0, f"qkv_split {T} x {W} bf16 -> f16 heads, row/col scales, rotary"
+    B, T, H, HD = 2, 8192, 40, 128
+    D, R = H * HD, B * T
+    raws = [torch.randn(R, 3 * D, device=dev, generator=g).to(torch.bfloat16) for _ in range(2)]   # 2 x 503 MB
+    row = torch.rand(R, device=dev, generator=g) * 0.02
+    col = torch.rand(3 * D, device=dev, generator=g)
+    bias = torch.randn(3 * D, device=dev, generator=g)
+    qn = torch.rand(D, device=dev, generator=g) + 0.5
+    kn = torch.rand(D, device=dev, generator=g) + 0.5
+    inv = rope_inv_freq(HD, 10000.0, dev)
+    pos = (torch.rand(T, 3, device=dev, generator=g) * 60).floor()
+    sec = (torch.arange(HD // 2, device=dev) % 3).int()
+    q = torch.empty(R, D, device=dev, dtype=torch.float16)
+    kp = torch.empty(B, T, D, device=dev, dtype=torch.float16)
+    vp = torch.empty_like(kp)
+    kw = dict(heads=H, head_dim=HD, tokens=T, k_pool=kp, v_pool=vp, row=row, col=col, bias=bias, q_norm=qn, k_norm=kn,
+              pos=pos, sections=sec, inv_freq=inv)
+    calls = [lambda r=r: wan_qkv(r, q, **kw) for r in raws]
+    return calls, R * 3 * D * 4.0, f"wan_qkv {R} x {3 * D} bf16 -> f16 q + pooled k/v, scales, bias, q/k norm, 3-axis rotary"
+
+
+def time_qkv_consumers(dev, with_reference):
+    """µs per launch of the two QKV consumers (CUDA events around a graph of launches over rotated
+    inputs), this build and -- when the reference imports -- its Triton kernels, A-B-B-A."""
+    stream = torch.cuda.current_stream(dev)
+    peaks = measured_peaks()
+    out = {}
+    for which in ("qkv_split", "wan_qkv"):
+        def graph_of(calls):
+            side = torch.cuda.Stream(dev)
+            side.wait_stream(stream)
+            with torch.cuda.stream(side):
+                for c in calls:
+                    c()
+            stream.wait_stream(side)
+            gr = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(gr):
+                for c in calls:
+                    c()
+            return gr
+        calls, nbytes, what = qkv_consumer_calls(dev, which)
+        gn = graph_of(calls)
+        gn.replay()
+        entry = {"workload": what}
+        gr = None
+        if with_reference:
+            try:
+                rcalls, _, _ = qkv_consumer_calls(dev, which, ref=True)
+                gr = graph_of(rcalls)
+                gr.replay()
+            except Exception as exc:   # noqa: BLE001
+                entry["gpu_reference"] = {"unavailable": f"{type(exc).__name__}: {exc}"[:160]}
+        n = 5
+        if gr is not None:
+            ms, ms_ref = abba(gn, gr, n, stream, dev)
+            entry["gpu_reference"] = {"us_per_launch": ms_ref / len(calls) * 1e3, "ratio": ms_ref / ms}
+        else:
+            ms = replay_ms(gn, 2 * n, stream, dev) / (2 * n)
+        us = ms / len(calls) * 1e3
+        gbs = nbytes / (us * 1e-6) / 1e9
+        entry.update({"us_per_launch": us, "roofline": {"bound": "hbm", "achieved": gbs, "peak": peaks["hbm_gbs"],
+                                                        "unit": "GB/s", "frac": gbs / peaks["hbm_gbs"]}})
+        out[which] = entry
+        del calls, gn, gr
+        torch.cuda.empty_cache()
+    return out
+
+
 def time_single_linear(dev, ref_ops, steps, warmup):
     """Configuration 1: one FP8 linear, x bf16 [64, 1024] -> per-token quantiser -> [4096, 1024]
     weight + bias -> bf16.  Thirty-two weight copies are rotated so the 4 MB weight is not served
@@ -620,7 +718,11 @@ def profile_operator(args, spec, dev):
     st.load(x, attn)
     st.forward()            # every buffer holds plausible values
     torch.cuda.synchronize(dev)
-    if args.profile_op == "layer":
+    if args.profile_op in ("qkv_split", "wan_qkv"):
+        calls, _, _ = qkv_consumer_calls(dev, args.profile_op)
+        for i in range(args.steps):
+            calls[i % len(calls)]()
+    elif args.profile_op == "layer":
         for _ in range(args.steps):
             st.forward()
     else:
@@ -668,7 +770,8 @@ def main():
     ap.add_argument("--fuse-residual", action="store_true", help="residual update in the GEMM epilogue as well")
     ap.add_argument("--profile-op", default=None,
                     help="for profilers: build ONE layer of the workload, launch only the named operator of the path "
-                         "`--steps` times (a linear of the stack: qkv, o, gate_up, down, ff1, ff2 ...; or 'layer' for "
+                         "`--steps` times (a linear of the stack: qkv, o, gate_up, down, ff1, ff2 ...; 'qkv_split' / 'wan_qkv' for the "
+                         "QKV consumers at benchmark size; or 'layer' for "
                          "one eager pass of the whole layer) and exit without timing anything")
     ap.add_argument("--gemm-group-m", type=int, default=0, help="band height of the GEMM's tile walk for the whole run (experiments)")
     ap.add_argument("--gemm-mode", type=int, default=0, help="iflb200_gemm_set_mode value for the whole run (experiments)")
@@ -920,6 +1023,8 @@ def main():
                 if cfg == args.workload:
                     continue
                 configs[cfg] = time_config(SPECS[cfg], dev, ref_ops, k, w, persistent=cfg == "c3")
+            torch.cuda.empty_cache()
+            configs["qkv_consumers"] = time_qkv_consumers(dev, ref_ops is not None)
         except Exception as exc:   # noqa: BLE001
             configs["error"] = f"{type(exc).__name__}: {exc}"[:300]
         check_no_timeout(dev)

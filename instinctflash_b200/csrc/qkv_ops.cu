@@ -333,7 +333,10 @@ cudaError_t launch_qkv_split_out(const QkvSplitArgs& a, int out_dtype, cudaStrea
 // stride obeys the 16-byte rule, the width is a multiple of 8 and the head width a multiple of 8,
 // so all accesses are 128-bit and a chunk lies inside one head.
 // --------------------------------------------------------------------------------------------
-constexpr int kWanMaxThreads = 256;
+#ifndef IFLB200_WAN_MAX_THREADS
+#define IFLB200_WAN_MAX_THREADS 256
+#endif
+constexpr int kWanMaxThreads = IFLB200_WAN_MAX_THREADS;
 constexpr int kWanMaxChunks = 8;
 
 struct WanQkvArgs {
