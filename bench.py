@@ -894,20 +894,32 @@ def main():
     clock_summary = clocks.summary()
 
     # ---- end to end: pinned host activations in, residual stream out, every step ---------------
-    x_stage = torch.empty_like(x_dev)
-    for _ in range(2):
-        x_stage.copy_(x_host, non_blocking=True)
-        stack.load(x_stage, attn)
-        graph.replay()
-        out_host.copy_(stack.res, non_blocking=True)
+    # Through the package's serving loop (stack.HostPipeline): every step copies its input from pinned
+    # host memory and its residual stream back; the copies of neighbouring steps overlap the compute.
+    from instinctflash_b200.stack import HostPipeline
+    if hasattr(stack, "res") and not persistent:
+        pipe = HostPipeline(stack, graph)
+        submit, drain = (lambda: pipe.submit(x_host, out_host, attn)), pipe.drain
+    else:
+        x_stage = torch.empty_like(x_dev)
+
+        def submit():
+            x_stage.copy_(x_host, non_blocking=True)
+            stack.load(x_stage, attn)
+            graph.replay()
+            out_host.copy_(stack.res, non_blocking=True)
+
+        def drain():
+            return None
+    for _ in range(3):
+        submit()
+    drain()
     barrier()
     f0, f1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     f0.record(stream)
     for _ in range(args.steps):
-        x_stage.copy_(x_host, non_blocking=True)
-        stack.load(x_stage, attn)
-        graph.replay()
-        out_host.copy_(stack.res, non_blocking=True)
+        submit()
+    drain()
     f1.record(stream)
     barrier()
     ms_e2e = f0.elapsed_time(f1)

@@ -281,6 +281,57 @@ class LinearStack:
         return graph
 
 
+class HostPipeline:
+    """Serving loop around one stack whose inputs arrive in pinned host memory and whose residual
+    stream goes back to the host: step i's host-to-device copy runs on a copy stream while step
+    i-1 computes, and step i's result leaves on a second copy stream while step i+1 computes (two
+    staging buffers each way).  Every step still copies its own input in and its own result out;
+    only the waiting is overlapped."""
+
+    def __init__(self, stack, graph, depth: int = 2):
+        self.stack, self.graph, self.depth = stack, graph, depth
+        dev = stack.dev
+        self.dev = dev
+        self.h2d, self.d2h = torch.cuda.Stream(dev), torch.cuda.Stream(dev)
+        self.x_stage = [torch.empty_like(stack.res) for _ in range(depth)]
+        self.out_stage = [torch.empty_like(stack.res) for _ in range(depth)]
+        self.x_ready = [torch.cuda.Event() for _ in range(depth)]      # staging input i holds this step's data
+        self.x_free = [torch.cuda.Event() for _ in range(depth)]       # the stack has consumed staging input i
+        self.out_ready = [torch.cuda.Event() for _ in range(depth)]    # staging output i holds this step's result
+        self.out_free = [torch.cuda.Event() for _ in range(depth)]     # staging output i has left for the host
+        self.step = 0
+
+    def submit(self, x_host: torch.Tensor, out_host: torch.Tensor, attn: torch.Tensor) -> None:
+        """Enqueue one inference: x_host (pinned) in, the residual stream into out_host (pinned).
+        Returns at once; ``drain`` waits for everything enqueued so far."""
+        i, k = self.step, self.step % self.depth
+        main = torch.cuda.current_stream(self.dev)
+        with torch.cuda.stream(self.h2d):
+            if i >= self.depth:
+                self.h2d.wait_event(self.x_free[k])
+            self.x_stage[k].copy_(x_host, non_blocking=True)
+            self.x_ready[k].record(self.h2d)
+        main.wait_event(self.x_ready[k])
+        self.stack.load(self.x_stage[k], attn)
+        self.x_free[k].record(main)
+        self.graph.replay()
+        if i >= self.depth:
+            main.wait_event(self.out_free[k])
+        self.out_stage[k].copy_(self.stack.res, non_blocking=True)
+        self.out_ready[k].record(main)
+        with torch.cuda.stream(self.d2h):
+            self.d2h.wait_event(self.out_ready[k])
+            out_host.copy_(self.out_stage[k], non_blocking=True)
+            self.out_free[k].record(self.d2h)
+        self.step += 1
+
+    def drain(self) -> None:
+        """Make the current stream wait for every copy enqueued so far (no host synchronisation)."""
+        main = torch.cuda.current_stream(self.dev)
+        main.wait_stream(self.h2d)
+        main.wait_stream(self.d2h)
+
+
 class EpisodeBatch:
     """``episodes`` independent inferences of one stack on one GPU: one ``LinearStack`` each (own
     activations, residual stream and scales) over shared weights, captured as parallel branches

@@ -434,3 +434,31 @@ def test_install_on_the_reference_engine_module_and_run_its_call_sequence_both_w
     assert torch.equal(native.forward(), got)                       # the installed names ARE this package's operators
     rel = float((got - ref_res).norm() / ref_res.norm())
     assert rel < 2e-2, rel
+
+
+def test_host_pipeline_returns_each_step_its_own_result():
+    """Pinned host inputs through the overlapped serving loop: step i's output is the residual
+    stream a lone run computes from step i's input, for more steps than staging buffers."""
+    from instinctflash_b200.stack import HostPipeline
+    spec = StackSpec("t", "gemma", 2, 200, 512, 1024, 768, o_in=512, outlier_frac=0.02, outlier_scale=10.0, seed=51)
+    weights = make_weights(spec, DEV)
+    xs, attn = [], None
+    for e in range(5):
+        x, attn = make_inputs(StackSpec(**{**spec.__dict__, "seed": 60 + e}), DEV)
+        xs.append(x)
+    st = LinearStack(spec, weights, DEV)
+    want = []
+    for x in xs:
+        st.load(x, attn)
+        want.append(st.forward().clone())
+    st.load(xs[0], attn)
+    graph = st.capture()
+    pipe = HostPipeline(st, graph)
+    x_hosts = [x.cpu().pin_memory() for x in xs]
+    out_hosts = [torch.empty(spec.M, spec.hidden, dtype=st.res.dtype).pin_memory() for _ in xs]
+    for xh, oh in zip(x_hosts, out_hosts):
+        pipe.submit(xh, oh, attn)
+    pipe.drain()
+    torch.cuda.synchronize()
+    for e, (oh, w) in enumerate(zip(out_hosts, want)):
+        assert torch.equal(oh, w.cpu()), e
