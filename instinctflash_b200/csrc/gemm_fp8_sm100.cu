@@ -450,6 +450,22 @@ __device__ __forceinline__ void epilogue_tma_store(const GemmParams& p, const CU
   }
 }
 
+// Column scales of the gated form for the chunks one epilogue warp handles (see epilogue_gated for
+// the split of a tile over the warps), fetched before the accumulator is waited for.
+template <int BN, int PARTS>
+__device__ __forceinline__ void gated_scales(const GemmParams& p, int n_base, int part, int lane, float (&cgl)[4],
+                                             float (&cul)[4]) {
+  constexpr int kChunks = BN / 2 / 32;
+  constexpr int kPerPart = kChunks >= PARTS ? kChunks / PARTS : 1;
+#pragma unroll
+  for (int k = 0; k < 4; ++k) {
+    const int n = n_base + part * kPerPart * 32 + 32 * k + lane;
+    const bool in = p.col && k < kPerPart && part * kPerPart < kChunks && n < p.N;
+    cgl[k] = in ? __ldg(p.col + n) : 0.0f;
+    cul[k] = in ? __ldg(p.col + p.N + n) : 0.0f;
+  }
+}
+
 // Epilogue of the gated form.  A tile of BN accumulator columns holds BN/2 gate columns followed
 // by the BN/2 up columns of the same hidden units (the producer loads the two halves of the
 // [gate | up] weight matrix side by side), so the gated activation of
@@ -467,7 +483,10 @@ __device__ __forceinline__ void epilogue_tma_store(const GemmParams& p, const CU
 template <int BN, int PARTS>
 __device__ __forceinline__ void epilogue_gated(const GemmParams& p, const CUtensorMap* tm_out, uint32_t t_row,
                                                uint32_t staging, uint8_t* staging_ptr, int row0, int n_base,
-                                               int part, int m, bool row_ok, float rs, int lane) {
+                                               int part, int m, bool row_ok, float rs, int lane,
+                                               const float (&cgl)[4], const float (&cul)[4]) {
+  // cgl[k] / cul[k]: the gate / up column scale of hidden unit n_base + c_begin + 32k + lane, fetched
+  // before the accumulator was waited for (gated_scales); every lane takes column i's from lane i.
   constexpr int HW = BN / 2;        // hidden units per tile
   constexpr int kChunks = HW / 32;  // chunks of 32 columns in a tile: 4, 2 or 1
   constexpr int kPerPart = kChunks >= PARTS ? kChunks / PARTS : 1;
@@ -477,7 +496,6 @@ __device__ __forceinline__ void epilogue_gated(const GemmParams& p, const CUtens
   // columns each (64-byte swizzle: 16-byte piece index ^ ((row >> 1) & 3)).
   constexpr bool kHalfRows = PARTS > 2;
   uint8_t* mine = staging_ptr + lane * (kHalfRows ? 64 : 128);
-  const bool vec_scales = p.col && ((reinterpret_cast<uintptr_t>(p.col) & 15) == 0);
   float row_max = 0.0f;
   bool any = false;
 #pragma unroll 1
@@ -526,20 +544,13 @@ __device__ __forceinline__ void epilogue_gated(const GemmParams& p, const CUtens
       if (p.col) {
         float cg[8], cu[8];
         const int n = n0 + 8 * j;
-        if (whole && vec_scales) {  // hidden widths are multiples of 16 and n of 8: both vectors are 16-byte aligned
-          const float4 a0 = __ldg(reinterpret_cast<const float4*>(p.col + n));
-          const float4 a1 = __ldg(reinterpret_cast<const float4*>(p.col + n + 4));
-          const float4 b0 = __ldg(reinterpret_cast<const float4*>(p.col + p.N + n));
-          const float4 b1 = __ldg(reinterpret_cast<const float4*>(p.col + p.N + n + 4));
-          cg[0] = a0.x; cg[1] = a0.y; cg[2] = a0.z; cg[3] = a0.w; cg[4] = a1.x; cg[5] = a1.y; cg[6] = a1.z; cg[7] = a1.w;
-          cu[0] = b0.x; cu[1] = b0.y; cu[2] = b0.z; cu[3] = b0.w; cu[4] = b1.x; cu[5] = b1.y; cu[6] = b1.z; cu[7] = b1.w;
-        } else {
+        (void)n;
+        const float gl = k == 0 ? cgl[0] : (k == 1 ? cgl[1] : (k == 2 ? cgl[2] : cgl[3]));  // k is uniform
+        const float ul = k == 0 ? cul[0] : (k == 1 ? cul[1] : (k == 2 ? cul[2] : cul[3]));
 #pragma unroll
-          for (int i = 0; i < 8; ++i) {
-            const bool in = n + i < p.N;
-            cg[i] = in ? __ldg(p.col + n + i) : 0.0f;
-            cu[i] = in ? __ldg(p.col + p.N + n + i) : 0.0f;
-          }
+        for (int i = 0; i < 8; ++i) {
+          cg[i] = __shfl_sync(0xFFFFFFFFu, gl, 8 * j + i);
+          cu[i] = __shfl_sync(0xFFFFFFFFu, ul, 8 * j + i);
         }
 #pragma unroll
         for (int i = 0; i < 8; i += 2) {
@@ -889,6 +900,11 @@ gemm_fp8_tc5_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
         cv = fetch_column_vectors(p, n_blk * BN + col_begin, col_end - col_begin, lane);
         rs_early = (row_ok && p.row) ? __ldg(p.row + (int64_t)(grp * p.group_rows + m) * p.row_stride) : 1.0f;
       }
+      float cgl[4], cul[4];
+      if constexpr (GATED) {
+        gated_scales<BN, EW / 4>(p, n_blk * (BN / 2), half, lane, cgl, cul);
+        rs_early = (row_ok && p.row) ? __ldg(p.row + (int64_t)m * p.row_stride) : 1.0f;
+      }
       ok = __all_sync(0xFFFFFFFFu, wait_bounded(tfull_bar(acc), acc_phase, abort_flag,
                                                 (3u << 24) | (4u << 16) | (it & 0xFFFF)));
       if (!ok) break;
@@ -902,10 +918,10 @@ gemm_fp8_tc5_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
         if (lane == 0) mbar_arrive(tempty_bar(acc));
         continue;
       }
-      const float rs = prefetch ? rs_early : ((row_ok && p.row) ? __ldg(p.row + (int64_t)m * p.row_stride) : 1.0f);
+      const float rs = (prefetch || GATED) ? rs_early : ((row_ok && p.row) ? __ldg(p.row + (int64_t)m * p.row_stride) : 1.0f);
       if constexpr (GATED) {
         epilogue_gated<BN, EW / 4>(p, &tm_out, t_row, staging, staging_ptr, m_blk * BM + quad * 32, n_blk * (BN / 2),
-                                   half, m, row_ok, rs, lane);
+                                   half, m, row_ok, rs, lane, cgl, cul);
         tc_fence_before();
         __syncwarp();
         if (lane == 0) mbar_arrive(tempty_bar(acc));
