@@ -551,7 +551,7 @@ __device__ __forceinline__ float round_through<__nv_bfloat16>(float x) {
 // PART: the delta arrives as fp32 partial sums of a K-split GEMM (a.dpart) instead of a raw bf16
 // accumulator; a separate instantiation so that the ordinary one keeps its registers.
 template <typename RT, int TPR, int IT, bool FAST, bool PART = false>
-__global__ void __launch_bounds__(kRowThreads, (PART && IT > 1) ? 2 : resnorm_min_blocks<IT>())
+__global__ void __launch_bounds__(kRowThreads, PART ? 2 : resnorm_min_blocks<IT>())
 residual_norm_quant_kernel(const ResNormArgs a) {
   row_dependency_wait();  // inputs may come from the kernel before this one in the stream
   row_trigger();
@@ -586,17 +586,19 @@ residual_norm_quant_kernel(const ResNormArgs a) {
       if (dr || PART) {
         float d[8], cs[8], bs[8], gs[8];
         if constexpr (PART) {
-          // four planes in flight together, added in split order
+          // kGroup planes in flight together (all eight for rows of one chunk per thread: the skinny
+          // expert shapes, where a second dependent round trip is a tenth of the kernel), added in split order
+          constexpr int kGroup = IT == 1 ? 8 : 4;
 #pragma unroll
           for (int i = 0; i < 8; ++i) d[i] = 0.0f;
 #pragma unroll 1
-          for (int s0 = 0; s0 < a.dsplits; s0 += 4) {
-            float e[4][8];
+          for (int s0 = 0; s0 < a.dsplits; s0 += kGroup) {
+            float e[kGroup][8];
 #pragma unroll
-            for (int sp = 0; sp < 4; ++sp)
+            for (int sp = 0; sp < kGroup; ++sp)
               if (s0 + sp < a.dsplits) load_f32<FAST>(dp + (s0 + sp) * dp_plane, c0, a.D, e[sp]);
 #pragma unroll
-            for (int sp = 0; sp < 4; ++sp) {
+            for (int sp = 0; sp < kGroup; ++sp) {
               if (s0 + sp < a.dsplits) {
 #pragma unroll
                 for (int i = 0; i < 8; ++i) d[i] = (s0 + sp == 0) ? e[sp][i] : __fadd_rn(d[i], e[sp][i]);
