@@ -78,6 +78,28 @@ struct GemmParams {
 __device__ uint32_t g_timeout_record[4];
 // Time budget of every wait inside the GEMM kernels (read only on the slow path of a wait).
 __device__ uint64_t g_gemm_wait_budget_ns = kWaitBudgetNs;
+#ifdef IFLB200_TRACE
+// Experiment builds only (-DIFLB200_TRACE; never in the product library): block 0 of each launch of
+// the single-CTA kernel stamps the SM clock at a few points; slot 0 holds globaltimer at entry.
+__device__ unsigned long long g_gemm_trace[64][16];
+__device__ unsigned int g_gemm_trace_launch;
+__device__ unsigned int g_gemm_trace_cur;  // id of the launch whose block 0 is tracing (helpers without the id)
+#define GEMM_TRACE_IN_HELPER(slot, cond)                                                                       \
+  do {                                                                                                         \
+    if (blockIdx.x == 0 && (cond)) g_gemm_trace[g_gemm_trace_cur & 63][slot] = (unsigned long long)clock64(); \
+  } while (0)
+#define GEMM_TRACE(slot)                                                              \
+  do {                                                                                \
+    if (blockIdx.x == 0) g_gemm_trace[trace_id & 63][slot] = (unsigned long long)clock64(); \
+  } while (0)
+#else
+#define GEMM_TRACE(slot) \
+  do {                   \
+  } while (0)
+#define GEMM_TRACE_IN_HELPER(slot, cond) \
+  do {                                   \
+  } while (0)
+#endif
 int set_stack_wait_budget_ns(uint64_t ns);  // stack_persistent.cu
 int set_peer_wait_budget_ns(uint64_t ns);   // xgpu_ops.cu
 
@@ -431,6 +453,7 @@ __device__ __forceinline__ void epilogue_tma_store(const GemmParams& p, const CU
       uint32_t r[32];
       tmem_ld_32x32b_x32(t_row + c + sub, r);
       tmem_ld_wait();
+      GEMM_TRACE_IN_HELPER(10, threadIdx.x == 64 && c == col_begin && sub == 0);  // first chunk out of tensor memory
       if (cv != nullptr) {
         const int k = (c + sub - col_begin) >> 5;  // which of the warp's 32-column chunks (uniform)
         const float csl = k == 0 ? cv->cs[0] : (k == 1 ? cv->cs[1] : (k == 2 ? cv->cs[2] : cv->cs[3]));
@@ -439,9 +462,12 @@ __device__ __forceinline__ void epilogue_tma_store(const GemmParams& p, const CU
       } else {
         stage_columns(p, r, n0 + sub, rs, mine, sub, lane);
       }
+      GEMM_TRACE_IN_HELPER(11, threadIdx.x == 64 && c == col_begin && sub == 0);  // first chunk staged
     }
+    GEMM_TRACE_IN_HELPER(12, threadIdx.x == 64 && c == col_begin);  // first piece staged
     fence_proxy_async_smem();  // generic-proxy writes visible to the TMA unit
     __syncwarp();
+    GEMM_TRACE_IN_HELPER(13, threadIdx.x == 64 && c == col_begin);  // fenced
     if (lane == 0) {
       if (z >= 0) tma_store_3d(tm_out, staging, n0, row0, z);  // partial sums: plane z of [splits][M][N]
       else tma_store_2d(tm_out, staging, n0, row0);
@@ -697,6 +723,19 @@ gemm_fp8_tc5_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
+#ifdef IFLB200_TRACE
+  __shared__ unsigned int trace_id_s;
+  if (threadIdx.x == 0) {
+    trace_id_s = blockIdx.x == 0 ? atomicAdd(&g_gemm_trace_launch, 1u) : 0u;
+    if (blockIdx.x == 0) {
+      g_gemm_trace_cur = trace_id_s;
+      g_gemm_trace[trace_id_s & 63][0] = globaltimer_ns();
+      g_gemm_trace[trace_id_s & 63][1] = (unsigned long long)clock64();
+    }
+  }
+  __syncthreads();
+  const unsigned int trace_id = trace_id_s;
+#endif
   // Split-K: the S CTAs of a cluster work on the same tile, CTA r on K steps [kb0, kb1); one
   // tile per CTA (the host launches tiles x S CTAs, at most one wave).
   // Partials: K split over independent CTAs (no cluster), each writing its fp32 partial sums.
@@ -734,6 +773,7 @@ gemm_fp8_tc5_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
+  if (threadIdx.x == 0) GEMM_TRACE(2);  // barriers initialised, tensor memory allocated
 
   // Everything above touched no global memory.  While the kernel before this one in the stream
   // drains, pull the first W boxes of this CTA's first tile towards L2 (a prefetch cannot read
@@ -760,19 +800,49 @@ gemm_fp8_tc5_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
     // are ordered behind it through the barriers (and re-check below), the MMA warp touches no
     // global memory.  Fewer waiting threads matter: a CTA that became resident early sits beside
     // a kernel that is still running.
+    // Skinny form: the weight boxes of the first stages are issued BEFORE the dependency wait.  The
+    // weights are not an output of the kernel before this one (the activations are), so their DRAM
+    // round trip -- the longest single latency of a 4 us kernel -- runs while that kernel drains;
+    // after the wait only the activation boxes (L2 hits) remain.  (Contract: see iflb200_gemm_fp8_raw.)
+    int early = 0;
+    if constexpr (SL > 1) {
+      if (lane == 0 && tile_first < p.num_tiles) {
+        int m_blk, n_blk, grp;
+        tile_place(p, tile_first, m_blk, n_blk, grp);
+        for (int kb = kb0; kb < kb1 && early < STAGES; kb += SL, ++early) {
+          mbar_arrive_expect_tx(full_bar(early), (uint32_t)(SL * p.a_bytes) + L::kBBytes);
+          tma_load_3d(base + early * L::kStageBytes + L::kABytes, &tm_w, full_bar(early), 0, n_blk * BN, kb);
+        }
+      }
+      early = __shfl_sync(0xFFFFFFFFu, early, 0);
+    }
     if (lane == 0) grid_dependency_wait();
+    if (lane == 0) GEMM_TRACE(3);  // the kernel before this one has completed
     __syncwarp();
     int stage = 0;
     uint32_t phase = 0;
-    uint32_t armed = 0;        // stages armed at least once
-    uint32_t last_parity = 0;  // parity of the last arming per stage
+    uint32_t armed = (1u << early) - 1u;  // stages armed at least once (the early ones: first phase, parity 0)
+    uint32_t last_parity = 0;             // parity of the last arming per stage
     bool ok = true;
     uint32_t it = 0;
+    int fill = 0;              // stage fills issued so far
     for (int tile = tile_first; ok && tile < p.num_tiles; tile += tile_stride, ++it) {
       int m_blk, n_blk, grp;
       tile_place(p, tile, m_blk, n_blk, grp);
       const int a_row = grp * p.group_rows + m_blk * BM;  // rows past a block's end belong to the next block: loaded, never stored
-      for (int kb = kb0; kb < kb1; kb += SL) {
+      for (int kb = kb0; kb < kb1; kb += SL, ++fill) {
+        if (SL > 1 && fill < early) {
+          // armed above with its weight box in flight (stage == fill, first phase): the activation box only
+          if (lane == 0) tma_load_3d(base + stage * L::kStageBytes, &tm_a, full_bar(stage), 0, a_row, kb);
+          armed |= 1u << stage;
+          last_parity = (last_parity & ~(1u << stage)) | (phase << stage);
+          __syncwarp();
+          if (++stage == STAGES) {
+            stage = 0;
+            phase ^= 1;
+          }
+          continue;
+        }
         ok = __all_sync(0xFFFFFFFFu, wait_bounded(empty_bar(stage), phase ^ 1, abort_flag,
                                                   (1u << 24) | (1u << 16) | (it & 0xFFFF)));
         if (!ok) break;
@@ -837,6 +907,7 @@ gemm_fp8_tc5_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
                                                   (2u << 24) | (3u << 16) | (it & 0xFFFF)));
         if (!ok) break;
         tc_fence_after();
+        if (lane == 0 && it == 0 && kb == kb0) GEMM_TRACE(4);  // first operands have landed
         if (lane == 0) {
           const uint32_t sa = base + stage * L::kStageBytes;
 #pragma unroll
@@ -861,6 +932,7 @@ gemm_fp8_tc5_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
       }
       if (!ok) break;
       if (lane == 0) mma_commit(tfull_bar(acc));  // accumulator complete
+      if (lane == 0 && it == 0) GEMM_TRACE(5);  // last MMA of the first tile issued
       __syncwarp();
     }
   } else {
@@ -909,6 +981,7 @@ gemm_fp8_tc5_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
                                                 (3u << 24) | (4u << 16) | (it & 0xFFFF)));
       if (!ok) break;
       tc_fence_after();
+      if (warp == 2 && lane == 0 && it == 0) GEMM_TRACE(6);  // first accumulator complete
       const uint32_t t_row = tmem_base + ((uint32_t)(quad * 32) << 16) + acc * kAccStride;
       if constexpr (SWAP) {
         epilogue_swapped<BN>(p, &tm_out, t_row, staging, staging_ptr, m_blk * BM + quad * 32, n_blk * BN, half, lane,
@@ -964,7 +1037,9 @@ gemm_fp8_tc5_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
       __syncwarp();
       if (lane == 0) mbar_arrive(tempty_bar(acc));
     }
+    if (warp == 2 && lane == 0) GEMM_TRACE(7);  // last store issued
     if (lane == 0) bulk_wait_group_read<0>();  // staging buffers no longer read by the TMA unit
+    if (warp == 2 && lane == 0) GEMM_TRACE(8);  // and read by the TMA unit
     __syncwarp();
   }
 
@@ -1087,6 +1162,7 @@ gemm_fp8_tc5_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
   }
   tc_fence_before();
   __syncthreads();
+  if (threadIdx.x == 0) GEMM_TRACE(9);  // all roles done
   if (warp == 1) {
     tc_fence_after();
     tmem_dealloc(tmem_base, kTmemCols);
@@ -2061,3 +2137,11 @@ extern "C" const char* iflb200_status_string(int status) {
     default: return status > 0 ? cudaGetErrorString((cudaError_t)status) : "unknown status";
   }
 }
+
+#ifdef IFLB200_TRACE
+extern "C" __attribute__((visibility("default"))) int iflb200_exp_gemm_trace(unsigned long long* out64x10, unsigned int* launches) {
+  cudaError_t e = cudaMemcpyFromSymbol(out64x10, g_gemm_trace, sizeof(unsigned long long) * 64 * 16);
+  if (e != cudaSuccess) return (int)e;
+  return (int)cudaMemcpyFromSymbol(launches, g_gemm_trace_launch, sizeof(unsigned int));
+}
+#endif
