@@ -64,6 +64,8 @@ struct GemmParams {
   int act;         // gated form: IFLB200_ACT_*
   uint32_t* amax;  // gated form: per-row maximum of |h| as float bits, raised with atomicMax
   int tma_store;  // 1: the epilogue stages 128-byte row pieces in shared memory and TMA-stores them
+  int half_rows;  // 1: 64-wide tiles of two-byte outputs leave as two 64-byte pieces per row, one per warp of a
+                  // quadrant (the output map then has a 64-byte box), so both warps drain the accumulator
   // Row blocks to several destinations (tensor parallel, row-split linears): the activation holds
   // `groups` blocks of `group_rows` rows (M = group_rows); block g's tiles are stored through
   // out_maps[g] (tensor maps in global memory, e.g. one per GPU's buffer).  Tiles of the blocks
@@ -390,6 +392,8 @@ __device__ __forceinline__ void stage_columns(const GemmParams& p, const uint32_
   if (es == 2) {
     // 32 values = 64 bytes = four 16-byte chunks; chunk index within the 128-byte row
     const int first = sub / 8;  // 0 or 4
+    // half-row pieces: 64-byte rows with the 64-byte swizzle (chunk index ^ ((row >> 1) & 3))
+    const int sw = p.half_rows ? ((lane >> 1) & 3) : (lane & 7);
     if (p.epilogue == EPI_RAW) {
 #pragma unroll
       for (int j = 0; j < 4; ++j) {
@@ -398,7 +402,7 @@ __device__ __forceinline__ void stage_columns(const GemmParams& p, const uint32_
         u.y = pack_bf16x2(__uint_as_float(r[8 * j + 2]), __uint_as_float(r[8 * j + 3]));
         u.z = pack_bf16x2(__uint_as_float(r[8 * j + 4]), __uint_as_float(r[8 * j + 5]));
         u.w = pack_bf16x2(__uint_as_float(r[8 * j + 6]), __uint_as_float(r[8 * j + 7]));
-        *reinterpret_cast<uint4*>(mine + (((first + j) ^ (lane & 7)) * 16)) = u;
+        *reinterpret_cast<uint4*>(mine + (((first + j) ^ sw) * 16)) = u;
       }
     } else {
       float y[32];
@@ -417,7 +421,7 @@ __device__ __forceinline__ void stage_columns(const GemmParams& p, const uint32_
           u.z = pack_f16x2(y[8 * j + 4], y[8 * j + 5]);
           u.w = pack_f16x2(y[8 * j + 6], y[8 * j + 7]);
         }
-        *reinterpret_cast<uint4*>(mine + (((first + j) ^ (lane & 7)) * 16)) = u;
+        *reinterpret_cast<uint4*>(mine + (((first + j) ^ sw) * 16)) = u;
       }
     }
   } else {
@@ -440,8 +444,9 @@ __device__ __forceinline__ void epilogue_tma_store(const GemmParams& p, const CU
                                                    int col_begin, int col_end, float rs, int lane, int z = -1,
                                                    const ColumnVectors* cv = nullptr) {
   const int es = (p.out_dtype == IFLB200_F32) ? 4 : 2;
-  const int cols_per_store = 128 / es;  // 64 or 32
-  uint8_t* mine = staging_ptr + lane * 128;
+  const int row_bytes = p.half_rows ? 64 : 128;
+  const int cols_per_store = row_bytes / es;  // 64 or 32
+  uint8_t* mine = staging_ptr + lane * row_bytes;
 #pragma unroll 1
   for (int c = col_begin; c < col_end; c += cols_per_store) {
     const int n0 = n_base + c;
@@ -943,7 +948,7 @@ gemm_fp8_tc5_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
     // store of two-byte outputs): 128 | rest for wide tiles, half | half for 128, all | none for 64
     constexpr int kColSplit = BN > 128 ? 128 : (BN == 128 ? 64 : BN);
     int col_begin = half == 0 ? 0 : kColSplit, col_end = half == 0 ? kColSplit : BN;
-    if (BN == 64 && p.tma_store && p.out_dtype == IFLB200_F32) {  // 32 four-byte columns per store
+    if (BN == 64 && p.tma_store && (p.out_dtype == IFLB200_F32 || p.half_rows)) {  // 32 columns per store and warp
       col_begin = half * 32;
       col_end = col_begin + 32;
     }
@@ -1007,7 +1012,7 @@ gemm_fp8_tc5_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
       } else if (p.tma_store) {
         // whole 128-byte pieces through shared memory and TMA; a 32-column remainder of a
         // 224-wide tile (two-byte outputs) straight from registers
-        const int per_store = (p.out_dtype == IFLB200_F32) ? 32 : 64;
+        const int per_store = (p.out_dtype == IFLB200_F32 || p.half_rows) ? 32 : 64;
         const int col_tma_end = col_begin + (col_end - col_begin) / per_store * per_store;
         epilogue_tma_store<BN>(p, tm_dst, t_row, staging, staging_ptr, m_blk * BM + quad * 32, n_blk * BN,
                                col_begin, col_tma_end, rs, lane,
@@ -1766,6 +1771,15 @@ static int run_gemm(const void* a, int64_t ld_a, const void* w, int64_t ld_w, Ge
   p.group_m = g_cfg_group_m > 0 ? g_cfg_group_m : 8;
   const int grid = split > 1 ? p.num_tiles * split : (p.num_tiles < dev->sm_count ? p.num_tiles : dev->sm_count);
 
+  // 64-wide tiles of two-byte outputs with consumer arithmetic: a 64-byte piece per warp instead of
+  // one 128-byte piece that the first warp of each quadrant stages alone (the epilogue of a skinny
+  // launch overlaps nothing: 64 x 4096 x 1024 with scales and bias 5.7 -> 5.1 us; raw outputs, whose
+  // staging is a handful of instructions, gain nothing from the second store and keep one piece).
+  if (bn == 64 && split == 1 && p.tma_store && oes == 2 && p.epilogue != EPI_RAW) {
+    st = make_out_map(&to, p.out, p.M, p.N, p.ld_out, oes, 64);
+    if (st != IFLB200_OK) return st;
+    p.half_rows = 1;
+  }
   CUtensorMap ta, tw;
   const int a_rows = activation_box_rows(p.M);
   p.a_bytes = a_rows * BK;
