@@ -735,7 +735,7 @@ def profile_operator(args, spec, dev):
         gated = st.fused and args.profile_op == "gate_up"
         for _ in range(args.steps):
             if gated:
-                K.fp8_linear_gated(a, st.scale[0], w, st.h, st.amax, act=0)
+                K.fp8_linear_gated(a, st.scale[0], w, st.h, st.amax[0], act=0)
             else:
                 K.gemm(a, w, st._raw(n))
     torch.cuda.synchronize(dev)
@@ -954,7 +954,7 @@ def main():
     gated_dom = bool(getattr(stack, "fused", False)) and name == "gate_up"
     if gated_dom:
         def dom_call(w):
-            K.fp8_linear_gated(a_dom, stack.scale[0], w, stack.h, stack.amax, act=0)
+            K.fp8_linear_gated(a_dom, stack.scale[0], w, stack.h, stack.amax[0], act=0)
         kernel_name = f"gemm_fp8_tc5_kernel (gated epilogue) {spec.M}x{n_dom}x{k_dom} ({name})"
         out_bytes = 4.0 * spec.M * (n_dom // 2)
     else:

@@ -322,6 +322,18 @@ IFLB200_API int iflb200_fp8_linear_gated(const void* a, int64_t ld_a, const void
                              int act, float* h, int64_t ld_h, uint32_t* amax, void* stream);
 
 /*
+ * The quantiser pass of iflb200_fp8_linear_gated as a flat kernel: q[m,f] = e4m3(h[m,f] * (448 /
+ * max(amax[m], 1e-8))), qs[m] = max(amax[m], 1e-8) / 448 with the arithmetic of iflb200_row_quant
+ * (the same bits as iflb200_row_quant_sharded phase 3).  Rows need no reduction here, so each is cut
+ * into pieces of 2048 columns for separate CTAs.  amax is only read; amax_zero (a DIFFERENT buffer
+ * of M floats, or NULL) is set to zero: callers alternate two buffers of row maxima between
+ * consecutive gated GEMMs, each pass clearing the buffer the next GEMM will raise.  M <= 65535.
+ * Replaces: the quantiser part of instinctflash/kernels/activation.py:44-56.
+ */
+IFLB200_API int iflb200_quant_from_amax(const float* h, int64_t ld_h, int M, int F, const float* amax, float* amax_zero,
+                            void* q, int64_t ld_q, float* qs, void* stream);
+
+/*
  * Per-tensor dynamic e4m3 pack (the torch-FP8-linear recipe):
  *   amax = max |x| (NaN propagates);  scale = max(amax, 1e-12) * fp32(1/448);
  *   q = e4m3_rn(clamp(x / scale, -448, 448))   (IEEE division, NaN propagates)

@@ -33,6 +33,7 @@ SIGNATURES = {
     "iflb200_row_quant": (_i, [_p, _i, _l, _i, _i, _p, _p, _p, _i, _p, _l, _p, _p]),
     "iflb200_row_quant_sharded": (_i, [_p, _i, _l, _i, _i, _p, _p, _p, _i, _i, _p, _p, _l, _p, _p]),
     "iflb200_row_max_sharded": (_i, [_p, _i, _l, _i, _i, _p, _p, _p, _i, _p, _p, _i, _p]),
+    "iflb200_quant_from_amax": (_i, [_p, _l, _i, _i, _p, _p, _p, _l, _p, _p]),
     "iflb200_dequant_rows": (_i, [_p, _i, _l, _i, _i, _p, _p, _p, _p, _i, _l, _p]),
     "iflb200_gated_act_quant": (_i, [_p, _i, _l, _i, _i, _p, _p, _i, _p, _l, _p, _p]),
     "iflb200_residual_norm_quant": (_i, [_p, _i, _l, _i, _i, _p, _l, _p, _p, _p, _p, _i, _i, _p, _p,

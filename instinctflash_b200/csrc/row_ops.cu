@@ -1058,6 +1058,52 @@ extern "C" int iflb200_row_max_sharded(const void* x, int x_dtype, int64_t ld_x,
 
 #endif
 
+#if IFLB200_ROW_PART == 0 || IFLB200_ROW_PART == -1
+// Quantiser pass over fp32 rows whose maxima are already known (the second half of the gated GEMM):
+// no reduction, so a row is cut into pieces of 2048 columns for separate CTAs and the pass runs as a
+// flat elementwise kernel (816 x 16384: 6528 CTAs instead of 816 CTAs that each hold a whole row).
+// The maxima are read, never written; `amax_zero` (another buffer, or NULL) is cleared for the
+// producer after next -- clearing the buffer that is being read would race with the row's other CTAs.
+template <bool FAST>
+__global__ void __launch_bounds__(kRowThreads)
+quant_from_amax_kernel(const float* __restrict__ h, int64_t ld_h, int M, int F, const float* __restrict__ amax,
+                       float* __restrict__ amax_zero, uint8_t* __restrict__ q, int64_t ld_q, float* __restrict__ qs) {
+  row_dependency_wait();  // h and amax come from the kernel before this one in the stream
+  row_trigger();
+  const int m = blockIdx.y;
+  const int c0 = (blockIdx.x * kRowThreads + threadIdx.x) * 8;
+  float scale, inv;
+  quant_scales(amax[m], scale, inv);
+  if (blockIdx.x == 0 && threadIdx.x == 0) {
+    qs[m] = scale;
+    if (amax_zero) amax_zero[m] = 0.0f;
+  }
+  if (c0 >= F) return;
+  float v[8];
+  load_f32<FAST>(h + (int64_t)m * ld_h, c0, F, v);
+  store_codes<FAST>(q + (int64_t)m * ld_q, c0, F, v, inv);
+}
+
+extern "C" int iflb200_quant_from_amax(const float* h, int64_t ld_h, int M, int F, const float* amax, float* amax_zero,
+                                       void* q, int64_t ld_q, float* qs, void* stream) {
+  if (M < 0 || F < 0) return IFLB200_ERR_ARG;
+  if (M == 0 || F == 0) return IFLB200_OK;
+  if (!h || !amax || !q || !qs || amax_zero == amax) return IFLB200_ERR_ARG;
+  if (ld_h < F || ld_q < F) return IFLB200_ERR_ARG;
+  if (M > 65535) return IFLB200_ERR_SHAPE;
+  const bool fast = F % 8 == 0 && aligned16(h) && (ld_h * 4) % 16 == 0 && aligned8(q) && ld_q % 8 == 0;
+  const dim3 grid((unsigned)((F + kRowThreads * 8 - 1) / (kRowThreads * 8)), (unsigned)M);
+  cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+  if (fast)
+    launch_dep(quant_from_amax_kernel<true>, grid, dim3(kRowThreads), 0, s, 1, dependent_launch_for(M), h, ld_h, M, F, amax,
+               amax_zero, reinterpret_cast<uint8_t*>(q), ld_q, qs);
+  else
+    launch_dep(quant_from_amax_kernel<false>, grid, dim3(kRowThreads), 0, s, 1, dependent_launch_for(M), h, ld_h, M, F, amax,
+               amax_zero, reinterpret_cast<uint8_t*>(q), ld_q, qs);
+  return (int)cudaGetLastError();
+}
+#endif
+
 #if IFLB200_ROW_PART == 1 || IFLB200_ROW_PART == -1
 extern "C" int iflb200_gated_act_quant(const void* gu, int gu_dtype, int64_t ld_gu, int M, int F,
                                        const float* row, const float* col, int act,

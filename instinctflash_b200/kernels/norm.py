@@ -84,6 +84,26 @@ def row_quant_from_amax(h, amax, q, q_scale):
     row_quant_sharded(h, q, q_scale, amax, 3)
 
 
+def quant_from_amax(h, amax, q, q_scale, zero=None):
+    """``row_quant_from_amax`` as a flat kernel (rows cut into pieces for separate CTAs): the same
+    codes and scales; ``amax`` is left as it is and ``zero`` (another [M] float32 buffer, or None) is
+    cleared instead -- two buffers of row maxima alternate between consecutive gated GEMMs."""
+    rows(h, "h", (torch.float32,))
+    M, F = h.shape
+    rows(q, "q", (E4M3,))
+    if tuple(q.shape) != (M, F):
+        raise ValueError(f"q must be [{M}, {F}], got {tuple(q.shape)}")
+    vec(amax, "amax", M, h.device)
+    vec(q_scale, "q_scale", M, h.device)
+    if zero is not None:
+        vec(zero, "zero", M, h.device)
+        if zero.data_ptr() == amax.data_ptr():
+            raise ValueError("zero must be another buffer than amax")
+    same_device(h, q=q)
+    launch("iflb200_quant_from_amax", h, h.data_ptr(), ld(h), M, F, amax.data_ptr(), _lib.ptr(zero), q.data_ptr(), ld(q),
+           q_scale.data_ptr())
+
+
 def dequant_rows(x, y, *, row=None, col=None, bias=None, block=None, num_warps=4):
     """y[m] = x[m] * row[m] * col + bias (float dtypes in and out)."""
     rows(x, "x", _FLOATS)

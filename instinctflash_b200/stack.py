@@ -33,6 +33,7 @@ def native_ops() -> SimpleNamespace:
                            residual_norm_quant=_norm.residual_norm_quant, gated_act_quant=_act.gated_act_quant,
                            GELU_TANH=_act.GELU_TANH, Fp8Weight=_fp8.Fp8Weight,
                            fp8_linear_gated=_fp8.fp8_linear_gated, row_quant_from_amax=_norm.row_quant_from_amax,
+                           quant_from_amax=_norm.quant_from_amax,
                            fp8_linear_residual=_fp8.fp8_linear_residual, gemm_partials=_fp8.gemm_partials,
                            partial_splits=_fp8.partial_splits)
 
@@ -179,7 +180,9 @@ class LinearStack:
         self.res = torch.zeros(M, D, dtype=bf16 if spec.kind == "wan" else f32, device=dev)
         if self.fused and spec.kind == "gemma":
             self.h = torch.zeros(M, F, dtype=f32, device=dev)     # act(g) * u, never rounded to 16 bits
-            self.amax = torch.zeros(M, dtype=f32, device=dev)     # row maxima of |h|; zero between calls
+            # row maxima of |h|: two buffers that consecutive gated GEMMs alternate (each quantiser pass
+            # clears the one the next GEMM will raise); both zero between forward passes
+            self.amax = torch.zeros(2, M, dtype=f32, device=dev)
         if self.split_partials:
             sms = torch.cuda.get_device_properties(dev).multi_processor_count
             ks = [k for name, n, k in spec.linears() if n == D and name in ("o", "down")]
@@ -205,6 +208,7 @@ class LinearStack:
         sp, o, s = self.spec, self.ops, self.scale
         D, F = sp.hidden, sp.ffn
         n = 0
+        gated = 0   # gated GEMMs issued so far in this pass
         for _ in range(sp.steps):
             for lw in self.weights:
                 W = lw.w
@@ -214,8 +218,10 @@ class LinearStack:
                         o.row_quant(self.attn, self._q8(sp.o_in), s[1]); n += 1
                         n += self._residual_linear(self._q8(sp.o_in), s[1], W["o"])
                     if self.fused:
-                        o.fp8_linear_gated(self._q8(D), s[0], W["gate_up"], self.h, self.amax, act=o.GELU_TANH); n += 1
-                        o.row_quant_from_amax(self.h, self.amax, self._q8(F), s[1]); n += 1
+                        cur, nxt = self.amax[gated & 1], self.amax[(gated + 1) & 1]
+                        gated += 1
+                        o.fp8_linear_gated(self._q8(D), s[0], W["gate_up"], self.h, cur, act=o.GELU_TANH); n += 1
+                        o.quant_from_amax(self.h, cur, self._q8(F), s[1], zero=nxt); n += 1
                     else:
                         o.gemm(self._q8(D), W["gate_up"], self._raw(2 * F)); n += 1
                         o.gated_act_quant(self._raw(2 * F), self._q8(F), s[1], row=s[0], col=W["gate_up"].scale,
@@ -244,6 +250,8 @@ class LinearStack:
                                           bias=W["ff2"].bias, gate=V["gate_ffn"], layernorm=True,
                                           mod_scale=V["mod_scale_f"], mod_shift=V["mod_shift_f"], q=self._q8(D),
                                           q_scale=s[0]); n += 1
+        if gated:
+            self.amax[(gated - 1) & 1].zero_()   # the last pass's own maxima: both buffers zero again
         self.launches_per_forward = n
         return self.res
 

@@ -565,6 +565,30 @@ def test_gated_epilogue_equals_gemm_plus_gated_act_quant(ops, unsplit, M, F, K, 
     no_timeout(ops)
 
 
+@pytest.mark.parametrize("M,F", [(816, 16384), (50, 4096), (130, 272), (7, 2052), (33, 100)])
+def test_flat_quantiser_pass_equals_the_row_kernel(ops, M, F):
+    """quant_from_amax (rows cut into pieces for separate CTAs) against row_quant_from_amax (one CTA per
+    row): the same codes and scales; the maxima it reads are left alone, the other buffer is cleared."""
+    norm = ops["norm"]
+    g = torch.Generator().manual_seed(M + F)
+    h = dev(torch.randn(M, F, generator=g) * torch.rand(M, 1, generator=g) * 50)
+    h[M // 2] = 0.0                                              # an all-zero row: the 1e-8 floor
+    amax = h.abs().amax(1).contiguous()
+    want_q = torch.empty(M, F, device=DEV, dtype=torch.uint8).view(E4M3)
+    want_s = torch.empty(M, device=DEV)
+    a1 = amax.clone()
+    norm.row_quant_from_amax(h, a1, want_q, want_s)
+    assert float(a1.abs().max()) == 0.0
+    q = torch.zeros(M, F, device=DEV, dtype=torch.uint8).view(E4M3)
+    qs = torch.zeros(M, device=DEV)
+    a2, other = amax.clone(), torch.full((M,), 3.0, device=DEV)
+    norm.quant_from_amax(h, a2, q, qs, zero=other)
+    assert torch.equal(qs, want_s) and torch.equal(q.view(torch.uint8), want_q.view(torch.uint8))
+    assert torch.equal(a2, amax) and float(other.abs().max()) == 0.0
+    with pytest.raises(ValueError):
+        norm.quant_from_amax(h, a2, q, qs, zero=a2)
+
+
 def test_gated_epilogue_rejects_bad_arguments(ops):
     fp8 = ops["fp8"]
     a = torch.zeros(4, 32, device=DEV, dtype=torch.uint8).view(E4M3)
