@@ -247,8 +247,8 @@ IFLB200_API int iflb200_residual_norm_quant_peers(void* res, int res_dtype, int6
  * accumulation on the tcgen05 tensor cores, unit scales.  K, N multiples of 16.
  * Ordering on the stream (this and every other GEMM entry point): with dependent launch enabled
  * (iflb200_set_dependent_launch, the default) the kernel becomes resident while the kernel enqueued
- * immediately before it is still running, prefetches `w` towards L2 and -- in the 64-wide-tile form
- * that skinny activations take -- loads its first weight boxes before it waits for that kernel; `a`, the scales and everything else are read
+ * immediately before it is still running and loads its first weight boxes before it waits for that
+ * kernel; `a`, the scales and everything else are read
  * after the wait.  So `w` must not be an OUTPUT of the kernel enqueued immediately before on the
  * same stream (weights are packed at load time; activations may of course come from that kernel).
  * Replaces: instinctflash/kernels/fp8.py:50-53 (gemm -> torch._scaled_mm).

@@ -805,18 +805,21 @@ gemm_fp8_tc5_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
     // are ordered behind it through the barriers (and re-check below), the MMA warp touches no
     // global memory.  Fewer waiting threads matter: a CTA that became resident early sits beside
     // a kernel that is still running.
-    // Skinny form: the weight boxes of the first stages are issued BEFORE the dependency wait.  The
-    // weights are not an output of the kernel before this one (the activations are), so their DRAM
-    // round trip -- the longest single latency of a 4 us kernel -- runs while that kernel drains;
-    // after the wait only the activation boxes (L2 hits) remain.  (Contract: see iflb200_gemm_fp8_raw.)
+    // The weight boxes of the first stages are issued BEFORE the dependency wait.  The weights are not
+    // an output of the kernel before this one (the activations are), so their DRAM round trip -- the
+    // longest single latency of a 4 us skinny kernel -- runs while that kernel drains; after the wait
+    // only the activation boxes (mostly L2 hits) remain.  (Contract: see iflb200_gemm_fp8_raw.)
     int early = 0;
-    if constexpr (SL > 1) {
+    if constexpr (!SWAP) {  // (in the swapped form the operand behind tm_a is the weight matrix)
       if (lane == 0 && tile_first < p.num_tiles) {
         int m_blk, n_blk, grp;
         tile_place(p, tile_first, m_blk, n_blk, grp);
         for (int kb = kb0; kb < kb1 && early < STAGES; kb += SL, ++early) {
           mbar_arrive_expect_tx(full_bar(early), (uint32_t)(SL * p.a_bytes) + L::kBBytes);
-          tma_load_3d(base + early * L::kStageBytes + L::kABytes, &tm_w, full_bar(early), 0, n_blk * BN, kb);
+          const uint32_t sw = base + early * L::kStageBytes + L::kABytes;
+          if constexpr (SL > 1) tma_load_3d(sw, &tm_w, full_bar(early), 0, n_blk * BN, kb);
+          else if constexpr (GATED) tma_load_3d(sw, &tm_w, full_bar(early), kb * BK, n_blk * (BN / 2), 0);
+          else tma_load_2d(sw, &tm_w, full_bar(early), kb * BK, n_blk * BN);
         }
       }
       early = __shfl_sync(0xFFFFFFFFu, early, 0);
@@ -836,9 +839,12 @@ gemm_fp8_tc5_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
       tile_place(p, tile, m_blk, n_blk, grp);
       const int a_row = grp * p.group_rows + m_blk * BM;  // rows past a block's end belong to the next block: loaded, never stored
       for (int kb = kb0; kb < kb1; kb += SL, ++fill) {
-        if (SL > 1 && fill < early) {
+        if (fill < early) {
           // armed above with its weight box in flight (stage == fill, first phase): the activation box only
-          if (lane == 0) tma_load_3d(base + stage * L::kStageBytes, &tm_a, full_bar(stage), 0, a_row, kb);
+          if (lane == 0) {
+            if constexpr (SL > 1) tma_load_3d(base + stage * L::kStageBytes, &tm_a, full_bar(stage), 0, a_row, kb);
+            else tma_load_2d(base + stage * L::kStageBytes, &tm_a, full_bar(stage), kb * BK, a_row);
+          }
           armed |= 1u << stage;
           last_parity = (last_parity & ~(1u << stage)) | (phase << stage);
           __syncwarp();
