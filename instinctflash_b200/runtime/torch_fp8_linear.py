@@ -12,7 +12,6 @@ from __future__ import annotations
 import torch
 from torch import nn
 
-from .. import _lib
 from ..kernels.fp8 import Fp8Weight, fp8_linear
 from .fp8_pack import dynamic_pack_bf16_e4m3
 

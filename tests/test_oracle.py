@@ -13,7 +13,7 @@ import torch
 
 import cases
 from oracle import oracle as O
-from util import (E4M3, assert_quant_close_to_oracle, golden, i32, sha, u8)
+from util import (E4M3, golden, i32, sha, u8)
 
 CPU = golden("golden_cpu.json")
 B200 = golden("golden_b200.json")

@@ -9,7 +9,7 @@ import pytest
 import torch
 
 import oracle_ops
-from instinctflash_b200.stack import SPECS, LinearStack, StackSpec, make_inputs, make_weights, small_spec
+from instinctflash_b200.stack import SPECS, LinearStack, StackSpec, make_inputs, make_weights
 from instinctflash_b200 import tp
 
 ROOT = Path(__file__).resolve().parents[1]

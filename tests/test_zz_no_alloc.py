@@ -8,7 +8,6 @@ the library image.  This file checks that it produces exactly what the workspace
 point produces, twice in a row (the array is shared and keeps the previous call's contents), and
 that it refuses inputs beyond its stated capacity.  Collected last on purpose.
 """
-import ctypes
 
 import pytest
 import torch
