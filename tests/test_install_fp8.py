@@ -6,7 +6,6 @@ import sys
 import types
 
 import pytest
-import torch
 from torch import nn
 
 from instinctflash_b200.runtime import install_fp8 as I
