@@ -744,6 +744,36 @@ def test_gemm_properties_at_full_size(ops, unsplit, oracle, name, M, N, K, seed)
     no_timeout(ops)
 
 
+FULL_OUTPUT = [("c2_gate_up", 816, 32768, 2048), ("c2_down", 816, 2048, 16384), ("c3_gate_up", 50, 8192, 1024),
+               ("c4_ff1", 4680, 14336, 3072), ("c4_ff2", 4680, 3072, 14336), ("c5_qkv", 16384, 15360, 5120),
+               ("c5_ff2", 16384, 5120, 13824)]
+
+
+@pytest.mark.parametrize("name,M,N,K", FULL_OUTPUT)
+def test_gemm_whole_output_against_the_reference_gemm_at_benchmark_sizes(ops, name, M, N, K):
+    """Every element of the raw output at the benchmark sizes, all knobs at their defaults (split-K,
+    CTA pairs as the heuristics choose), against the reference's GEMM itself running on this GPU
+    (gemm of instinctflash/kernels/fp8.py:50-53 is torch._scaled_mm with unit scales): relative
+    Frobenius error <= 1e-3 and max |difference| <= 2^-7 x the row's absolute maximum (the bar for GEMM
+    outputs); in practice the two differ in a handful of bf16 roundings or not at all."""
+    fp8 = ops["fp8"]
+    g = torch.Generator().manual_seed(K + N)
+    x = cases.activations(M, K, 6100 + K % 71, outlier_frac=0.005, outlier_scale=30.0)
+    a, _ = quantise(ops, dev(x))
+    wq = dev((torch.randn(N, K, generator=g) * 120).clamp(-448, 448).to(E4M3))
+    raw = torch.full((M, N), float("nan"), device=DEV, dtype=torch.bfloat16)
+    fp8.gemm(a, fp8.Fp8Weight(wq, None, None), raw)
+    one = torch.ones((), device=DEV)
+    want = torch._scaled_mm(a, wq.t(), scale_a=one, scale_b=one, out_dtype=torch.bfloat16)
+    assert not torch.isnan(raw.float()).any()
+    got32, want32 = raw.float(), want.float()
+    assert rel_frobenius(got32, want32) <= 1e-3
+    row_max = want32.abs().amax(1, keepdim=True).clamp_min(1e-30)
+    assert float(((got32 - want32).abs() / row_max).max()) <= 2.0 ** -7
+    assert (raw != want).float().mean().item() < 2e-3
+    no_timeout(ops)
+
+
 def test_gemm_is_deterministic_and_graph_replayable(ops, unsplit):
     fp8, norm = ops["fp8"], ops["norm"]
     x = dev(cases.activations(816, 2048, 31))
